@@ -1,0 +1,246 @@
+"""B200-native padding-free BERT encoder path.
+
+Python mirror of the reference's package shim
+(python/effective_transformer/__init__.py): the same three operators
+(`effective_transformer_input`, `effective_transformer`,
+`effective_transformer_output`) and `get_sequence_output`, with the same
+argument meaning, on top of the C ABI in include/et_b200.h.  PyTorch is used
+for device memory and streams only; all arithmetic runs in the sm_100a kernels
+of libet_b200.so.  There is no CPU fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from . import _capi
+from ._capi import EtError  # noqa: F401
+
+__all__ = ["BertConfig", "EffectiveTransformer", "get_sequence_output", "EtError"]
+
+
+@dataclass
+class BertConfig:
+    """The fields of sample/tensorflow/modeling.py's BertConfig that the
+    encoder path reads (sample/tensorflow/bert_config.json)."""
+    hidden_size: int = 768
+    num_hidden_layers: int = 12
+    num_attention_heads: int = 12
+    intermediate_size: int = 3072
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+class EffectiveTransformer:
+    """One handle = the weights of all layers + workspace on one GPU.
+
+    Replaces the three TF op kernels and their constructors
+    (tf_op/bert_transformer_op.cc:84-447)."""
+
+    def __init__(self, num_layers: int, head_num: int, size_per_head: int, ffn_dim: int,
+                 max_batch_size: int, max_seq_length: int, dtype: torch.dtype = torch.float16,
+                 device: int = 0, layernorm_eps: float = 0.0):
+        if dtype not in (torch.float16, torch.float32):
+            raise ValueError("dtype must be torch.float16 or torch.float32")
+        self._lib = _capi.load()
+        self.dtype = dtype
+        self.np_dtype = np.float16 if dtype == torch.float16 else np.float32
+        self.et_dtype = _capi.ET_FP16 if dtype == torch.float16 else _capi.ET_FP32
+        self.num_layers, self.head_num, self.size_per_head = num_layers, head_num, size_per_head
+        self.hidden, self.ffn_dim = head_num * size_per_head, ffn_dim
+        self.max_batch_size, self.max_seq_length = max_batch_size, max_seq_length
+        self.device = torch.device("cuda", device)
+        cfg = _capi.Config(self.et_dtype, num_layers, head_num, size_per_head, ffn_dim,
+                           max_batch_size, max_seq_length, layernorm_eps, device)
+        handle = C.c_void_p()
+        _capi.check(self._lib.et_create(C.byref(cfg), C.byref(handle)))
+        self._h = handle
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._lib.et_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ---- weights ---------------------------------------------------------
+    def set_layer_weights(self, layer: int, weights: Sequence) -> None:
+        """16 arrays in the order of python/effective_transformer/__init__.py:55-74
+        (numpy arrays or torch tensors; converted to the handle's dtype)."""
+        if len(weights) != 16:
+            raise ValueError("a layer takes 16 weight arrays")
+        host: List[np.ndarray] = []
+        for w in weights:
+            a = w.detach().cpu().numpy() if isinstance(w, torch.Tensor) else np.asarray(w)
+            host.append(np.ascontiguousarray(a.astype(self.np_dtype, copy=False)))
+        arr = (C.c_void_p * 16)(*[a.ctypes.data for a in host])
+        _capi.check(self._lib.et_set_layer_weights(self._h, layer, arr, 1), self._h)
+
+    def set_weights(self, weights_value: Sequence) -> None:
+        if len(weights_value) != 16 * self.num_layers:
+            raise ValueError("weights_value must hold 16 arrays per layer")
+        for l in range(self.num_layers):
+            self.set_layer_weights(l, weights_value[l * 16:(l + 1) * 16])
+
+    def set_debug_simt(self, on: bool) -> None:
+        _capi.check(self._lib.et_set_debug_simt(self._h, 1 if on else 0), self._h)
+
+    # ---- the three operators ----------------------------------------------
+    def _check_act(self, t: torch.Tensor, name: str) -> None:
+        if t.dtype != self.dtype or not t.is_cuda or not t.is_contiguous():
+            raise ValueError(f"{name} must be a contiguous CUDA tensor of dtype {self.dtype}")
+
+    def effective_transformer_input(self, from_tensor: torch.Tensor, input_mask: torch.Tensor
+                                    ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+        """(from_tensor [B,S,H], mask int32 [B,S]) -> (to_tensor [B,S,H] with the
+        first T rows packed, valid_word_num [1], batch_idx [B,S], word_idx [B,S])
+        as tf_op/bert_transformer_op.cc:249-274."""
+        self._check_act(from_tensor, "from_tensor")
+        b, s, _ = from_tensor.shape
+        mask = input_mask.to(torch.int32).contiguous()
+        to_tensor = torch.empty_like(from_tensor)
+        valid = torch.zeros(1, dtype=torch.int32, device=from_tensor.device)
+        batch_idx = torch.zeros((b, s), dtype=torch.int32, device=from_tensor.device)
+        word_idx = torch.zeros((b, s), dtype=torch.int32, device=from_tensor.device)
+        p = _capi.InputParam(_ptr(from_tensor), _ptr(mask), _ptr(valid), _ptr(batch_idx), _ptr(word_idx),
+                             b, s, self.head_num, self.size_per_head, _ptr(to_tensor), _stream())
+        _capi.check(self._lib.et_input(self._h, C.byref(p)), self._h)
+        return to_tensor, valid, batch_idx, word_idx
+
+    def effective_transformer(self, layer_idx: int, from_tensor: torch.Tensor, to_tensor: torch.Tensor,
+                              attention_mask: Optional[torch.Tensor], valid_word_num: torch.Tensor,
+                              batch_idx: torch.Tensor, word_idx: torch.Tensor) -> torch.Tensor:
+        """One encoder layer on the packed layout (tf_op/bert_transformer_op.cc:44-77);
+        the layer's weights are those registered with set_layer_weights."""
+        self._check_act(from_tensor, "from_tensor")
+        if to_tensor.data_ptr() != from_tensor.data_ptr():
+            raise ValueError("to_tensor must be from_tensor (self-attention)")
+        b, s, _ = from_tensor.shape
+        out = torch.empty_like(from_tensor)
+        p = _capi.EncoderParam()
+        p.from_tensor, p.to_tensor = _ptr(from_tensor), _ptr(to_tensor)
+        p.attr_mask = _ptr(attention_mask)
+        p.batch_idx, p.word_idx, p.valid_word_num = _ptr(batch_idx), _ptr(word_idx), _ptr(valid_word_num)
+        p.transformer_out, p.stream = _ptr(out), _stream()
+        tp = _capi.TransformerParam(b, s, s, self.head_num, self.size_per_head)
+        _capi.check(self._lib.et_layer(self._h, layer_idx, C.byref(p), C.byref(tp)), self._h)
+        return out
+
+    def effective_transformer_output(self, from_tensor: torch.Tensor, valid_word_num: torch.Tensor,
+                                     batch_idx: torch.Tensor, word_idx: torch.Tensor) -> torch.Tensor:
+        """Packed [T,H] (inside a [B,S,H] tensor) -> padded [B,S,H], padding rows
+        zero (tf_op/bert_transformer_op.cc:359-380)."""
+        self._check_act(from_tensor, "from_tensor")
+        b, s, _ = from_tensor.shape
+        out = torch.empty_like(from_tensor)
+        p = _capi.OutputParam(_ptr(from_tensor), _ptr(valid_word_num), _ptr(batch_idx), _ptr(word_idx),
+                              b, s, self.head_num, self.size_per_head, _ptr(out), _stream())
+        _capi.check(self._lib.et_output(self._h, C.byref(p)), self._h)
+        return out
+
+    # ---- whole path --------------------------------------------------------
+    def forward(self, from_tensor: torch.Tensor, input_mask: torch.Tensor,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Input op, all layers, output op on the current stream (device tensors)."""
+        self._check_act(from_tensor, "from_tensor")
+        b, s, _ = from_tensor.shape
+        if input_mask.dtype != torch.int32 or not input_mask.is_contiguous():
+            input_mask = input_mask.to(torch.int32).contiguous()
+        if out is None:
+            out = torch.empty_like(from_tensor)
+        _capi.check(self._lib.et_forward(self._h, _ptr(from_tensor), _ptr(input_mask), _ptr(out), b, s,
+                                         _stream()), self._h)
+        return out
+
+    def forward_host(self, from_tensor: np.ndarray, input_mask: np.ndarray,
+                     out: Optional[np.ndarray] = None) -> Tuple[np.ndarray, int]:
+        """Same with host arrays: host->device copies, the forward pass and the
+        device->host copy of the result happen inside the call."""
+        if from_tensor.dtype != self.np_dtype or input_mask.dtype != np.int32:
+            raise ValueError("from_tensor must have the handle's dtype and input_mask must be int32")
+        from_tensor = np.ascontiguousarray(from_tensor)
+        input_mask = np.ascontiguousarray(input_mask)
+        b, s, _ = from_tensor.shape
+        if out is None:
+            out = np.empty_like(from_tensor)
+        t = C.c_int(0)
+        _capi.check(self._lib.et_forward_host(self._h, from_tensor.ctypes.data, input_mask.ctypes.data,
+                                              out.ctypes.data, b, s, C.byref(t)), self._h)
+        return out, int(t.value)
+
+    def set_profiling(self, on: bool) -> None:
+        _capi.check(self._lib.et_set_profiling(self._h, 1 if on else 0), self._h)
+
+    def get_profile(self, reset: bool = True):
+        """{category: (device ms, kernels launched)} since the last reset; the
+        times are non-zero only while profiling is enabled."""
+        n = len(_capi.PROF_NAMES)
+        ms = (C.c_double * n)()
+        cnt = (C.c_longlong * n)()
+        _capi.check(self._lib.et_get_profile(self._h, ms, cnt, 1 if reset else 0), self._h)
+        return {name: (float(ms[i]), int(cnt[i])) for i, name in enumerate(_capi.PROF_NAMES)}
+
+    def device_status(self) -> int:
+        st = C.c_int(0)
+        _capi.check(self._lib.et_device_status(self._h, _stream(), C.byref(st)), self._h)
+        return int(st.value)
+
+    def last_padding_info(self, batch: int, tokens: int, seq: int):
+        """cu_seqlens, seq_len, padding_offset, prefix_sum of the last input op
+        as CPU int32 arrays."""
+        ptrs = [C.c_void_p() for _ in range(4)]
+        _capi.check(self._lib.et_last_padding_info(self._h, *[C.byref(p) for p in ptrs]), self._h)
+        sizes = [batch + 1, batch, tokens, batch * seq]
+        outs = []
+        for p, n in zip(ptrs, sizes):
+            host = np.empty(n, dtype=np.int32)
+            _capi.check(self._lib.et_copy_to_host(host.ctypes.data, p.value, n * 4, _stream()), self._h)
+            outs.append(host)
+        return outs
+
+
+def get_sequence_output(config, max_batch_size: int, max_seq_length: int, attention_mask,
+                        input_mask: torch.Tensor, from_tensor: torch.Tensor, weights_value: Sequence,
+                        engine: Optional[EffectiveTransformer] = None) -> torch.Tensor:
+    """Same wiring as python/effective_transformer/__init__.py:32-84: the input
+    op, one layer op per hidden layer (weights taken 16 at a time from
+    `weights_value`), the output op.  `attention_mask` is accepted for
+    signature compatibility; it must be the key-only tile of `input_mask`."""
+    head_num = config.num_attention_heads
+    size_per_head = int(config.hidden_size / config.num_attention_heads)
+    num_layers = config.num_hidden_layers
+    ffn = getattr(config, "intermediate_size", 4 * config.hidden_size)
+    own = engine is None
+    if own:
+        engine = EffectiveTransformer(num_layers, head_num, size_per_head, ffn, max_batch_size,
+                                      max_seq_length, dtype=from_tensor.dtype,
+                                      device=from_tensor.device.index or 0)
+        engine.set_weights(weights_value)
+    try:
+        # 1. rm padding
+        x, valid_word_num, batch_idx, word_idx = engine.effective_transformer_input(from_tensor, input_mask)
+        # 2. transformer loop
+        for layer_idx in range(num_layers):
+            x = engine.effective_transformer(layer_idx, x, x, attention_mask, valid_word_num, batch_idx,
+                                             word_idx)
+        # 3. pad back
+        out = engine.effective_transformer_output(x, valid_word_num, batch_idx, word_idx)
+        torch.cuda.current_stream().synchronize()
+        return out
+    finally:
+        if own:
+            engine.close()

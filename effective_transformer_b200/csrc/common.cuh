@@ -1,0 +1,184 @@
+// Shared device/host helpers for the sm_100a encoder kernels.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace etb {
+
+// ---- launch geometry ------------------------------------------------------
+constexpr int kNumSMsB200 = 148;
+
+inline int sm_count() {
+  static int cached = 0;
+  if (cached == 0) {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess &&
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
+      cached = n;
+    else
+      cached = kNumSMsB200;
+  }
+  return cached;
+}
+
+// ---- device status word ---------------------------------------------------
+// A kernel whose bounded wait expires records (kernel id << 8 | site) once.
+enum KernelId : int { kKernelGemmTc = 1, kKernelAttnTc = 2 };
+
+__device__ __forceinline__ void report_timeout(int* status_word, int kernel_id, int site) {
+  if (status_word != nullptr) atomicCAS(status_word, 0, (kernel_id << 8) | site);
+}
+
+// ---- 16-byte vector access ------------------------------------------------
+struct alignas(16) Vec16 {
+  uint32_t x, y, z, w;
+};
+
+__device__ __forceinline__ Vec16 ld_global_nc_v4(const void* p) {
+  Vec16 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ Vec16 ld_global_v4(const void* p) {
+  return *reinterpret_cast<const Vec16*>(p);
+}
+__device__ __forceinline__ void st_global_v4(void* p, const Vec16& v) {
+  *reinterpret_cast<Vec16*>(p) = v;
+}
+__device__ __forceinline__ void st_global_cs_v4(void* p, const Vec16& v) {
+  asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
+               : "memory");
+}
+
+// Elements of T held by one 16-byte vector.
+template <typename T>
+struct VecTraits;
+template <>
+struct VecTraits<float> {
+  static constexpr int kElems = 4;
+  __device__ static void unpack(const Vec16& v, float* f) {
+    f[0] = __uint_as_float(v.x);
+    f[1] = __uint_as_float(v.y);
+    f[2] = __uint_as_float(v.z);
+    f[3] = __uint_as_float(v.w);
+  }
+  __device__ static Vec16 pack(const float* f) {
+    Vec16 v;
+    v.x = __float_as_uint(f[0]);
+    v.y = __float_as_uint(f[1]);
+    v.z = __float_as_uint(f[2]);
+    v.w = __float_as_uint(f[3]);
+    return v;
+  }
+};
+template <>
+struct VecTraits<__half> {
+  static constexpr int kElems = 8;
+  __device__ static void unpack(const Vec16& v, float* f) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+      float2 t = __half22float2(h);
+      f[2 * i] = t.x;
+      f[2 * i + 1] = t.y;
+    }
+  }
+  __device__ static Vec16 pack(const float* f) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __half2 h = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    Vec16 v;
+    v.x = w[0];
+    v.y = w[1];
+    v.z = w[2];
+    v.w = w[3];
+    return v;
+  }
+};
+
+// ---- math -----------------------------------------------------------------
+// tanh-form GELU with the constants of the reference kernel
+// (cuda/cuda_kernels.cu:29-37); evaluated in fp32.
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+  return x * (0.5f * (1.0f + tanhf(u)));
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// ---- kernel launchers implemented in the .cu files -------------------------
+// Every launcher returns the cudaError_t of the launch.  `t_ptr` is a device
+// pointer to the valid-token count; kernels never need it on the host.
+
+cudaError_t launch_padding_offsets(const int* mask, int batch, int seq, int* prefix_sum,
+                                   int* valid_word_num, int* batch_idx, int* word_idx,
+                                   int* seq_len_out, int* cu_seqlens, int* padding_offset,
+                                   int* scratch, cudaStream_t stream);
+cudaError_t launch_seq_bounds_from_batch_idx(const int* batch_idx, const int* t_ptr, int batch,
+                                             int max_tokens, int* cu_seqlens, cudaStream_t stream);
+template <typename T>
+cudaError_t launch_remove_padding(const T* from, const int* batch_idx, const int* word_idx,
+                                  const int* t_ptr, T* to, int batch, int seq, int hidden,
+                                  cudaStream_t stream);
+template <typename T>
+cudaError_t launch_restore_padding(const T* from, const int* batch_idx, const int* word_idx,
+                                   const int* t_ptr, T* to, int batch, int seq, int hidden,
+                                   cudaStream_t stream);
+template <typename T>
+cudaError_t launch_add_qkv_bias_transpose(const T* q, const T* bq, const T* k, const T* bk,
+                                          const T* v, const T* bv, T* out, const int* t_ptr,
+                                          int max_tokens, int heads, int d, cudaStream_t stream);
+template <typename T>
+cudaError_t launch_add_bias_gelu(T* out, const T* bias, const int* t_ptr, int max_tokens, int n,
+                                 cudaStream_t stream);
+template <typename T>
+cudaError_t launch_add_bias_input_layernorm(T* out, const T* input, const T* bias, const T* gamma,
+                                            const T* beta, const int* t_ptr, int max_tokens, int n,
+                                            float eps, cudaStream_t stream);
+// Weight repacking (runs once per layer when weights are registered).
+template <typename T>
+cudaError_t launch_transpose(const T* src, T* dst, int rows, int cols, cudaStream_t stream);
+template <typename T>
+cudaError_t launch_copy_columns(const T* src, T* dst, int rows, int cols, int dst_ld, int dst_col0,
+                                cudaStream_t stream);
+
+enum Epilogue : int { kEpiNone = 0, kEpiBias = 1, kEpiBiasGelu = 2 };
+
+// CUDA-core GEMM: C[M,N] = epi(A[M,K] * W[K,N]); W row-major [K,N].
+template <typename T>
+cudaError_t launch_gemm_simt(const T* a, const T* w, const T* bias, T* c, const int* m_ptr,
+                             int max_m, int n, int k, int epilogue, cudaStream_t stream);
+// CUDA-core attention on the packed layout.
+template <typename T>
+cudaError_t launch_attention_simt(const T* q, const T* k, const T* v, long long token_stride,
+                                  long long head_stride, T* ctx, const int* cu_seqlens, int batch,
+                                  int max_seq, int heads, int d, cudaStream_t stream);
+// Tensor-core (mma.sync) attention, fp16.
+cudaError_t launch_attention_tc(const __half* q, const __half* k, const __half* v,
+                                long long token_stride, long long head_stride, __half* ctx,
+                                const int* cu_seqlens, int batch, int max_seq, int heads, int d,
+                                int* status_word, cudaStream_t stream);
+// tcgen05 GEMM, fp16 in / fp32 accumulate / fp16 out.  w_packed is [N,K].
+cudaError_t launch_gemm_tcgen05(const __half* a, const __half* w_packed, const __half* bias,
+                                __half* c, const int* m_ptr, int max_m, int n, int k, int epilogue,
+                                int* status_word, cudaStream_t stream);
+
+}  // namespace etb

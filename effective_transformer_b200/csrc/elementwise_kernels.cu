@@ -1,0 +1,291 @@
+// Fused element-wise kernels on the packed [T, *] layout: QKV bias + head
+// transpose, bias + GELU, bias + residual + LayerNorm, and the weight
+// repacking helpers.  They replace add_QKV_bias_padding (cuda/attention.cu:
+// 106-242), add_bias_act and add_bias_input_layernorm (cuda/cuda_kernels.cu:
+// 88-271).  All arithmetic is fp32; every global access is a 16-byte vector.
+#include "common.cuh"
+
+namespace etb {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kCtasPerSm = 8;
+
+__device__ __forceinline__ int clamp_tokens(const int* t_ptr, int max_tokens) {
+  const int t = *t_ptr;
+  return t < 0 ? 0 : (t > max_tokens ? max_tokens : t);
+}
+
+// out[which][head][token][0:d] = src_which[token][head*d : head*d+d] + bias_which[...]
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+add_qkv_bias_transpose_kernel(const T* __restrict__ q, const T* __restrict__ bq,
+                              const T* __restrict__ k, const T* __restrict__ bk,
+                              const T* __restrict__ v, const T* __restrict__ bv,
+                              T* __restrict__ out, const int* __restrict__ t_ptr, int max_tokens,
+                              int heads, int d) {
+  constexpr int E = VecTraits<T>::kElems;
+  const int t = clamp_tokens(t_ptr, max_tokens);
+  const int hidden = heads * d;
+  const int vpr = hidden / E;   // vectors per row
+  const int vph = d / E;        // vectors per head
+  const long long total = static_cast<long long>(t) * vpr;
+  const T* srcs[3] = {q, k, v};
+  const T* biases[3] = {bq, bk, bv};
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int token = static_cast<int>(i / vpr);
+    const int c = static_cast<int>(i - static_cast<long long>(token) * vpr);
+    const int head = c / vph, within = c - head * vph;
+    Vec16 x[3], b[3];
+#pragma unroll
+    for (int w = 0; w < 3; ++w) {
+      x[w] = ld_global_nc_v4(srcs[w] + static_cast<size_t>(token) * hidden + c * E);
+      b[w] = ld_global_v4(biases[w] + c * E);
+    }
+#pragma unroll
+    for (int w = 0; w < 3; ++w) {
+      float fx[E], fb[E];
+      VecTraits<T>::unpack(x[w], fx);
+      VecTraits<T>::unpack(b[w], fb);
+#pragma unroll
+      for (int e = 0; e < E; ++e) fx[e] += fb[e];
+      T* dst = out + ((static_cast<size_t>(w) * heads + head) * max_tokens + token) * d + within * E;
+      st_global_v4(dst, VecTraits<T>::pack(fx));
+    }
+  }
+}
+
+// out[token][c] = gelu(out[token][c] + bias[c]) in place.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+add_bias_gelu_kernel(T* __restrict__ out, const T* __restrict__ bias, const int* __restrict__ t_ptr,
+                     int max_tokens, int n) {
+  constexpr int E = VecTraits<T>::kElems;
+  constexpr int kBatch = 4;
+  const int t = clamp_tokens(t_ptr, max_tokens);
+  const int vpr = n / E;
+  const long long total = static_cast<long long>(t) * vpr;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < total;
+       i0 += stride * kBatch) {
+    Vec16 x[kBatch];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const long long i = i0 + j * stride;
+      if (i < total) x[j] = ld_global_v4(out + i * E);
+    }
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const long long i = i0 + j * stride;
+      if (i < total) {
+        const int c = static_cast<int>(i % vpr);
+        float fx[E], fb[E];
+        VecTraits<T>::unpack(x[j], fx);
+        VecTraits<T>::unpack(ld_global_v4(bias + c * E), fb);
+#pragma unroll
+        for (int e = 0; e < E; ++e) fx[e] = gelu_tanh(fx[e] + fb[e]);
+        st_global_v4(out + i * E, VecTraits<T>::pack(fx));
+      }
+    }
+  }
+}
+
+// out[row] = LN(out[row] + input[row] + bias) * gamma + beta, one warp per
+// row, the row held in registers (fp32) between the two statistics passes.
+// bias / gamma / beta are re-read per row: they stay L1-resident, and not
+// keeping them in registers doubles the number of resident warps.
+template <typename T, int kVPL>
+__global__ void __launch_bounds__(kThreads, (kVPL <= 4 ? 3 : 1))
+add_bias_input_layernorm_kernel(T* __restrict__ out, const T* __restrict__ input,
+                                const T* __restrict__ bias, const T* __restrict__ gamma,
+                                const T* __restrict__ beta, const int* __restrict__ t_ptr,
+                                int max_tokens, int n, float eps) {
+  constexpr int E = VecTraits<T>::kElems;
+  const int t = clamp_tokens(t_ptr, max_tokens);
+  const int lane = threadIdx.x & 31;
+  const int warp = blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+  const int nwarps = gridDim.x * (kThreads / 32);
+  const int vpr = n / E;
+  const float inv_n = 1.0f / static_cast<float>(n);
+
+  for (int row = warp; row < t; row += nwarps) {
+    T* orow = out + static_cast<size_t>(row) * n;
+    const T* irow = input + static_cast<size_t>(row) * n;
+    Vec16 vo[kVPL], vi[kVPL];
+#pragma unroll
+    for (int j = 0; j < kVPL; ++j) {
+      const int c = j * 32 + lane;
+      if (c < vpr) {
+        vo[j] = ld_global_v4(orow + c * E);
+        vi[j] = ld_global_nc_v4(irow + c * E);
+      }
+    }
+    float x[kVPL][E];
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < kVPL; ++j) {
+      const int c = j * 32 + lane;
+      if (c < vpr) {
+        float fo[E], fi[E], fb[E];
+        VecTraits<T>::unpack(vo[j], fo);
+        VecTraits<T>::unpack(vi[j], fi);
+        VecTraits<T>::unpack(ld_global_v4(bias + c * E), fb);
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          x[j][e] = fo[e] + fi[e] + fb[e];
+          sum += x[j][e];
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < E; ++e) x[j][e] = 0.f;
+      }
+    }
+    const float mean = warp_sum(sum) * inv_n;
+    float sq = 0.f;
+#pragma unroll
+    for (int j = 0; j < kVPL; ++j) {
+      const int c = j * 32 + lane;
+      if (c < vpr) {
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          const float dlt = x[j][e] - mean;
+          sq += dlt * dlt;
+        }
+      }
+    }
+    const float rstd = rsqrtf(warp_sum(sq) * inv_n + eps);
+#pragma unroll
+    for (int j = 0; j < kVPL; ++j) {
+      const int c = j * 32 + lane;
+      if (c < vpr) {
+        float fg[E], fbe[E], y[E];
+        VecTraits<T>::unpack(ld_global_v4(gamma + c * E), fg);
+        VecTraits<T>::unpack(ld_global_v4(beta + c * E), fbe);
+#pragma unroll
+        for (int e = 0; e < E; ++e) y[e] = (x[j][e] - mean) * rstd * fg[e] + fbe[e];
+        st_global_v4(orow + c * E, VecTraits<T>::pack(y));
+      }
+    }
+  }
+}
+
+template <typename T>
+__global__ void transpose_kernel(const T* __restrict__ src, T* __restrict__ dst, int rows, int cols) {
+  __shared__ T tile[32][33];
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    const int r = r0 + i, c = c0 + threadIdx.x;
+    if (r < rows && c < cols) tile[i][threadIdx.x] = src[static_cast<size_t>(r) * cols + c];
+  }
+  __syncthreads();
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    const int c = c0 + i, r = r0 + threadIdx.x;
+    if (r < rows && c < cols) dst[static_cast<size_t>(c) * rows + r] = tile[threadIdx.x][i];
+  }
+}
+
+template <typename T>
+__global__ void copy_columns_kernel(const T* __restrict__ src, T* __restrict__ dst, int rows,
+                                    int cols, int dst_ld, int dst_col0) {
+  const long long total = static_cast<long long>(rows) * cols;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / cols, c = i - r * cols;
+    dst[r * dst_ld + dst_col0 + c] = src[i];
+  }
+}
+
+inline int grid_for(long long work_items) {
+  long long ctas = (work_items + kThreads - 1) / kThreads;
+  const long long cap = static_cast<long long>(sm_count()) * kCtasPerSm;
+  if (ctas > cap) ctas = cap;
+  return ctas < 1 ? 1 : static_cast<int>(ctas);
+}
+
+}  // namespace
+
+template <typename T>
+cudaError_t launch_add_qkv_bias_transpose(const T* q, const T* bq, const T* k, const T* bk,
+                                          const T* v, const T* bv, T* out, const int* t_ptr,
+                                          int max_tokens, int heads, int d, cudaStream_t stream) {
+  constexpr int E = VecTraits<T>::kElems;
+  if (max_tokens <= 0) return cudaSuccess;
+  if (d % E != 0) return cudaErrorInvalidValue;
+  const long long work = static_cast<long long>(max_tokens) * (heads * d / E);
+  add_qkv_bias_transpose_kernel<T><<<grid_for(work), kThreads, 0, stream>>>(
+      q, bq, k, bk, v, bv, out, t_ptr, max_tokens, heads, d);
+  return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t launch_add_bias_gelu(T* out, const T* bias, const int* t_ptr, int max_tokens, int n,
+                                 cudaStream_t stream) {
+  constexpr int E = VecTraits<T>::kElems;
+  if (max_tokens <= 0) return cudaSuccess;
+  if (n % E != 0) return cudaErrorInvalidValue;
+  const long long work = static_cast<long long>(max_tokens) * (n / E) / 4 + 1;
+  add_bias_gelu_kernel<T><<<grid_for(work), kThreads, 0, stream>>>(out, bias, t_ptr, max_tokens, n);
+  return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t launch_add_bias_input_layernorm(T* out, const T* input, const T* bias, const T* gamma,
+                                            const T* beta, const int* t_ptr, int max_tokens, int n,
+                                            float eps, cudaStream_t stream) {
+  constexpr int E = VecTraits<T>::kElems;
+  if (max_tokens <= 0) return cudaSuccess;
+  if (n % E != 0 || n <= 0) return cudaErrorInvalidValue;
+  const int vpl = (n / E + 31) / 32;
+  const long long rows_per_cta = kThreads / 32;
+  long long ctas = (max_tokens + rows_per_cta - 1) / rows_per_cta;
+  const long long cap = static_cast<long long>(sm_count()) * kCtasPerSm;
+  if (ctas > cap) ctas = cap;
+  const int grid = static_cast<int>(ctas);
+#define ETB_LN(V)                                                                         \
+  add_bias_input_layernorm_kernel<T, V><<<grid, kThreads, 0, stream>>>(out, input, bias, gamma, \
+                                                                       beta, t_ptr, max_tokens, n, eps)
+  if (vpl <= 1) ETB_LN(1);
+  else if (vpl <= 2) ETB_LN(2);
+  else if (vpl <= 3) ETB_LN(3);
+  else if (vpl <= 4) ETB_LN(4);
+  else if (vpl <= 6) ETB_LN(6);
+  else if (vpl <= 8) ETB_LN(8);
+  else return cudaErrorInvalidValue;
+#undef ETB_LN
+  return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t launch_transpose(const T* src, T* dst, int rows, int cols, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return cudaSuccess;
+  dim3 grid((cols + 31) / 32, (rows + 31) / 32), block(32, 8);
+  transpose_kernel<T><<<grid, block, 0, stream>>>(src, dst, rows, cols);
+  return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t launch_copy_columns(const T* src, T* dst, int rows, int cols, int dst_ld, int dst_col0,
+                                cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return cudaSuccess;
+  copy_columns_kernel<T><<<grid_for(static_cast<long long>(rows) * cols), kThreads, 0, stream>>>(
+      src, dst, rows, cols, dst_ld, dst_col0);
+  return cudaGetLastError();
+}
+
+#define ETB_INST(T)                                                                              \
+  template cudaError_t launch_add_qkv_bias_transpose<T>(const T*, const T*, const T*, const T*,  \
+                                                        const T*, const T*, T*, const int*, int, \
+                                                        int, int, cudaStream_t);                 \
+  template cudaError_t launch_add_bias_gelu<T>(T*, const T*, const int*, int, int, cudaStream_t); \
+  template cudaError_t launch_add_bias_input_layernorm<T>(T*, const T*, const T*, const T*,      \
+                                                          const T*, const int*, int, int, float, \
+                                                          cudaStream_t);                         \
+  template cudaError_t launch_transpose<T>(const T*, T*, int, int, cudaStream_t);                \
+  template cudaError_t launch_copy_columns<T>(const T*, T*, int, int, int, int, cudaStream_t);
+ETB_INST(float)
+ETB_INST(__half)
+#undef ETB_INST
+
+}  // namespace etb

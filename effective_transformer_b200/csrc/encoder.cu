@@ -1,0 +1,818 @@
+// Host side of the encoder path and its C ABI (include/et_b200.h): handle,
+// weight repacking, workspace, the three operators and the whole-path calls.
+// It plays the role of the reference's GPU functors
+// (tf_op/bert_transformer_op.cu.cc:33-373) without TensorFlow: the caller's
+// stream and buffers come in through POD structs, work is only enqueued, and
+// the valid-token count never travels to the host between kernels.
+#include "../../include/et_b200.h"
+
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+#include <type_traits>
+#include <vector>
+
+#include "common.cuh"
+
+using namespace etb;
+
+namespace {
+
+inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct LayerWeights {
+  // row-major [in, out] copies (QKV concatenated along out) for the CUDA-core GEMM
+  void* wqkv = nullptr;  // [H, 3H]
+  void* wo = nullptr;    // [H, H]
+  void* w1 = nullptr;    // [H, F]
+  void* w2 = nullptr;    // [F, H]
+  // K-major [out, in] copies for the tcgen05 GEMM (fp16 handles only)
+  void* wqkv_t = nullptr;  // [3H, H]
+  void* wo_t = nullptr;    // [H, H]
+  void* w1_t = nullptr;    // [F, H]
+  void* w2_t = nullptr;    // [H, F]
+  void* bqkv = nullptr;    // [3H]
+  void* bo = nullptr;
+  void* ln1_gamma = nullptr;
+  void* ln1_beta = nullptr;
+  void* b1 = nullptr;      // [F]
+  void* b2 = nullptr;
+  void* ln2_gamma = nullptr;
+  void* ln2_beta = nullptr;
+  bool ready = false;
+};
+
+struct Workspace {
+  size_t cap_tokens = 0;  // rows every token buffer can hold (multiple of 128)
+  void* x = nullptr;      // [cap, H]  packed activations (layer input/output)
+  void* qkv = nullptr;    // [cap, 3H]
+  void* ctx = nullptr;    // [cap, H]
+  void* att = nullptr;    // [cap, H]
+  void* ffn = nullptr;    // [cap, F]
+  void* stage_in = nullptr;   // [B*S, H] device staging for the host-buffer call
+  void* stage_out = nullptr;  // [B*S, H]
+  int* stage_mask = nullptr;  // [B*S]
+  int* batch_idx = nullptr;
+  int* word_idx = nullptr;
+  int* padding_offset = nullptr;
+  int* prefix_sum = nullptr;
+  int* seq_len = nullptr;     // [B]
+  int* cu_seqlens = nullptr;  // [B+1]
+  int* lens_scratch = nullptr;
+  int* valid_word_num = nullptr;
+  int* status = nullptr;
+  std::vector<void*> allocations;
+};
+
+}  // namespace
+
+struct Profiler {
+  bool enabled = false;
+  long long launches[ET_PROF_NUM] = {};
+  double ms[ET_PROF_NUM] = {};
+  struct Span { int cat; cudaEvent_t a, b; };
+  std::vector<Span> pending;
+  std::vector<cudaEvent_t> free_events;
+  cudaEvent_t get() {
+    if (!free_events.empty()) {
+      cudaEvent_t e = free_events.back();
+      free_events.pop_back();
+      return e;
+    }
+    cudaEvent_t e = nullptr;
+    cudaEventCreate(&e);
+    return e;
+  }
+};
+
+struct et_handle_s {
+  et_config_t cfg{};
+  Profiler prof;
+  int hidden = 0;
+  size_t esize = 0;
+  float eps = 1e-6f;
+  bool use_simt = false;
+  std::vector<LayerWeights> layers;
+  Workspace ws;
+  cudaStream_t own_stream = nullptr;
+  int* host_pinned = nullptr;  // [2]: valid_word_num, status
+  std::string last_error;
+};
+
+namespace {
+
+thread_local std::string g_create_error;
+
+int set_error(et_handle_t h, int code, const std::string& msg) {
+  if (h != nullptr) h->last_error = msg;
+  else g_create_error = msg;
+  return code;
+}
+int cuda_fail(et_handle_t h, cudaError_t e, const char* what) {
+  return set_error(h, ET_CUDA_ERROR,
+                   std::string("[ET][ERROR] CUDA runtime error: ") + cudaGetErrorString(e) + " in " + what);
+}
+#define ET_CUDA(h, expr)                                   \
+  do {                                                     \
+    cudaError_t e__ = (expr);                              \
+    if (e__ != cudaSuccess) return cuda_fail(h, e__, #expr); \
+  } while (0)
+
+// Runs one launcher call; counts its kernels and, when profiling is on,
+// brackets it with CUDA events on the launching stream.
+#define ET_LAUNCH(h, cat, nkernels, stream, expr)                          \
+  do {                                                                     \
+    Profiler& pr__ = (h)->prof;                                            \
+    cudaEvent_t ea__ = nullptr, eb__ = nullptr;                            \
+    if (pr__.enabled) {                                                    \
+      ea__ = pr__.get();                                                   \
+      eb__ = pr__.get();                                                   \
+      if (ea__ && eb__) cudaEventRecord(ea__, stream);                     \
+    }                                                                      \
+    cudaError_t e__ = (expr);                                              \
+    if (ea__ && eb__) {                                                    \
+      cudaEventRecord(eb__, stream);                                       \
+      pr__.pending.push_back({cat, ea__, eb__});                           \
+    }                                                                      \
+    if (e__ != cudaSuccess) return cuda_fail(h, e__, #expr);               \
+    pr__.launches[cat] += (nkernels);                                      \
+  } while (0)
+
+struct DeviceGuard {
+  int prev = -1;
+  bool ok = true;
+  explicit DeviceGuard(int dev) {
+    if (cudaGetDevice(&prev) != cudaSuccess) ok = false;
+    if (ok && prev != dev && cudaSetDevice(dev) != cudaSuccess) ok = false;
+  }
+  ~DeviceGuard() {
+    if (prev >= 0) cudaSetDevice(prev);
+  }
+};
+
+int ws_alloc(et_handle_t h, void** p, size_t bytes) {
+  bytes = round_up(bytes == 0 ? 16 : bytes, 256);
+  ET_CUDA(h, cudaMalloc(p, bytes));
+  h->ws.allocations.push_back(*p);
+  return ET_OK;
+}
+
+size_t workspace_bytes_for(const et_handle_s* h, size_t batch, size_t seq) {
+  const size_t cap = round_up(batch * seq, 128);
+  const size_t hid = h->hidden, f = h->cfg.ffn_dim, e = h->esize;
+  size_t total = 0;
+  total += cap * hid * e * 3;          // x, ctx, att
+  total += cap * 3 * hid * e;          // qkv
+  total += cap * f * e;                // ffn
+  total += batch * seq * hid * e * 2;  // staging in/out
+  total += batch * seq * 4 * 5;        // mask staging + 4 index arrays
+  total += (batch * 3 + 8) * 4;
+  return total;
+}
+
+template <typename T>
+int pack_layer(et_handle_t h, LayerWeights& lw, const void* const* w, cudaStream_t s) {
+  const int hid = h->hidden, f = h->cfg.ffn_dim;
+  auto W = [&](int i) { return static_cast<const T*>(w[i]); };
+  // row-major concat [H, 3H]
+  for (int j = 0; j < 3; ++j)
+    ET_CUDA(h, launch_copy_columns<T>(W(2 * j), static_cast<T*>(lw.wqkv), hid, hid, 3 * hid, j * hid, s));
+  ET_CUDA(h, cudaMemcpyAsync(lw.wo, w[6], sizeof(T) * hid * hid, cudaMemcpyDeviceToDevice, s));
+  ET_CUDA(h, cudaMemcpyAsync(lw.w1, w[10], sizeof(T) * hid * f, cudaMemcpyDeviceToDevice, s));
+  ET_CUDA(h, cudaMemcpyAsync(lw.w2, w[12], sizeof(T) * f * hid, cudaMemcpyDeviceToDevice, s));
+  if (lw.wqkv_t != nullptr) {
+    for (int j = 0; j < 3; ++j)
+      ET_CUDA(h, launch_transpose<T>(W(2 * j), static_cast<T*>(lw.wqkv_t) + static_cast<size_t>(j) * hid * hid,
+                                     hid, hid, s));
+    ET_CUDA(h, launch_transpose<T>(W(6), static_cast<T*>(lw.wo_t), hid, hid, s));
+    ET_CUDA(h, launch_transpose<T>(W(10), static_cast<T*>(lw.w1_t), hid, f, s));
+    ET_CUDA(h, launch_transpose<T>(W(12), static_cast<T*>(lw.w2_t), f, hid, s));
+  }
+  for (int j = 0; j < 3; ++j)
+    ET_CUDA(h, cudaMemcpyAsync(static_cast<T*>(lw.bqkv) + j * hid, w[2 * j + 1], sizeof(T) * hid,
+                               cudaMemcpyDeviceToDevice, s));
+  ET_CUDA(h, cudaMemcpyAsync(lw.bo, w[7], sizeof(T) * hid, cudaMemcpyDeviceToDevice, s));
+  ET_CUDA(h, cudaMemcpyAsync(lw.ln1_beta, w[8], sizeof(T) * hid, cudaMemcpyDeviceToDevice, s));
+  ET_CUDA(h, cudaMemcpyAsync(lw.ln1_gamma, w[9], sizeof(T) * hid, cudaMemcpyDeviceToDevice, s));
+  ET_CUDA(h, cudaMemcpyAsync(lw.b1, w[11], sizeof(T) * f, cudaMemcpyDeviceToDevice, s));
+  ET_CUDA(h, cudaMemcpyAsync(lw.b2, w[13], sizeof(T) * hid, cudaMemcpyDeviceToDevice, s));
+  ET_CUDA(h, cudaMemcpyAsync(lw.ln2_beta, w[14], sizeof(T) * hid, cudaMemcpyDeviceToDevice, s));
+  ET_CUDA(h, cudaMemcpyAsync(lw.ln2_gamma, w[15], sizeof(T) * hid, cudaMemcpyDeviceToDevice, s));
+  lw.ready = true;
+  return ET_OK;
+}
+
+int pack_layer_any(et_handle_t h, int layer, const void* const* w, cudaStream_t s) {
+  LayerWeights& lw = h->layers[layer];
+  return h->cfg.dtype == ET_FP16 ? pack_layer<__half>(h, lw, w, s) : pack_layer<float>(h, lw, w, s);
+}
+
+// One encoder layer on the packed layout.  x_out may alias x_in.
+template <typename T>
+int run_layer(et_handle_t h, const LayerWeights& lw, const T* x_in, T* x_out, const int* t_ptr,
+              int max_m, const int* cu_seqlens, int batch, int seq, cudaStream_t s) {
+  const int hid = h->hidden, f = h->cfg.ffn_dim, heads = h->cfg.head_num, d = h->cfg.size_per_head;
+  Workspace& ws = h->ws;
+  T* qkv = static_cast<T*>(ws.qkv);
+  T* ctx = static_cast<T*>(ws.ctx);
+  T* att = static_cast<T*>(ws.att);
+  T* ffn = static_cast<T*>(ws.ffn);
+  auto B = [](const void* p) { return static_cast<const T*>(p); };
+  const bool tc = std::is_same<T, __half>::value && !h->use_simt;
+
+  auto gemm = [&](const T* a, const void* w_rm, const void* w_t, const void* bias, T* c, int n, int k,
+                  int epi) -> cudaError_t {
+    if (tc)
+      return launch_gemm_tcgen05(reinterpret_cast<const __half*>(a), static_cast<const __half*>(w_t),
+                                 static_cast<const __half*>(bias), reinterpret_cast<__half*>(c), t_ptr,
+                                 max_m, n, k, epi, ws.status, s);
+    return launch_gemm_simt<T>(a, B(w_rm), B(bias), c, t_ptr, max_m, n, k, epi, s);
+  };
+
+  // Q,K,V projections + bias in one GEMM -> [T, 3H]
+  ET_LAUNCH(h, ET_PROF_GEMM_QKV, 1, s, gemm(x_in, lw.wqkv, lw.wqkv_t, lw.bqkv, qkv, 3 * hid, hid, kEpiBias));
+  // attention straight from the [T, 3H] buffer to packed context [T, H]
+  if (tc)
+    ET_LAUNCH(h, ET_PROF_ATTENTION, 1, s, launch_attention_tc(reinterpret_cast<const __half*>(qkv),
+                                   reinterpret_cast<const __half*>(qkv) + hid,
+                                   reinterpret_cast<const __half*>(qkv) + 2 * hid, 3LL * hid, d,
+                                   reinterpret_cast<__half*>(ctx), cu_seqlens, batch, seq, heads, d,
+                                   ws.status, s));
+  else
+    ET_LAUNCH(h, ET_PROF_ATTENTION, 1, s, launch_attention_simt<T>(qkv, qkv + hid, qkv + 2 * hid, 3LL * hid, d, ctx, cu_seqlens,
+                                        batch, seq, heads, d, s));
+  // attention output projection, then +bias +residual, LayerNorm
+  ET_LAUNCH(h, ET_PROF_GEMM_ATTN_OUT, 1, s, gemm(ctx, lw.wo, lw.wo_t, nullptr, att, hid, hid, kEpiNone));
+  ET_LAUNCH(h, ET_PROF_LAYERNORM, 1, s, launch_add_bias_input_layernorm<T>(att, x_in, B(lw.bo), B(lw.ln1_gamma), B(lw.ln1_beta),
+                                                t_ptr, max_m, hid, h->eps, s));
+  // feed-forward: bias + GELU fused into the first GEMM
+  ET_LAUNCH(h, ET_PROF_GEMM_FFN1, 1, s, gemm(att, lw.w1, lw.w1_t, lw.b1, ffn, f, hid, kEpiBiasGelu));
+  ET_LAUNCH(h, ET_PROF_GEMM_FFN2, 1, s, gemm(ffn, lw.w2, lw.w2_t, nullptr, x_out, hid, f, kEpiNone));
+  ET_LAUNCH(h, ET_PROF_LAYERNORM, 1, s, launch_add_bias_input_layernorm<T>(x_out, att, B(lw.b2), B(lw.ln2_gamma), B(lw.ln2_beta),
+                                                t_ptr, max_m, hid, h->eps, s));
+  return ET_OK;
+}
+
+int check_shape(et_handle_t h, int batch, int seq, int heads, int d) {
+  if (batch < 0 || seq < 0) return set_error(h, ET_INVALID_ARGUMENT, "negative batch_size or seq_len");
+  if (batch > h->cfg.max_batch_size)
+    return set_error(h, ET_INVALID_ARGUMENT, "batch_size exceeds the handle's max_batch_size");
+  if (seq > h->cfg.max_seq_len)
+    return set_error(h, ET_INVALID_ARGUMENT, "seq_len exceeds the handle's max_seq_len");
+  if (heads != h->cfg.head_num || d != h->cfg.size_per_head)
+    return set_error(h, ET_INVALID_ARGUMENT, "head_num / size_per_head differ from the handle's");
+  return ET_OK;
+}
+
+int input_impl(et_handle_t h, const et_input_param_t* p) {
+  cudaStream_t s = static_cast<cudaStream_t>(p->stream);
+  Workspace& ws = h->ws;
+  ET_LAUNCH(h, ET_PROF_PADDING_OFFSETS, (p->batch_size > 0 && p->from_seq_len > 0) ? 2 : 1, s, launch_padding_offsets(p->mask, p->batch_size, p->from_seq_len, ws.prefix_sum,
+                                    p->valid_word_num, p->batch_idx, p->word_idx, ws.seq_len,
+                                    ws.cu_seqlens, ws.padding_offset, ws.lens_scratch, s));
+  if (h->cfg.dtype == ET_FP16)
+    ET_LAUNCH(h, ET_PROF_REMOVE_PADDING, 1, s, launch_remove_padding<__half>(static_cast<const __half*>(p->from_tensor), p->batch_idx,
+                                             p->word_idx, p->valid_word_num,
+                                             static_cast<__half*>(p->to_tensor), p->batch_size,
+                                             p->from_seq_len, h->hidden, s));
+  else
+    ET_LAUNCH(h, ET_PROF_REMOVE_PADDING, 1, s, launch_remove_padding<float>(static_cast<const float*>(p->from_tensor), p->batch_idx,
+                                            p->word_idx, p->valid_word_num,
+                                            static_cast<float*>(p->to_tensor), p->batch_size,
+                                            p->from_seq_len, h->hidden, s));
+  return ET_OK;
+}
+
+int output_impl(et_handle_t h, const et_output_param_t* p) {
+  cudaStream_t s = static_cast<cudaStream_t>(p->stream);
+  if (h->cfg.dtype == ET_FP16)
+    ET_LAUNCH(h, ET_PROF_RESTORE_PADDING, 1, s, launch_restore_padding<__half>(static_cast<const __half*>(p->from_tensor), p->batch_idx,
+                                              p->word_idx, p->valid_word_num,
+                                              static_cast<__half*>(p->to_tensor), p->batch_size,
+                                              p->from_seq_len, h->hidden, s));
+  else
+    ET_LAUNCH(h, ET_PROF_RESTORE_PADDING, 1, s, launch_restore_padding<float>(static_cast<const float*>(p->from_tensor), p->batch_idx,
+                                             p->word_idx, p->valid_word_num,
+                                             static_cast<float*>(p->to_tensor), p->batch_size,
+                                             p->from_seq_len, h->hidden, s));
+  return ET_OK;
+}
+
+int forward_impl(et_handle_t h, const void* from_tensor, const int* mask, void* out, int batch, int seq,
+                 cudaStream_t s) {
+  int rc = check_shape(h, batch, seq, h->cfg.head_num, h->cfg.size_per_head);
+  if (rc != ET_OK) return rc;
+  if (from_tensor == nullptr || mask == nullptr || out == nullptr)
+    return set_error(h, ET_INVALID_ARGUMENT, "null tensor pointer");
+  for (int l = 0; l < h->cfg.num_layers; ++l)
+    if (!h->layers[l].ready) return set_error(h, ET_NOT_READY, "weights of a layer were never set");
+  Workspace& ws = h->ws;
+  et_input_param_t ip{};
+  ip.from_tensor = from_tensor;
+  ip.mask = mask;
+  ip.valid_word_num = ws.valid_word_num;
+  ip.batch_idx = ws.batch_idx;
+  ip.word_idx = ws.word_idx;
+  ip.batch_size = batch;
+  ip.from_seq_len = seq;
+  ip.head_num = h->cfg.head_num;
+  ip.size_per_head = h->cfg.size_per_head;
+  ip.to_tensor = ws.x;
+  ip.stream = s;
+  rc = input_impl(h, &ip);
+  if (rc != ET_OK) return rc;
+  const int max_m = batch * seq;
+  for (int l = 0; l < h->cfg.num_layers; ++l) {
+    if (h->cfg.dtype == ET_FP16)
+      rc = run_layer<__half>(h, h->layers[l], static_cast<const __half*>(ws.x), static_cast<__half*>(ws.x),
+                             ws.valid_word_num, max_m, ws.cu_seqlens, batch, seq, s);
+    else
+      rc = run_layer<float>(h, h->layers[l], static_cast<const float*>(ws.x), static_cast<float*>(ws.x),
+                            ws.valid_word_num, max_m, ws.cu_seqlens, batch, seq, s);
+    if (rc != ET_OK) return rc;
+  }
+  et_output_param_t op{};
+  op.from_tensor = ws.x;
+  op.valid_word_num = ws.valid_word_num;
+  op.batch_idx = ws.batch_idx;
+  op.word_idx = ws.word_idx;
+  op.batch_size = batch;
+  op.from_seq_len = seq;
+  op.head_num = h->cfg.head_num;
+  op.size_per_head = h->cfg.size_per_head;
+  op.to_tensor = out;
+  op.stream = s;
+  return output_impl(h, &op);
+}
+
+}  // namespace
+
+// =============================== C ABI =====================================
+#define ET_TRY try {
+#define ET_CATCH(h)                                                              \
+  }                                                                              \
+  catch (const std::bad_alloc&) { return set_error(h, ET_CUDA_ERROR, "host allocation failed"); } \
+  catch (const std::exception& e) { return set_error(h, ET_CUDA_ERROR, e.what()); }             \
+  catch (...) { return set_error(h, ET_CUDA_ERROR, "Runtime error"); }
+
+extern "C" {
+
+int et_create(const et_config_t* config, et_handle_t* out_handle) {
+  et_handle_t h = nullptr;
+  ET_TRY
+  if (config == nullptr || out_handle == nullptr)
+    return set_error(nullptr, ET_INVALID_ARGUMENT, "null config or out_handle");
+  *out_handle = nullptr;
+  const et_config_t& c = *config;
+  if (c.dtype != ET_FP32 && c.dtype != ET_FP16)
+    return set_error(nullptr, ET_INVALID_ARGUMENT, "dtype must be ET_FP32 or ET_FP16");
+  if (c.num_layers <= 0 || c.head_num <= 0 || c.max_batch_size <= 0 || c.max_seq_len <= 0)
+    return set_error(nullptr, ET_INVALID_ARGUMENT, "num_layers, head_num, max_batch_size, max_seq_len must be positive");
+  if (c.size_per_head != 64)
+    return set_error(nullptr, ET_INVALID_ARGUMENT, "size_per_head must be 64");
+  const int hid = c.head_num * c.size_per_head;
+  if (c.ffn_dim <= 0 || (c.ffn_dim % 128) != 0 || (hid % 128) != 0)
+    return set_error(nullptr, ET_INVALID_ARGUMENT, "hidden and ffn_dim must be positive multiples of 128");
+  int ndev = 0;
+  if (cudaGetDeviceCount(&ndev) != cudaSuccess || c.device < 0 || c.device >= ndev)
+    return set_error(nullptr, ET_CUDA_ERROR, "no such CUDA device");
+  DeviceGuard guard(c.device);
+  if (!guard.ok) return set_error(nullptr, ET_CUDA_ERROR, "cudaSetDevice failed");
+  cudaDeviceProp prop{};
+  if (cudaGetDeviceProperties(&prop, c.device) != cudaSuccess || prop.major != 10)
+    return set_error(nullptr, ET_CUDA_ERROR, "this library contains sm_100a code only: a B200-class GPU is required");
+
+  h = new et_handle_s();
+  h->cfg = c;
+  h->hidden = hid;
+  h->esize = c.dtype == ET_FP16 ? 2 : 4;
+  h->eps = c.layernorm_eps > 0.f ? c.layernorm_eps : 1e-6f;
+  h->use_simt = (c.dtype == ET_FP32);
+  h->layers.resize(c.num_layers);
+  auto bail = [&](int rc) {
+    std::string msg = h->last_error;
+    et_destroy(h);
+    g_create_error = msg;
+    return rc;
+  };
+  int rc = ET_OK;
+  const size_t e = h->esize, f = c.ffn_dim;
+  const size_t H = hid;
+  for (auto& lw : h->layers) {
+    struct { void** p; size_t n; } items[] = {
+        {&lw.wqkv, 3 * H * H}, {&lw.wo, H * H}, {&lw.w1, H * f}, {&lw.w2, f * H},
+        {&lw.bqkv, 3 * H}, {&lw.bo, H}, {&lw.ln1_gamma, H}, {&lw.ln1_beta, H},
+        {&lw.b1, f}, {&lw.b2, H}, {&lw.ln2_gamma, H}, {&lw.ln2_beta, H}};
+    for (auto& it : items)
+      if ((rc = ws_alloc(h, it.p, it.n * e)) != ET_OK) return bail(rc);
+    if (c.dtype == ET_FP16) {
+      struct { void** p; size_t n; } packed[] = {
+          {&lw.wqkv_t, 3 * H * H}, {&lw.wo_t, H * H}, {&lw.w1_t, H * f}, {&lw.w2_t, f * H}};
+      for (auto& it : packed)
+        if ((rc = ws_alloc(h, it.p, it.n * e)) != ET_OK) return bail(rc);
+    }
+  }
+  Workspace& ws = h->ws;
+  const size_t bs = static_cast<size_t>(c.max_batch_size) * c.max_seq_len;
+  ws.cap_tokens = round_up(bs, 128);
+  const size_t cap = ws.cap_tokens;
+  struct { void** p; size_t bytes; } bufs[] = {
+      {&ws.x, cap * H * e}, {&ws.qkv, cap * 3 * H * e}, {&ws.ctx, cap * H * e}, {&ws.att, cap * H * e},
+      {&ws.ffn, cap * f * e}, {&ws.stage_in, bs * H * e}, {&ws.stage_out, bs * H * e},
+      {reinterpret_cast<void**>(&ws.stage_mask), bs * 4},
+      {reinterpret_cast<void**>(&ws.batch_idx), cap * 4}, {reinterpret_cast<void**>(&ws.word_idx), cap * 4},
+      {reinterpret_cast<void**>(&ws.padding_offset), cap * 4},
+      {reinterpret_cast<void**>(&ws.prefix_sum), cap * 4},
+      {reinterpret_cast<void**>(&ws.seq_len), static_cast<size_t>(c.max_batch_size) * 4},
+      {reinterpret_cast<void**>(&ws.cu_seqlens), (static_cast<size_t>(c.max_batch_size) + 1) * 4},
+      {reinterpret_cast<void**>(&ws.lens_scratch), static_cast<size_t>(c.max_batch_size) * 4},
+      {reinterpret_cast<void**>(&ws.valid_word_num), 4}, {reinterpret_cast<void**>(&ws.status), 4}};
+  for (auto& b : bufs)
+    if ((rc = ws_alloc(h, b.p, b.bytes)) != ET_OK) return bail(rc);
+  if (cudaMemset(ws.status, 0, 4) != cudaSuccess || cudaMemset(ws.valid_word_num, 0, 4) != cudaSuccess)
+    return bail(cuda_fail(h, cudaGetLastError(), "cudaMemset"));
+  if (cudaStreamCreateWithFlags(&h->own_stream, cudaStreamNonBlocking) != cudaSuccess)
+    return bail(cuda_fail(h, cudaGetLastError(), "cudaStreamCreate"));
+  if (cudaMallocHost(reinterpret_cast<void**>(&h->host_pinned), 2 * sizeof(int)) != cudaSuccess)
+    return bail(cuda_fail(h, cudaGetLastError(), "cudaMallocHost"));
+  *out_handle = h;
+  return ET_OK;
+  ET_CATCH(nullptr)
+}
+
+int et_destroy(et_handle_t h) {
+  if (h == nullptr) return ET_OK;
+  DeviceGuard guard(h->cfg.device);
+  cudaDeviceSynchronize();
+  for (void* p : h->ws.allocations) cudaFree(p);
+  for (auto& sp : h->prof.pending) {
+    cudaEventDestroy(sp.a);
+    cudaEventDestroy(sp.b);
+  }
+  for (cudaEvent_t e : h->prof.free_events) cudaEventDestroy(e);
+  if (h->own_stream) cudaStreamDestroy(h->own_stream);
+  if (h->host_pinned) cudaFreeHost(h->host_pinned);
+  delete h;
+  return ET_OK;
+}
+
+const char* et_last_error(et_handle_t h) {
+  return h != nullptr ? h->last_error.c_str() : g_create_error.c_str();
+}
+
+int et_set_debug_simt(et_handle_t h, int use_simt) {
+  if (h == nullptr) return ET_INVALID_ARGUMENT;
+  h->use_simt = (use_simt != 0) || h->cfg.dtype == ET_FP32;
+  return ET_OK;
+}
+
+int et_set_layer_weights(et_handle_t h, int layer, const void* const* weights, int on_host) {
+  ET_TRY
+  if (h == nullptr) return ET_INVALID_ARGUMENT;
+  if (layer < 0 || layer >= h->cfg.num_layers || weights == nullptr)
+    return set_error(h, ET_INVALID_ARGUMENT, "layer out of range or null weights");
+  for (int i = 0; i < 16; ++i)
+    if (weights[i] == nullptr) return set_error(h, ET_INVALID_ARGUMENT, "null weight pointer");
+  DeviceGuard guard(h->cfg.device);
+  const size_t H = h->hidden, f = h->cfg.ffn_dim, e = h->esize;
+  const size_t counts[16] = {H * H, H, H * H, H, H * H, H, H * H, H, H, H, H * f, f, f * H, H, H, H};
+  const void* dev[16];
+  std::vector<void*> temps;
+  int rc = ET_OK;
+  if (on_host) {
+    for (int i = 0; i < 16 && rc == ET_OK; ++i) {
+      void* p = nullptr;
+      cudaError_t ce = cudaMalloc(&p, round_up(counts[i] * e, 256));
+      if (ce == cudaSuccess) {
+        temps.push_back(p);
+        ce = cudaMemcpyAsync(p, weights[i], counts[i] * e, cudaMemcpyHostToDevice, h->own_stream);
+      }
+      if (ce != cudaSuccess) rc = cuda_fail(h, ce, "weight upload");
+      dev[i] = p;
+    }
+  } else {
+    for (int i = 0; i < 16; ++i) dev[i] = weights[i];
+  }
+  if (rc == ET_OK) rc = pack_layer_any(h, layer, dev, h->own_stream);
+  cudaError_t se = cudaStreamSynchronize(h->own_stream);
+  for (void* p : temps) cudaFree(p);
+  if (rc == ET_OK && se != cudaSuccess) rc = cuda_fail(h, se, "cudaStreamSynchronize");
+  return rc;
+  ET_CATCH(h)
+}
+
+int et_workspace_bytes(et_handle_t h, int batch_size, int seq_len, size_t* out_bytes) {
+  if (h == nullptr || out_bytes == nullptr) return ET_INVALID_ARGUMENT;
+  if (batch_size < 0 || seq_len < 0) return set_error(h, ET_INVALID_ARGUMENT, "negative shape");
+  *out_bytes = workspace_bytes_for(h, static_cast<size_t>(batch_size), static_cast<size_t>(seq_len));
+  return ET_OK;
+}
+
+int et_input(et_handle_t h, const et_input_param_t* p) {
+  ET_TRY
+  if (h == nullptr) return ET_INVALID_ARGUMENT;
+  if (p == nullptr) return set_error(h, ET_INVALID_ARGUMENT, "null param");
+  int rc = check_shape(h, p->batch_size, p->from_seq_len, p->head_num, p->size_per_head);
+  if (rc != ET_OK) return rc;
+  if (!p->from_tensor || !p->mask || !p->valid_word_num || !p->batch_idx || !p->word_idx || !p->to_tensor)
+    return set_error(h, ET_INVALID_ARGUMENT, "null tensor pointer");
+  DeviceGuard guard(h->cfg.device);
+  return input_impl(h, p);
+  ET_CATCH(h)
+}
+
+int et_output(et_handle_t h, const et_output_param_t* p) {
+  ET_TRY
+  if (h == nullptr) return ET_INVALID_ARGUMENT;
+  if (p == nullptr) return set_error(h, ET_INVALID_ARGUMENT, "null param");
+  int rc = check_shape(h, p->batch_size, p->from_seq_len, p->head_num, p->size_per_head);
+  if (rc != ET_OK) return rc;
+  if (!p->from_tensor || !p->valid_word_num || !p->batch_idx || !p->word_idx || !p->to_tensor)
+    return set_error(h, ET_INVALID_ARGUMENT, "null tensor pointer");
+  DeviceGuard guard(h->cfg.device);
+  return output_impl(h, p);
+  ET_CATCH(h)
+}
+
+int et_layer(et_handle_t h, int layer, const et_encoder_param_t* p, const et_transformer_param_t* tp) {
+  ET_TRY
+  if (h == nullptr) return ET_INVALID_ARGUMENT;
+  if (p == nullptr || tp == nullptr) return set_error(h, ET_INVALID_ARGUMENT, "null param");
+  if (layer < 0 || layer >= h->cfg.num_layers) return set_error(h, ET_INVALID_ARGUMENT, "layer out of range");
+  if (tp->from_seq_len != tp->to_seq_len)
+    return set_error(h, ET_INVALID_ARGUMENT, "only support from_seq_len == to_seq_len");
+  int rc = check_shape(h, tp->batch_size, tp->from_seq_len, tp->head_num, tp->size_per_head);
+  if (rc != ET_OK) return rc;
+  if (!p->from_tensor || !p->transformer_out || !p->batch_idx || !p->word_idx || !p->valid_word_num)
+    return set_error(h, ET_INVALID_ARGUMENT, "null tensor pointer");
+  if (p->to_tensor != nullptr && p->to_tensor != p->from_tensor)
+    return set_error(h, ET_INVALID_ARGUMENT, "to_tensor must equal from_tensor (self-attention)");
+  DeviceGuard guard(h->cfg.device);
+  cudaStream_t s = static_cast<cudaStream_t>(p->stream);
+  if (p->attr_kernel_Q != nullptr) {
+    const void* w[16] = {p->attr_kernel_Q, p->attr_bias_Q, p->attr_kernel_K, p->attr_bias_K,
+                         p->attr_kernel_V, p->attr_bias_V, p->attr_output_kernel, p->attr_output_bias,
+                         p->attr_output_layernorm_beta, p->attr_output_layernorm_gamma, p->inter_kernel,
+                         p->inter_bias, p->output_kernel, p->output_bias, p->output_layernorm_beta,
+                         p->output_layernorm_gamma};
+    for (int i = 0; i < 16; ++i)
+      if (w[i] == nullptr) return set_error(h, ET_INVALID_ARGUMENT, "null weight pointer");
+    rc = pack_layer_any(h, layer, w, s);
+    if (rc != ET_OK) return rc;
+  }
+  if (!h->layers[layer].ready) return set_error(h, ET_NOT_READY, "weights of this layer were never set");
+  const int batch = tp->batch_size, seq = tp->from_seq_len, max_m = batch * seq;
+  ET_LAUNCH(h, ET_PROF_PADDING_OFFSETS, 1, s, launch_seq_bounds_from_batch_idx(p->batch_idx, p->valid_word_num, batch, max_m,
+                                              h->ws.cu_seqlens, s));
+  if (h->cfg.dtype == ET_FP16)
+    return run_layer<__half>(h, h->layers[layer], static_cast<const __half*>(p->from_tensor),
+                             static_cast<__half*>(p->transformer_out), p->valid_word_num, max_m,
+                             h->ws.cu_seqlens, batch, seq, s);
+  return run_layer<float>(h, h->layers[layer], static_cast<const float*>(p->from_tensor),
+                          static_cast<float*>(p->transformer_out), p->valid_word_num, max_m,
+                          h->ws.cu_seqlens, batch, seq, s);
+  ET_CATCH(h)
+}
+
+int et_forward(et_handle_t h, const void* from_tensor, const int* mask, void* out, int batch_size,
+               int seq_len, void* stream) {
+  ET_TRY
+  if (h == nullptr) return ET_INVALID_ARGUMENT;
+  DeviceGuard guard(h->cfg.device);
+  return forward_impl(h, from_tensor, mask, out, batch_size, seq_len, static_cast<cudaStream_t>(stream));
+  ET_CATCH(h)
+}
+
+int et_forward_host(et_handle_t h, const void* from_host, const int* mask_host, void* out_host,
+                    int batch_size, int seq_len, int* valid_word_num_out) {
+  ET_TRY
+  if (h == nullptr) return ET_INVALID_ARGUMENT;
+  int rc = check_shape(h, batch_size, seq_len, h->cfg.head_num, h->cfg.size_per_head);
+  if (rc != ET_OK) return rc;
+  if (!from_host || !mask_host || !out_host) return set_error(h, ET_INVALID_ARGUMENT, "null host pointer");
+  DeviceGuard guard(h->cfg.device);
+  Workspace& ws = h->ws;
+  cudaStream_t s = h->own_stream;
+  const size_t rows = static_cast<size_t>(batch_size) * seq_len;
+  const size_t bytes = rows * h->hidden * h->esize;
+  if (rows > 0) {
+    ET_CUDA(h, cudaMemcpyAsync(ws.stage_in, from_host, bytes, cudaMemcpyHostToDevice, s));
+    ET_CUDA(h, cudaMemcpyAsync(ws.stage_mask, mask_host, rows * 4, cudaMemcpyHostToDevice, s));
+  }
+  rc = forward_impl(h, ws.stage_in, ws.stage_mask, ws.stage_out, batch_size, seq_len, s);
+  if (rc != ET_OK) return rc;
+  if (rows > 0) ET_CUDA(h, cudaMemcpyAsync(out_host, ws.stage_out, bytes, cudaMemcpyDeviceToHost, s));
+  ET_CUDA(h, cudaMemcpyAsync(&h->host_pinned[0], ws.valid_word_num, 4, cudaMemcpyDeviceToHost, s));
+  ET_CUDA(h, cudaMemcpyAsync(&h->host_pinned[1], ws.status, 4, cudaMemcpyDeviceToHost, s));
+  ET_CUDA(h, cudaStreamSynchronize(s));
+  if (valid_word_num_out) *valid_word_num_out = h->host_pinned[0];
+  if (h->host_pinned[1] != 0) {
+    char msg[96];
+    snprintf(msg, sizeof msg, "device-side wait expired, status word 0x%x", h->host_pinned[1]);
+    cudaMemsetAsync(ws.status, 0, 4, s);
+    cudaStreamSynchronize(s);
+    return set_error(h, ET_DEVICE_TIMEOUT, msg);
+  }
+  return ET_OK;
+  ET_CATCH(h)
+}
+
+int et_device_status(et_handle_t h, void* stream, int* out_status) {
+  ET_TRY
+  if (h == nullptr || out_status == nullptr) return ET_INVALID_ARGUMENT;
+  DeviceGuard guard(h->cfg.device);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  ET_CUDA(h, cudaMemcpyAsync(&h->host_pinned[1], h->ws.status, 4, cudaMemcpyDeviceToHost, s));
+  ET_CUDA(h, cudaStreamSynchronize(s));
+  *out_status = h->host_pinned[1];
+  if (*out_status != 0) {
+    ET_CUDA(h, cudaMemsetAsync(h->ws.status, 0, 4, s));
+    ET_CUDA(h, cudaStreamSynchronize(s));
+  }
+  return ET_OK;
+  ET_CATCH(h)
+}
+
+int et_last_padding_info(et_handle_t h, const int** cu_seqlens, const int** seq_len,
+                         const int** padding_offset, const int** prefix_sum) {
+  if (h == nullptr) return ET_INVALID_ARGUMENT;
+  if (cu_seqlens) *cu_seqlens = h->ws.cu_seqlens;
+  if (seq_len) *seq_len = h->ws.seq_len;
+  if (padding_offset) *padding_offset = h->ws.padding_offset;
+  if (prefix_sum) *prefix_sum = h->ws.prefix_sum;
+  return ET_OK;
+}
+
+int et_set_profiling(et_handle_t h, int enable) {
+  if (h == nullptr) return ET_INVALID_ARGUMENT;
+  h->prof.enabled = enable != 0;
+  return ET_OK;
+}
+
+int et_get_profile(et_handle_t h, double* ms_out, long long* launches_out, int reset) {
+  ET_TRY
+  if (h == nullptr) return ET_INVALID_ARGUMENT;
+  DeviceGuard guard(h->cfg.device);
+  Profiler& pr = h->prof;
+  for (auto& sp : pr.pending) {
+    ET_CUDA(h, cudaEventSynchronize(sp.b));
+    float ms = 0.f;
+    ET_CUDA(h, cudaEventElapsedTime(&ms, sp.a, sp.b));
+    pr.ms[sp.cat] += ms;
+    pr.free_events.push_back(sp.a);
+    pr.free_events.push_back(sp.b);
+  }
+  pr.pending.clear();
+  for (int i = 0; i < ET_PROF_NUM; ++i) {
+    if (ms_out) ms_out[i] = pr.ms[i];
+    if (launches_out) launches_out[i] = pr.launches[i];
+    if (reset) {
+      pr.ms[i] = 0.0;
+      pr.launches[i] = 0;
+    }
+  }
+  return ET_OK;
+  ET_CATCH(h)
+}
+
+int et_copy_to_host(void* dst_host, const void* src_device, size_t bytes, void* stream) {
+  if (bytes == 0) return ET_OK;
+  if (dst_host == nullptr || src_device == nullptr) return ET_INVALID_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (cudaMemcpyAsync(dst_host, src_device, bytes, cudaMemcpyDeviceToHost, s) != cudaSuccess)
+    return ET_CUDA_ERROR;
+  return cudaStreamSynchronize(s) == cudaSuccess ? ET_OK : ET_CUDA_ERROR;
+}
+
+// ---- kernel-level entry points ---------------------------------------------
+static int to_status(cudaError_t e) {
+  if (e == cudaSuccess) return ET_OK;
+  if (e == cudaErrorInvalidValue || e == cudaErrorMisalignedAddress) return ET_INVALID_ARGUMENT;
+  return ET_CUDA_ERROR;
+}
+
+int et_padding_offsets(const int* mask, int batch_size, int seq_len, int* prefix_sum,
+                       int* valid_word_num, int* batch_idx, int* word_idx, int* seq_len_out,
+                       int* cu_seqlens, int* padding_offset, int* scratch, void* stream) {
+  if (batch_size < 0 || seq_len < 0) return ET_INVALID_ARGUMENT;
+  if (batch_size > 0 && seq_len > 0 && (mask == nullptr || scratch == nullptr)) return ET_INVALID_ARGUMENT;
+  return to_status(launch_padding_offsets(mask, batch_size, seq_len, prefix_sum, valid_word_num, batch_idx,
+                                          word_idx, seq_len_out, cu_seqlens, padding_offset, scratch,
+                                          static_cast<cudaStream_t>(stream)));
+}
+
+#define ET_DISPATCH(dtype, CALL_HALF, CALL_FLOAT) \
+  ((dtype) == ET_FP16 ? to_status(CALL_HALF) : (dtype) == ET_FP32 ? to_status(CALL_FLOAT) : ET_INVALID_ARGUMENT)
+
+int et_remove_padding(int dtype, const void* from, const int* batch_idx, const int* word_idx,
+                      const int* t_ptr, void* to, int batch, int seq, int hidden, void* stream) {
+  if (!from || !batch_idx || !word_idx || !t_ptr || !to || batch < 0 || seq < 0 || hidden <= 0 ||
+      (hidden * (dtype == ET_FP16 ? 2 : 4)) % 16 != 0)
+    return ET_INVALID_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return ET_DISPATCH(dtype,
+                     launch_remove_padding<__half>(static_cast<const __half*>(from), batch_idx, word_idx, t_ptr,
+                                                   static_cast<__half*>(to), batch, seq, hidden, s),
+                     launch_remove_padding<float>(static_cast<const float*>(from), batch_idx, word_idx, t_ptr,
+                                                  static_cast<float*>(to), batch, seq, hidden, s));
+}
+
+int et_restore_padding(int dtype, const void* from, const int* batch_idx, const int* word_idx,
+                       const int* t_ptr, void* to, int batch, int seq, int hidden, void* stream) {
+  if (!from || !batch_idx || !word_idx || !t_ptr || !to || batch < 0 || seq < 0 || hidden <= 0 ||
+      (hidden * (dtype == ET_FP16 ? 2 : 4)) % 16 != 0)
+    return ET_INVALID_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return ET_DISPATCH(dtype,
+                     launch_restore_padding<__half>(static_cast<const __half*>(from), batch_idx, word_idx, t_ptr,
+                                                    static_cast<__half*>(to), batch, seq, hidden, s),
+                     launch_restore_padding<float>(static_cast<const float*>(from), batch_idx, word_idx, t_ptr,
+                                                   static_cast<float*>(to), batch, seq, hidden, s));
+}
+
+int et_add_qkv_bias_transpose(int dtype, const void* q, const void* bq, const void* k, const void* bk,
+                              const void* v, const void* bv, void* out, const int* t_ptr, int max_tokens,
+                              int heads, int d, void* stream) {
+  if (!q || !bq || !k || !bk || !v || !bv || !out || !t_ptr || max_tokens < 0 || heads <= 0 || d <= 0)
+    return ET_INVALID_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define H_(p) static_cast<const __half*>(p)
+#define F_(p) static_cast<const float*>(p)
+  return ET_DISPATCH(dtype,
+                     launch_add_qkv_bias_transpose<__half>(H_(q), H_(bq), H_(k), H_(bk), H_(v), H_(bv),
+                                                           static_cast<__half*>(out), t_ptr, max_tokens, heads, d, s),
+                     launch_add_qkv_bias_transpose<float>(F_(q), F_(bq), F_(k), F_(bk), F_(v), F_(bv),
+                                                          static_cast<float*>(out), t_ptr, max_tokens, heads, d, s));
+}
+
+int et_add_bias_gelu(int dtype, void* out, const void* bias, const int* t_ptr, int max_tokens, int n,
+                     void* stream) {
+  if (!out || !bias || !t_ptr || max_tokens < 0 || n <= 0) return ET_INVALID_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return ET_DISPATCH(dtype,
+                     launch_add_bias_gelu<__half>(static_cast<__half*>(out), H_(bias), t_ptr, max_tokens, n, s),
+                     launch_add_bias_gelu<float>(static_cast<float*>(out), F_(bias), t_ptr, max_tokens, n, s));
+}
+
+int et_add_bias_input_layernorm(int dtype, void* out, const void* input, const void* bias,
+                                const void* gamma, const void* beta, const int* t_ptr, int max_tokens,
+                                int n, float eps, void* stream) {
+  if (!out || !input || !bias || !gamma || !beta || !t_ptr || max_tokens < 0 || n <= 0)
+    return ET_INVALID_ARGUMENT;
+  if (!(eps > 0.f)) eps = 1e-6f;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return ET_DISPATCH(dtype,
+                     launch_add_bias_input_layernorm<__half>(static_cast<__half*>(out), H_(input), H_(bias),
+                                                             H_(gamma), H_(beta), t_ptr, max_tokens, n, eps, s),
+                     launch_add_bias_input_layernorm<float>(static_cast<float*>(out), F_(input), F_(bias),
+                                                            F_(gamma), F_(beta), t_ptr, max_tokens, n, eps, s));
+}
+
+int et_attention(int dtype, const void* q, const void* k, const void* v, long long token_stride,
+                 long long head_stride, void* ctx, const int* cu_seqlens, int batch, int max_seq,
+                 int heads, int d, int use_simt, int* status_word, void* stream) {
+  if (!q || !k || !v || !ctx || !cu_seqlens || batch < 0 || heads <= 0 || d != 64 || max_seq < 0)
+    return ET_INVALID_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == ET_FP16 && !use_simt)
+    return to_status(launch_attention_tc(H_(q), H_(k), H_(v), token_stride, head_stride,
+                                         static_cast<__half*>(ctx), cu_seqlens, batch, max_seq, heads, d,
+                                         status_word, s));
+  return ET_DISPATCH(dtype,
+                     launch_attention_simt<__half>(H_(q), H_(k), H_(v), token_stride, head_stride,
+                                                   static_cast<__half*>(ctx), cu_seqlens, batch, max_seq, heads, d, s),
+                     launch_attention_simt<float>(F_(q), F_(k), F_(v), token_stride, head_stride,
+                                                  static_cast<float*>(ctx), cu_seqlens, batch, max_seq, heads, d, s));
+}
+
+int et_gemm(int dtype, const void* a, const void* w, const void* w_packed, const void* bias, void* c,
+            const int* m_ptr, int max_m, int n, int k, int epilogue, int use_simt, int* status_word,
+            void* stream) {
+  if (!a || !c || !m_ptr || max_m < 0 || n <= 0 || k <= 0 || epilogue < 0 || epilogue > 2)
+    return ET_INVALID_ARGUMENT;
+  if (epilogue != 0 && !bias) return ET_INVALID_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == ET_FP16 && !use_simt) {
+    if (!w_packed) return ET_INVALID_ARGUMENT;
+    return to_status(launch_gemm_tcgen05(H_(a), H_(w_packed), H_(bias), static_cast<__half*>(c), m_ptr, max_m,
+                                         n, k, epilogue, status_word, s));
+  }
+  if (!w) return ET_INVALID_ARGUMENT;
+  return ET_DISPATCH(dtype,
+                     launch_gemm_simt<__half>(H_(a), H_(w), H_(bias), static_cast<__half*>(c), m_ptr, max_m, n, k,
+                                              epilogue, s),
+                     launch_gemm_simt<float>(F_(a), F_(w), F_(bias), static_cast<float*>(c), m_ptr, max_m, n, k,
+                                             epilogue, s));
+}
+
+int et_pack_weight(int dtype, const void* w, void* w_packed, int k, int n, void* stream) {
+  if (!w || !w_packed || k <= 0 || n <= 0) return ET_INVALID_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return ET_DISPATCH(dtype, launch_transpose<__half>(H_(w), static_cast<__half*>(w_packed), k, n, s),
+                     launch_transpose<float>(F_(w), static_cast<float*>(w_packed), k, n, s));
+}
+#undef H_
+#undef F_
+
+}  // extern "C"

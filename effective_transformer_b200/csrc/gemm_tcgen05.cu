@@ -1,0 +1,331 @@
+// Dense projections on the 5th-generation tensor cores:
+//   C[M,N] = epilogue(A[M,K] * Wp[N,K]^T (+ bias)),  fp16 in, fp32 accumulate in
+//   TMEM, fp16 out.
+// Replaces the cublasGemmEx call sites of the reference's layer functor
+// (tf_op/bert_transformer_op.cu.cc:110-141,200-209,215-225,229-240) and folds
+// add_bias_act (cuda/cuda_kernels.cu:88-134) / the bias half of
+// add_QKV_bias_padding (cuda/attention.cu:106-175) into the epilogue.
+//
+// Structure (one persistent CTA per SM, 192 threads):
+//   warp 0   TMA producer: A tile [128 x 64] and W tile [BN x 64] per k-block
+//            into a kStages-deep shared-memory ring (128-byte swizzle)
+//   warp 1   MMA issuer: tcgen05.mma cta_group::1 kind::f16, M=128, N=BN, K=16,
+//            accumulating into one of two TMEM buffers of BN columns
+//   warps 2-5 epilogue: tcgen05.ld of the finished accumulator (one TMEM lane
+//            quadrant per warp), bias / GELU in fp32, 16-byte stores to C,
+//            overlapping the next tile's main loop
+// M is read from device memory, so no host synchronisation is needed between
+// the padding-offset kernel and the projections.  Every mbarrier wait is
+// bounded; on expiry the kernel records a code in the status word, all roles
+// unwind, TMEM is freed and the kernel returns.
+#include "common.cuh"
+#include "ptx_sm100.cuh"
+
+#include <mutex>
+
+namespace etb {
+
+namespace {
+
+using namespace ptx;
+
+constexpr int BM = 128;
+constexpr int BK = 64;  // 64 fp16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int kNumThreads = 192;
+constexpr int kEpilogueThreads = 128;
+
+template <int BN>
+struct Cfg {
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kNumBars = 2 * kStages + 5;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int kTmemCols = 2 * BN;
+};
+
+enum Site : int {
+  kSiteProducerEmpty = 1,
+  kSiteProducerDrain = 2,
+  kSiteMmaTmemEmpty = 3,
+  kSiteMmaFull = 4,
+  kSiteMmaDrain = 5,
+  kSiteEpilogueFull = 6,
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kNumThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                    const __grid_constant__ CUtensorMap tmap_b, __half* __restrict__ C,
+                    const __half* __restrict__ bias, const int* __restrict__ m_ptr, int max_m, int N,
+                    int K, int epilogue, int* status_word) {
+  using cfg = Cfg<BN>;
+  constexpr int S = cfg::kStages;
+
+  int M = *m_ptr;
+  M = M < 0 ? 0 : (M > max_m ? max_m : M);
+  const int m_tiles = (M + BM - 1) / BM;
+  const int n_tiles = N / BN;
+  const int num_tiles = m_tiles * n_tiles;
+  const int num_kb = (K + BK - 1) / BK;
+  if (num_tiles == 0) return;  // uniform for the whole grid
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t tiles_addr = (raw_addr + 1023u) & ~1023u;
+  uint8_t* tiles = smem_raw + (tiles_addr - raw_addr);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + S * cfg::kStageBytes);
+  const uint32_t bar0 = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (S + s); };
+  auto tmem_full_bar = [&](int a) { return bar0 + 8u * (2 * S + a); };
+  auto tmem_empty_bar = [&](int a) { return bar0 + 8u * (2 * S + 2 + a); };
+  const uint32_t drain_bar = bar0 + 8u * (2 * S + 4);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + cfg::kNumBars);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tmem_full_bar(a), 1);
+      mbar_init(tmem_empty_bar(a), kEpilogueThreads);
+    }
+    mbar_init(drain_bar, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto fail = [&](int site) {
+    *abort_flag = 1;
+    report_timeout(status_word, kKernelGemmTc, site);
+  };
+
+  if (warp == 0) {
+    // ------------------------- TMA producer -------------------------
+    if (lane == 0) {
+      prefetch_tensormap(&tmap_a);
+      prefetch_tensormap(&tmap_b);
+      uint32_t stage = 0, phase = 0;
+      long long issued = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m_tile = tile / n_tiles, n_tile = tile - m_tile * n_tiles;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+            fail(kSiteProducerEmpty);
+            ok = false;
+            break;
+          }
+          const uint32_t a_dst = tiles_addr + stage * cfg::kStageBytes;
+          const uint32_t b_dst = a_dst + cfg::kABytes;
+          mbar_arrive_expect_tx(full_bar(stage), cfg::kStageBytes);
+          tma_load_2d(a_dst, &tmap_a, kb * BK, m_tile * BM, full_bar(stage));
+          tma_load_2d(b_dst, &tmap_b, kb * BK, n_tile * BN, full_bar(stage));
+          ++issued;
+          if (++stage == S) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      // Copies still in flight must land before the CTA's shared memory goes away.
+      const long long pending = issued < S ? issued : S;
+      for (long long i = 0; i < pending; ++i) {
+        const long long f = issued - 1 - i;
+        if (!mbar_wait(full_bar(static_cast<int>(f % S)), static_cast<uint32_t>((f / S) & 1),
+                       abort_flag) && *abort_flag == 0)
+          fail(kSiteProducerDrain);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------- MMA issuer -------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_f16_f32acc(BM, BN);
+      uint32_t stage = 0, phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag)) {
+          fail(kSiteMmaTmemEmpty);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+            fail(kSiteMmaFull);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = tiles_addr + stage * cfg::kStageBytes;
+          const uint64_t adesc = make_kmajor_sw128_desc(a_addr);
+          const uint64_t bdesc = make_kmajor_sw128_desc(a_addr + cfg::kABytes);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // advancing K by 16 fp16 = 32 bytes inside the swizzle row: +2 in the address field
+            umma_f16_ss(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(empty_bar(stage));
+          if (++stage == S) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) umma_commit(tmem_full_bar(acc));
+      }
+      // All MMAs must have retired before TMEM is freed.
+      umma_commit(drain_bar);
+      if (!mbar_wait(drain_bar, 0u, abort_flag) && *abort_flag == 0) fail(kSiteMmaDrain);
+    }
+  } else {
+    // ------------------------- epilogue -------------------------
+    const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad + 32)
+    int it = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+      const int m_tile = tile / n_tiles, n_tile = tile - m_tile * n_tiles;
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      // every lane polls; the vote makes the outcome uniform and reconverges the
+      // warp for the .sync.aligned TMEM loads below
+      const bool got = mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag);
+      if (!__all_sync(0xffffffffu, got)) {
+        if (lane == 0) fail(kSiteEpilogueFull);
+        break;
+      }
+      tc_fence_after();
+      const int row = m_tile * BM + quad * 32 + lane;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
+      __half* crow = C + static_cast<size_t>(row) * N + n_tile * BN;
+      const __half* brow = (epilogue != kEpiNone) ? bias + n_tile * BN : nullptr;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_row + c * 32, r);
+        tmem_ld_wait();
+        if (row < M) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            float f[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[g * 8 + e]);
+            if (epilogue != kEpiNone) {
+              float fb[8];
+              VecTraits<__half>::unpack(ld_global_v4(brow + c * 32 + g * 8), fb);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) f[e] += fb[e];
+              if (epilogue == kEpiBiasGelu) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[e] = gelu_tanh(f[e]);
+              }
+            }
+            st_global_v4(crow + c * 32 + g * 8, VecTraits<__half>::pack(f));
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(tmem_empty_bar(acc));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, cfg::kTmemCols);
+  }
+}
+
+template <int BN>
+cudaError_t launch_bn(const CUtensorMap& ta, const CUtensorMap& tb, const __half* bias, __half* c,
+                      const int* m_ptr, int max_m, int n, int k, int epilogue, int* status_word,
+                      cudaStream_t stream) {
+  using cfg = Cfg<BN>;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, cfg::kSmemBytes);
+  });
+  if (attr_err != cudaSuccess) return attr_err;
+  const long long max_tiles = static_cast<long long>((max_m + BM - 1) / BM) * (n / BN);
+  long long grid = sm_count();
+  if (grid > max_tiles) grid = max_tiles;
+  if (grid < 1) grid = 1;
+  gemm_tcgen05_kernel<BN><<<static_cast<int>(grid), kNumThreads, cfg::kSmemBytes, stream>>>(
+      ta, tb, c, bias, m_ptr, max_m, n, k, epilogue, status_word);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+EncodeTiledFn get_encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+bool encode_2d_fp16_sw128(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
+                          uint64_t row_stride_elems, uint32_t box_rows, uint32_t box_cols) {
+  EncodeTiledFn fn = get_encode_tiled();
+  if (fn == nullptr) return false;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {row_stride_elems * 2};
+  const cuuint32_t box[2] = {box_cols, box_rows};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims,
+                        strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+cudaError_t launch_gemm_tcgen05(const __half* a, const __half* w_packed, const __half* bias,
+                                __half* c, const int* m_ptr, int max_m, int n, int k, int epilogue,
+                                int* status_word, cudaStream_t stream) {
+  if (max_m <= 0) return cudaSuccess;
+  if (n <= 0 || k <= 0 || (n % 128) != 0 || (k % 8) != 0) return cudaErrorInvalidValue;
+  if ((reinterpret_cast<uintptr_t>(a) & 15u) || (reinterpret_cast<uintptr_t>(w_packed) & 15u) ||
+      (reinterpret_cast<uintptr_t>(c) & 15u) || (bias && (reinterpret_cast<uintptr_t>(bias) & 15u)))
+    return cudaErrorMisalignedAddress;
+  if (epilogue != kEpiNone && bias == nullptr) return cudaErrorInvalidValue;
+  const int bn = (n % 256 == 0) ? 256 : 128;
+  CUtensorMap ta, tb;
+  if (!encode_2d_fp16_sw128(&ta, a, static_cast<uint64_t>(max_m), static_cast<uint64_t>(k),
+                            static_cast<uint64_t>(k), BM, BK))
+    return cudaErrorInvalidValue;
+  if (!encode_2d_fp16_sw128(&tb, w_packed, static_cast<uint64_t>(n), static_cast<uint64_t>(k),
+                            static_cast<uint64_t>(k), static_cast<uint32_t>(bn), BK))
+    return cudaErrorInvalidValue;
+  if (bn == 256)
+    return launch_bn<256>(ta, tb, bias, c, m_ptr, max_m, n, k, epilogue, status_word, stream);
+  return launch_bn<128>(ta, tb, bias, c, m_ptr, max_m, n, k, epilogue, status_word, stream);
+}
+
+}  // namespace etb

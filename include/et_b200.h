@@ -1,0 +1,283 @@
+/*
+ * C ABI of the B200 (sm_100a) padding-free BERT encoder path.
+ *
+ * Every entry point takes plain pointers and sizes; device pointers are raw
+ * CUDA device addresses, `stream` is a cudaStream_t passed as void*.  No C++
+ * exception crosses this boundary: every function returns an et_status_t and
+ * the text of the last error of a handle is available from et_last_error().
+ *
+ * The three operators mirror the reference's TensorFlow ops
+ *   EffectiveTransformerInput   (tf_op/bert_transformer_op.cc:249-274)
+ *   EffectiveTransformer        (tf_op/bert_transformer_op.cc:44-77)
+ *   EffectiveTransformerOutput  (tf_op/bert_transformer_op.cc:359-380)
+ * and the parameter structs mirror, field for field, the C++ encoder-layer
+ * interface of tf_op/bert_transformer_op.h:50-128, so a framework shim is a
+ * pointer copy.
+ *
+ * A handle is bound to one CUDA device, owns the repacked weights, the
+ * workspace and a device status word, and is not re-entrant: calls on one
+ * handle must be issued from one thread at a time (the reference serialises
+ * its layer op with a mutex, tf_op/bert_transformer_op.cc:213).
+ */
+#ifndef ET_B200_H_
+#define ET_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct et_handle_s* et_handle_t;
+
+typedef enum {
+  ET_OK = 0,
+  ET_INVALID_ARGUMENT = 1,   /* reference: errors::InvalidArgument via OP_REQUIRES */
+  ET_CUDA_ERROR = 2,         /* reference: check_cuda_error -> errors::Internal (common.h:73-81) */
+  ET_WORKSPACE_TOO_SMALL = 3,
+  ET_DEVICE_TIMEOUT = 4,     /* a bounded device-side wait expired; see et_device_status */
+  ET_NOT_READY = 5           /* weights of a layer were never set */
+} et_status_t;
+
+/* Mirrors effectivetransformer::OperationType {FP32, HALF} (common.h:26). */
+typedef enum { ET_FP32 = 0, ET_FP16 = 1 } et_dtype_t;
+
+typedef struct {
+  int dtype;            /* et_dtype_t: element type of activations AND weights */
+  int num_layers;
+  int head_num;         /* attr head_num       (tf_op/bert_transformer_op.cc:56) */
+  int size_per_head;    /* attr size_per_head  (tf_op/bert_transformer_op.cc:57); must be 64 */
+  int ffn_dim;          /* the reference hard-codes 4*hidden (tf_op/bert_transformer_op.cu.cc:215) */
+  int max_batch_size;   /* attr batch_size: a maximum, the run-time batch may be smaller */
+  int max_seq_len;      /* attr from_seq_len == to_seq_len */
+  float layernorm_eps;  /* 0 selects the reference kernel's 1e-6 (cuda/cuda_kernels.cu:183) */
+  int device;           /* CUDA device ordinal */
+} et_config_t;
+
+/* Mirrors TransformerParam (tf_op/bert_transformer_op.h:50-66). */
+typedef struct {
+  int batch_size;
+  int from_seq_len;
+  int to_seq_len;       /* must equal from_seq_len (tf_op/bert_transformer_op.cc:130-131) */
+  int head_num;
+  int size_per_head;
+} et_transformer_param_t;
+
+/* Mirrors EncoderInitParam<T> (tf_op/bert_transformer_op.h:68-96); T is the
+ * handle's dtype.  Weight kernels are [in, out] row-major as TensorFlow's
+ * dense layers store them.  If attr_kernel_Q is NULL the weights registered
+ * with et_set_layer_weights for that layer are used and all other weight
+ * fields are ignored; otherwise all 16 weight fields must be device pointers
+ * and are repacked on `stream` before the layer runs.  attr_mask ([B,S,S]) is
+ * accepted for signature compatibility and must be the key-only tile of the
+ * input mask (sample/tensorflow/benchmark.py:59-61); it is not read. */
+typedef struct {
+  const void* from_tensor;   /* packed [T, H] inside a [B,S,H]-sized buffer */
+  const void* to_tensor;     /* must equal from_tensor (self-attention) */
+  const void* attr_kernel_Q;
+  const void* attr_kernel_K;
+  const void* attr_kernel_V;
+  const void* attr_bias_Q;
+  const void* attr_bias_K;
+  const void* attr_bias_V;
+  const void* attr_mask;
+  const void* attr_output_kernel;
+  const void* attr_output_bias;
+  const void* attr_output_layernorm_gamma;
+  const void* attr_output_layernorm_beta;
+  const void* inter_kernel;
+  const void* inter_bias;
+  const void* output_kernel;
+  const void* output_bias;
+  const void* output_layernorm_gamma;
+  const void* output_layernorm_beta;
+  const int* batch_idx;
+  const int* word_idx;
+  const int* valid_word_num;
+  void* transformer_out;     /* packed [T, H]; may alias from_tensor */
+  void* stream;              /* replaces cublas_handle + stream of the reference struct */
+} et_encoder_param_t;
+
+/* Mirrors EncoderInputInitParam<T> (tf_op/bert_transformer_op.h:98-112). */
+typedef struct {
+  const void* from_tensor;   /* [B, S, H] */
+  const int* mask;           /* [B, S], 0/1 */
+  int* valid_word_num;       /* [1] */
+  int* batch_idx;            /* [B*S], first T entries written */
+  int* word_idx;             /* [B*S], first T entries written */
+  int batch_size;
+  int from_seq_len;
+  int head_num;
+  int size_per_head;
+  void* to_tensor;           /* [B,S,H]-sized buffer, first T rows written */
+  void* stream;
+} et_input_param_t;
+
+/* Mirrors EncoderOutputInitParam<T> (tf_op/bert_transformer_op.h:114-128). */
+typedef struct {
+  const void* from_tensor;   /* packed [T, H] */
+  const int* valid_word_num;
+  const int* batch_idx;
+  const int* word_idx;
+  int batch_size;
+  int from_seq_len;
+  int head_num;
+  int size_per_head;
+  void* to_tensor;           /* [B, S, H]; padded rows are written as zero */
+  void* stream;
+} et_output_param_t;
+
+/* ---- life cycle --------------------------------------------------------- */
+
+/* Replaces the op constructors (tf_op/bert_transformer_op.cc:84-178): checks
+ * the attributes, binds the device, allocates weights slots, workspace and
+ * the status word. */
+int et_create(const et_config_t* config, et_handle_t* out_handle);
+int et_destroy(et_handle_t handle);
+const char* et_last_error(et_handle_t handle);
+
+/* Replaces the attr -> device weight tensors step of the layer op constructor
+ * (tf_op/bert_transformer_op.cc:91-103).  `weights` holds 16 pointers in the
+ * order of python/effective_transformer/__init__.py:55-74.  `on_host` != 0:
+ * host arrays (copied synchronously); 0: device arrays.  The handle keeps its
+ * own repacked copy; the caller's arrays are not referenced afterwards. */
+int et_set_layer_weights(et_handle_t handle, int layer, const void* const* weights, int on_host);
+
+/* Bytes of handle-owned workspace for a [B, S] batch (size_t arithmetic; the
+ * reference's int formula overflows, tf_op/bert_transformer_op.cu.cc:75-77). */
+int et_workspace_bytes(et_handle_t handle, int batch_size, int seq_len, size_t* out_bytes);
+
+/* ---- the three operators ------------------------------------------------ */
+
+/* EffectiveTransformerInputOpFunctor::Compute
+ * (tf_op/bert_transformer_op.cu.cc:266-331).  No host synchronisation. */
+int et_input(et_handle_t handle, const et_input_param_t* param);
+
+/* EffectiveTransformerOpFunctor::Compute (tf_op/bert_transformer_op.cu.cc:37-259). */
+int et_layer(et_handle_t handle, int layer, const et_encoder_param_t* param,
+             const et_transformer_param_t* t_param);
+
+/* EffectiveTransformerOutputOpFunctor::Compute
+ * (tf_op/bert_transformer_op.cu.cc:339-373). */
+int et_output(et_handle_t handle, const et_output_param_t* param);
+
+/* ---- whole path ---------------------------------------------------------- */
+
+/* get_sequence_output (python/effective_transformer/__init__.py:32-84) as one
+ * call: input op, num_layers layer ops, output op, all on `stream`, device
+ * buffers.  `out` is [B,S,H].  Asynchronous; nothing is read back. */
+int et_forward(et_handle_t handle, const void* from_tensor, const int* mask, void* out,
+               int batch_size, int seq_len, void* stream);
+
+/* Same with HOST buffers (pinned or pageable): copies from_tensor and mask to
+ * the device, runs et_forward, copies the [B,S,H] result back and waits for
+ * it, like one sess.run of sample/tensorflow/benchmark.py:114-124.
+ * `valid_word_num_out` (may be NULL) receives T. */
+int et_forward_host(et_handle_t handle, const void* from_tensor_host, const int* mask_host,
+                    void* out_host, int batch_size, int seq_len, int* valid_word_num_out);
+
+/* Reads the device status word (synchronises `stream`): 0 = no device-side
+ * wait expired since the last call.  Non-zero encodes kernel id and wait site;
+ * the word is cleared. */
+int et_device_status(et_handle_t handle, void* stream, int* out_status);
+
+/* Device arrays produced by the last et_input/et_forward on this handle:
+ * cu_seqlens int32[B+1], seq_len int32[B], padding_offset int32[T],
+ * prefix_sum int32[B*S].  Valid until the next call on the handle. */
+int et_last_padding_info(et_handle_t handle, const int** cu_seqlens, const int** seq_len,
+                         const int** padding_offset, const int** prefix_sum);
+
+/* Per-kernel accounting.  Launch counts are always kept; with profiling
+ * enabled every launcher call is also bracketed by CUDA events on the stream
+ * it is launched on.  et_get_profile waits for the recorded events and
+ * returns, per category, the summed device time in ms and the number of
+ * kernels launched since the last reset. */
+enum {
+  ET_PROF_PADDING_OFFSETS = 0,
+  ET_PROF_REMOVE_PADDING = 1,
+  ET_PROF_GEMM_QKV = 2,
+  ET_PROF_ATTENTION = 3,
+  ET_PROF_GEMM_ATTN_OUT = 4,
+  ET_PROF_LAYERNORM = 5,
+  ET_PROF_GEMM_FFN1 = 6,
+  ET_PROF_GEMM_FFN2 = 7,
+  ET_PROF_RESTORE_PADDING = 8,
+  ET_PROF_NUM = 9
+};
+int et_set_profiling(et_handle_t handle, int enable);
+int et_get_profile(et_handle_t handle, double* ms_out, long long* launches_out, int reset);
+
+/* Utility for bindings without a CUDA runtime of their own: copies `bytes`
+ * from device to host on `stream` and waits for it. */
+int et_copy_to_host(void* dst_host, const void* src_device, size_t bytes, void* stream);
+
+/* Selects the GEMM / attention implementation of an fp16 handle:
+ * 0 = tcgen05 tensor-core kernels (default), 1 = CUDA-core kernels (the fp32
+ * handle always uses these; on fp16 they exist for debugging only). */
+int et_set_debug_simt(et_handle_t handle, int use_simt);
+
+/* ---- kernel-level entry points (one per reference launcher) --------------
+ * dtype is an et_dtype_t; all pointers are device pointers; `valid_word_num`
+ * is a DEVICE pointer to T (row counts are never read back to the host). */
+
+/* exclusiveScan_kernelLauncher (cuda/cuda_kernels.cu:704-718) fused with the
+ * index outputs of compress_bert_input (cuda/cuda_kernels.cu:292-299).  Any
+ * output pointer may be NULL.  `scratch` must hold batch_size ints. */
+int et_padding_offsets(const int* mask, int batch_size, int seq_len, int* prefix_sum,
+                       int* valid_word_num, int* batch_idx, int* word_idx, int* seq_len_out,
+                       int* cu_seqlens, int* padding_offset, int* scratch, void* stream);
+
+/* compressBertInput_kernelLauncher (cuda/cuda_kernels.cu:340-372), copy part. */
+int et_remove_padding(int dtype, const void* from_tensor, const int* batch_idx, const int* word_idx,
+                      const int* valid_word_num, void* to_tensor, int batch_size, int seq_len,
+                      int hidden, void* stream);
+
+/* cudaMemsetAsync + restoreBertOutput_kernelLauncher
+ * (tf_op/bert_transformer_op.cu.cc:354-360, cuda/cuda_kernels.cu:429-459) in one pass. */
+int et_restore_padding(int dtype, const void* from_tensor, const int* batch_idx, const int* word_idx,
+                       const int* valid_word_num, void* to_tensor, int batch_size, int seq_len,
+                       int hidden, void* stream);
+
+/* add_QKV_bias_padding_kernelLauncher (cuda/attention.cu:106-242) without the
+ * re-padding: q,k,v packed [T,H] + bias -> head-major packed [3, heads, max_tokens, d]. */
+int et_add_qkv_bias_transpose(int dtype, const void* q, const void* bias_q, const void* k,
+                              const void* bias_k, const void* v, const void* bias_v, void* qkv_out,
+                              const int* valid_word_num, int max_tokens, int head_num,
+                              int size_per_head, void* stream);
+
+/* add_bias_act_kernelLauncher (cuda/cuda_kernels.cu:136-150): in place on [T, n]. */
+int et_add_bias_gelu(int dtype, void* out, const void* bias, const int* valid_word_num,
+                     int max_tokens, int n, void* stream);
+
+/* add_bias_input_layernorm_kernelLauncher (cuda/cuda_kernels.cu:238-271): in place on out [T, n]. */
+int et_add_bias_input_layernorm(int dtype, void* out, const void* input, const void* bias,
+                                const void* gamma, const void* beta, const int* valid_word_num,
+                                int max_tokens, int n, float eps, void* stream);
+
+/* The attention block of the layer functor (batched QK^T, softmax_kernel,
+ * batched P*V, transpose_rm_padding: tf_op/bert_transformer_op.cu.cc:158-191,
+ * cuda/attention.cu:249-492) on the packed layout.  q/k/v are addressed as
+ * base + token*token_stride + head*head_stride (elements); ctx is packed
+ * [T, heads*d].  use_simt selects the CUDA-core kernel (always for fp32). */
+int et_attention(int dtype, const void* q, const void* k, const void* v, long long token_stride,
+                 long long head_stride, void* ctx, const int* cu_seqlens, int batch_size,
+                 int max_seq_len, int head_num, int size_per_head, int use_simt, int* status_word,
+                 void* stream);
+
+/* cublasGemmEx call sites of the layer functor
+ * (tf_op/bert_transformer_op.cu.cc:110-141,200-209,215-225,229-240):
+ * C[M,N] = epilogue(A[M,K] * W[K,N] (+ bias)), W row-major [in,out] as the
+ * reference passes it.  epilogue: 0 none, 1 +bias, 2 gelu(+bias).  M is read
+ * from the device (`m_ptr`), `max_m` bounds it.  The tcgen05 path needs
+ * `w_packed` = the [N,K] K-major copy made by et_pack_weight (w may be NULL);
+ * the CUDA-core path (use_simt, always for fp32) reads `w`. */
+int et_gemm(int dtype, const void* a, const void* w, const void* w_packed, const void* bias, void* c,
+            const int* m_ptr, int max_m, int n, int k, int epilogue, int use_simt, int* status_word,
+            void* stream);
+int et_pack_weight(int dtype, const void* w, void* w_packed, int k, int n, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif  /* ET_B200_H_ */

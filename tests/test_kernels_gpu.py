@@ -1,0 +1,277 @@
+"""GPU parity tests, kernel by kernel, through the C ABI: every CUDA kernel is
+compared with the CPU oracle on the same seeded inputs.  Integer and copy
+kernels must be bit-exact; floating-point kernels are compared against the
+oracle evaluated in float64 on the fp16/fp32-rounded inputs."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from effective_transformer_b200 import _capi
+from effective_transformer_b200 import workloads as W
+from oracle import bert_encoder as O
+from oracle import padding as P
+
+from util import DT, dev, iptr, lib, ok, padding_offsets, status_word, stream
+
+pytestmark = pytest.mark.gpu
+
+
+def _check_padding(mask_np):
+    b, s = mask_np.shape
+    out = padding_offsets(dev(mask_np.astype(np.int32)))
+    ref = P.padding_indices(mask_np)
+    t = int(ref["valid_word_num"][0])
+    assert int(out["valid_word_num"][0]) == t
+    assert np.array_equal(out["cu_seqlens"].cpu().numpy(), ref["cu_seqlens"])
+    if b * s == 0:
+        return
+    assert np.array_equal(out["prefix_sum"].cpu().numpy()[:b * s], ref["prefix_sum"].ravel())
+    assert np.array_equal(out["seq_len"].cpu().numpy()[:b], ref["seq_len"])
+    for k in ("batch_idx", "word_idx", "padding_offset"):
+        got = out[k].cpu().numpy()
+        assert np.array_equal(got[:t], ref[k]), k
+        assert np.all(got[t:] == -7), k + ": wrote past the valid count"
+
+
+@pytest.mark.parametrize("b,s", [(1, 1), (3, 7), (8, 32), (5, 33), (100, 32), (17, 129), (1000, 64), (4096, 128)])
+def test_padding_offsets_prefix_masks(b, s):
+    rng = np.random.RandomState(b * 1000 + s)
+    lens = rng.randint(0, s + 1, size=b)
+    _check_padding(W.prefix_mask(lens.astype(np.int32), s))
+
+
+@pytest.mark.parametrize("b,s,p", [(4, 16, 0.5), (64, 37, 0.3), (9, 1024, 0.9), (300, 65, 0.05)])
+def test_padding_offsets_arbitrary_masks(b, s, p):
+    rng = np.random.RandomState(7)
+    _check_padding((rng.rand(b, s) < p).astype(np.int32))
+
+
+def test_padding_offsets_edge_cases():
+    _check_padding(np.zeros((6, 10), np.int32))            # nothing valid
+    _check_padding(np.ones((6, 10), np.int32))             # nothing padded, last mask = 1
+    m = np.zeros((4, 8), np.int32); m[3, 7] = 1            # only the very last position
+    _check_padding(m)
+    m = np.ones((4, 8), np.int32); m[3, 7] = 0             # last mask = 0
+    _check_padding(m)
+    _check_padding(np.zeros((0, 8), np.int32))             # empty batch
+    cfg4 = W.WORKLOADS[4]
+    lens = W.draw_lengths(cfg4, np.random.RandomState(cfg4.seed))
+    _check_padding(W.prefix_mask(lens, cfg4.max_seq_len))  # 524 288 positions, skewed lengths
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+@pytest.mark.parametrize("b,s,h", [(5, 12, 128), (8, 32, 768), (64, 64, 1024), (3, 5, 64)])
+def test_remove_restore_padding_bit_exact(dtype, b, s, h):
+    rng = np.random.RandomState(b + s + h)
+    mask_np = (rng.rand(b, s) < 0.6).astype(np.int32)
+    mask_np[0, :] = 0                                       # an empty sequence
+    x = dev(rng.randn(b, s, h).astype(np.float32), dtype)
+    idx = padding_offsets(dev(mask_np))
+    t = int(idx["valid_word_num"][0])
+    packed = torch.full((b, s, h), 77.0, dtype=dtype, device="cuda")
+    ok(lib().et_remove_padding(DT[dtype], iptr(x), iptr(idx["batch_idx"]), iptr(idx["word_idx"]),
+                               iptr(idx["valid_word_num"]), iptr(packed), b, s, h, stream()))
+    torch.cuda.synchronize()
+    ref = P.remove_padding(x.cpu().numpy(), mask_np)
+    got = packed.cpu().numpy().reshape(b * s, h)
+    assert np.array_equal(got[:t], ref)
+    assert np.all(got[t:] == 77.0)                          # rows past T untouched
+    restored = torch.full((b, s, h), 55.0, dtype=dtype, device="cuda")
+    ok(lib().et_restore_padding(DT[dtype], iptr(packed), iptr(idx["batch_idx"]), iptr(idx["word_idx"]),
+                                iptr(idx["valid_word_num"]), iptr(restored), b, s, h, stream()))
+    torch.cuda.synchronize()
+    ref_back = P.restore_padding(ref, idx["batch_idx"].cpu().numpy()[:t], idx["word_idx"].cpu().numpy()[:t], b, s)
+    assert np.array_equal(restored.cpu().numpy(), ref_back)  # padded rows are exactly zero
+
+
+def test_restore_padding_all_padding_and_no_padding():
+    for fill in (0, 1):
+        b, s, h = 4, 9, 64
+        mask_np = np.full((b, s), fill, np.int32)
+        x = dev(np.random.RandomState(1).randn(b, s, h).astype(np.float32), torch.float16)
+        idx = padding_offsets(dev(mask_np))
+        packed = torch.zeros_like(x)
+        ok(lib().et_remove_padding(_capi.ET_FP16, iptr(x), iptr(idx["batch_idx"]), iptr(idx["word_idx"]),
+                                   iptr(idx["valid_word_num"]), iptr(packed), b, s, h, stream()))
+        out = torch.full_like(x, 9.0)
+        ok(lib().et_restore_padding(_capi.ET_FP16, iptr(packed), iptr(idx["batch_idx"]), iptr(idx["word_idx"]),
+                                    iptr(idx["valid_word_num"]), iptr(out), b, s, h, stream()))
+        torch.cuda.synchronize()
+        assert torch.equal(out, x * fill)
+
+
+def _tol(dtype):
+    # one rounding of an O(1..10) value in the output type
+    return dict(rtol=2e-3, atol=2e-3) if dtype == torch.float16 else dict(rtol=2e-5, atol=2e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+@pytest.mark.parametrize("t,cap,heads", [(37, 64, 2), (1954, 3200, 12), (300, 300, 16)])
+def test_add_qkv_bias_transpose(dtype, t, cap, heads):
+    d, h = 64, heads * 64
+    rng = np.random.RandomState(t)
+    q, k, v = [dev(rng.randn(cap, h).astype(np.float32), dtype) for _ in range(3)]
+    bq, bk, bv = [dev(rng.randn(h).astype(np.float32), dtype) for _ in range(3)]
+    out = torch.full((3, heads, cap, d), 5.0, dtype=dtype, device="cuda")
+    tn = dev(np.array([t], np.int32))
+    ok(lib().et_add_qkv_bias_transpose(DT[dtype], iptr(q), iptr(bq), iptr(k), iptr(bk), iptr(v), iptr(bv),
+                                       iptr(out), iptr(tn), cap, heads, d, stream()))
+    torch.cuda.synchronize()
+    for w, (x, bias) in enumerate(((q, bq), (k, bk), (v, bv))):
+        ref = (x[:t].double() + bias.double()).reshape(t, heads, d).permute(1, 0, 2)
+        torch.testing.assert_close(out[w, :, :t].double(), ref, **_tol(dtype))
+    assert torch.all(out[:, :, t:] == 5.0)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+@pytest.mark.parametrize("t,cap,n", [(37, 64, 256), (1954, 3200, 3072), (129, 129, 4096)])
+def test_add_bias_gelu(dtype, t, cap, n):
+    rng = np.random.RandomState(n)
+    x = dev((2.0 * rng.randn(cap, n)).astype(np.float32), dtype)
+    bias = dev(rng.randn(n).astype(np.float32), dtype)
+    ref = O.add_bias_gelu(x[:t].double(), bias.double())
+    keep = x[t:].clone()
+    tn = dev(np.array([t], np.int32))
+    ok(lib().et_add_bias_gelu(DT[dtype], iptr(x), iptr(bias), iptr(tn), cap, n, stream()))
+    torch.cuda.synchronize()
+    torch.testing.assert_close(x[:t].double(), ref, **_tol(dtype))
+    assert torch.equal(x[t:], keep)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+@pytest.mark.parametrize("t,cap,n", [(37, 64, 128), (1954, 3200, 768), (200, 256, 1024), (50, 50, 2048)])
+def test_add_bias_input_layernorm(dtype, t, cap, n):
+    rng = np.random.RandomState(n + 1)
+    out = dev(rng.randn(cap, n).astype(np.float32), dtype)
+    inp = dev(rng.randn(cap, n).astype(np.float32), dtype)
+    bias, beta = [dev(0.5 * rng.randn(n).astype(np.float32), dtype) for _ in range(2)]
+    gamma = dev((1 + 0.2 * rng.randn(n)).astype(np.float32), dtype)
+    ref = O.add_bias_input_layernorm(out[:t].double(), inp[:t].double(), bias.double(), gamma.double(),
+                                     beta.double(), eps=1e-6)
+    keep = out[t:].clone()
+    tn = dev(np.array([t], np.int32))
+    ok(lib().et_add_bias_input_layernorm(DT[dtype], iptr(out), iptr(inp), iptr(bias), iptr(gamma), iptr(beta),
+                                         iptr(tn), cap, n, 1e-6, stream()))
+    torch.cuda.synchronize()
+    torch.testing.assert_close(out[:t].double(), ref, **(dict(rtol=2e-3, atol=4e-3) if dtype == torch.float16
+                                                       else dict(rtol=1e-5, atol=1e-5)))
+    assert torch.equal(out[t:], keep)
+
+
+def _gemm_case(dtype, m, cap, n, k, epi, use_simt, seed=0):
+    rng = np.random.RandomState(seed + m + n + k)
+    a = dev(rng.randn(cap, k).astype(np.float32), dtype)
+    w = dev((rng.randn(k, n) / math.sqrt(k)).astype(np.float32), dtype)
+    bias = dev(rng.randn(n).astype(np.float32), dtype)
+    c = torch.full((cap, n), 3.0, dtype=dtype, device="cuda")
+    wp = torch.empty((n, k), dtype=dtype, device="cuda")
+    ok(lib().et_pack_weight(DT[dtype], iptr(w), iptr(wp), k, n, stream()))
+    torch.cuda.synchronize()
+    assert torch.equal(wp, w.t().contiguous())
+    mt = dev(np.array([m], np.int32))
+    st = status_word()
+    ok(lib().et_gemm(DT[dtype], iptr(a), iptr(w), iptr(wp), iptr(bias) if epi else None, iptr(c), iptr(mt),
+                     cap, n, k, epi, 1 if use_simt else 0, iptr(st), stream()))
+    torch.cuda.synchronize()
+    assert int(st[0]) == 0, f"device-side wait expired: status 0x{int(st[0]):x}"
+    ref = a[:m].double() @ w.double()
+    if epi >= 1:
+        ref = ref + bias.double()
+    if epi == 2:
+        ref = O.gelu(ref)
+    if dtype == torch.float16:
+        torch.testing.assert_close(c[:m].double(), ref, rtol=2e-3, atol=3e-3)
+    else:
+        torch.testing.assert_close(c[:m].double(), ref, rtol=1e-5, atol=2e-5)
+    assert torch.all(c[m:] == 3.0), "rows past M were written"
+
+
+@pytest.mark.parametrize("m,cap,n,k", [(1, 1, 128, 64), (60, 60, 128, 128), (134, 256, 768, 768),
+                                       (300, 384, 2304, 768), (257, 300, 768, 3072), (128, 128, 256, 64),
+                                       (1000, 1000, 3072, 768), (0, 64, 256, 128)])
+@pytest.mark.parametrize("epi", [0, 1, 2])
+def test_gemm_tcgen05(m, cap, n, k, epi):
+    _gemm_case(torch.float16, m, cap, n, k, epi, use_simt=False)
+
+
+def test_gemm_tcgen05_many_tiles_per_cta():
+    # more tiles than CTAs: exercises both TMEM accumulator buffers and ring wrap-around
+    _gemm_case(torch.float16, 5000, 5000, 3072, 768, 2, use_simt=False)
+    _gemm_case(torch.float16, 4111, 4200, 768, 3072, 0, use_simt=False)
+    _gemm_case(torch.float16, 3000, 3000, 1152, 1024, 1, use_simt=False)   # N = 9 * 128: BN = 128 path
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("m,cap,n,k", [(1, 1, 128, 64), (60, 60, 128, 128), (134, 256, 768, 768),
+                                       (257, 300, 768, 3072), (300, 300, 2304, 768), (0, 64, 256, 128)])
+@pytest.mark.parametrize("epi", [0, 1, 2])
+def test_gemm_simt(dtype, m, cap, n, k, epi):
+    _gemm_case(dtype, m, cap, n, k, epi, use_simt=True)
+
+
+def _attention_case(dtype, lens, heads, use_simt, layout):
+    d = 64
+    h = heads * d
+    lens = np.asarray(lens, np.int32)
+    cu = np.zeros(len(lens) + 1, np.int32)
+    cu[1:] = np.cumsum(lens)
+    t = int(cu[-1])
+    cap = max(t, 1)
+    rng = np.random.RandomState(int(lens.sum()) + heads)
+    if layout == "qkv":        # [T, 3H] as the fused projection writes it
+        qkv = dev(rng.randn(cap, 3 * h).astype(np.float32), dtype)
+        q, k, v = qkv[:, :h], qkv[:, h:2 * h], qkv[:, 2 * h:]
+        qp, kp, vp = qkv.data_ptr(), qkv.data_ptr() + h * qkv.element_size(), qkv.data_ptr() + 2 * h * qkv.element_size()
+        tstride, hstride = 3 * h, d
+    else:                      # head-major [3, heads, cap, d] as et_add_qkv_bias_transpose writes it
+        buf = dev(rng.randn(3, heads, cap, d).astype(np.float32), dtype)
+        q, k, v = [buf[i].permute(1, 0, 2).reshape(cap, h) for i in range(3)]
+        es = buf.element_size()
+        qp, kp, vp = [buf.data_ptr() + i * heads * cap * d * es for i in range(3)]
+        tstride, hstride = d, cap * d
+    ctx = torch.full((cap, h), 2.0, dtype=dtype, device="cuda")
+    st = status_word()
+    ok(lib().et_attention(DT[dtype], qp, kp, vp, tstride, hstride, iptr(ctx), iptr(dev(cu)), len(lens),
+                          int(lens.max()) if len(lens) else 0, heads, d, 1 if use_simt else 0, iptr(st), stream()))
+    torch.cuda.synchronize()
+    assert int(st[0]) == 0
+    ref = O.packed_attention(q[:t].double().cpu(), k[:t].double().cpu(), v[:t].double().cpu(), cu, heads, d)
+    tol = dict(rtol=3e-3, atol=3e-3) if dtype == torch.float16 else dict(rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(ctx[:t].double().cpu(), ref, **tol)
+    assert torch.all(ctx[t:] == 2.0)
+
+
+LEN_CASES = [[1], [5, 1, 16, 0, 33], [64] * 3, [20, 23, 29, 8, 11, 11, 15, 17], [128, 1, 100, 127, 65, 64, 63],
+             [200, 3, 129]]
+
+
+@pytest.mark.parametrize("lens", LEN_CASES)
+@pytest.mark.parametrize("layout", ["qkv", "headmajor"])
+def test_attention_tensor_core(lens, layout):
+    _attention_case(torch.float16, lens, 2, use_simt=False, layout=layout)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("lens", LEN_CASES)
+def test_attention_simt(dtype, lens):
+    _attention_case(dtype, lens, 3, use_simt=True, layout="qkv")
+
+
+def test_attention_full_size_softmax_rows_sum_to_one():
+    """cfg2 shape (B=1000, 12 heads): with V = 1 every context element must be 1
+    (each probability row sums to one over the sequence's own keys only)."""
+    spec = W.WORKLOADS[2]
+    lens = W.draw_lengths(spec, np.random.RandomState(spec.seed))
+    cu = np.zeros(len(lens) + 1, np.int32); cu[1:] = np.cumsum(lens)
+    t, h = int(cu[-1]), 768
+    qkv = torch.randn(t, 3 * h, dtype=torch.float16, device="cuda")
+    qkv[:, 2 * h:] = 1.0
+    ctx = torch.zeros(t, h, dtype=torch.float16, device="cuda")
+    st = status_word()
+    es = 2
+    ok(lib().et_attention(_capi.ET_FP16, qkv.data_ptr(), qkv.data_ptr() + h * es, qkv.data_ptr() + 2 * h * es,
+                          3 * h, 64, iptr(ctx), iptr(dev(cu)), len(lens), 64, 12, 64, 0, iptr(st), stream()))
+    torch.cuda.synchronize()
+    assert float((ctx.float() - 1.0).abs().max()) < 2e-3

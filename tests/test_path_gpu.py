@@ -1,0 +1,224 @@
+"""GPU parity tests of the whole path (input op -> layers -> output op) against
+the CPU oracle, through the reference-shaped Python API and the C ABI.
+
+Tolerances (valid tokens only, as sample/tensorflow/benchmark.py:105-112):
+  fp32: max|delta| <= 1e-4 * RMS(oracle activations)
+  fp16: max|delta| <= 2e-2 and mean|delta| <= 2e-3 after all layers
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import effective_transformer_b200 as et
+from effective_transformer_b200 import _capi
+from effective_transformer_b200 import workloads as W
+from oracle import bert_encoder as O
+from oracle import padding as P
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+FP32_REL_RMS = 1e-4
+FP16_MAX_ABS, FP16_MEAN_ABS = 2e-2, 2e-3
+
+
+def make_engine(spec: W.WorkloadSpec, wl: W.Workload, simt: bool = False) -> et.EffectiveTransformer:
+    dtype = torch.float16 if spec.dtype == "fp16" else torch.float32
+    sh = spec.shape
+    eng = et.EffectiveTransformer(sh.num_layers, sh.head_num, sh.size_per_head, sh.ffn_dim,
+                                  wl.mask.shape[0], spec.max_seq_len, dtype=dtype)
+    eng.set_weights(wl.weights)
+    if simt:
+        eng.set_debug_simt(True)
+    return eng
+
+
+def run_forward(eng, wl):
+    x = torch.from_numpy(wl.from_tensor).to(eng.dtype).cuda()
+    m = torch.from_numpy(wl.mask).cuda()
+    y = eng.forward(x, m)
+    torch.cuda.synchronize()
+    assert eng.device_status() == 0
+    return y
+
+
+def assert_parity(y_dev: torch.Tensor, y_ref_valid: torch.Tensor, mask: np.ndarray, fp16: bool):
+    got = O.valid_rows(y_dev.detach().cpu().double(), mask)
+    ref = y_ref_valid.double()
+    diff = (got - ref).abs()
+    if fp16:
+        assert float(diff.max()) <= FP16_MAX_ABS, f"max abs {float(diff.max())}"
+        assert float(diff.mean()) <= FP16_MEAN_ABS, f"mean abs {float(diff.mean())}"
+    else:
+        rms = float(ref.pow(2).mean().sqrt())
+        assert float(diff.max()) <= FP32_REL_RMS * rms, f"max abs {float(diff.max())} vs rms {rms}"
+    # padded rows come back as exact zeros
+    b, s, h = y_dev.shape
+    pad = torch.from_numpy(mask.ravel() == 0)
+    assert torch.all(y_dev.detach().cpu().reshape(b * s, h)[pad] == 0)
+
+
+def oracle_valid(wl, spec, dtype64=False):
+    am = W.attention_mask_from_input_mask(wl.mask)
+    y = O.transformer_model(wl.from_tensor, am, wl.weights, spec.shape.head_num, spec.shape.size_per_head,
+                            compute_dtype=torch.float64 if dtype64 else torch.float32,
+                            round_to_fp16=(spec.dtype == "fp16"))
+    return O.valid_rows(y, wl.mask)
+
+
+@pytest.mark.parametrize("dtype,simt", [("fp32", False), ("fp16", True), ("fp16", False)])
+def test_tiny_against_golden(dtype, simt):
+    d = np.load(os.path.join(GOLD, "tiny_fp64.npz"))
+    spec = W.tiny_spec(dtype=dtype)
+    wl = W.make_workload(spec, random_gamma_beta=True)
+    eng = make_engine(spec, wl, simt)
+    y = run_forward(eng, wl)
+    if dtype == "fp32":
+        ref = torch.from_numpy(d["oracle64"])
+    else:
+        ref = oracle_valid(wl, spec, dtype64=True)
+    assert_parity(y, ref, wl.mask, fp16=(dtype == "fp16"))
+    eng.close()
+
+
+def test_cfg0_fp32_against_golden():
+    d = np.load(os.path.join(GOLD, "cfg0_fp64_subsampled.npz"))
+    spec = W.WORKLOADS[0]
+    wl = W.make_workload(spec)
+    eng = make_engine(spec, wl)
+    y = run_forward(eng, wl)
+    got = O.valid_rows(y.cpu().double(), wl.mask).numpy()[:, ::8]
+    assert np.abs(got - d["oracle64"]).max() <= FP32_REL_RMS * float(d["rms"][0])
+    # integer outputs of the input op, bit-exact
+    cu, sl, po, pre = eng.last_padding_info(spec.batch, wl.valid_tokens, spec.max_seq_len)
+    assert np.array_equal(cu, d["idx_cu_seqlens"]) and np.array_equal(sl, d["idx_seq_len"])
+    assert np.array_equal(po, d["idx_padding_offset"]) and np.array_equal(pre, d["idx_prefix_sum"].ravel())
+    eng.close()
+
+
+@pytest.mark.parametrize("simt", [False, True])
+def test_cfg1_fp16_twelve_layers(simt):
+    spec = W.WORKLOADS[1]
+    wl = W.make_workload(spec)
+    eng = make_engine(spec, wl, simt)
+    y = run_forward(eng, wl)
+    assert_parity(y, oracle_valid(wl, spec), wl.mask, fp16=True)
+    eng.close()
+
+
+def test_operator_api_matches_forward_and_reference_wiring():
+    """get_sequence_output wires the three operators exactly like
+    python/effective_transformer/__init__.py:42-82 and equals et_forward."""
+    spec = W.tiny_spec(dtype="fp16", layers=3, batch=7, max_seq_len=20, seed=11)
+    wl = W.make_workload(spec, random_gamma_beta=True)
+    wl.mask[2, :] = 0                                         # an empty sequence
+    wl.mask[4, :] = 1                                         # a full one
+    eng = make_engine(spec, wl)
+    x = torch.from_numpy(wl.from_tensor).half().cuda()
+    m = torch.from_numpy(wl.mask).cuda()
+    am = torch.from_numpy(W.attention_mask_from_input_mask(wl.mask)).half().cuda()
+    cfg = et.BertConfig(spec.shape.hidden, spec.shape.num_layers, spec.shape.head_num, spec.shape.ffn_dim)
+    y_ops = et.get_sequence_output(cfg, spec.batch, spec.max_seq_len, am, m, x, wl.weights, engine=eng)
+    y_fwd = eng.forward(x, m)
+    torch.cuda.synchronize()
+    assert torch.equal(y_ops, y_fwd)
+    # input op outputs
+    packed, valid, bidx, widx = eng.effective_transformer_input(x, m)
+    torch.cuda.synchronize()
+    ref = P.padding_indices(wl.mask)
+    t = int(ref["valid_word_num"][0])
+    assert int(valid[0]) == t
+    assert np.array_equal(bidx.cpu().numpy().ravel()[:t], ref["batch_idx"])
+    assert np.array_equal(widx.cpu().numpy().ravel()[:t], ref["word_idx"])
+    assert np.array_equal(packed.cpu().numpy().reshape(-1, spec.shape.hidden)[:t],
+                          P.remove_padding(x.cpu().numpy(), wl.mask))
+    assert_parity(y_fwd, oracle_valid(wl, spec, dtype64=True), wl.mask, fp16=True)
+    eng.close()
+
+
+def test_arbitrary_input_mask():
+    """Non-prefix masks are legal for the input/output ops (word_idx keeps the
+    true positions) and, with the key-only attention mask, for the layers."""
+    spec = W.tiny_spec(dtype="fp32", batch=6, max_seq_len=17, seed=5)
+    wl = W.make_workload(spec)
+    rng = np.random.RandomState(9)
+    wl.mask[:] = (rng.rand(*wl.mask.shape) < 0.55).astype(np.int32)
+    eng = make_engine(spec, wl)
+    y = run_forward(eng, wl)
+    assert_parity(y, oracle_valid(wl, spec, dtype64=True), wl.mask, fp16=False)
+    eng.close()
+
+
+def test_forward_host_equals_device_forward():
+    spec = W.tiny_spec(dtype="fp16", batch=9, max_seq_len=31, seed=21)
+    wl = W.make_workload(spec)
+    eng = make_engine(spec, wl)
+    y_dev = run_forward(eng, wl).cpu().numpy()
+    y_host, t = eng.forward_host(wl.from_tensor.astype(np.float16), wl.mask)
+    assert t == wl.valid_tokens
+    assert np.array_equal(y_host, y_dev)
+    # a smaller run-time batch on the same handle (attr batch_size is only a maximum)
+    y_small, t2 = eng.forward_host(wl.from_tensor[:4].astype(np.float16), wl.mask[:4])
+    assert t2 == int(wl.mask[:4].sum())
+    sel = wl.mask[:4].ravel() > 0
+    a = y_small.reshape(-1, spec.shape.hidden)[sel].astype(np.float32)
+    b = y_dev[:4].reshape(-1, spec.shape.hidden)[sel].astype(np.float32)
+    assert np.abs(a - b).max() <= 2e-3       # sequences are independent of their batch mates
+    eng.close()
+
+
+def test_error_conventions():
+    spec = W.tiny_spec(dtype="fp16")
+    wl = W.make_workload(spec)
+    sh = spec.shape
+    with pytest.raises(et.EtError) as e:
+        et.EffectiveTransformer(sh.num_layers, sh.head_num, 32, sh.ffn_dim, 4, 8)      # size_per_head != 64
+    assert e.value.code == _capi.ET_INVALID_ARGUMENT
+    eng = et.EffectiveTransformer(sh.num_layers, sh.head_num, 64, sh.ffn_dim, spec.batch, spec.max_seq_len)
+    x = torch.from_numpy(wl.from_tensor).half().cuda()
+    m = torch.from_numpy(wl.mask).cuda()
+    with pytest.raises(et.EtError) as e:
+        eng.forward(x, m)                                                            # weights never set
+    assert e.value.code == _capi.ET_NOT_READY
+    eng.set_weights(wl.weights)
+    big = torch.zeros(spec.batch + 1, spec.max_seq_len, sh.hidden, dtype=torch.float16, device="cuda")
+    with pytest.raises(et.EtError) as e:
+        eng.forward(big, torch.ones(spec.batch + 1, spec.max_seq_len, dtype=torch.int32, device="cuda"))
+    assert e.value.code == _capi.ET_INVALID_ARGUMENT
+    with pytest.raises(et.EtError):
+        eng.set_layer_weights(99, wl.weights[:16])
+    # all-padding batch: T = 0, output all zeros, no error
+    y = eng.forward(x, torch.zeros_like(m))
+    torch.cuda.synchronize()
+    assert eng.device_status() == 0 and torch.all(y == 0)
+    eng.close()
+
+
+def test_cfg2_full_size_properties():
+    """Headline workload (B=1000, S=64, 12 layers, fp16) at full size, checked
+    through size-independent properties: a sub-batch against the oracle,
+    independence of a sequence from its batch mates, invariance under a
+    permutation of the sequences, zero padding rows."""
+    spec = W.WORKLOADS[2]
+    wl = W.make_workload(spec)
+    eng = make_engine(spec, wl)
+    y = run_forward(eng, wl)
+    h = spec.shape.hidden
+    # (1) first 32 sequences against the CPU oracle
+    sub = W.Workload(spec, wl.lengths[:32], wl.mask[:32], wl.from_tensor[:32], wl.weights)
+    ref = oracle_valid(sub, spec)
+    got = O.valid_rows(y[:32].cpu().double(), sub.mask)
+    diff = (got - ref.double()).abs()
+    assert float(diff.max()) <= FP16_MAX_ABS and float(diff.mean()) <= FP16_MEAN_ABS
+    # (2) padding rows are zero everywhere
+    pad = torch.from_numpy(wl.mask.ravel() == 0).cuda()
+    assert torch.all(y.reshape(-1, h)[pad] == 0)
+    # (3) permuting the sequences permutes the output
+    perm = np.random.RandomState(0).permutation(spec.batch)
+    wl_p = W.Workload(spec, wl.lengths[perm], wl.mask[perm], wl.from_tensor[perm], wl.weights)
+    y_p = run_forward(eng, wl_p)
+    d = (y_p.float() - y[torch.from_numpy(perm).cuda()].float()).abs()
+    assert float(d.max()) <= 4e-3
+    eng.close()
