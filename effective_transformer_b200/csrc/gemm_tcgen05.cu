@@ -35,6 +35,8 @@ constexpr int UMMA_K = 16;
 constexpr int kNumThreads = 192;
 constexpr int kEpilogueThreads = 128;
 
+constexpr int kStagingPerWarp = 2 * 32 * 128;  // two buffers of 32 rows x 128 bytes
+
 template <int BN>
 struct Cfg {
   static constexpr int kStages = (BN == 256) ? 4 : 6;
@@ -42,9 +44,32 @@ struct Cfg {
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kNumBars = 2 * kStages + 5;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int kStagingBytes = 4 * kStagingPerWarp;
+  static constexpr int kSmemBytes =
+      kStages * kStageBytes + kStagingBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
   static constexpr int kTmemCols = 2 * BN;
 };
+
+__device__ __forceinline__ float gelu_tanh_fast(float x) {
+  // same polynomial as gelu_tanh, with the hardware tanh approximation (its
+  // error is below fp16 resolution of the result)
+  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+  float th;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(u));
+  return 0.5f * x * (1.0f + th);
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, const Vec16& v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ Vec16 ld_shared_v4(uint32_t addr) {
+  Vec16 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr)
+               : "memory");
+  return v;
+}
 
 enum Site : int {
   kSiteProducerEmpty = 1,
@@ -55,12 +80,12 @@ enum Site : int {
   kSiteEpilogueFull = 6,
 };
 
-template <int BN>
+template <int BN, int EPI>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b, __half* __restrict__ C,
                     const __half* __restrict__ bias, const int* __restrict__ m_ptr, int max_m, int N,
-                    int K, int epilogue, int* status_word) {
+                    int K, int* status_word) {
   using cfg = Cfg<BN>;
   constexpr int S = cfg::kStages;
 
@@ -76,7 +101,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t tiles_addr = (raw_addr + 1023u) & ~1023u;
   uint8_t* tiles = smem_raw + (tiles_addr - raw_addr);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + S * cfg::kStageBytes);
+  const uint32_t staging_addr = tiles_addr + S * cfg::kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + S * cfg::kStageBytes + cfg::kStagingBytes);
   const uint32_t bar0 = smem_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (S + s); };
@@ -198,7 +224,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   } else {
     // ------------------------- epilogue -------------------------
+    // Per 64-column chunk: TMEM -> registers (one row per thread) -> bias/GELU
+    // -> fp16 -> this warp's swizzled staging buffer -> 128-byte-per-row
+    // coalesced global stores (one instruction writes 4 full rows of the chunk).
     const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad + 32)
+    const uint32_t stage_warp = staging_addr + quad * kStagingPerWarp;
     int it = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
       const int m_tile = tile / n_tiles, n_tile = tile - m_tile * n_tiles;
@@ -212,37 +242,47 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         break;
       }
       tc_fence_after();
-      const int row = m_tile * BM + quad * 32 + lane;
+      const int row0 = m_tile * BM + quad * 32;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
-      __half* crow = C + static_cast<size_t>(row) * N + n_tile * BN;
-      const __half* brow = (epilogue != kEpiNone) ? bias + n_tile * BN : nullptr;
+      __half* ctile = C + static_cast<size_t>(row0) * N + n_tile * BN;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(t_row + c * 32, r);
+      for (int c = 0; c < BN / 64; ++c) {
+        uint32_t r[64];
+        tmem_ld_32x32b_x32(t_row + c * 64, r);
+        tmem_ld_32x32b_x32(t_row + c * 64 + 32, r + 32);
         tmem_ld_wait();
-        if (row < M) {
+        if (c == BN / 64 - 1) {
+          // the accumulator now lives in registers: hand the TMEM buffer back
+          tc_fence_before();
+          mbar_arrive(tmem_empty_bar(acc));
+        }
+        const uint32_t buf = stage_warp + (c & 1) * (32 * 128);
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            float f[8];
+        for (int p = 0; p < 8; ++p) {
+          float f[8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[g * 8 + e]);
-            if (epilogue != kEpiNone) {
-              float fb[8];
-              VecTraits<__half>::unpack(ld_global_v4(brow + c * 32 + g * 8), fb);
+          for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[p * 8 + e]);
+          if (EPI != kEpiNone) {
+            float fb[8];
+            VecTraits<__half>::unpack(ld_global_v4(bias + n_tile * BN + c * 64 + p * 8), fb);
 #pragma unroll
-              for (int e = 0; e < 8; ++e) f[e] += fb[e];
-              if (epilogue == kEpiBiasGelu) {
+            for (int e = 0; e < 8; ++e) f[e] += fb[e];
+            if (EPI == kEpiBiasGelu) {
 #pragma unroll
-                for (int e = 0; e < 8; ++e) f[e] = gelu_tanh(f[e]);
-              }
+              for (int e = 0; e < 8; ++e) f[e] = gelu_tanh_fast(f[e]);
             }
-            st_global_v4(crow + c * 32 + g * 8, VecTraits<__half>::pack(f));
           }
+          st_shared_v4(buf + lane * 128 + ((p ^ (lane & 7)) << 4), VecTraits<__half>::pack(f));
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int rr = 4 * i + (lane >> 3), piece = lane & 7;
+          const Vec16 v = ld_shared_v4(buf + rr * 128 + ((piece ^ (rr & 7)) << 4));
+          if (row0 + rr < M)
+            st_global_v4(ctile + static_cast<size_t>(rr) * N + c * 64 + piece * 8, v);
         }
       }
-      tc_fence_before();
-      mbar_arrive(tmem_empty_bar(acc));
     }
   }
 
@@ -255,15 +295,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
 }
 
-template <int BN>
-cudaError_t launch_bn(const CUtensorMap& ta, const CUtensorMap& tb, const __half* bias, __half* c,
-                      const int* m_ptr, int max_m, int n, int k, int epilogue, int* status_word,
-                      cudaStream_t stream) {
+template <int BN, int EPI>
+cudaError_t launch_bn_epi(const CUtensorMap& ta, const CUtensorMap& tb, const __half* bias, __half* c,
+                          const int* m_ptr, int max_m, int n, int k, int* status_word,
+                          cudaStream_t stream) {
   using cfg = Cfg<BN>;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN>,
+    attr_err = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI>,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, cfg::kSmemBytes);
   });
   if (attr_err != cudaSuccess) return attr_err;
@@ -271,9 +311,25 @@ cudaError_t launch_bn(const CUtensorMap& ta, const CUtensorMap& tb, const __half
   long long grid = sm_count();
   if (grid > max_tiles) grid = max_tiles;
   if (grid < 1) grid = 1;
-  gemm_tcgen05_kernel<BN><<<static_cast<int>(grid), kNumThreads, cfg::kSmemBytes, stream>>>(
-      ta, tb, c, bias, m_ptr, max_m, n, k, epilogue, status_word);
+  gemm_tcgen05_kernel<BN, EPI><<<static_cast<int>(grid), kNumThreads, cfg::kSmemBytes, stream>>>(
+      ta, tb, c, bias, m_ptr, max_m, n, k, status_word);
   return cudaGetLastError();
+}
+
+template <int BN>
+cudaError_t launch_bn(const CUtensorMap& ta, const CUtensorMap& tb, const __half* bias, __half* c,
+                      const int* m_ptr, int max_m, int n, int k, int epilogue, int* status_word,
+                      cudaStream_t stream) {
+  switch (epilogue) {
+    case kEpiNone:
+      return launch_bn_epi<BN, kEpiNone>(ta, tb, bias, c, m_ptr, max_m, n, k, status_word, stream);
+    case kEpiBias:
+      return launch_bn_epi<BN, kEpiBias>(ta, tb, bias, c, m_ptr, max_m, n, k, status_word, stream);
+    case kEpiBiasGelu:
+      return launch_bn_epi<BN, kEpiBiasGelu>(ta, tb, bias, c, m_ptr, max_m, n, k, status_word, stream);
+    default:
+      return cudaErrorInvalidValue;
+  }
 }
 
 }  // namespace
