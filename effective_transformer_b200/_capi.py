@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(PKG_DIR, "libet_b200.so")
 
 ET_OK, ET_INVALID_ARGUMENT, ET_CUDA_ERROR, ET_WORKSPACE_TOO_SMALL, ET_DEVICE_TIMEOUT, ET_NOT_READY = range(6)
 ET_FP32, ET_FP16 = 0, 1
+NOALLOC_MAX_BATCH = 16384   # ET_NOALLOC_MAX_BATCH in include/et_b200.h
 STATUS_NAMES = {0: "ET_OK", 1: "ET_INVALID_ARGUMENT", 2: "ET_CUDA_ERROR", 3: "ET_WORKSPACE_TOO_SMALL",
                 4: "ET_DEVICE_TIMEOUT", 5: "ET_NOT_READY"}
 
@@ -74,6 +75,7 @@ SIGNATURES = {
     "et_copy_to_host": (i32, [vp, vp, C.c_size_t, vp]),
     "et_set_debug_simt": (i32, [vp, i32]),
     "et_padding_offsets": (i32, [vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp]),
+    "et_padding_offsets_noalloc": (i32, [vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp]),
     "et_remove_padding": (i32, [i32, vp, vp, vp, vp, vp, i32, i32, i32, vp]),
     "et_restore_padding": (i32, [i32, vp, vp, vp, vp, vp, i32, i32, i32, vp]),
     "et_add_qkv_bias_transpose": (i32, [i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp]),

@@ -5,7 +5,12 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <string>
+
 namespace etb {
+
+// Text returned by et_last_error(NULL): errors of calls that take no handle.
+void set_global_error(const std::string& msg);
 
 // ---- launch geometry ------------------------------------------------------
 constexpr int kNumSMsB200 = 148;

@@ -104,6 +104,12 @@ namespace {
 
 thread_local std::string g_create_error;
 
+}  // namespace
+namespace etb {
+void set_global_error(const std::string& msg) { g_create_error = msg; }
+}  // namespace etb
+namespace {
+
 int set_error(et_handle_t h, int code, const std::string& msg) {
   if (h != nullptr) h->last_error = msg;
   else g_create_error = msg;

@@ -5,6 +5,11 @@
 // bit-exact with cumsum(mask) - mask.
 #include "common.cuh"
 
+#include <mutex>
+#include <string>
+
+#include "../../include/et_b200.h"
+
 namespace etb {
 
 namespace {
@@ -238,4 +243,85 @@ ETB_INST(float)
 ETB_INST(__half)
 #undef ETB_INST
 
+// ---------------------------------------------------------------------------
+// et_padding_offsets_noalloc: the padding-offset computation for callers that
+// must not allocate device memory.
+//
+// et_padding_offsets needs a scratch array of batch_size ints (the per-row
+// token counts that pass 1 hands to pass 2) and leaves its allocation to the
+// caller.  Some callers cannot provide one: a framework custom-op whose
+// allocator may not be re-entered from the op, code that runs while a memory
+// pool is frozen, or a plain C plug-in host that has no device allocator at
+// all.  For them the scratch lives in the library image itself, as the
+// file-scope device array below; every GPU that loads the library holds these
+// ET_NOALLOC_MAX_BATCH * 4 bytes until the process exits.
+//
+// The array's name is only a host-side handle for the symbol: the device
+// address is looked up with cudaGetSymbolAddress, once per device, with that
+// device current, the first time the entry point runs there.
+// ---------------------------------------------------------------------------
+namespace {
+
+static __device__ __align__(256) int g_noalloc_row_lengths[ET_NOALLOC_MAX_BATCH];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_noalloc_mutex;
+int* g_noalloc_ptr[kMaxDevices] = {};
+
+// Device address of the scratch array on the current device (set-up on first use).
+cudaError_t noalloc_scratch(int** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    int* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_row_lengths);
+    if (e != cudaSuccess) return e;
+    if (p == nullptr) return cudaErrorInvalidSymbol;
+    g_noalloc_ptr[dev] = p;
+  }
+  *out = g_noalloc_ptr[dev];
+  return cudaSuccess;
+}
+
+}  // namespace
 }  // namespace etb
+
+extern "C" int et_padding_offsets_noalloc(const int* mask, int batch_size, int seq_len, int* prefix_sum,
+                                          int* valid_word_num, int* batch_idx, int* word_idx,
+                                          int* seq_len_out, int* cu_seqlens, int* padding_offset,
+                                          void* stream) {
+  if (batch_size < 0 || seq_len < 0) {
+    etb::set_global_error("et_padding_offsets_noalloc: negative batch_size or seq_len");
+    return ET_INVALID_ARGUMENT;
+  }
+  if (batch_size > ET_NOALLOC_MAX_BATCH) {
+    etb::set_global_error("et_padding_offsets_noalloc: batch_size " + std::to_string(batch_size) +
+                          " exceeds ET_NOALLOC_MAX_BATCH (" + std::to_string(ET_NOALLOC_MAX_BATCH) +
+                          "); use et_padding_offsets with caller-provided scratch");
+    return ET_INVALID_ARGUMENT;
+  }
+  if (batch_size > 0 && seq_len > 0 && mask == nullptr) {
+    etb::set_global_error("et_padding_offsets_noalloc: null mask");
+    return ET_INVALID_ARGUMENT;
+  }
+  int* scratch = nullptr;
+  cudaError_t e = etb::noalloc_scratch(&scratch);
+  if (e != cudaSuccess) {
+    etb::set_global_error(std::string("et_padding_offsets_noalloc: cudaGetSymbolAddress failed: ") +
+                          cudaGetErrorString(e));
+    return ET_CUDA_ERROR;
+  }
+  // Nothing in the scratch has to start at zero: pass 1 overwrites the first
+  // batch_size entries before pass 2 reads them, and no other entry is read.
+  e = etb::launch_padding_offsets(mask, batch_size, seq_len, prefix_sum, valid_word_num, batch_idx,
+                                  word_idx, seq_len_out, cu_seqlens, padding_offset, scratch,
+                                  static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) {
+    etb::set_global_error(std::string("et_padding_offsets_noalloc: launch failed: ") + cudaGetErrorString(e));
+    return ET_CUDA_ERROR;
+  }
+  return ET_OK;
+}

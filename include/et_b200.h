@@ -228,6 +228,30 @@ int et_padding_offsets(const int* mask, int batch_size, int seq_len, int* prefix
                        int* valid_word_num, int* batch_idx, int* word_idx, int* seq_len_out,
                        int* cu_seqlens, int* padding_offset, int* scratch, void* stream);
 
+/* et_padding_offsets for callers that cannot hand over device scratch.  It has
+ * no counterpart in the reference (whose input functor takes its scratch from
+ * TensorFlow's allocator).  Some hosts of this library cannot call cudaMalloc
+ * or any allocator around the call: a framework op that must not re-enter its
+ * own allocator, code running while a memory pool is frozen, a bare C plug-in
+ * with no device allocator.  The per-row token counts that et_padding_offsets
+ * keeps in `scratch` live instead in a device array that is part of the
+ * library image: ET_NOALLOC_MAX_BATCH ints (64 KiB) on every GPU that loads
+ * the library, until the process exits.  The call itself allocates nothing
+ * (no cudaMalloc/cudaFree, no allocating library routine).
+ *   - batch_size > ET_NOALLOC_MAX_BATCH is rejected with ET_INVALID_ARGUMENT
+ *     (text in et_last_error(NULL)); seq_len is not limited.
+ *   - The first call on a device looks up the array's device address
+ *     (cudaGetSymbolAddress) and caches it; make that first call before any
+ *     stream capture begins on that device.
+ *   - All calls on a device share the one array.  Nothing in it has to be
+ *     cleared between calls (each call overwrites the entries it reads), but
+ *     two calls that overlap on the GPU (different streams) race: serialise
+ *     them.  Outputs are those of et_padding_offsets, bit for bit. */
+#define ET_NOALLOC_MAX_BATCH 16384
+int et_padding_offsets_noalloc(const int* mask, int batch_size, int seq_len, int* prefix_sum,
+                               int* valid_word_num, int* batch_idx, int* word_idx, int* seq_len_out,
+                               int* cu_seqlens, int* padding_offset, void* stream);
+
 /* compressBertInput_kernelLauncher (cuda/cuda_kernels.cu:340-372), copy part. */
 int et_remove_padding(int dtype, const void* from_tensor, const int* batch_idx, const int* word_idx,
                       const int* valid_word_num, void* to_tensor, int batch_size, int seq_len,
