@@ -46,19 +46,39 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-// Copies `rows` rows of 64 fp16 (128 bytes) into a padded shared tile and
-// zero-fills the rows up to `tile_rows`.
-__device__ __forceinline__ void load_tile(__half (*dst)[kLd], const __half* __restrict__ src,
-                                          long long token_stride, int rows, int tile_rows) {
-  for (int idx = threadIdx.x; idx < tile_rows * 8; idx += kThreads) {
-    const int r = idx >> 3, c = idx & 7;
-    Vec16 v = {0u, 0u, 0u, 0u};
-    if (r < rows) v = ld_global_nc_v4(src + static_cast<size_t>(r) * token_stride + c * 8);
-    *reinterpret_cast<Vec16*>(&dst[r][c * 8]) = v;
+struct TileSrc {
+  __half (*dst)[kLd];
+  const __half* src;
+  int rows;
+};
+// Copies `rows` rows of 64 fp16 (128 bytes) into each padded 64-row shared
+// tile and zero-fills the rest.  All global loads of all tiles are issued
+// before the first shared-memory store, so one memory latency covers them.
+template <int kTiles>
+__device__ __forceinline__ void load_tiles(const TileSrc (&t)[kTiles], long long token_stride) {
+  constexpr int kPerThread = 64 * 8 / kThreads;  // 16-byte vectors per thread and tile
+  Vec16 v[kTiles][kPerThread];
+#pragma unroll
+  for (int i = 0; i < kTiles; ++i) {
+#pragma unroll
+    for (int j = 0; j < kPerThread; ++j) {
+      const int idx = threadIdx.x + j * kThreads;
+      const int r = idx >> 3, c = idx & 7;
+      v[i][j] = Vec16{0u, 0u, 0u, 0u};
+      if (r < t[i].rows) v[i][j] = ld_global_nc_v4(t[i].src + static_cast<size_t>(r) * token_stride + c * 8);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < kTiles; ++i) {
+#pragma unroll
+    for (int j = 0; j < kPerThread; ++j) {
+      const int idx = threadIdx.x + j * kThreads;
+      *reinterpret_cast<Vec16*>(&t[i].dst[idx >> 3][(idx & 7) * 8]) = v[i][j];
+    }
   }
 }
 
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 4)
 attention_tc_kernel(const __half* __restrict__ q, const __half* __restrict__ k,
                     const __half* __restrict__ v, long long token_stride, long long head_stride,
                     __half* __restrict__ ctx, const int* __restrict__ cu_seqlens, int heads,
@@ -80,8 +100,15 @@ attention_tc_kernel(const __half* __restrict__ q, const __half* __restrict__ k,
 
   for (int q0 = 0; q0 < len; q0 += kQBlock) {
     const int nq = min(kQBlock, len - q0);
-    __syncthreads();  // previous iteration's readers of Qs are done
-    load_tile(Qs, q + static_cast<size_t>(lo + q0) * token_stride + hoff, token_stride, nq, kQBlock);
+    __syncthreads();  // previous iteration's readers of the tiles are done
+    {
+      // the Q block together with the first K/V block
+      const TileSrc first[3] = {
+          {Qs, q + static_cast<size_t>(lo + q0) * token_stride + hoff, nq},
+          {Ks, k + static_cast<size_t>(lo) * token_stride + hoff, min(kKBlock, len)},
+          {Vs, v + static_cast<size_t>(lo) * token_stride + hoff, min(kKBlock, len)}};
+      load_tiles<3>(first, token_stride);
+    }
     __syncthreads();
     const bool warp_active = warp * 16 < nq;
 
@@ -104,10 +131,13 @@ attention_tc_kernel(const __half* __restrict__ q, const __half* __restrict__ k,
 
     for (int k0 = 0; k0 < len; k0 += kKBlock) {
       const int nk = min(kKBlock, len - k0);
-      __syncthreads();  // previous block's readers of Ks/Vs are done
-      load_tile(Ks, k + static_cast<size_t>(lo + k0) * token_stride + hoff, token_stride, nk, kKBlock);
-      load_tile(Vs, v + static_cast<size_t>(lo + k0) * token_stride + hoff, token_stride, nk, kKBlock);
-      __syncthreads();
+      if (k0 > 0) {
+        __syncthreads();  // previous block's readers of Ks/Vs are done
+        const TileSrc next[2] = {{Ks, k + static_cast<size_t>(lo + k0) * token_stride + hoff, nk},
+                                 {Vs, v + static_cast<size_t>(lo + k0) * token_stride + hoff, nk}};
+        load_tiles<2>(next, token_stride);
+        __syncthreads();
+      }
       if (!warp_active) continue;
 
       // S = Q K^T : 16 x 64 scores as 8 n-tiles of 8 keys

@@ -6,13 +6,14 @@
 // add_bias_act (cuda/cuda_kernels.cu:88-134) / the bias half of
 // add_QKV_bias_padding (cuda/attention.cu:106-175) into the epilogue.
 //
-// Structure (one persistent CTA per SM, 192 threads):
+// Structure (one persistent CTA per SM, 320 threads):
 //   warp 0   TMA producer: A tile [128 x 64] and W tile [BN x 64] per k-block
 //            into a kStages-deep shared-memory ring (128-byte swizzle)
 //   warp 1   MMA issuer: tcgen05.mma cta_group::1 kind::f16, M=128, N=BN, K=16,
 //            accumulating into one of two TMEM buffers of BN columns
-//   warps 2-5 epilogue: tcgen05.ld of the finished accumulator (one TMEM lane
-//            quadrant per warp), bias / GELU in fp32, 16-byte stores to C,
+//   warps 2-9 epilogue: tcgen05.ld of the finished accumulator (one TMEM lane
+//            quadrant and one half of the columns per warp), bias / GELU in
+//            fp32, staged through shared memory to coalesced stores of C,
 //            overlapping the next tile's main loop
 // M is read from device memory, so no host synchronisation is needed between
 // the padding-offset kernel and the projections.  Every mbarrier wait is
@@ -32,10 +33,11 @@ using namespace ptx;
 constexpr int BM = 128;
 constexpr int BK = 64;  // 64 fp16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
-constexpr int kNumThreads = 192;
-constexpr int kEpilogueThreads = 128;
+constexpr int kEpilogueWarps = 8;  // two per TMEM lane quadrant, each owning half of the tile's columns
+constexpr int kEpilogueThreads = kEpilogueWarps * 32;
+constexpr int kNumThreads = 64 + kEpilogueThreads;
 
-constexpr int kStagingPerWarp = 2 * 32 * 128;  // two buffers of 32 rows x 128 bytes
+constexpr int kStagingPerWarp = 32 * 128;  // 32 rows x 128 bytes (64 fp16 columns)
 
 template <int BN>
 struct Cfg {
@@ -44,9 +46,10 @@ struct Cfg {
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kNumBars = 2 * kStages + 5;
-  static constexpr int kStagingBytes = 4 * kStagingPerWarp;
-  static constexpr int kSmemBytes =
-      kStages * kStageBytes + kStagingBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int kStagingBytes = kEpilogueWarps * kStagingPerWarp;
+  static constexpr int kColsPerWarp = BN / 2;
+  static constexpr int kBiasBytes = kEpilogueWarps * kColsPerWarp * 2;  // per-warp fp16 bias slice
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + kBiasBytes + 256 /*barriers*/;
   static constexpr int kTmemCols = 2 * BN;
 };
 
@@ -78,6 +81,7 @@ enum Site : int {
   kSiteMmaFull = 4,
   kSiteMmaDrain = 5,
   kSiteEpilogueFull = 6,
+  kSiteSmemAlign = 7,
 };
 
 template <int BN, int EPI>
@@ -97,12 +101,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int num_kb = (K + BK - 1) / BK;
   if (num_tiles == 0) return;  // uniform for the whole grid
 
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t raw_addr = smem_u32(smem_raw);
-  const uint32_t tiles_addr = (raw_addr + 1023u) & ~1023u;
-  uint8_t* tiles = smem_raw + (tiles_addr - raw_addr);
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t tiles_addr = smem_u32(smem_raw);
+  if ((tiles_addr & 1023u) != 0u) {  // the swizzled tiles need 1024-byte alignment
+    if (threadIdx.x == 0) report_timeout(status_word, kKernelGemmTc, kSiteSmemAlign);
+    return;
+  }
+  uint8_t* tiles = smem_raw;
   const uint32_t staging_addr = tiles_addr + S * cfg::kStageBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + S * cfg::kStageBytes + cfg::kStagingBytes);
+  const uint32_t bias_addr = staging_addr + cfg::kStagingBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + S * cfg::kStageBytes + cfg::kStagingBytes + cfg::kBiasBytes);
   const uint32_t bar0 = smem_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (S + s); };
@@ -224,16 +232,29 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   } else {
     // ------------------------- epilogue -------------------------
-    // Per 64-column chunk: TMEM -> registers (one row per thread) -> bias/GELU
-    // -> fp16 -> this warp's swizzled staging buffer -> 128-byte-per-row
-    // coalesced global stores (one instruction writes 4 full rows of the chunk).
-    const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad + 32)
-    const uint32_t stage_warp = staging_addr + quad * kStagingPerWarp;
+    // Eight warps: warp w works on TMEM lanes [32*(w%4), +32) (the rows it may
+    // access) and on one half of the tile's columns, two warps per scheduler
+    // so that TMEM, shared-memory and MUFU latencies overlap.  Per 64-column
+    // chunk: TMEM -> registers (one row per thread) -> bias/GELU in fp32 ->
+    // fp16 -> the warp's swizzled staging buffer -> coalesced global stores
+    // (one instruction writes 4 full 128-byte row segments).
+    const int quad = warp & 3;
+    const int ew = warp - 2;            // 0..7
+    const int half = ew >> 2;           // which half of the columns
+    constexpr int kCols = cfg::kColsPerWarp;
+    const uint32_t buf = staging_addr + ew * kStagingPerWarp;
+    const uint32_t bias_s = bias_addr + ew * (kCols * 2);
     int it = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
       const int m_tile = tile / n_tiles, n_tile = tile - m_tile * n_tiles;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
+      const int col0 = n_tile * BN + half * kCols;
+      if (EPI != kEpiNone) {
+        // this warp's bias slice -> shared memory (read back as broadcasts)
+        if (lane < kCols / 8) st_shared_v4(bias_s + lane * 16, ld_global_v4(bias + col0 + lane * 8));
+        __syncwarp();
+      }
       // every lane polls; the vote makes the outcome uniform and reconverges the
       // warp for the .sync.aligned TMEM loads below
       const bool got = mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag);
@@ -243,20 +264,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
       tc_fence_after();
       const int row0 = m_tile * BM + quad * 32;
-      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
-      __half* ctile = C + static_cast<size_t>(row0) * N + n_tile * BN;
+      const uint32_t t_row =
+          tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN + half * kCols;
+      __half* ctile = C + static_cast<size_t>(row0) * N + col0;
 #pragma unroll 1
-      for (int c = 0; c < BN / 64; ++c) {
+      for (int c = 0; c < kCols / 64; ++c) {
         uint32_t r[64];
         tmem_ld_32x32b_x32(t_row + c * 64, r);
         tmem_ld_32x32b_x32(t_row + c * 64 + 32, r + 32);
         tmem_ld_wait();
-        if (c == BN / 64 - 1) {
+        if (c == kCols / 64 - 1) {
           // the accumulator now lives in registers: hand the TMEM buffer back
           tc_fence_before();
           mbar_arrive(tmem_empty_bar(acc));
         }
-        const uint32_t buf = stage_warp + (c & 1) * (32 * 128);
 #pragma unroll
         for (int p = 0; p < 8; ++p) {
           float f[8];
@@ -264,7 +285,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[p * 8 + e]);
           if (EPI != kEpiNone) {
             float fb[8];
-            VecTraits<__half>::unpack(ld_global_v4(bias + n_tile * BN + c * 64 + p * 8), fb);
+            VecTraits<__half>::unpack(ld_shared_v4(bias_s + (c * 64 + p * 8) * 2), fb);
 #pragma unroll
             for (int e = 0; e < 8; ++e) f[e] += fb[e];
             if (EPI == kEpiBiasGelu) {
@@ -282,6 +303,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (row0 + rr < M)
             st_global_v4(ctile + static_cast<size_t>(rr) * N + c * 64 + piece * 8, v);
         }
+        __syncwarp();  // the staging buffer is rewritten by the next chunk / tile
       }
     }
   }

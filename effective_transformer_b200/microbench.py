@@ -1,0 +1,163 @@
+"""Per-kernel micro-benchmark through the C ABI.
+
+    python -m effective_transformer_b200.microbench [--kernel NAME|all] [--workload 2] [--iters 20]
+
+Each kernel of the encoder path runs alone on tensors of a benchmark
+configuration's shapes (default: BERT-base fp16, B=1000, S=64, T=39778), an
+L2-sized buffer is overwritten between iterations, and every iteration is
+timed with CUDA events on the launching stream.  One JSON line per kernel:
+algorithmic bytes or FLOPs per launch, median time, achieved GB/s or TFLOP/s
+and the fraction of the measured peak (MEASURED_PEAKS.json at the repository
+root when present, else the stated fallback).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+
+import numpy as np
+import torch
+
+from . import _capi
+from . import workloads as W
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+FALLBACK = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"])}, "measured"
+    return dict(FALLBACK), "fallback"
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--kernel", default="all")
+    ap.add_argument("--workload", type=int, default=2)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--no-flush", action="store_true")
+    args = ap.parse_args()
+
+    lib = _capi.load()
+    spec = W.WORKLOADS[args.workload]
+    lens = W.draw_lengths(spec, np.random.RandomState(spec.seed))
+    b, s, h, f = spec.batch, spec.max_seq_len, spec.shape.hidden, spec.shape.ffn_dim
+    heads = spec.shape.head_num
+    t = int(lens.sum())
+    fp16 = spec.dtype == "fp16"
+    tdt = torch.float16 if fp16 else torch.float32
+    dt = _capi.ET_FP16 if fp16 else _capi.ET_FP32
+    e = 2 if fp16 else 4
+    dev = torch.device("cuda", 0)
+    st = torch.cuda.current_stream().cuda_stream
+    g = torch.Generator(device="cuda").manual_seed(0)
+    rnd = lambda *shape: torch.randn(*shape, device=dev, generator=g, dtype=torch.float32).to(tdt)
+
+    mask = torch.from_numpy(W.prefix_mask(lens, s)).to(dev)
+    i32 = dict(dtype=torch.int32, device=dev)
+    tn = torch.tensor([t], **i32)
+    n_pos = b * s
+    prefix, bidx, widx, poff = [torch.zeros(n_pos, **i32) for _ in range(4)]
+    slen, cu, scratch = torch.zeros(b, **i32), torch.zeros(b + 1, **i32), torch.zeros(b, **i32)
+    valid = torch.zeros(1, **i32)
+    status = torch.zeros(1, **i32)
+    P = lambda x: None if x is None else x.data_ptr()
+
+    def run_padding():
+        return lib.et_padding_offsets(P(mask), b, s, P(prefix), P(valid), P(bidx), P(widx), P(slen), P(cu),
+                                      P(poff), P(scratch), st)
+    assert run_padding() == 0
+    torch.cuda.synchronize()
+
+    x_pad = rnd(b, s, h)
+    x_packed = rnd(n_pos, h)
+    out_pad = torch.empty_like(x_pad)
+    res = rnd(n_pos, h)
+    bias_h, gamma_h, beta_h = rnd(h), rnd(h), rnd(h)
+    bias_f = rnd(f)
+    qkv = rnd(n_pos, 3 * h)
+    q, k, v = rnd(n_pos, h), rnd(n_pos, h), rnd(n_pos, h)
+    qkv_t = torch.empty(3 * heads * n_pos * 64, device=dev, dtype=tdt)
+    ctx = torch.empty(n_pos, h, device=dev, dtype=tdt)
+    ffn = rnd(n_pos, f)
+    bias3 = rnd(3 * h)
+    weights = {}
+    for name, (kk, nn) in {"gemm_qkv": (h, 3 * h), "gemm_attn_out": (h, h), "gemm_ffn1": (h, f),
+                           "gemm_ffn2": (f, h)}.items():
+        w = (rnd(kk, nn) * 0.02).contiguous()
+        wp = torch.empty(nn, kk, device=dev, dtype=tdt)
+        assert lib.et_pack_weight(dt, P(w), P(wp), kk, nn, st) == 0
+        weights[name] = (w, wp, kk, nn)
+    gemm_out = torch.empty(n_pos, max(3 * h, f), device=dev, dtype=tdt)
+    simt = 0 if fp16 else 1
+
+    def gemm(name, a, bias, epi):
+        w, wp, kk, nn = weights[name]
+        return lambda: lib.et_gemm(dt, P(a), P(w), P(wp), P(bias), P(gemm_out), P(tn), n_pos, nn, kk, epi, simt,
+                                   P(status), st)
+
+    sum_len2 = float((lens.astype(np.int64) ** 2).sum())
+    # name -> (callable, bound, algorithmic units per launch)
+    kernels = {
+        "padding_offsets": (run_padding, "hbm", 4.0 * n_pos + 12.0 * t + 8.0 * b),
+        "remove_padding": (lambda: lib.et_remove_padding(dt, P(x_pad), P(bidx), P(widx), P(tn), P(x_packed), b, s, h, st),
+                           "hbm", 2.0 * t * h * e),
+        "restore_padding": (lambda: lib.et_restore_padding(dt, P(x_packed), P(bidx), P(widx), P(tn), P(out_pad), b, s, h, st),
+                            "hbm", (t + n_pos) * h * e * 1.0),
+        "qkv_bias_transpose": (lambda: lib.et_add_qkv_bias_transpose(dt, P(q), P(bias_h), P(k), P(bias_h), P(v), P(bias_h),
+                                                                    P(qkv_t), P(tn), n_pos, heads, 64, st),
+                               "hbm", 6.0 * t * h * e),
+        "bias_gelu": (lambda: lib.et_add_bias_gelu(dt, P(ffn), P(bias_f), P(tn), n_pos, f, st), "hbm", 2.0 * t * f * e),
+        "bias_residual_layernorm": (lambda: lib.et_add_bias_input_layernorm(dt, P(x_packed), P(res), P(bias_h), P(gamma_h),
+                                                                            P(beta_h), P(tn), n_pos, h, 1e-6, st),
+                                    "hbm", 3.0 * t * h * e),
+        "attention": (lambda: lib.et_attention(dt, qkv.data_ptr(), qkv.data_ptr() + h * e, qkv.data_ptr() + 2 * h * e,
+                                               3 * h, 64, P(ctx), P(cu), b, s, heads, 64, simt, P(status), st),
+                      "hbm", 4.0 * t * h * e),
+        "gemm_qkv": (gemm("gemm_qkv", x_packed, bias3, 1), "tensor", 2.0 * t * h * 3 * h),
+        "gemm_attn_out": (gemm("gemm_attn_out", x_packed, None, 0), "tensor", 2.0 * t * h * h),
+        "gemm_ffn1": (gemm("gemm_ffn1", x_packed, bias_f, 2), "tensor", 2.0 * t * h * f),
+        "gemm_ffn2": (gemm("gemm_ffn2", ffn, None, 0), "tensor", 2.0 * t * h * f),
+    }
+    names = list(kernels) if args.kernel == "all" else [args.kernel]
+    pk, src = peaks()
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    for name in names:
+        fn, bound, units = kernels[name]
+        for _ in range(args.warmup):
+            assert fn() == 0, name
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(args.iters):
+            if not args.no_flush:
+                flush.zero_()
+            a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            rc = fn()
+            z.record()
+            assert rc == 0, name
+            z.synchronize()
+            times.append(a.elapsed_time(z))
+        assert int(status[0]) == 0, "a device-side wait expired"
+        ms = statistics.median(times)
+        if bound == "hbm":
+            ach, peak, unit = units / (ms * 1e-3) / 1e9, pk["hbm_gbs"], "GB/s"
+        else:
+            ach, peak, unit = units / (ms * 1e-3) / 1e12, pk["bf16_tflops"], "TFLOP/s"
+        print(json.dumps({"kernel": name, "workload": spec.name, "valid_tokens": t, "bound": bound,
+                          "algorithmic_per_launch": units, "ms_median": ms, "ms_min": min(times),
+                          "achieved": ach, "peak": peak, "unit": unit, "frac": ach / peak,
+                          "peak_source": src + (" hbm_gbs" if bound == "hbm" else " bf16_tflops (burst)")}),
+              flush=True)
+
+
+if __name__ == "__main__":
+    main()
