@@ -22,6 +22,7 @@
 #include "common.cuh"
 #include "ptx_sm100.cuh"
 
+#include <cstdlib>
 #include <mutex>
 
 namespace etb {
@@ -72,6 +73,55 @@ __device__ __forceinline__ Vec16 ld_shared_v4(uint32_t addr) {
                : "r"(addr)
                : "memory");
   return v;
+}
+
+// Epilogue of one warp for one finished accumulator: its 32 rows (TMEM lanes
+// starting at the lane field of t_row) x kCols columns.  Per 64-column chunk:
+// TMEM -> registers (one row per thread) -> bias/GELU in fp32 -> fp16 -> the
+// warp's swizzled staging buffer -> coalesced global stores (one instruction
+// writes 4 full 128-byte row segments).  `release` runs once all TMEM reads of
+// the warp have completed.  rows_valid = M - (first row of this warp).
+template <int EPI, int kCols, typename Release>
+__device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, __half* ctile, int N, int rows_valid,
+                                                   uint32_t bias_s, uint32_t buf, int lane,
+                                                   Release release) {
+#pragma unroll 1
+  for (int c = 0; c < kCols / 64; ++c) {
+    uint32_t r[64];
+    tmem_ld_32x32b_x32(t_row + c * 64, r);
+    tmem_ld_32x32b_x32(t_row + c * 64 + 32, r + 32);
+    tmem_ld_wait();
+    if (c == kCols / 64 - 1) {
+      // the accumulator now lives in registers: hand the TMEM buffer back
+      tc_fence_before();
+      release();
+    }
+#pragma unroll
+    for (int p = 0; p < 8; ++p) {
+      float f[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[p * 8 + e]);
+      if (EPI != kEpiNone) {
+        float fb[8];
+        VecTraits<__half>::unpack(ld_shared_v4(bias_s + (c * 64 + p * 8) * 2), fb);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] += fb[e];
+        if (EPI == kEpiBiasGelu) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[e] = gelu_tanh_fast(f[e]);
+        }
+      }
+      st_shared_v4(buf + lane * 128 + ((p ^ (lane & 7)) << 4), VecTraits<__half>::pack(f));
+    }
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int rr = 4 * i + (lane >> 3), piece = lane & 7;
+      const Vec16 v = ld_shared_v4(buf + rr * 128 + ((piece ^ (rr & 7)) << 4));
+      if (rr < rows_valid) st_global_v4(ctile + static_cast<size_t>(rr) * N + c * 64 + piece * 8, v);
+    }
+    __syncwarp();  // the staging buffer is rewritten by the next chunk / tile
+  }
 }
 
 enum Site : int {
@@ -234,10 +284,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // ------------------------- epilogue -------------------------
     // Eight warps: warp w works on TMEM lanes [32*(w%4), +32) (the rows it may
     // access) and on one half of the tile's columns, two warps per scheduler
-    // so that TMEM, shared-memory and MUFU latencies overlap.  Per 64-column
-    // chunk: TMEM -> registers (one row per thread) -> bias/GELU in fp32 ->
-    // fp16 -> the warp's swizzled staging buffer -> coalesced global stores
-    // (one instruction writes 4 full 128-byte row segments).
+    // so that TMEM, shared-memory and MUFU latencies overlap.
     const int quad = warp & 3;
     const int ew = warp - 2;            // 0..7
     const int half = ew >> 2;           // which half of the columns
@@ -267,44 +314,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t t_row =
           tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN + half * kCols;
       __half* ctile = C + static_cast<size_t>(row0) * N + col0;
-#pragma unroll 1
-      for (int c = 0; c < kCols / 64; ++c) {
-        uint32_t r[64];
-        tmem_ld_32x32b_x32(t_row + c * 64, r);
-        tmem_ld_32x32b_x32(t_row + c * 64 + 32, r + 32);
-        tmem_ld_wait();
-        if (c == kCols / 64 - 1) {
-          // the accumulator now lives in registers: hand the TMEM buffer back
-          tc_fence_before();
-          mbar_arrive(tmem_empty_bar(acc));
-        }
-#pragma unroll
-        for (int p = 0; p < 8; ++p) {
-          float f[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[p * 8 + e]);
-          if (EPI != kEpiNone) {
-            float fb[8];
-            VecTraits<__half>::unpack(ld_shared_v4(bias_s + (c * 64 + p * 8) * 2), fb);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) f[e] += fb[e];
-            if (EPI == kEpiBiasGelu) {
-#pragma unroll
-              for (int e = 0; e < 8; ++e) f[e] = gelu_tanh_fast(f[e]);
-            }
-          }
-          st_shared_v4(buf + lane * 128 + ((p ^ (lane & 7)) << 4), VecTraits<__half>::pack(f));
-        }
-        __syncwarp();
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int rr = 4 * i + (lane >> 3), piece = lane & 7;
-          const Vec16 v = ld_shared_v4(buf + rr * 128 + ((piece ^ (rr & 7)) << 4));
-          if (row0 + rr < M)
-            st_global_v4(ctile + static_cast<size_t>(rr) * N + c * 64 + piece * 8, v);
-        }
-        __syncwarp();  // the staging buffer is rewritten by the next chunk / tile
-      }
+      epilogue_warp_tile<EPI, kCols>(t_row, ctile, N, M - row0, bias_s, buf, lane,
+                                     [&] { mbar_arrive(tmem_empty_bar(acc)); });
     }
   }
 
@@ -314,6 +325,274 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem_base, cfg::kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// CTA-pair variant: a cluster of two CTAs (one per SM of a TPC) computes a
+// 256 x 256 tile with tcgen05.mma cta_group::2.  Each CTA loads 128 rows of A
+// and 128 of the tile's 256 W rows per k-block (32 KB instead of 48 KB per
+// 128 x 256 of output, i.e. one third less L2 -> shared-memory traffic per
+// FLOP) and keeps the 128 x 256 accumulator of its own rows in its own TMEM.
+// CTA 0 of the pair issues the MMAs for both; barriers that cross the pair:
+//   full[s]      lives in CTA 0, counts the TMA bytes of both CTAs
+//   empty[s]     one per CTA, CTA 0's MMA thread commits to both
+//   tmem_full[a] one per CTA, CTA 0's MMA thread commits to both
+//   tmem_empty[a] lives in CTA 0, one arrival per epilogue warp of both CTAs
+// No load is multicast: each CTA fetches its own operand rows.
+// ---------------------------------------------------------------------------
+struct PairCfg {
+  static constexpr int BN = 256;
+  static constexpr int kStages = 6;
+  static constexpr int kABytes = BM * BK * 2;          // this CTA's 128 A rows
+  static constexpr int kBBytes = (BN / 2) * BK * 2;    // this CTA's 128 W rows
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kNumBars = 2 * kStages + 5;
+  static constexpr int kStagingBytes = kEpilogueWarps * kStagingPerWarp;
+  static constexpr int kColsPerWarp = BN / 2;
+  static constexpr int kBiasBytes = kEpilogueWarps * kColsPerWarp * 2;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + kBiasBytes + 256;
+  static constexpr int kTmemCols = 2 * BN;
+};
+
+template <int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                         const __grid_constant__ CUtensorMap tmap_b, __half* __restrict__ C,
+                         const __half* __restrict__ bias, const int* __restrict__ m_ptr, int max_m,
+                         int N, int K, int* status_word) {
+  using cfg = PairCfg;
+  constexpr int S = cfg::kStages;
+  constexpr int BN = cfg::BN;
+  constexpr int BM2 = 2 * BM;
+
+  int M = *m_ptr;
+  M = M < 0 ? 0 : (M > max_m ? max_m : M);
+  const int m_tiles = (M + BM2 - 1) / BM2;
+  const int n_tiles = N / BN;
+  const int num_tiles = m_tiles * n_tiles;
+  const int num_kb = (K + BK - 1) / BK;
+  if (num_tiles == 0) return;  // uniform for the whole grid
+
+  const uint32_t rank = cluster_ctarank();  // 0 issues the MMAs
+  const int pair_id = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t tiles_addr = smem_u32(smem_raw);
+  if ((tiles_addr & 1023u) != 0u) {  // same layout in both CTAs: uniform for the pair
+    if (threadIdx.x == 0) report_timeout(status_word, kKernelGemmTc, kSiteSmemAlign);
+    return;
+  }
+  uint8_t* tiles = smem_raw;
+  const uint32_t staging_addr = tiles_addr + S * cfg::kStageBytes;
+  const uint32_t bias_addr = staging_addr + cfg::kStagingBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + S * cfg::kStageBytes + cfg::kStagingBytes + cfg::kBiasBytes);
+  const uint32_t bar0 = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (S + s); };
+  auto tmem_full_bar = [&](int a) { return bar0 + 8u * (2 * S + a); };
+  auto tmem_empty_bar = [&](int a) { return bar0 + 8u * (2 * S + 2 + a); };
+  const uint32_t drain_bar = bar0 + 8u * (2 * S + 4);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + cfg::kNumBars);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tmem_full_bar(a), 1);
+      mbar_init(tmem_empty_bar(a), 2 * kEpilogueWarps);
+    }
+    mbar_init(drain_bar, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(tmem_slot), cfg::kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers are initialised before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto fail = [&](int site) {
+    *abort_flag = 1;
+    report_timeout(status_word, kKernelGemmTc, site);
+  };
+
+  if (warp == 0) {
+    // ------------------------- TMA producer (both CTAs) -------------------------
+    if (lane == 0) {
+      prefetch_tensormap(&tmap_a);
+      prefetch_tensormap(&tmap_b);
+      uint32_t stage = 0, phase = 0;
+      long long issued = 0;
+      bool ok = true;
+      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+        const int m_tile = tile / n_tiles, n_tile = tile - m_tile * n_tiles;
+        const int a_row = m_tile * BM2 + static_cast<int>(rank) * BM;
+        const int b_row = n_tile * BN + static_cast<int>(rank) * (BN / 2);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+            fail(kSiteProducerEmpty);
+            ok = false;
+            break;
+          }
+          const uint32_t a_dst = tiles_addr + stage * cfg::kStageBytes;
+          const uint32_t b_dst = a_dst + cfg::kABytes;
+          const uint32_t full0 = mapa_shared(full_bar(stage), 0);
+          if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * cfg::kStageBytes);
+          tma_load_2d_pair(a_dst, &tmap_a, kb * BK, a_row, full0);
+          tma_load_2d_pair(b_dst, &tmap_b, kb * BK, b_row, full0);
+          ++issued;
+          if (++stage == S) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (rank == 0) {
+        // full[] counts both CTAs' bytes: once these phases are complete no copy
+        // of the pair is in flight; the peer learns it at the closing cluster barrier.
+        const long long pending = issued < S ? issued : S;
+        for (long long i = 0; i < pending; ++i) {
+          const long long f = issued - 1 - i;
+          if (!mbar_wait(full_bar(static_cast<int>(f % S)), static_cast<uint32_t>((f / S) & 1),
+                         abort_flag) && *abort_flag == 0)
+            fail(kSiteProducerDrain);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------- MMA issuer (CTA 0 only) -------------------------
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc_f16_f32acc(BM2, BN);
+      uint32_t stage = 0, phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag)) {
+          fail(kSiteMmaTmemEmpty);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+            fail(kSiteMmaFull);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = tiles_addr + stage * cfg::kStageBytes;
+          const uint64_t adesc = make_kmajor_sw128_desc(a_addr);
+          const uint64_t bdesc = make_kmajor_sw128_desc(a_addr + cfg::kABytes);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_f16_ss_pair(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          umma_commit_pair(empty_bar(stage));
+          umma_commit_pair(mapa_shared(empty_bar(stage), 1));
+          if (++stage == S) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) {
+          umma_commit_pair(tmem_full_bar(acc));
+          umma_commit_pair(mapa_shared(tmem_full_bar(acc), 1));
+        }
+      }
+      umma_commit_pair(drain_bar);
+      if (!mbar_wait(drain_bar, 0u, abort_flag) && *abort_flag == 0) fail(kSiteMmaDrain);
+    }
+  } else {
+    // ------------------------- epilogue (both CTAs) -------------------------
+    const int quad = warp & 3;
+    const int ew = warp - 2;
+    const int half = ew >> 2;
+    constexpr int kCols = cfg::kColsPerWarp;
+    const uint32_t buf = staging_addr + ew * kStagingPerWarp;
+    const uint32_t bias_s = bias_addr + ew * (kCols * 2);
+    int it = 0;
+    for (int tile = pair_id; tile < num_tiles; tile += num_pairs, ++it) {
+      const int m_tile = tile / n_tiles, n_tile = tile - m_tile * n_tiles;
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      const int col0 = n_tile * BN + half * kCols;
+      if (EPI != kEpiNone) {
+        if (lane < kCols / 8) st_shared_v4(bias_s + lane * 16, ld_global_v4(bias + col0 + lane * 8));
+        __syncwarp();
+      }
+      const bool got = mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag);
+      if (!__all_sync(0xffffffffu, got)) {
+        if (lane == 0) fail(kSiteEpilogueFull);
+        break;
+      }
+      tc_fence_after();
+      const int row0 = m_tile * BM2 + static_cast<int>(rank) * BM + quad * 32;
+      const uint32_t t_row =
+          tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN + half * kCols;
+      __half* ctile = C + static_cast<size_t>(row0) * N + col0;
+      const uint32_t empty0 = mapa_shared(tmem_empty_bar(acc), 0);
+      epilogue_warp_tile<EPI, kCols>(t_row, ctile, N, M - row0, bias_s, buf, lane, [&] {
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(empty0);
+      });
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA leaves while the other may still touch its barriers or TMEM
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, cfg::kTmemCols);
+  }
+}
+
+template <int EPI>
+cudaError_t launch_pair_epi(const CUtensorMap& ta, const CUtensorMap& tb, const __half* bias, __half* c,
+                            const int* m_ptr, int max_m, int n, int k, int* status_word,
+                            cudaStream_t stream) {
+  using cfg = PairCfg;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<EPI>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, cfg::kSmemBytes);
+  });
+  if (attr_err != cudaSuccess) return attr_err;
+  const long long max_tiles = static_cast<long long>((max_m + 2 * BM - 1) / (2 * BM)) * (n / cfg::BN);
+  long long pairs = sm_count() / 2;
+  if (pairs > max_tiles) pairs = max_tiles;
+  if (pairs < 1) pairs = 1;
+  gemm_tcgen05_pair_kernel<EPI><<<static_cast<int>(2 * pairs), kNumThreads, cfg::kSmemBytes, stream>>>(
+      ta, tb, c, bias, m_ptr, max_m, n, k, status_word);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const __half* bias, __half* c,
+                        const int* m_ptr, int max_m, int n, int k, int epilogue, int* status_word,
+                        cudaStream_t stream) {
+  switch (epilogue) {
+    case kEpiNone:
+      return launch_pair_epi<kEpiNone>(ta, tb, bias, c, m_ptr, max_m, n, k, status_word, stream);
+    case kEpiBias:
+      return launch_pair_epi<kEpiBias>(ta, tb, bias, c, m_ptr, max_m, n, k, status_word, stream);
+    case kEpiBiasGelu:
+      return launch_pair_epi<kEpiBiasGelu>(ta, tb, bias, c, m_ptr, max_m, n, k, status_word, stream);
+    default:
+      return cudaErrorInvalidValue;
   }
 }
 
@@ -394,13 +673,19 @@ cudaError_t launch_gemm_tcgen05(const __half* a, const __half* w_packed, const _
     return cudaErrorMisalignedAddress;
   if (epilogue != kEpiNone && bias == nullptr) return cudaErrorInvalidValue;
   const int bn = (n % 256 == 0) ? 256 : 128;
+  static const bool single_cta = [] {
+    const char* e = getenv("ETB_GEMM_SINGLE_CTA");   // debugging: force the one-CTA kernel
+    return e != nullptr && e[0] == '1';
+  }();
+  const bool pair = (bn == 256) && !single_cta;
   CUtensorMap ta, tb;
   if (!encode_2d_fp16_sw128(&ta, a, static_cast<uint64_t>(max_m), static_cast<uint64_t>(k),
                             static_cast<uint64_t>(k), BM, BK))
     return cudaErrorInvalidValue;
   if (!encode_2d_fp16_sw128(&tb, w_packed, static_cast<uint64_t>(n), static_cast<uint64_t>(k),
-                            static_cast<uint64_t>(k), static_cast<uint32_t>(bn), BK))
+                            static_cast<uint64_t>(k), static_cast<uint32_t>(pair ? 128 : bn), BK))
     return cudaErrorInvalidValue;
+  if (pair) return launch_pair(ta, tb, bias, c, m_ptr, max_m, n, k, epilogue, status_word, stream);
   if (bn == 256)
     return launch_bn<256>(ta, tb, bias, c, m_ptr, max_m, n, k, epilogue, status_word, stream);
   return launch_bn<128>(ta, tb, bias, c, m_ptr, max_m, n, k, epilogue, status_word, stream);
