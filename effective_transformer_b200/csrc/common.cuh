@@ -176,11 +176,11 @@ template <typename T>
 cudaError_t launch_attention_simt(const T* q, const T* k, const T* v, long long token_stride,
                                   long long head_stride, T* ctx, const int* cu_seqlens, int batch,
                                   int max_seq, int heads, int d, cudaStream_t stream);
-// Tensor-core (mma.sync) attention, fp16.
+// Tensor-core attention (TMA-fed, mma.sync), fp16.  q/k/v hold max_tokens rows.
 cudaError_t launch_attention_tc(const __half* q, const __half* k, const __half* v,
                                 long long token_stride, long long head_stride, __half* ctx,
-                                const int* cu_seqlens, int batch, int max_seq, int heads, int d,
-                                int* status_word, cudaStream_t stream);
+                                const int* cu_seqlens, int batch, int max_seq, int max_tokens, int heads,
+                                int d, int* status_word, cudaStream_t stream);
 // tcgen05 GEMM, fp16 in / fp32 accumulate / fp16 out.  w_packed is [N,K].
 cudaError_t launch_gemm_tcgen05(const __half* a, const __half* w_packed, const __half* bias,
                                 __half* c, const int* m_ptr, int max_m, int n, int k, int epilogue,

@@ -243,7 +243,7 @@ int run_layer(et_handle_t h, const LayerWeights& lw, const T* x_in, T* x_out, co
     ET_LAUNCH(h, ET_PROF_ATTENTION, 1, s, launch_attention_tc(reinterpret_cast<const __half*>(qkv),
                                    reinterpret_cast<const __half*>(qkv) + hid,
                                    reinterpret_cast<const __half*>(qkv) + 2 * hid, 3LL * hid, d,
-                                   reinterpret_cast<__half*>(ctx), cu_seqlens, batch, seq, heads, d,
+                                   reinterpret_cast<__half*>(ctx), cu_seqlens, batch, seq, max_m, heads, d,
                                    ws.status, s));
   else
     ET_LAUNCH(h, ET_PROF_ATTENTION, 1, s, launch_attention_simt<T>(qkv, qkv + hid, qkv + 2 * hid, 3LL * hid, d, ctx, cu_seqlens,
@@ -777,14 +777,15 @@ int et_add_bias_input_layernorm(int dtype, void* out, const void* input, const v
 
 int et_attention(int dtype, const void* q, const void* k, const void* v, long long token_stride,
                  long long head_stride, void* ctx, const int* cu_seqlens, int batch, int max_seq,
-                 int heads, int d, int use_simt, int* status_word, void* stream) {
-  if (!q || !k || !v || !ctx || !cu_seqlens || batch < 0 || heads <= 0 || d != 64 || max_seq < 0)
+                 int max_tokens, int heads, int d, int use_simt, int* status_word, void* stream) {
+  if (!q || !k || !v || !ctx || !cu_seqlens || batch < 0 || heads <= 0 || d != 64 || max_seq < 0 ||
+      max_tokens < 0)
     return ET_INVALID_ARGUMENT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == ET_FP16 && !use_simt)
     return to_status(launch_attention_tc(H_(q), H_(k), H_(v), token_stride, head_stride,
-                                         static_cast<__half*>(ctx), cu_seqlens, batch, max_seq, heads, d,
-                                         status_word, s));
+                                         static_cast<__half*>(ctx), cu_seqlens, batch, max_seq, max_tokens,
+                                         heads, d, status_word, s));
   return ET_DISPATCH(dtype,
                      launch_attention_simt<__half>(H_(q), H_(k), H_(v), token_stride, head_stride,
                                                    static_cast<__half*>(ctx), cu_seqlens, batch, max_seq, heads, d, s),

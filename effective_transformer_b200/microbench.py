@@ -120,7 +120,7 @@ def main() -> None:
                                                                             P(beta_h), P(tn), n_pos, h, 1e-6, st),
                                     "hbm", 3.0 * t * h * e),
         "attention": (lambda: lib.et_attention(dt, qkv.data_ptr(), qkv.data_ptr() + h * e, qkv.data_ptr() + 2 * h * e,
-                                               3 * h, 64, P(ctx), P(cu), b, s, heads, 64, simt, P(status), st),
+                                               3 * h, 64, P(ctx), P(cu), b, s, n_pos, heads, 64, simt, P(status), st),
                       "hbm", 4.0 * t * h * e),
         "gemm_qkv": (gemm("gemm_qkv", x_packed, bias3, 1), "tensor", 2.0 * t * h * 3 * h),
         "gemm_attn_out": (gemm("gemm_attn_out", x_packed, None, 0), "tensor", 2.0 * t * h * h),

@@ -282,12 +282,15 @@ int et_add_bias_input_layernorm(int dtype, void* out, const void* input, const v
 /* The attention block of the layer functor (batched QK^T, softmax_kernel,
  * batched P*V, transpose_rm_padding: tf_op/bert_transformer_op.cu.cc:158-191,
  * cuda/attention.cu:249-492) on the packed layout.  q/k/v are addressed as
- * base + token*token_stride + head*head_stride (elements); ctx is packed
- * [T, heads*d].  use_simt selects the CUDA-core kernel (always for fp32). */
+ * base + token*token_stride + head*head_stride (elements): either heads side
+ * by side inside a token row ([T, 3H] as the fused projection writes it) or
+ * one [max_tokens, d] block per head; ctx is packed [T, heads*d].  q/k/v/ctx
+ * hold max_tokens rows (rows past T are never needed, reads past max_tokens
+ * never happen).  use_simt selects the CUDA-core kernel (always for fp32). */
 int et_attention(int dtype, const void* q, const void* k, const void* v, long long token_stride,
                  long long head_stride, void* ctx, const int* cu_seqlens, int batch_size,
-                 int max_seq_len, int head_num, int size_per_head, int use_simt, int* status_word,
-                 void* stream);
+                 int max_seq_len, int max_tokens, int head_num, int size_per_head, int use_simt,
+                 int* status_word, void* stream);
 
 /* cublasGemmEx call sites of the layer functor
  * (tf_op/bert_transformer_op.cu.cc:110-141,200-209,215-225,229-240):

@@ -241,7 +241,8 @@ def _attention_case(dtype, lens, heads, use_simt, layout):
     ctx = torch.full((cap, h), 2.0, dtype=dtype, device="cuda")
     st = status_word()
     ok(lib().et_attention(DT[dtype], qp, kp, vp, tstride, hstride, iptr(ctx), iptr(dev(cu)), len(lens),
-                          int(lens.max()) if len(lens) else 0, heads, d, 1 if use_simt else 0, iptr(st), stream()))
+                          int(lens.max()) if len(lens) else 0, cap, heads, d, 1 if use_simt else 0, iptr(st),
+                          stream()))
     torch.cuda.synchronize()
     assert int(st[0]) == 0
     ref = O.packed_attention(q[:t].double().cpu(), k[:t].double().cpu(), v[:t].double().cpu(), cu, heads, d)
@@ -279,6 +280,6 @@ def test_attention_full_size_softmax_rows_sum_to_one():
     st = status_word()
     es = 2
     ok(lib().et_attention(_capi.ET_FP16, qkv.data_ptr(), qkv.data_ptr() + h * es, qkv.data_ptr() + 2 * h * es,
-                          3 * h, 64, iptr(ctx), iptr(dev(cu)), len(lens), 64, 12, 64, 0, iptr(st), stream()))
+                          3 * h, 64, iptr(ctx), iptr(dev(cu)), len(lens), 64, t, 12, 64, 0, iptr(st), stream()))
     torch.cuda.synchronize()
     assert float((ctx.float() - 1.0).abs().max()) < 2e-3
