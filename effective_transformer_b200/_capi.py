@@ -82,6 +82,9 @@ SIGNATURES = {
     "et_add_bias_gelu": (i32, [i32, vp, vp, vp, i32, i32, vp]),
     "et_add_bias_input_layernorm": (i32, [i32, vp, vp, vp, vp, vp, vp, i32, i32, C.c_float, vp]),
     "et_attention": (i32, [i32, vp, vp, vp, i64, i64, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp]),
+    "et_attention_plan_ints": (C.c_size_t, [i32, i32]),
+    "et_attention_plan": (i32, [vp, i32, i32, vp, vp]),
+    "et_attention_tiles": (i32, [vp, vp, vp, i64, i64, vp, vp, i32, i32, i32, i32, i32, vp, vp]),
     "et_gemm": (i32, [i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp]),
     "et_pack_weight": (i32, [i32, vp, vp, i32, i32, vp]),
 }

@@ -1,0 +1,464 @@
+// Self-attention on the packed, variable-length layout with the 5th-generation
+// tensor cores (fp16 in, fp32 scores/softmax/accumulation, fp16 out), for
+// sequences of up to 128 tokens.  Replaces the padded batched QK^T / softmax /
+// P*V / transpose_rm_padding sequence of the reference
+// (tf_op/bert_transformer_op.cu.cc:158-191, cuda/attention.cu:249-492).
+//
+// Whole sequences are packed greedily into tiles of at most 128 consecutive
+// token rows (attention_plan_kernel, once per batch).  One work item is a
+// (tile, head) pair:
+//   TMA        Q, K, V rows of the tile -> shared memory (128-byte swizzle)
+//   tcgen05    S = Q K^T, M = 128, N = rows rounded to 16, into TMEM
+//   softmax    one thread per query row reads its row from TMEM, keeps only
+//              the columns of its own sequence (block-diagonal mask), writes
+//              P (fp16) to shared memory in the K-major operand layout
+//   tcgen05    O = P V (V is the MN-major B operand), into TMEM
+//   epilogue   O / rowsum -> fp16 -> packed context [T, heads*64]
+// Keys of other sequences contribute exact zeros; padded positions do not
+// exist in this layout at all.  Four CTAs per SM overlap the phases of four
+// items.  Every mbarrier wait is bounded.
+#include "common.cuh"
+#include "ptx_sm100.cuh"
+
+#include <mutex>
+
+namespace etb {
+
+namespace {
+
+using namespace ptx;
+
+constexpr int kD = 64;
+constexpr int kTileRows = 128;
+constexpr int kBoxRows = 32;
+constexpr int kBoxBytes = kBoxRows * kD * 2;        // 4096
+constexpr int kTileBytes = kTileRows * kD * 2;      // 16384: 128 rows of 128 bytes
+constexpr int kThreads = 128;
+constexpr int kTmemCols = 128;   // S: columns [0,128); O takes columns [0,64) once the softmax has read S
+constexpr int kOCol = 0;
+constexpr int kCtasPerSm = 4;    // 4 x 128 TMEM columns, 4 x 48 KB shared memory
+// One {Q, K, V} buffer + barriers.  P (two 64-key atoms) takes the place of
+// the item's Q and K tiles, which are dead once the scores are in TMEM.  Four
+// CTAs per SM keep the phases of four items in flight.
+constexpr int kBufBytes = 3 * kTileBytes;
+constexpr int kSmemBytes = kBufBytes + 64;
+
+enum Site : int { kSiteLoad = 1, kSiteScores = 2, kSiteContext = 3, kSiteSmemAlign = 4 };
+
+__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+// kind::f16 instruction descriptor, fp32 accumulate, A K-major; B K-major or MN-major.
+__device__ __forceinline__ uint32_t idesc_f16(int m, int n, bool b_mn_major) {
+  return (1u << 4) | (b_mn_major ? (1u << 16) : 0u) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+// Layout of the plan in device memory (ints):
+//   [0] number of tiles   [4, 4+B) first token row of tile i   [4+B, 4+2B) rows of tile i
+//   [4+2B, 4+2B+cap) first token of the sequence that owns token t   [.., +cap) one past its last token
+//   [4+2B+2cap, +B+1) scratch of the planning kernel (first sequence of tile i)
+__host__ __device__ inline size_t plan_ints(int batch, int max_tokens) {
+  return 4 + 3 * static_cast<size_t>(batch) + 1 + 2 * static_cast<size_t>(max_tokens);
+}
+
+// One CTA: packs whole sequences greedily into tiles of <= 128 rows, then
+// labels every token with its sequence's token range.
+__global__ void attention_plan_kernel(const int* __restrict__ cu_seqlens, int batch, int max_tokens,
+                                      int* __restrict__ plan) {
+  int* tile_start = plan + 4;
+  int* tile_rows = plan + 4 + batch;
+  int* seq_lo = plan + 4 + 2 * batch;
+  int* seq_hi = seq_lo + max_tokens;
+  // Greedy packing = following a chain: a tile that starts with sequence b ends
+  // before next(b), the first sequence whose last token lies more than 128 rows
+  // behind the tile's first token.  next() is found for every b in parallel (a
+  // binary search over the sorted boundaries); only the walk along the chain,
+  // one step per tile, is sequential.
+  constexpr int kSharedSeqs = 8192;
+  __shared__ int s_next[kSharedSeqs];
+  int* next = batch <= kSharedSeqs ? s_next : seq_hi;   // larger batches: global scratch (slower walk)
+  const bool scratch_ok = batch <= kSharedSeqs || batch <= max_tokens;
+  auto cu = [&](int b) { return min(cu_seqlens[b], max_tokens); };
+  if (scratch_ok) {
+    for (int b = threadIdx.x; b < batch; b += blockDim.x) {
+      const int limit = cu(b) + kTileRows;
+      int lo_b = b, hi_b = batch;  // first j in [b, batch] with cu(j + 1) > limit (batch if none)
+      while (lo_b < hi_b) {
+        const int mid = (lo_b + hi_b) >> 1;
+        if (cu(mid + 1) > limit) hi_b = mid; else lo_b = mid + 1;
+      }
+      next[b] = lo_b > b ? lo_b : b + 1;  // a sequence longer than a tile still advances
+    }
+  }
+  __syncthreads();
+  int* tile_seq = seq_hi + max_tokens;   // first sequence of every tile, then one end marker
+  __shared__ int s_nt;
+  if (threadIdx.x == 0) {
+    // the sequential part touches shared memory only (plus fire-and-forget stores)
+    int nt = 0;
+    for (int b = 0; b < batch;) {
+      int e;
+      if (scratch_ok) {
+        e = next[b];
+      } else {
+        const int limit = cu(b) + kTileRows;
+        e = b;
+        while (e < batch && cu(e + 1) <= limit) ++e;
+        if (e == b) e = b + 1;
+      }
+      tile_seq[nt++] = b;
+      b = e;
+    }
+    tile_seq[nt] = batch;
+    s_nt = nt;
+  }
+  __syncthreads();
+  {
+    int nt = s_nt;
+    for (int i = threadIdx.x; i < nt; i += blockDim.x) {
+      const int first = cu(tile_seq[i]);
+      int rows = cu(tile_seq[i + 1]) - first;
+      rows = rows > kTileRows ? kTileRows : rows;  // longer sequences are not handled by this kernel
+      tile_start[i] = first;
+      tile_rows[i] = rows;
+    }
+    // only the last tile can be empty (nothing but empty sequences at the end of the batch)
+    if (threadIdx.x == 0) {
+      if (nt > 0 && cu(batch) - cu(tile_seq[nt - 1]) <= 0) --nt;
+      plan[0] = nt;
+    }
+  }
+  __syncthreads();  // next[] is dead: seq_hi may be written
+  for (int b = threadIdx.x; b < batch; b += blockDim.x) {
+    int lo = cu_seqlens[b], hi = cu_seqlens[b + 1];
+    hi = hi > max_tokens ? max_tokens : hi;
+    for (int t = lo; t < hi; ++t) {
+      seq_lo[t] = lo;
+      seq_hi[t] = hi;
+    }
+  }
+}
+
+struct Coords {
+  int x_per_head, y_per_head;  // TMA coordinates: x = head * x_per_head, y = head * y_per_head + token
+};
+
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
+attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                         const __grid_constant__ CUtensorMap tmap_v, Coords co, __half* __restrict__ ctx,
+                         const int* __restrict__ plan, int batch, int max_tokens, int heads,
+                         float scale_log2e, int* status_word) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t base = smem_u32(smem_raw);
+  if ((base & 1023u) != 0u) {
+    if (threadIdx.x == 0) report_timeout(status_word, kKernelAttnTc, kSiteSmemAlign);
+    return;
+  }
+  const int num_tiles = plan[0];
+  const int total = num_tiles * heads;
+  if (static_cast<int>(blockIdx.x) >= total) return;
+  const int* tile_start = plan + 4;
+  const int* tile_rows = plan + 4 + batch;
+  const int* seq_lo = plan + 4 + 2 * batch;
+  const int* seq_hi = seq_lo + max_tokens;
+
+  const uint32_t bar_load0 = base + kBufBytes, bar_mma = bar_load0 + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + kBufBytes + 24);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + kBufBytes + 32);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = threadIdx.x;  // this thread's query row inside the tile = its TMEM lane
+  const int hidden = heads * kD;
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar_load0, 1);
+    mbar_init(bar_load0 + 8, 1);
+    mbar_init(bar_mma, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    fence_proxy_async_smem();
+    prefetch_tensormap(&tmap_q);
+    prefetch_tensormap(&tmap_k);
+    prefetch_tensormap(&tmap_v);
+  }
+  if (warp == 0) {
+    __syncwarp();
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+
+  uint32_t mma_phase = 0;
+  bool ok = true;
+  // Thread 0: the Q, K, V rows of one item -> buffer `b`, completion on its barrier.
+  auto issue = [&](int item_idx, int b) {
+    const int tile_i = item_idx / heads, head_i = item_idx - tile_i * heads;
+    int rows = tile_rows[tile_i];
+    rows = rows < 1 ? 1 : (rows > kTileRows ? kTileRows : rows);
+    const int boxes = (rows + kBoxRows - 1) / kBoxRows;
+    const uint32_t bar = bar_load0 + 8u * b;
+    const uint32_t dst = base + b * kBufBytes;
+    mbar_arrive_expect_tx(bar, static_cast<uint32_t>(3 * boxes * kBoxBytes));
+    const int x = head_i * co.x_per_head, y = head_i * co.y_per_head + tile_start[tile_i];
+    for (int j = 0; j < boxes; ++j) {
+      tma_load_2d(dst + j * kBoxBytes, &tmap_q, x, y + j * kBoxRows, bar);
+      tma_load_2d(dst + kTileBytes + j * kBoxBytes, &tmap_k, x, y + j * kBoxRows, bar);
+      tma_load_2d(dst + 2 * kTileBytes + j * kBoxBytes, &tmap_v, x, y + j * kBoxRows, bar);
+    }
+  };
+  if (threadIdx.x == 0) issue(blockIdx.x, 0);
+  int it_n = 0;
+  auto wait_all = [&](uint32_t bar, uint32_t phase, int site) {
+    bool got = mbar_wait(bar, phase, abort_flag);
+    if (!got) {
+      *abort_flag = 1;
+      report_timeout(status_word, kKernelAttnTc, site);
+    }
+    return __syncthreads_and(got) != 0;
+  };
+
+  for (int item = blockIdx.x; item < total && ok; item += gridDim.x, ++it_n) {
+    const int tile = item / heads, head = item - tile * heads;
+    const int t0 = tile_start[tile];
+    int n = tile_rows[tile];
+    n = n < 1 ? 1 : (n > kTileRows ? kTileRows : n);
+    const int n16 = (n + 15) & ~15;
+    const uint32_t sq = base, sk = sq + kTileBytes, sv = sk + kTileBytes;
+    const uint32_t sp = sq;  // P overwrites Q and K after the scores are computed
+    const uint32_t bar_load = bar_load0;
+    const uint32_t load_phase = static_cast<uint32_t>(it_n & 1);
+
+    // this row's sequence, relative to the tile
+    int lo = 0, hi = 0;
+    if (r < n) {
+      lo = seq_lo[t0 + r] - t0;
+      hi = seq_hi[t0 + r] - t0;
+      lo = lo < 0 ? 0 : lo;
+      hi = hi > n ? n : hi;
+    }
+    ok = wait_all(bar_load, load_phase, kSiteLoad);
+    if (!ok) break;
+
+    // V rows [n, n16) may belong to the next tile or be stale: P is zero there,
+    // so make V finite there too.
+    for (int idx = threadIdx.x; idx < (n16 - n) * 8; idx += kThreads)
+      st_shared_v4(sv + (n + (idx >> 3)) * 128 + ((idx & 7) << 4), 0u, 0u, 0u, 0u);
+    fence_proxy_async_smem();
+    tc_fence_before();
+    __syncthreads();
+
+    // ---- S = Q K^T ----
+    if (threadIdx.x == 0) {
+      tc_fence_after();
+      const uint32_t idesc = idesc_f16(kTileRows, n16, false);
+      const uint64_t qd = make_kmajor_sw128_desc(sq), kd = make_kmajor_sw128_desc(sk);
+#pragma unroll
+      for (int k = 0; k < kD / 16; ++k) umma_f16_ss(tmem_base, qd + 2u * k, kd + 2u * k, idesc, k != 0 ? 1u : 0u);
+      umma_commit(bar_mma);
+    }
+    ok = wait_all(bar_mma, mma_phase, kSiteScores);
+    mma_phase ^= 1u;
+    if (!ok) break;
+    tc_fence_after();
+
+    // ---- softmax over the row's own sequence; P -> shared memory ----
+    const bool warp_has_rows = warp * 32 < n;
+    float inv_l = 1.0f;
+    if (warp_has_rows) {
+      // columns any row of this warp needs, in 16-column chunks (uniform in the warp)
+      int ulo = (r < n) ? lo : kTileRows, uhi = (r < n) ? hi : 0;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        ulo = min(ulo, __shfl_xor_sync(0xffffffffu, ulo, o));
+        uhi = max(uhi, __shfl_xor_sync(0xffffffffu, uhi, o));
+      }
+      ulo &= ~31;   // 32-column loads stay inside the 128 allocated columns
+      uhi = (uhi + 15) & ~15;
+      // (32 columns per TMEM load; a load may run up to 16 columns past n16, into
+      // allocated columns whose values the range test discards)
+      float m = -INFINITY;
+      for (int c0 = ulo; c0 < uhi; c0 += 32) {
+        uint32_t s32[32];
+        tmem_ld_32x32b_x32(t_lane + c0, s32);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int c = c0 + e;
+          if (c >= lo && c < hi) m = fmaxf(m, __uint_as_float(s32[e]));
+        }
+      }
+      const float ms = (r < n && hi > lo) ? -m * scale_log2e : 0.f;
+      float l = 0.f;
+      const uint32_t prow = sp + r * 128;
+      const uint32_t swz = static_cast<uint32_t>(r & 7);
+      for (int c0 = 0; c0 < n16; c0 += 32) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) pk[e] = 0u;
+        if (c0 < uhi && c0 + 32 > ulo) {   // uniform in the warp
+          uint32_t s32[32];
+          tmem_ld_32x32b_x32(t_lane + c0, s32);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            float p2[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int c = c0 + 2 * e + u;
+              const float pe = ex2_approx(fmaf(__uint_as_float(s32[2 * e + u]), scale_log2e, ms));
+              p2[u] = (c >= lo && c < hi) ? pe : 0.f;
+              l += p2[u];
+            }
+            pk[e] = pack_half2(p2[0], p2[1]);
+          }
+        }
+        // 32 keys = four 16-byte chunks of this row inside the 64-key atom
+        const uint32_t atom = prow + static_cast<uint32_t>(c0 >> 6) * kTileBytes;
+        const uint32_t ch = static_cast<uint32_t>((c0 & 63) >> 3);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          st_shared_v4(atom + (((ch + j) ^ swz) << 4), pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+      }
+      inv_l = (l > 0.f) ? 1.0f / l : 0.f;
+    }
+    fence_proxy_async_smem();
+    tc_fence_before();
+    __syncthreads();
+
+    // ---- O = P V ----
+    if (threadIdx.x == 0) {
+      tc_fence_after();
+      const uint32_t idesc = idesc_f16(kTileRows, kD, true);
+      for (int ks = 0; ks < n16 / 16; ++ks) {
+        const uint64_t pd = make_kmajor_sw128_desc(sp + (ks >> 2) * kTileBytes + (ks & 3) * 32);
+        const uint64_t vd = make_kmajor_sw128_desc(sv + ks * 2048);  // MN-major: 16 keys = two 8-row groups
+        umma_f16_ss(tmem_base + kOCol, pd, vd, idesc, ks != 0 ? 1u : 0u);
+      }
+      umma_commit(bar_mma);
+    }
+    ok = wait_all(bar_mma, mma_phase, kSiteContext);
+    mma_phase ^= 1u;
+    if (!ok) break;
+    tc_fence_after();
+    // Q, K, V and P are dead: the next item's rows stream in under the epilogue
+    if (threadIdx.x == 0 && item + static_cast<int>(gridDim.x) < total) {
+      fence_proxy_async_smem();
+      issue(item + gridDim.x, 0);
+    }
+
+    // ---- epilogue: O / l -> fp16 -> packed context ----
+    if (warp_has_rows) {
+      uint32_t ov[64];
+      tmem_ld_32x32b_x32(t_lane + kOCol, ov);
+      tmem_ld_32x32b_x32(t_lane + kOCol + 32, ov + 32);
+      tmem_ld_wait();
+      if (r < n) {
+        __half* op = ctx + static_cast<size_t>(t0 + r) * hidden + head * kD;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint32_t w[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e)
+            w[e] = pack_half2(__uint_as_float(ov[q4 * 16 + 2 * e]) * inv_l,
+                              __uint_as_float(ov[q4 * 16 + 2 * e + 1]) * inv_l);
+          asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(op + q4 * 16), "r"(w[0]),
+                       "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+                       : "memory");
+        }
+      }
+    }
+    tc_fence_before();
+    __syncthreads();  // TMEM and the tiles are reused by the next item
+    if (threadIdx.x == 0) fence_proxy_async_smem();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace
+
+size_t attention_plan_ints(int batch, int max_tokens) { return plan_ints(batch, max_tokens); }
+
+cudaError_t launch_attention_plan(const int* cu_seqlens, int batch, int max_tokens, int* plan,
+                                  cudaStream_t stream) {
+  if (batch <= 0) return cudaSuccess;
+  attention_plan_kernel<<<1, 1024, 0, stream>>>(cu_seqlens, batch, max_tokens, plan);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_attention_tcgen05(const __half* q, const __half* k, const __half* v,
+                                     long long token_stride, long long head_stride, __half* ctx,
+                                     const int* plan, int batch, int max_tokens, int heads, int d,
+                                     int* status_word, cudaStream_t stream) {
+  if (batch <= 0 || heads <= 0 || max_tokens <= 0) return cudaSuccess;
+  if (d != kD || token_stride < kD || (token_stride % 8) != 0 || (head_stride % 8) != 0 || head_stride < 0)
+    return cudaErrorInvalidValue;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+       reinterpret_cast<uintptr_t>(ctx)) & 31u)
+    return cudaErrorMisalignedAddress;
+  Coords co;
+  uint64_t cols, rows;
+  if (static_cast<long long>(heads - 1) * head_stride + kD <= token_stride) {
+    co = {static_cast<int>(head_stride), 0};
+    cols = static_cast<uint64_t>(heads - 1) * head_stride + kD;
+    rows = static_cast<uint64_t>(max_tokens);
+  } else if (token_stride == kD && head_stride % token_stride == 0 && head_stride / token_stride >= max_tokens) {
+    co = {0, static_cast<int>(head_stride / token_stride)};
+    cols = kD;
+    rows = static_cast<uint64_t>(heads - 1) * (head_stride / token_stride) + max_tokens;
+  } else {
+    return cudaErrorInvalidValue;
+  }
+  CUtensorMap tq, tk, tv;
+  if (!encode_2d_fp16_sw128(&tq, q, rows, cols, static_cast<uint64_t>(token_stride), kBoxRows, kD) ||
+      !encode_2d_fp16_sw128(&tk, k, rows, cols, static_cast<uint64_t>(token_stride), kBoxRows, kD) ||
+      !encode_2d_fp16_sw128(&tv, v, rows, cols, static_cast<uint64_t>(token_stride), kBoxRows, kD))
+    return cudaErrorInvalidValue;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    kSmemBytes);
+  });
+  if (attr_err != cudaSuccess) return attr_err;
+  const float scale_log2e = (1.0f / sqrtf(static_cast<float>(d))) * 1.4426950408889634f;
+  // every tile holds at least one sequence, so batch * heads bounds the item count
+  long long grid = static_cast<long long>(sm_count()) * kCtasPerSm;
+  const long long max_items = static_cast<long long>(batch) * heads;
+  if (grid > max_items) grid = max_items;
+  attention_tcgen05_kernel<<<static_cast<int>(grid), kThreads, kSmemBytes, stream>>>(
+      tq, tk, tv, co, ctx, plan, batch, max_tokens, heads, scale_log2e, status_word);
+  return cudaGetLastError();
+}
+
+}  // namespace etb

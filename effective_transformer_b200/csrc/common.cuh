@@ -181,6 +181,15 @@ cudaError_t launch_attention_tc(const __half* q, const __half* k, const __half* 
                                 long long token_stride, long long head_stride, __half* ctx,
                                 const int* cu_seqlens, int batch, int max_seq, int max_tokens, int heads,
                                 int d, int* status_word, cudaStream_t stream);
+// tcgen05 attention for sequences of at most 128 tokens: a plan (sequences
+// packed into 128-row tiles) made once per batch, then one launch per layer.
+size_t attention_plan_ints(int batch, int max_tokens);
+cudaError_t launch_attention_plan(const int* cu_seqlens, int batch, int max_tokens, int* plan,
+                                  cudaStream_t stream);
+cudaError_t launch_attention_tcgen05(const __half* q, const __half* k, const __half* v,
+                                     long long token_stride, long long head_stride, __half* ctx,
+                                     const int* plan, int batch, int max_tokens, int heads, int d,
+                                     int* status_word, cudaStream_t stream);
 // tcgen05 GEMM, fp16 in / fp32 accumulate / fp16 out.  w_packed is [N,K].
 cudaError_t launch_gemm_tcgen05(const __half* a, const __half* w_packed, const __half* bias,
                                 __half* c, const int* m_ptr, int max_m, int n, int k, int epilogue,

@@ -60,6 +60,7 @@ struct Workspace {
   int* seq_len = nullptr;     // [B]
   int* cu_seqlens = nullptr;  // [B+1]
   int* lens_scratch = nullptr;
+  int* attn_plan = nullptr;   // tile plan of the tcgen05 attention (made once per batch)
   int* valid_word_num = nullptr;
   int* status = nullptr;
   std::vector<void*> allocations;
@@ -239,7 +240,14 @@ int run_layer(et_handle_t h, const LayerWeights& lw, const T* x_in, T* x_out, co
   // Q,K,V projections + bias in one GEMM -> [T, 3H]
   ET_LAUNCH(h, ET_PROF_GEMM_QKV, 1, s, gemm(x_in, lw.wqkv, lw.wqkv_t, lw.bqkv, qkv, 3 * hid, hid, kEpiBias));
   // attention straight from the [T, 3H] buffer to packed context [T, H]
-  if (tc)
+  if (tc && seq <= 128)
+    ET_LAUNCH(h, ET_PROF_ATTENTION, 1, s,
+              launch_attention_tcgen05(reinterpret_cast<const __half*>(qkv),
+                                       reinterpret_cast<const __half*>(qkv) + hid,
+                                       reinterpret_cast<const __half*>(qkv) + 2 * hid, 3LL * hid, d,
+                                       reinterpret_cast<__half*>(ctx), ws.attn_plan, batch, max_m, heads, d,
+                                       ws.status, s));
+  else if (tc)
     ET_LAUNCH(h, ET_PROF_ATTENTION, 1, s, launch_attention_tc(reinterpret_cast<const __half*>(qkv),
                                    reinterpret_cast<const __half*>(qkv) + hid,
                                    reinterpret_cast<const __half*>(qkv) + 2 * hid, 3LL * hid, d,
@@ -329,6 +337,9 @@ int forward_impl(et_handle_t h, const void* from_tensor, const int* mask, void* 
   rc = input_impl(h, &ip);
   if (rc != ET_OK) return rc;
   const int max_m = batch * seq;
+  if (h->cfg.dtype == ET_FP16 && !h->use_simt && seq <= 128 && max_m > 0)
+    ET_LAUNCH(h, ET_PROF_PADDING_OFFSETS, 1, s,
+              launch_attention_plan(ws.cu_seqlens, batch, max_m, ws.attn_plan, s));
   for (int l = 0; l < h->cfg.num_layers; ++l) {
     if (h->cfg.dtype == ET_FP16)
       rc = run_layer<__half>(h, h->layers[l], static_cast<const __half*>(ws.x), static_cast<__half*>(ws.x),
@@ -433,6 +444,7 @@ int et_create(const et_config_t* config, et_handle_t* out_handle) {
       {reinterpret_cast<void**>(&ws.seq_len), static_cast<size_t>(c.max_batch_size) * 4},
       {reinterpret_cast<void**>(&ws.cu_seqlens), (static_cast<size_t>(c.max_batch_size) + 1) * 4},
       {reinterpret_cast<void**>(&ws.lens_scratch), static_cast<size_t>(c.max_batch_size) * 4},
+      {reinterpret_cast<void**>(&ws.attn_plan), attention_plan_ints(c.max_batch_size, static_cast<int>(cap)) * 4},
       {reinterpret_cast<void**>(&ws.valid_word_num), 4}, {reinterpret_cast<void**>(&ws.status), 4}};
   for (auto& b : bufs)
     if ((rc = ws_alloc(h, b.p, b.bytes)) != ET_OK) return bail(rc);
@@ -571,6 +583,9 @@ int et_layer(et_handle_t h, int layer, const et_encoder_param_t* p, const et_tra
   const int batch = tp->batch_size, seq = tp->from_seq_len, max_m = batch * seq;
   ET_LAUNCH(h, ET_PROF_PADDING_OFFSETS, 1, s, launch_seq_bounds_from_batch_idx(p->batch_idx, p->valid_word_num, batch, max_m,
                                               h->ws.cu_seqlens, s));
+  if (h->cfg.dtype == ET_FP16 && !h->use_simt && seq <= 128 && max_m > 0)
+    ET_LAUNCH(h, ET_PROF_PADDING_OFFSETS, 1, s,
+              launch_attention_plan(h->ws.cu_seqlens, batch, max_m, h->ws.attn_plan, s));
   if (h->cfg.dtype == ET_FP16)
     return run_layer<__half>(h, h->layers[layer], static_cast<const __half*>(p->from_tensor),
                              static_cast<__half*>(p->transformer_out), p->valid_word_num, max_m,
@@ -791,6 +806,28 @@ int et_attention(int dtype, const void* q, const void* k, const void* v, long lo
                                                    static_cast<__half*>(ctx), cu_seqlens, batch, max_seq, heads, d, s),
                      launch_attention_simt<float>(F_(q), F_(k), F_(v), token_stride, head_stride,
                                                   static_cast<float*>(ctx), cu_seqlens, batch, max_seq, heads, d, s));
+}
+
+size_t et_attention_plan_ints(int batch_size, int max_tokens) {
+  if (batch_size < 0 || max_tokens < 0) return 0;
+  return attention_plan_ints(batch_size, max_tokens);
+}
+
+int et_attention_plan(const int* cu_seqlens, int batch_size, int max_tokens, int* plan, void* stream) {
+  if (!cu_seqlens || !plan || batch_size < 0 || max_tokens < 0) return ET_INVALID_ARGUMENT;
+  return to_status(launch_attention_plan(cu_seqlens, batch_size, max_tokens, plan,
+                                         static_cast<cudaStream_t>(stream)));
+}
+
+int et_attention_tiles(const void* q, const void* k, const void* v, long long token_stride,
+                       long long head_stride, void* ctx, const int* plan, int batch_size, int max_seq_len,
+                       int max_tokens, int head_num, int size_per_head, int* status_word, void* stream) {
+  if (!q || !k || !v || !ctx || !plan || batch_size < 0 || head_num <= 0 || size_per_head != 64 ||
+      max_seq_len < 0 || max_seq_len > 128 || max_tokens < 0)
+    return ET_INVALID_ARGUMENT;
+  return to_status(launch_attention_tcgen05(H_(q), H_(k), H_(v), token_stride, head_stride,
+                                            static_cast<__half*>(ctx), plan, batch_size, max_tokens, head_num,
+                                            size_per_head, status_word, static_cast<cudaStream_t>(stream)));
 }
 
 int et_gemm(int dtype, const void* a, const void* w, const void* w_packed, const void* bias, void* c,

@@ -104,6 +104,9 @@ def main() -> None:
         return lambda: lib.et_gemm(dt, P(a), P(w), P(wp), P(bias), P(gemm_out), P(tn), n_pos, nn, kk, epi, simt,
                                    P(status), st)
 
+    plan = torch.zeros(int(lib.et_attention_plan_ints(b, n_pos)), **i32)
+    if fp16 and s <= 128:
+        assert lib.et_attention_plan(P(cu), b, n_pos, P(plan), st) == 0
     sum_len2 = float((lens.astype(np.int64) ** 2).sum())
     # name -> (callable, bound, algorithmic units per launch)
     kernels = {
@@ -122,12 +125,19 @@ def main() -> None:
         "attention": (lambda: lib.et_attention(dt, qkv.data_ptr(), qkv.data_ptr() + h * e, qkv.data_ptr() + 2 * h * e,
                                                3 * h, 64, P(ctx), P(cu), b, s, n_pos, heads, 64, simt, P(status), st),
                       "hbm", 4.0 * t * h * e),
+        "attention_tiles": (lambda: lib.et_attention_tiles(qkv.data_ptr(), qkv.data_ptr() + h * e,
+                                                           qkv.data_ptr() + 2 * h * e, 3 * h, 64, P(ctx), P(plan), b, s,
+                                                           n_pos, heads, 64, P(status), st),
+                            "hbm", 4.0 * t * h * e),
+        "attention_plan": (lambda: lib.et_attention_plan(P(cu), b, n_pos, P(plan), st), "hbm", 4.0 * b + 8.0 * t),
         "gemm_qkv": (gemm("gemm_qkv", x_packed, bias3, 1), "tensor", 2.0 * t * h * 3 * h),
         "gemm_attn_out": (gemm("gemm_attn_out", x_packed, None, 0), "tensor", 2.0 * t * h * h),
         "gemm_ffn1": (gemm("gemm_ffn1", x_packed, bias_f, 2), "tensor", 2.0 * t * h * f),
         "gemm_ffn2": (gemm("gemm_ffn2", ffn, None, 0), "tensor", 2.0 * t * h * f),
     }
-    names = list(kernels) if args.kernel == "all" else [args.kernel]
+    if not (fp16 and s <= 128):
+        kernels.pop("attention_tiles"), kernels.pop("attention_plan")
+    names = list(kernels) if args.kernel == "all" else args.kernel.split(",")
     pk, src = peaks()
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
     for name in names:

@@ -292,6 +292,19 @@ int et_attention(int dtype, const void* q, const void* k, const void* v, long lo
                  int max_seq_len, int max_tokens, int head_num, int size_per_head, int use_simt,
                  int* status_word, void* stream);
 
+/* The same attention block on the tcgen05 tensor cores, fp16, for batches whose
+ * sequences have at most 128 tokens (max_seq_len <= 128).  A plan packs whole
+ * sequences into tiles of at most 128 token rows; it depends only on
+ * cu_seqlens, so it is made once per batch (et_attention_plan) and reused by
+ * every layer (et_attention_tiles).  `plan` holds
+ * et_attention_plan_ints(batch_size, max_tokens) ints of device memory.
+ * q/k/v/ctx as for et_attention, additionally 32-byte aligned. */
+size_t et_attention_plan_ints(int batch_size, int max_tokens);
+int et_attention_plan(const int* cu_seqlens, int batch_size, int max_tokens, int* plan, void* stream);
+int et_attention_tiles(const void* q, const void* k, const void* v, long long token_stride,
+                       long long head_stride, void* ctx, const int* plan, int batch_size, int max_seq_len,
+                       int max_tokens, int head_num, int size_per_head, int* status_word, void* stream);
+
 /* cublasGemmEx call sites of the layer functor
  * (tf_op/bert_transformer_op.cu.cc:110-141,200-209,215-225,229-240):
  * C[M,N] = epilogue(A[M,K] * W[K,N] (+ bias)), W row-major [in,out] as the

@@ -267,6 +267,65 @@ def test_attention_simt(dtype, lens):
     _attention_case(dtype, lens, 3, use_simt=True, layout="qkv")
 
 
+def _attention_tiles_case(lens, heads, layout, seed=0):
+    """et_attention_plan + et_attention_tiles (tcgen05, sequences of <= 128 tokens)."""
+    d = 64
+    h = heads * d
+    lens = np.asarray(lens, np.int32)
+    cu = np.zeros(len(lens) + 1, np.int32)
+    cu[1:] = np.cumsum(lens)
+    t = int(cu[-1])
+    cap = max(t, 1) + 5          # a few stale rows behind the last token
+    rng = np.random.RandomState(int(lens.sum()) + heads + seed)
+    if layout == "qkv":
+        qkv = dev(rng.randn(cap, 3 * h).astype(np.float32), torch.float16)
+        qkv[t:] = float("nan")   # stale rows must never reach a valid output
+        q, k, v = qkv[:, :h], qkv[:, h:2 * h], qkv[:, 2 * h:]
+        qp, kp, vp = qkv.data_ptr(), qkv.data_ptr() + h * 2, qkv.data_ptr() + 2 * h * 2
+        tstride, hstride = 3 * h, d
+    else:
+        buf = dev(rng.randn(3, heads, cap, d).astype(np.float32), torch.float16)
+        buf[:, :, t:] = float("nan")
+        q, k, v = [buf[i].permute(1, 0, 2).reshape(cap, h) for i in range(3)]
+        qp, kp, vp = [buf.data_ptr() + i * heads * cap * d * 2 for i in range(3)]
+        tstride, hstride = d, cap * d
+    ctx = torch.full((cap, h), 2.0, dtype=torch.float16, device="cuda")
+    st = status_word()
+    cu_d = dev(cu)
+    plan = torch.zeros(int(lib().et_attention_plan_ints(len(lens), cap)), dtype=torch.int32, device="cuda")
+    ok(lib().et_attention_plan(iptr(cu_d), len(lens), cap, iptr(plan), stream()))
+    ok(lib().et_attention_tiles(qp, kp, vp, tstride, hstride, iptr(ctx), iptr(plan), len(lens),
+                                int(lens.max()) if len(lens) else 0, cap, heads, d, iptr(st), stream()))
+    torch.cuda.synchronize()
+    assert int(st[0]) == 0, f"device-side wait expired: status 0x{int(st[0]):x}"
+    # the plan: whole sequences, at most 128 rows per tile, every token covered once
+    pl = plan.cpu().numpy()
+    nt, b = int(pl[0]), len(lens)
+    starts, rows = pl[4:4 + nt], pl[4 + b:4 + b + nt]
+    assert np.all(rows >= 1) and np.all(rows <= 128) and int(rows.sum()) == t
+    assert np.all(np.isin(starts, cu)) and np.all(np.isin(starts + rows, cu))
+    ref = O.packed_attention(q[:t].double().cpu(), k[:t].double().cpu(), v[:t].double().cpu(), cu, heads, d)
+    torch.testing.assert_close(ctx[:t].double().cpu(), ref, rtol=3e-3, atol=3e-3)
+    assert torch.all(ctx[t:] == 2.0)
+
+
+TILE_LEN_CASES = [[1], [5, 1, 16, 0, 33], [64] * 3, [20, 23, 29, 8, 11, 11, 15, 17], [128, 1, 100, 127, 65, 64, 63],
+                  [128] * 4, [1] * 300, [17] * 40 + [0] * 3 + [111]]
+
+
+@pytest.mark.parametrize("lens", TILE_LEN_CASES)
+@pytest.mark.parametrize("layout", ["qkv", "headmajor"])
+def test_attention_tcgen05_tiles(lens, layout):
+    _attention_tiles_case(lens, 2, layout)
+
+
+def test_attention_tcgen05_tiles_benchmark_shapes():
+    for cfg, heads in ((1, 12), (4, 16)):
+        spec = W.WORKLOADS[cfg]
+        lens = W.draw_lengths(spec, np.random.RandomState(spec.seed))[:400]
+        _attention_tiles_case(lens, heads, "qkv", seed=cfg)
+
+
 def test_attention_full_size_softmax_rows_sum_to_one():
     """cfg2 shape (B=1000, 12 heads): with V = 1 every context element must be 1
     (each probability row sums to one over the sequence's own keys only)."""

@@ -219,6 +219,8 @@ def test_cfg2_full_size_properties():
     perm = np.random.RandomState(0).permutation(spec.batch)
     wl_p = W.Workload(spec, wl.lengths[perm], wl.mask[perm], wl.from_tensor[perm], wl.weights)
     y_p = run_forward(eng, wl_p)
+    # (a sequence's tile mates change with the order, so the fp32 summation order inside the
+    # attention MMAs changes: equal up to a few fp16 roundings after 12 layers, not bit for bit)
     d = (y_p.float() - y[torch.from_numpy(perm).cuda()].float()).abs()
-    assert float(d.max()) <= 4e-3
+    assert float(d.max()) <= FP16_MAX_ABS and float(d.mean()) <= FP16_MEAN_ABS
     eng.close()
