@@ -7,6 +7,7 @@
 #include "../../include/et_b200.h"
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <string>
@@ -97,7 +98,13 @@ struct et_handle_s {
   std::vector<LayerWeights> layers;
   Workspace ws;
   cudaStream_t own_stream = nullptr;
-  int* host_pinned = nullptr;  // [2]: valid_word_num, status
+  // host-buffer entry: copies run on their own streams so that the upload of
+  // chunk i+1 and the download of chunk i-1 overlap the computation of chunk i
+  static constexpr int kMaxChunks = 8;
+  cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;
+  cudaEvent_t in_done[kMaxChunks] = {}, comp_done[kMaxChunks] = {};
+  int host_chunks = 2;
+  int* host_pinned = nullptr;  // [2 + kMaxChunks]: valid_word_num, status, per-chunk token counts
   std::string last_error;
 };
 
@@ -452,7 +459,19 @@ int et_create(const et_config_t* config, et_handle_t* out_handle) {
     return bail(cuda_fail(h, cudaGetLastError(), "cudaMemset"));
   if (cudaStreamCreateWithFlags(&h->own_stream, cudaStreamNonBlocking) != cudaSuccess)
     return bail(cuda_fail(h, cudaGetLastError(), "cudaStreamCreate"));
-  if (cudaMallocHost(reinterpret_cast<void**>(&h->host_pinned), 2 * sizeof(int)) != cudaSuccess)
+  if (cudaStreamCreateWithFlags(&h->h2d_stream, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaStreamCreateWithFlags(&h->d2h_stream, cudaStreamNonBlocking) != cudaSuccess)
+    return bail(cuda_fail(h, cudaGetLastError(), "cudaStreamCreate"));
+  for (int i = 0; i < et_handle_s::kMaxChunks; ++i)
+    if (cudaEventCreateWithFlags(&h->in_done[i], cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&h->comp_done[i], cudaEventDisableTiming) != cudaSuccess)
+      return bail(cuda_fail(h, cudaGetLastError(), "cudaEventCreate"));
+  if (const char* e = getenv("ETB_HOST_CHUNKS")) {
+    const int n = atoi(e);
+    if (n >= 1 && n <= et_handle_s::kMaxChunks) h->host_chunks = n;
+  }
+  if (cudaMallocHost(reinterpret_cast<void**>(&h->host_pinned),
+                     (2 + et_handle_s::kMaxChunks) * sizeof(int)) != cudaSuccess)
     return bail(cuda_fail(h, cudaGetLastError(), "cudaMallocHost"));
   *out_handle = h;
   return ET_OK;
@@ -469,7 +488,13 @@ int et_destroy(et_handle_t h) {
     cudaEventDestroy(sp.b);
   }
   for (cudaEvent_t e : h->prof.free_events) cudaEventDestroy(e);
+  for (int i = 0; i < et_handle_s::kMaxChunks; ++i) {
+    if (h->in_done[i]) cudaEventDestroy(h->in_done[i]);
+    if (h->comp_done[i]) cudaEventDestroy(h->comp_done[i]);
+  }
   if (h->own_stream) cudaStreamDestroy(h->own_stream);
+  if (h->h2d_stream) cudaStreamDestroy(h->h2d_stream);
+  if (h->d2h_stream) cudaStreamDestroy(h->d2h_stream);
   if (h->host_pinned) cudaFreeHost(h->host_pinned);
   delete h;
   return ET_OK;
@@ -615,19 +640,51 @@ int et_forward_host(et_handle_t h, const void* from_host, const int* mask_host, 
   DeviceGuard guard(h->cfg.device);
   Workspace& ws = h->ws;
   cudaStream_t s = h->own_stream;
-  const size_t rows = static_cast<size_t>(batch_size) * seq_len;
-  const size_t bytes = rows * h->hidden * h->esize;
-  if (rows > 0) {
-    ET_CUDA(h, cudaMemcpyAsync(ws.stage_in, from_host, bytes, cudaMemcpyHostToDevice, s));
-    ET_CUDA(h, cudaMemcpyAsync(ws.stage_mask, mask_host, rows * 4, cudaMemcpyHostToDevice, s));
+  // The batch is cut into chunks of whole sequences (they are independent):
+  // all uploads are queued on the upload stream at once, chunk i is computed
+  // when its upload has landed, and its result goes back on the download
+  // stream while chunk i+1 is being computed.
+  const size_t seq_bytes = static_cast<size_t>(seq_len) * h->hidden * h->esize;
+  int chunks = h->host_chunks;
+  if (static_cast<size_t>(batch_size) * seq_bytes < (8u << 20)) chunks = 1;  // too small to be worth it
+  if (chunks > batch_size) chunks = batch_size > 0 ? batch_size : 1;
+  const int per = (batch_size + chunks - 1) / chunks;
+  int nchunks = 0;
+  for (int b0 = 0; b0 < batch_size; b0 += per, ++nchunks) {
+    const int nb = batch_size - b0 < per ? batch_size - b0 : per;
+    ET_CUDA(h, cudaMemcpyAsync(static_cast<char*>(ws.stage_in) + b0 * seq_bytes,
+                               static_cast<const char*>(from_host) + b0 * seq_bytes, nb * seq_bytes,
+                               cudaMemcpyHostToDevice, h->h2d_stream));
+    ET_CUDA(h, cudaMemcpyAsync(ws.stage_mask + static_cast<size_t>(b0) * seq_len,
+                               mask_host + static_cast<size_t>(b0) * seq_len,
+                               static_cast<size_t>(nb) * seq_len * 4, cudaMemcpyHostToDevice, h->h2d_stream));
+    ET_CUDA(h, cudaEventRecord(h->in_done[nchunks], h->h2d_stream));
   }
-  rc = forward_impl(h, ws.stage_in, ws.stage_mask, ws.stage_out, batch_size, seq_len, s);
-  if (rc != ET_OK) return rc;
-  if (rows > 0) ET_CUDA(h, cudaMemcpyAsync(out_host, ws.stage_out, bytes, cudaMemcpyDeviceToHost, s));
-  ET_CUDA(h, cudaMemcpyAsync(&h->host_pinned[0], ws.valid_word_num, 4, cudaMemcpyDeviceToHost, s));
+  int c = 0;
+  for (int b0 = 0; b0 < batch_size; b0 += per, ++c) {
+    const int nb = batch_size - b0 < per ? batch_size - b0 : per;
+    ET_CUDA(h, cudaStreamWaitEvent(s, h->in_done[c], 0));
+    rc = forward_impl(h, static_cast<char*>(ws.stage_in) + b0 * seq_bytes,
+                      ws.stage_mask + static_cast<size_t>(b0) * seq_len,
+                      static_cast<char*>(ws.stage_out) + b0 * seq_bytes, nb, seq_len, s);
+    if (rc != ET_OK) {
+      cudaDeviceSynchronize();
+      return rc;
+    }
+    ET_CUDA(h, cudaMemcpyAsync(&h->host_pinned[2 + c], ws.valid_word_num, 4, cudaMemcpyDeviceToHost, s));
+    ET_CUDA(h, cudaEventRecord(h->comp_done[c], s));
+    ET_CUDA(h, cudaStreamWaitEvent(h->d2h_stream, h->comp_done[c], 0));
+    ET_CUDA(h, cudaMemcpyAsync(static_cast<char*>(out_host) + b0 * seq_bytes,
+                               static_cast<char*>(ws.stage_out) + b0 * seq_bytes, nb * seq_bytes,
+                               cudaMemcpyDeviceToHost, h->d2h_stream));
+  }
   ET_CUDA(h, cudaMemcpyAsync(&h->host_pinned[1], ws.status, 4, cudaMemcpyDeviceToHost, s));
   ET_CUDA(h, cudaStreamSynchronize(s));
-  if (valid_word_num_out) *valid_word_num_out = h->host_pinned[0];
+  ET_CUDA(h, cudaStreamSynchronize(h->d2h_stream));
+  ET_CUDA(h, cudaStreamSynchronize(h->h2d_stream));
+  int total_tokens = 0;
+  for (int i = 0; i < nchunks; ++i) total_tokens += h->host_pinned[2 + i];
+  if (valid_word_num_out) *valid_word_num_out = total_tokens;
   if (h->host_pinned[1] != 0) {
     char msg[96];
     snprintf(msg, sizeof msg, "device-side wait expired, status word 0x%x", h->host_pinned[1]);
