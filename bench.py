@@ -40,6 +40,12 @@ from effective_transformer_b200 import workloads as W  # noqa: E402
 
 METRIC = "valid_tokens_per_sec"
 UNIT = "tokens/s"
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
+# captures summarised in profiles/gemm_tcgen05_cfg2_ncu.md: mean of the FFN1 launch (66.1 + 189.2 MB)
+# and the QKV launch (64.9 + 129.4 MB) of the headline workload.
+NCU_GEMM_TRAFFIC = {"cfg2_base_fp16_b1000_s64": 224.8e6}
+NCU_GEMM_TRAFFIC_NOTE = ("bytes per launch, ncu dram read+write, mean of the captured FFN1 and QKV launches; their "
+                         "algorithmic bytes (A + W + C) are 310.2e6 and 247.9e6 (part of C is still in L2 at kernel end)")
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -296,7 +302,10 @@ def main():
                        "l2": "256 MB buffer written between timed steps (untimed)"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
                          "frac": (achieved / peak_tf) if (achieved and peak_tf) else None,
-                         "traffic": None, "kernel": "gemm_tcgen05_kernel" if fp16 else "gemm_simt_kernel",
+                         "traffic": NCU_GEMM_TRAFFIC.get(spec.name),
+                         "traffic_note": NCU_GEMM_TRAFFIC_NOTE if spec.name in NCU_GEMM_TRAFFIC else None,
+                         "kernel": "gemm_tcgen05_pair_kernel" if fp16 else "gemm_simt_kernel",
+                         "algorithmic_flops_per_launch": gemm_flops_step / max(gemm_launches / args.steps, 1),
                          "launches_per_step": gemm_launches / args.steps,
                          "avg_launch_ms": gemm_ms / max(gemm_launches, 1),
                          "peak_source": peak_src + " bf16_tflops_sustained"},
