@@ -2,9 +2,13 @@
 path.  Only tests, the smoke check and the benchmark's CPU-baseline leg may
 import this module; the product path never does.
 
-Parity status: UNPINNED by the reference (it ships no tests, fixtures or
-golden vectors); each function below restates the integer arithmetic of the
-reference kernels it cites, in numpy, for arbitrary 0/1 masks.
+Parity status: the reference ships no tests, fixtures or golden vectors, so
+this oracle is pinned against outputs of the reference itself: its scan,
+compress and restore kernels, compiled unmodified from the reference checkout
+(oracle/build_ref.py) and run on the GPU box, agree bit for bit with the
+functions below (tests/test_reference_kernels_gpu.py).  Each function restates
+the integer arithmetic of the reference kernels it cites, in numpy, for
+arbitrary 0/1 masks.
 """
 from __future__ import annotations
 
