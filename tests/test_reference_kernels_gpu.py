@@ -211,3 +211,86 @@ def test_attention_block_against_reference_kernels(dtype, batch, seq, heads):
     tol = dict(rtol=4e-3, atol=4e-3) if dtype == torch.float16 else dict(rtol=2e-5, atol=2e-5)
     torch.testing.assert_close(r_ctx.double().cpu(), want, **tol)            # reference kernels vs oracle
     torch.testing.assert_close(m_ctx.double().cpu(), r_ctx.double().cpu(), **tol)   # ours vs reference kernels
+
+
+def reference_kernel_chain(x_pad, mask_np, weights, heads, dtype):
+    """The reference's three functors replayed on its own kernels in its own order
+    (tf_op/bert_transformer_op.cu.cc:104-246, 266-331, 339-373); the cublasGemmEx /
+    cublasGemmStridedBatchedEx calls are torch.matmul."""
+    b, s, h = x_pad.shape
+    d = h // heads
+    prefix, t, bidx, widx, packed = ref_input_op(x_pad, mask_np)
+    x = packed.reshape(b * s, h)[:t].contiguous()
+    attr_mask = dev(W.attention_mask_from_input_mask(mask_np).astype(np.float32), dtype)
+    wd = [dev(np.asarray(w, np.float32), dtype) for w in weights]
+    for l in range(len(weights) // 16):
+        w = wd[l * 16:(l + 1) * 16]
+        q, k, v = (x @ w[0]).contiguous(), (x @ w[2]).contiguous(), (x @ w[4]).contiguous()
+        qb, kb, vb = [torch.zeros(b, heads, s, d, dtype=dtype, device="cuda") for _ in range(3)]
+        rok(ref().ref_add_qkv_bias_padding(DT[dtype], iptr(q), iptr(w[1]), iptr(k), iptr(w[3]), iptr(v), iptr(w[5]),
+                                           iptr(qb), iptr(kb), iptr(vb), t, b, s, heads, d, iptr(bidx), iptr(widx),
+                                           stream()))
+        scores = torch.matmul(qb, kb.transpose(-1, -2)).contiguous()
+        rok(ref().ref_softmax(DT[dtype], iptr(scores), iptr(attr_mask), b, heads, s, 1.0 / math.sqrt(d), stream()))
+        ctx_pad = torch.matmul(scores, vb).contiguous()
+        attr_out = torch.zeros(t, h, dtype=dtype, device="cuda")
+        rok(ref().ref_transpose_rm_padding(DT[dtype], iptr(ctx_pad), iptr(attr_out), t, b, s, heads, d, iptr(bidx),
+                                           iptr(widx), stream()))
+        att = (attr_out @ w[6]).contiguous()
+        rok(ref().ref_add_bias_input_layernorm(DT[dtype], iptr(att), iptr(x), iptr(w[7]), iptr(w[9]), iptr(w[8]),
+                                               t, h, stream()))
+        inter = (att @ w[10]).contiguous()
+        rok(ref().ref_add_bias_act(DT[dtype], iptr(inter), iptr(w[11]), t, inter.shape[1], stream()))
+        out = (inter @ w[12]).contiguous()
+        rok(ref().ref_add_bias_input_layernorm(DT[dtype], iptr(out), iptr(att), iptr(w[13]), iptr(w[15]), iptr(w[14]),
+                                               t, h, stream()))
+        x = out
+    full = torch.zeros(b, s, h, dtype=dtype, device="cuda")
+    pk = torch.zeros(b * s, h, dtype=dtype, device="cuda")
+    pk[:t] = x
+    rok(ref().ref_restore_output(DT[dtype], iptr(full), iptr(pk), iptr(bidx), iptr(widx), t, s, h, stream()))
+    torch.cuda.synchronize()
+    return full
+
+
+@pytest.mark.parametrize("cfg", [0, 1])
+def test_whole_path_against_reference_kernel_chain(cfg):
+    """12 BERT-base layers (cfg0 fp32, cfg1 fp16): reference kernels in the reference's
+    order vs the CPU oracle vs this library's et_forward, on valid tokens."""
+    import effective_transformer_b200 as et
+    spec = W.WORKLOADS[cfg]
+    wl = W.make_workload(spec)
+    fp16 = spec.dtype == "fp16"
+    dtype = torch.float16 if fp16 else torch.float32
+    x = dev(wl.from_tensor, dtype)
+    y_ref = reference_kernel_chain(x, wl.mask, wl.weights, spec.shape.head_num, dtype)
+    am = W.attention_mask_from_input_mask(wl.mask)
+    y_orc = O.valid_rows(O.transformer_model(wl.from_tensor, am, wl.weights, 12, 64, compute_dtype=torch.float64,
+                                             round_to_fp16=fp16), wl.mask)
+    sh = spec.shape
+    eng = et.EffectiveTransformer(sh.num_layers, sh.head_num, sh.size_per_head, sh.ffn_dim, spec.batch,
+                                  spec.max_seq_len, dtype=dtype)
+    eng.set_weights(wl.weights)
+    y_me = eng.forward(x, dev(wl.mask))
+    torch.cuda.synchronize()
+    r = O.valid_rows(y_ref.cpu().double(), wl.mask)
+    m = O.valid_rows(y_me.cpu().double(), wl.mask)
+    d_ref, d_me, d_cross = (r - y_orc).abs(), (m - y_orc).abs(), (m - r).abs()
+    if fp16:
+        # this library against the oracle: the stated gate
+        assert float(d_me.max()) <= 2e-2 and float(d_me.mean()) <= 2e-3, (float(d_me.max()), float(d_me.mean()))
+        # The reference's half kernels round more often (fp16 bias adds and cube, Q/K/V written
+        # before the bias): its own chain sits at the edge of that gate (measured max 2.1e-2, mean
+        # 1.5e-3 on cfg1), so it is held to twice the gate, and this library must not be further
+        # from the oracle than the reference's kernels are.
+        assert float(d_ref.max()) <= 4e-2 and float(d_ref.mean()) <= 4e-3, (float(d_ref.max()), float(d_ref.mean()))
+        assert float(d_cross.max()) <= 4e-2 and float(d_cross.mean()) <= 4e-3
+        assert float(d_me.mean()) <= float(d_ref.mean())
+    else:
+        rms = float(y_orc.pow(2).mean().sqrt())
+        for dd, what in ((d_ref, "reference kernels vs oracle"), (d_me, "this library vs oracle"),
+                         (d_cross, "this library vs reference kernels")):
+            assert float(dd.max()) <= 1e-4 * rms, (what, float(dd.max()), rms)
+    pad = torch.from_numpy(wl.mask.ravel() == 0)
+    assert torch.all(y_ref.cpu().reshape(-1, sh.hidden)[pad] == 0) and torch.all(y_me.cpu().reshape(-1, sh.hidden)[pad] == 0)
+    eng.close()
