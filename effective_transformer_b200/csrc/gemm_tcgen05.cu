@@ -54,13 +54,22 @@ struct Cfg {
   static constexpr int kTmemCols = 2 * BN;
 };
 
-__device__ __forceinline__ float gelu_tanh_fast(float x) {
-  // same polynomial as gelu_tanh, with the hardware tanh approximation (its
-  // error is below fp16 resolution of the result)
-  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-  float th;
-  asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(u));
-  return 0.5f * x * (1.0f + th);
+// tanh-form GELU on a pair of fp16 values (x + bias was formed in fp32 and
+// rounded once).  The reference's half kernel does the same step in half2
+// (cuda/cuda_kernels.cu:38-51); here the tanh is the hardware f16x2
+// approximation too.  Large |x| saturates cleanly: tanh(+-inf) = +-1.
+__device__ __forceinline__ uint32_t gelu_tanh_half2(uint32_t xbits) {
+  const __half2 x = *reinterpret_cast<const __half2*>(&xbits);
+  const __half2 c1 = __float2half2_rn(0.7978845608028654f);
+  const __half2 c2 = __float2half2_rn(0.7978845608028654f * 0.044715f);
+  const __half2 u = __hmul2(x, __hfma2(__hmul2(x, x), c2, c1));
+  const uint32_t ubits = *reinterpret_cast<const uint32_t*>(&u);
+  uint32_t tbits;
+  asm("tanh.approx.f16x2 %0, %1;" : "=r"(tbits) : "r"(ubits));
+  const __half2 th = *reinterpret_cast<const __half2*>(&tbits);
+  const __half2 hx = __hmul2(x, __float2half2_rn(0.5f));
+  const __half2 y = __hfma2(hx, th, hx);
+  return *reinterpret_cast<const uint32_t*>(&y);
 }
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, const Vec16& v) {
   asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
@@ -106,12 +115,15 @@ __device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, __half* ctile
         VecTraits<__half>::unpack(ld_shared_v4(bias_s + (c * 64 + p * 8) * 2), fb);
 #pragma unroll
         for (int e = 0; e < 8; ++e) f[e] += fb[e];
-        if (EPI == kEpiBiasGelu) {
-#pragma unroll
-          for (int e = 0; e < 8; ++e) f[e] = gelu_tanh_fast(f[e]);
-        }
       }
-      st_shared_v4(buf + lane * 128 + ((p ^ (lane & 7)) << 4), VecTraits<__half>::pack(f));
+      Vec16 o = VecTraits<__half>::pack(f);
+      if (EPI == kEpiBiasGelu) {
+        o.x = gelu_tanh_half2(o.x);
+        o.y = gelu_tanh_half2(o.y);
+        o.z = gelu_tanh_half2(o.z);
+        o.w = gelu_tanh_half2(o.w);
+      }
+      st_shared_v4(buf + lane * 128 + ((p ^ (lane & 7)) << 4), o);
     }
     __syncwarp();
 #pragma unroll
