@@ -31,6 +31,9 @@ class BertConfig:
     num_hidden_layers: int = 12
     num_attention_heads: int = 12
     intermediate_size: int = 3072
+    vocab_size: int = 30522
+    type_vocab_size: int = 2
+    max_position_embeddings: int = 512
 
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
@@ -181,6 +184,85 @@ class EffectiveTransformer:
         _capi.check(self._lib.et_forward_host(self._h, from_tensor.ctypes.data, input_mask.ctypes.data,
                                               out.ctypes.data, b, s, C.byref(t)), self._h)
         return out, int(t.value)
+
+    # ---- the model around the stack ----------------------------------------
+    def _host(self, a) -> Optional[np.ndarray]:
+        if a is None:
+            return None
+        a = a.detach().cpu().numpy() if isinstance(a, torch.Tensor) else np.asarray(a)
+        return np.ascontiguousarray(a.astype(self.np_dtype, copy=False))
+
+    def set_embeddings(self, word_table, type_table, position_table, ln_gamma, ln_beta,
+                       layernorm_eps: float = 0.0) -> None:
+        """Tables of embedding_lookup / embedding_postprocessor
+        (sample/tensorflow/modeling.py:380-521).  type_table / position_table may be
+        None (use_token_type / use_position_embeddings = False)."""
+        w, t, p = self._host(word_table), self._host(type_table), self._host(position_table)
+        g, b = self._host(ln_gamma), self._host(ln_beta)
+        for name, a in (("word_table", w), ("type_table", t), ("position_table", p)):
+            if a is not None and (a.ndim != 2 or a.shape[1] != self.hidden):
+                raise ValueError(f"{name} must be [rows, {self.hidden}]")
+        _capi.check(self._lib.et_set_embedding_weights(
+            self._h, w.ctypes.data, w.shape[0], None if t is None else t.ctypes.data,
+            0 if t is None else t.shape[0], None if p is None else p.ctypes.data,
+            0 if p is None else p.shape[0], g.ctypes.data, b.ctypes.data, layernorm_eps, 1), self._h)
+
+    def set_pooler(self, kernel, bias) -> None:
+        """The pooler's dense layer (sample/tensorflow/modeling.py:229-232): kernel [H, H] as [in, out]."""
+        k, b = self._host(kernel), self._host(bias)
+        if k.shape != (self.hidden, self.hidden) or b.shape != (self.hidden,):
+            raise ValueError("pooler kernel must be [H, H] and bias [H]")
+        _capi.check(self._lib.et_set_pooler_weights(self._h, k.ctypes.data, b.ctypes.data, 1), self._h)
+
+    @staticmethod
+    def _i32(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        if t is None or (t.dtype == torch.int32 and t.is_contiguous()):
+            return t
+        return t.to(torch.int32).contiguous()
+
+    def forward_ids(self, input_ids: torch.Tensor, input_mask: torch.Tensor,
+                    token_type_ids: Optional[torch.Tensor] = None, sequence_output: bool = True,
+                    pooled_output: bool = False) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
+        """BertModel (sample/tensorflow/modeling.py:107-235) from token ids on the
+        current stream: (get_sequence_output() [B,S,H] or None, get_pooled_output()
+        [B,H] or None).  Embedding rows are gathered for valid tokens only."""
+        ids, mask, types = self._i32(input_ids), self._i32(input_mask), self._i32(token_type_ids)
+        b, s = ids.shape
+        seq = torch.empty((b, s, self.hidden), dtype=self.dtype, device=ids.device) if sequence_output else None
+        pooled = torch.empty((b, self.hidden), dtype=self.dtype, device=ids.device) if pooled_output else None
+        _capi.check(self._lib.et_forward_ids(self._h, _ptr(ids), _ptr(types), _ptr(mask), _ptr(seq),
+                                             _ptr(pooled), b, s, _stream()), self._h)
+        return seq, pooled
+
+    def forward_ids_host(self, input_ids: np.ndarray, input_mask: np.ndarray,
+                         token_type_ids: Optional[np.ndarray] = None, sequence_output: bool = True,
+                         pooled_output: bool = False):
+        """Same with host int32 arrays; returns (sequence or None, pooled or None, T)."""
+        arrs = [input_ids, input_mask] + ([token_type_ids] if token_type_ids is not None else [])
+        if any(a.dtype != np.int32 for a in arrs):
+            raise ValueError("ids and masks must be int32")
+        ids, mask = np.ascontiguousarray(input_ids), np.ascontiguousarray(input_mask)
+        types = None if token_type_ids is None else np.ascontiguousarray(token_type_ids)
+        b, s = ids.shape
+        seq = np.empty((b, s, self.hidden), dtype=self.np_dtype) if sequence_output else None
+        pooled = np.empty((b, self.hidden), dtype=self.np_dtype) if pooled_output else None
+        t = C.c_int(0)
+        _capi.check(self._lib.et_forward_ids_host(
+            self._h, ids.ctypes.data, None if types is None else types.ctypes.data, mask.ctypes.data,
+            None if seq is None else seq.ctypes.data, None if pooled is None else pooled.ctypes.data,
+            b, s, C.byref(t)), self._h)
+        return seq, pooled, int(t.value)
+
+    def pooler(self, packed: torch.Tensor, batch_size: int, seq_len: int,
+               cu_seqlens: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """tanh(dense(first token of every sequence)) read from a packed [T,H] tensor
+        (sample/tensorflow/modeling.py:224-232); cu_seqlens None = those of the last
+        input op on this handle."""
+        self._check_act(packed, "packed")
+        out = torch.empty((batch_size, self.hidden), dtype=self.dtype, device=packed.device)
+        _capi.check(self._lib.et_pooler(self._h, _ptr(packed), _ptr(self._i32(cu_seqlens)), _ptr(out),
+                                        batch_size, seq_len, _stream()), self._h)
+        return out
 
     def set_profiling(self, on: bool) -> None:
         _capi.check(self._lib.et_set_profiling(self._h, 1 if on else 0), self._h)

@@ -19,7 +19,7 @@ STATUS_NAMES = {0: "ET_OK", 1: "ET_INVALID_ARGUMENT", 2: "ET_CUDA_ERROR", 3: "ET
                 4: "ET_DEVICE_TIMEOUT", 5: "ET_NOT_READY"}
 
 PROF_NAMES = ["padding_offsets", "remove_padding", "gemm_qkv", "attention", "gemm_attn_out", "layernorm",
-              "gemm_ffn1", "gemm_ffn2", "restore_padding"]
+              "gemm_ffn1", "gemm_ffn2", "restore_padding", "embedding", "pooler"]
 
 vp, ip, i32, i64 = C.c_void_p, C.POINTER(C.c_int), C.c_int, C.c_longlong
 
@@ -68,6 +68,12 @@ SIGNATURES = {
     "et_output": (i32, [vp, C.POINTER(OutputParam)]),
     "et_forward": (i32, [vp, vp, vp, vp, i32, i32, vp]),
     "et_forward_host": (i32, [vp, vp, vp, vp, i32, i32, ip]),
+    "et_set_embedding_weights": (i32, [vp, vp, i32, vp, i32, vp, i32, vp, vp, C.c_float, i32]),
+    "et_set_pooler_weights": (i32, [vp, vp, vp, i32]),
+    "et_forward_ids": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, vp]),
+    "et_forward_ids_host": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, ip]),
+    "et_pooler": (i32, [vp, vp, vp, vp, i32, i32, vp]),
+    "et_last_packed_output": (i32, [vp, C.POINTER(vp), C.POINTER(vp)]),
     "et_device_status": (i32, [vp, vp, ip]),
     "et_last_padding_info": (i32, [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.POINTER(vp)]),
     "et_set_profiling": (i32, [vp, i32]),
@@ -81,6 +87,9 @@ SIGNATURES = {
     "et_add_qkv_bias_transpose": (i32, [i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp]),
     "et_add_bias_gelu": (i32, [i32, vp, vp, vp, i32, i32, vp]),
     "et_add_bias_input_layernorm": (i32, [i32, vp, vp, vp, vp, vp, vp, i32, i32, C.c_float, vp]),
+    "et_embedding_layernorm": (i32, [i32, vp, vp, vp, vp, vp, vp, i32, vp, i32, vp, vp, vp, C.c_float, vp,
+                                     i32, i32, i32, vp]),
+    "et_gather_first_tokens": (i32, [i32, vp, vp, vp, i32, i32, i32, vp]),
     "et_attention": (i32, [i32, vp, vp, vp, i64, i64, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp]),
     "et_attention_plan_ints": (C.c_size_t, [i32, i32]),
     "et_attention_plan": (i32, [vp, i32, i32, vp, vp]),

@@ -158,6 +158,19 @@ template <typename T>
 cudaError_t launch_add_bias_input_layernorm(T* out, const T* input, const T* bias, const T* gamma,
                                             const T* beta, const int* t_ptr, int max_tokens, int n,
                                             float eps, cudaStream_t stream);
+// Embedding rows + LayerNorm for valid tokens only, written packed [T, n].
+// token_type_ids / type_table / pos_table may be null.
+template <typename T>
+cudaError_t launch_embedding_layernorm(const int* input_ids, const int* token_type_ids,
+                                       const int* batch_idx, const int* word_idx, const int* t_ptr,
+                                       const T* word_table, int vocab, const T* type_table,
+                                       int type_vocab, const T* pos_table, const T* gamma,
+                                       const T* beta, T* out, int batch, int seq, int n, float eps,
+                                       cudaStream_t stream);
+// out[b] = packed[cu_seqlens[b]] (zero row for an empty sequence); *count_out = batch.
+cudaError_t launch_gather_first_tokens(const void* packed, const int* cu_seqlens, void* out, int batch,
+                                       int max_tokens, int row_bytes, int* count_out,
+                                       cudaStream_t stream);
 // Weight repacking (runs once per layer when weights are registered).
 template <typename T>
 cudaError_t launch_transpose(const T* src, T* dst, int rows, int cols, cudaStream_t stream);
@@ -165,7 +178,8 @@ template <typename T>
 cudaError_t launch_copy_columns(const T* src, T* dst, int rows, int cols, int dst_ld, int dst_col0,
                                 cudaStream_t stream);
 
-enum Epilogue : int { kEpiNone = 0, kEpiBias = 1, kEpiBiasGelu = 2 };
+// kEpiBiasTanh is the pooler's activation (sample/tensorflow/modeling.py:224-232).
+enum Epilogue : int { kEpiNone = 0, kEpiBias = 1, kEpiBiasGelu = 2, kEpiBiasTanh = 3 };
 
 // CUDA-core GEMM: C[M,N] = epi(A[M,K] * W[K,N]); W row-major [K,N].
 template <typename T>

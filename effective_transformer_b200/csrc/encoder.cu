@@ -44,6 +44,23 @@ struct LayerWeights {
   bool ready = false;
 };
 
+// Embedding tables and pooler weights (the stages in front of and behind the stack).
+struct ModelWeights {
+  void* word = nullptr;   // [vocab, H]
+  void* type = nullptr;   // [type_vocab, H] or null
+  void* pos = nullptr;    // [max_pos, H] or null
+  void* emb_gamma = nullptr;
+  void* emb_beta = nullptr;
+  int vocab = 0, type_vocab = 0, max_pos = 0;
+  float emb_eps = 1e-12f;
+  bool emb_ready = false;
+  void* pool_w = nullptr;    // [H, H] row-major [in, out]
+  void* pool_w_t = nullptr;  // [H, H] K-major copy for the tcgen05 GEMM (fp16 handles)
+  void* pool_b = nullptr;
+  bool pool_ready = false;
+  std::vector<void*> emb_allocs, pool_allocs;
+};
+
 struct Workspace {
   size_t cap_tokens = 0;  // rows every token buffer can hold (multiple of 128)
   void* x = nullptr;      // [cap, H]  packed activations (layer input/output)
@@ -54,6 +71,11 @@ struct Workspace {
   void* stage_in = nullptr;   // [B*S, H] device staging for the host-buffer call
   void* stage_out = nullptr;  // [B*S, H]
   int* stage_mask = nullptr;  // [B*S]
+  int* stage_ids = nullptr;   // [B*S] token ids of the host-buffer model call
+  int* stage_types = nullptr; // [B*S]
+  void* first_tok = nullptr;  // [round_up(B,128), H] first-token rows (pooler input)
+  void* pooled = nullptr;     // [round_up(B,128), H] pooler output staging
+  int* pool_m = nullptr;      // device copy of the batch size (row count of the pooler GEMM)
   int* batch_idx = nullptr;
   int* word_idx = nullptr;
   int* padding_offset = nullptr;
@@ -96,6 +118,7 @@ struct et_handle_s {
   float eps = 1e-6f;
   bool use_simt = false;
   std::vector<LayerWeights> layers;
+  ModelWeights model;
   Workspace ws;
   cudaStream_t own_stream = nullptr;
   // host-buffer entry: copies run on their own streams so that the upload of
@@ -180,7 +203,8 @@ size_t workspace_bytes_for(const et_handle_s* h, size_t batch, size_t seq) {
   total += cap * 3 * hid * e;          // qkv
   total += cap * f * e;                // ffn
   total += batch * seq * hid * e * 2;  // staging in/out
-  total += batch * seq * 4 * 5;        // mask staging + 4 index arrays
+  total += batch * seq * 4 * 7;        // mask / id / type staging + 4 index arrays
+  total += round_up(batch, 128) * hid * e * 2;  // first-token rows, pooled output
   total += (batch * 3 + 8) * 4;
   return total;
 }
@@ -320,6 +344,9 @@ int output_impl(et_handle_t h, const et_output_param_t* p) {
   return ET_OK;
 }
 
+int stack_impl(et_handle_t h, int batch, int seq, cudaStream_t s);
+int restore_impl(et_handle_t h, void* out, int batch, int seq, cudaStream_t s);
+
 int forward_impl(et_handle_t h, const void* from_tensor, const int* mask, void* out, int batch, int seq,
                  cudaStream_t s) {
   int rc = check_shape(h, batch, seq, h->cfg.head_num, h->cfg.size_per_head);
@@ -343,6 +370,16 @@ int forward_impl(et_handle_t h, const void* from_tensor, const int* mask, void* 
   ip.stream = s;
   rc = input_impl(h, &ip);
   if (rc != ET_OK) return rc;
+  rc = stack_impl(h, batch, seq, s);
+  if (rc != ET_OK) return rc;
+  return restore_impl(h, out, batch, seq, s);
+}
+
+// The layer stack in place on the packed tensor ws.x (attention tiles are
+// planned once per batch).
+int stack_impl(et_handle_t h, int batch, int seq, cudaStream_t s) {
+  Workspace& ws = h->ws;
+  int rc = ET_OK;
   const int max_m = batch * seq;
   if (h->cfg.dtype == ET_FP16 && !h->use_simt && seq <= 128 && max_m > 0)
     ET_LAUNCH(h, ET_PROF_PADDING_OFFSETS, 1, s,
@@ -356,6 +393,12 @@ int forward_impl(et_handle_t h, const void* from_tensor, const int* mask, void* 
                             ws.valid_word_num, max_m, ws.cu_seqlens, batch, seq, s);
     if (rc != ET_OK) return rc;
   }
+  return ET_OK;
+}
+
+// Output op from the handle's packed tensor to a padded [B,S,H] buffer.
+int restore_impl(et_handle_t h, void* out, int batch, int seq, cudaStream_t s) {
+  Workspace& ws = h->ws;
   et_output_param_t op{};
   op.from_tensor = ws.x;
   op.valid_word_num = ws.valid_word_num;
@@ -368,6 +411,95 @@ int forward_impl(et_handle_t h, const void* from_tensor, const int* mask, void* 
   op.to_tensor = out;
   op.stream = s;
   return output_impl(h, &op);
+}
+
+// pooled_out[b] = tanh(packed[cu_seqlens[b]] * W + bias): first-token gather,
+// then one GEMM whose epilogue adds the bias and applies tanh.
+int pooler_impl(et_handle_t h, const void* packed, const int* cu_seqlens, void* pooled_out, int batch,
+                int max_tokens, cudaStream_t s) {
+  if (!h->model.pool_ready) return set_error(h, ET_NOT_READY, "pooler weights were never set");
+  if (batch == 0) return ET_OK;
+  Workspace& ws = h->ws;
+  const ModelWeights& mw = h->model;
+  const int hid = h->hidden;
+  ET_LAUNCH(h, ET_PROF_POOLER, 1, s,
+            launch_gather_first_tokens(packed, cu_seqlens, ws.first_tok, batch, max_tokens,
+                                       hid * static_cast<int>(h->esize), ws.pool_m, s));
+  if (h->cfg.dtype == ET_FP16 && !h->use_simt)
+    ET_LAUNCH(h, ET_PROF_POOLER, 1, s,
+              launch_gemm_tcgen05(static_cast<const __half*>(ws.first_tok), static_cast<const __half*>(mw.pool_w_t),
+                                  static_cast<const __half*>(mw.pool_b), static_cast<__half*>(pooled_out),
+                                  ws.pool_m, batch, hid, hid, kEpiBiasTanh, ws.status, s));
+  else if (h->cfg.dtype == ET_FP16)
+    ET_LAUNCH(h, ET_PROF_POOLER, 1, s,
+              launch_gemm_simt<__half>(static_cast<const __half*>(ws.first_tok), static_cast<const __half*>(mw.pool_w),
+                                       static_cast<const __half*>(mw.pool_b), static_cast<__half*>(pooled_out),
+                                       ws.pool_m, batch, hid, hid, kEpiBiasTanh, s));
+  else
+    ET_LAUNCH(h, ET_PROF_POOLER, 1, s,
+              launch_gemm_simt<float>(static_cast<const float*>(ws.first_tok), static_cast<const float*>(mw.pool_w),
+                                      static_cast<const float*>(mw.pool_b), static_cast<float*>(pooled_out),
+                                      ws.pool_m, batch, hid, hid, kEpiBiasTanh, s));
+  return ET_OK;
+}
+
+// Token ids -> embeddings of the valid tokens (packed) -> stack -> outputs.
+int forward_ids_impl(et_handle_t h, const int* input_ids, const int* token_type_ids, const int* mask,
+                     void* sequence_out, void* pooled_out, int batch, int seq, cudaStream_t s) {
+  int rc = check_shape(h, batch, seq, h->cfg.head_num, h->cfg.size_per_head);
+  if (rc != ET_OK) return rc;
+  if (input_ids == nullptr || mask == nullptr) return set_error(h, ET_INVALID_ARGUMENT, "null tensor pointer");
+  const ModelWeights& mw = h->model;
+  if (!mw.emb_ready) return set_error(h, ET_NOT_READY, "embedding weights were never set");
+  if (pooled_out != nullptr && !mw.pool_ready) return set_error(h, ET_NOT_READY, "pooler weights were never set");
+  if (mw.pos != nullptr && seq > mw.max_pos)
+    return set_error(h, ET_INVALID_ARGUMENT, "seq_len exceeds max_position_embeddings");
+  for (int l = 0; l < h->cfg.num_layers; ++l)
+    if (!h->layers[l].ready) return set_error(h, ET_NOT_READY, "weights of a layer were never set");
+  Workspace& ws = h->ws;
+  ET_LAUNCH(h, ET_PROF_PADDING_OFFSETS, (batch > 0 && seq > 0) ? 2 : 1, s,
+            launch_padding_offsets(mask, batch, seq, ws.prefix_sum, ws.valid_word_num, ws.batch_idx,
+                                   ws.word_idx, ws.seq_len, ws.cu_seqlens, ws.padding_offset,
+                                   ws.lens_scratch, s));
+  if (h->cfg.dtype == ET_FP16) {
+    auto H = [](const void* p) { return static_cast<const __half*>(p); };
+    ET_LAUNCH(h, ET_PROF_EMBEDDING, 1, s,
+              launch_embedding_layernorm<__half>(input_ids, token_type_ids, ws.batch_idx, ws.word_idx,
+                                                 ws.valid_word_num, H(mw.word), mw.vocab, H(mw.type),
+                                                 mw.type_vocab, H(mw.pos), H(mw.emb_gamma), H(mw.emb_beta),
+                                                 static_cast<__half*>(ws.x), batch, seq, h->hidden,
+                                                 mw.emb_eps, s));
+  } else {
+    auto F = [](const void* p) { return static_cast<const float*>(p); };
+    ET_LAUNCH(h, ET_PROF_EMBEDDING, 1, s,
+              launch_embedding_layernorm<float>(input_ids, token_type_ids, ws.batch_idx, ws.word_idx,
+                                                ws.valid_word_num, F(mw.word), mw.vocab, F(mw.type),
+                                                mw.type_vocab, F(mw.pos), F(mw.emb_gamma), F(mw.emb_beta),
+                                                static_cast<float*>(ws.x), batch, seq, h->hidden,
+                                                mw.emb_eps, s));
+  }
+  rc = stack_impl(h, batch, seq, s);
+  if (rc != ET_OK) return rc;
+  if (pooled_out != nullptr) {
+    rc = pooler_impl(h, ws.x, ws.cu_seqlens, pooled_out, batch, batch * seq, s);
+    if (rc != ET_OK) return rc;
+  }
+  if (sequence_out != nullptr) return restore_impl(h, sequence_out, batch, seq, s);
+  return ET_OK;
+}
+
+// Copies `count` elements of the handle's dtype into a fresh device array.
+int upload_array(et_handle_t h, void** dst, const void* src, size_t count, int on_host,
+                 std::vector<void*>& owner, cudaStream_t s) {
+  *dst = nullptr;
+  if (src == nullptr) return ET_OK;
+  void* p = nullptr;
+  const size_t bytes = count * h->esize;
+  ET_CUDA(h, cudaMalloc(&p, round_up(bytes == 0 ? 16 : bytes, 256)));
+  owner.push_back(p);
+  ET_CUDA(h, cudaMemcpyAsync(p, src, bytes, on_host ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToDevice, s));
+  *dst = p;
+  return ET_OK;
 }
 
 }  // namespace
@@ -445,6 +577,10 @@ int et_create(const et_config_t* config, et_handle_t* out_handle) {
       {&ws.x, cap * H * e}, {&ws.qkv, cap * 3 * H * e}, {&ws.ctx, cap * H * e}, {&ws.att, cap * H * e},
       {&ws.ffn, cap * f * e}, {&ws.stage_in, bs * H * e}, {&ws.stage_out, bs * H * e},
       {reinterpret_cast<void**>(&ws.stage_mask), bs * 4},
+      {reinterpret_cast<void**>(&ws.stage_ids), bs * 4}, {reinterpret_cast<void**>(&ws.stage_types), bs * 4},
+      {&ws.first_tok, round_up(static_cast<size_t>(c.max_batch_size), 128) * H * e},
+      {&ws.pooled, round_up(static_cast<size_t>(c.max_batch_size), 128) * H * e},
+      {reinterpret_cast<void**>(&ws.pool_m), 4},
       {reinterpret_cast<void**>(&ws.batch_idx), cap * 4}, {reinterpret_cast<void**>(&ws.word_idx), cap * 4},
       {reinterpret_cast<void**>(&ws.padding_offset), cap * 4},
       {reinterpret_cast<void**>(&ws.prefix_sum), cap * 4},
@@ -483,6 +619,8 @@ int et_destroy(et_handle_t h) {
   DeviceGuard guard(h->cfg.device);
   cudaDeviceSynchronize();
   for (void* p : h->ws.allocations) cudaFree(p);
+  for (void* p : h->model.emb_allocs) cudaFree(p);
+  for (void* p : h->model.pool_allocs) cudaFree(p);
   for (auto& sp : h->prof.pending) {
     cudaEventDestroy(sp.a);
     cudaEventDestroy(sp.b);
@@ -696,6 +834,146 @@ int et_forward_host(et_handle_t h, const void* from_host, const int* mask_host, 
   ET_CATCH(h)
 }
 
+int et_set_embedding_weights(et_handle_t h, const void* word_table, int vocab_size, const void* type_table,
+                             int type_vocab_size, const void* position_table, int max_position,
+                             const void* gamma, const void* beta, float layernorm_eps, int on_host) {
+  ET_TRY
+  if (h == nullptr) return ET_INVALID_ARGUMENT;
+  if (word_table == nullptr || vocab_size <= 0 || gamma == nullptr || beta == nullptr)
+    return set_error(h, ET_INVALID_ARGUMENT, "word_table, gamma and beta are required");
+  if ((type_table != nullptr && type_vocab_size <= 0) || (position_table != nullptr && max_position <= 0))
+    return set_error(h, ET_INVALID_ARGUMENT, "a table was given with a non-positive row count");
+  DeviceGuard guard(h->cfg.device);
+  ModelWeights& mw = h->model;
+  cudaStream_t s = h->own_stream;
+  ET_CUDA(h, cudaDeviceSynchronize());  // nothing may still read the tables being replaced
+  for (void* p : mw.emb_allocs) cudaFree(p);
+  mw.emb_allocs.clear();
+  mw.emb_ready = false;
+  const size_t H = h->hidden;
+  int rc = upload_array(h, &mw.word, word_table, static_cast<size_t>(vocab_size) * H, on_host, mw.emb_allocs, s);
+  if (rc == ET_OK)
+    rc = upload_array(h, &mw.type, type_table, static_cast<size_t>(type_vocab_size) * H, on_host, mw.emb_allocs, s);
+  if (rc == ET_OK)
+    rc = upload_array(h, &mw.pos, position_table, static_cast<size_t>(max_position) * H, on_host, mw.emb_allocs, s);
+  if (rc == ET_OK) rc = upload_array(h, &mw.emb_gamma, gamma, H, on_host, mw.emb_allocs, s);
+  if (rc == ET_OK) rc = upload_array(h, &mw.emb_beta, beta, H, on_host, mw.emb_allocs, s);
+  cudaError_t se = cudaStreamSynchronize(s);
+  if (rc == ET_OK && se != cudaSuccess) rc = cuda_fail(h, se, "cudaStreamSynchronize");
+  if (rc != ET_OK) return rc;
+  mw.vocab = vocab_size;
+  mw.type_vocab = type_table ? type_vocab_size : 0;
+  mw.max_pos = position_table ? max_position : 0;
+  mw.emb_eps = layernorm_eps > 0.f ? layernorm_eps : 1e-12f;
+  mw.emb_ready = true;
+  return ET_OK;
+  ET_CATCH(h)
+}
+
+int et_set_pooler_weights(et_handle_t h, const void* kernel, const void* bias, int on_host) {
+  ET_TRY
+  if (h == nullptr) return ET_INVALID_ARGUMENT;
+  if (kernel == nullptr || bias == nullptr) return set_error(h, ET_INVALID_ARGUMENT, "null weight pointer");
+  DeviceGuard guard(h->cfg.device);
+  ModelWeights& mw = h->model;
+  cudaStream_t s = h->own_stream;
+  ET_CUDA(h, cudaDeviceSynchronize());
+  for (void* p : mw.pool_allocs) cudaFree(p);
+  mw.pool_allocs.clear();
+  mw.pool_ready = false;
+  mw.pool_w_t = nullptr;
+  const size_t H = h->hidden;
+  int rc = upload_array(h, &mw.pool_w, kernel, H * H, on_host, mw.pool_allocs, s);
+  if (rc == ET_OK) rc = upload_array(h, &mw.pool_b, bias, H, on_host, mw.pool_allocs, s);
+  if (rc == ET_OK && h->cfg.dtype == ET_FP16) {
+    void* p = nullptr;
+    ET_CUDA(h, cudaMalloc(&p, round_up(H * H * 2, 256)));
+    mw.pool_allocs.push_back(p);
+    mw.pool_w_t = p;
+    ET_CUDA(h, launch_transpose<__half>(static_cast<const __half*>(mw.pool_w), static_cast<__half*>(p),
+                                        h->hidden, h->hidden, s));
+  }
+  cudaError_t se = cudaStreamSynchronize(s);
+  if (rc == ET_OK && se != cudaSuccess) rc = cuda_fail(h, se, "cudaStreamSynchronize");
+  if (rc != ET_OK) return rc;
+  mw.pool_ready = true;
+  return ET_OK;
+  ET_CATCH(h)
+}
+
+int et_forward_ids(et_handle_t h, const int* input_ids, const int* token_type_ids, const int* mask,
+                   void* sequence_out, void* pooled_out, int batch_size, int seq_len, void* stream) {
+  ET_TRY
+  if (h == nullptr) return ET_INVALID_ARGUMENT;
+  DeviceGuard guard(h->cfg.device);
+  return forward_ids_impl(h, input_ids, token_type_ids, mask, sequence_out, pooled_out, batch_size, seq_len,
+                          static_cast<cudaStream_t>(stream));
+  ET_CATCH(h)
+}
+
+int et_forward_ids_host(et_handle_t h, const int* ids_host, const int* types_host, const int* mask_host,
+                        void* sequence_out_host, void* pooled_out_host, int batch_size, int seq_len,
+                        int* valid_word_num_out) {
+  ET_TRY
+  if (h == nullptr) return ET_INVALID_ARGUMENT;
+  int rc = check_shape(h, batch_size, seq_len, h->cfg.head_num, h->cfg.size_per_head);
+  if (rc != ET_OK) return rc;
+  if (!ids_host || !mask_host) return set_error(h, ET_INVALID_ARGUMENT, "null host pointer");
+  DeviceGuard guard(h->cfg.device);
+  Workspace& ws = h->ws;
+  cudaStream_t s = h->own_stream;
+  const size_t n = static_cast<size_t>(batch_size) * seq_len;
+  ET_CUDA(h, cudaMemcpyAsync(ws.stage_ids, ids_host, n * 4, cudaMemcpyHostToDevice, s));
+  ET_CUDA(h, cudaMemcpyAsync(ws.stage_mask, mask_host, n * 4, cudaMemcpyHostToDevice, s));
+  if (types_host) ET_CUDA(h, cudaMemcpyAsync(ws.stage_types, types_host, n * 4, cudaMemcpyHostToDevice, s));
+  rc = forward_ids_impl(h, ws.stage_ids, types_host ? ws.stage_types : nullptr, ws.stage_mask,
+                        sequence_out_host ? ws.stage_out : nullptr, pooled_out_host ? ws.pooled : nullptr,
+                        batch_size, seq_len, s);
+  if (rc != ET_OK) {
+    cudaDeviceSynchronize();
+    return rc;
+  }
+  if (pooled_out_host)
+    ET_CUDA(h, cudaMemcpyAsync(pooled_out_host, ws.pooled, static_cast<size_t>(batch_size) * h->hidden * h->esize,
+                               cudaMemcpyDeviceToHost, s));
+  if (sequence_out_host)
+    ET_CUDA(h, cudaMemcpyAsync(sequence_out_host, ws.stage_out, n * h->hidden * h->esize,
+                               cudaMemcpyDeviceToHost, s));
+  ET_CUDA(h, cudaMemcpyAsync(&h->host_pinned[0], ws.valid_word_num, 4, cudaMemcpyDeviceToHost, s));
+  ET_CUDA(h, cudaMemcpyAsync(&h->host_pinned[1], ws.status, 4, cudaMemcpyDeviceToHost, s));
+  ET_CUDA(h, cudaStreamSynchronize(s));
+  if (valid_word_num_out) *valid_word_num_out = h->host_pinned[0];
+  if (h->host_pinned[1] != 0) {
+    char msg[96];
+    snprintf(msg, sizeof msg, "device-side wait expired, status word 0x%x", h->host_pinned[1]);
+    cudaMemsetAsync(ws.status, 0, 4, s);
+    cudaStreamSynchronize(s);
+    return set_error(h, ET_DEVICE_TIMEOUT, msg);
+  }
+  return ET_OK;
+  ET_CATCH(h)
+}
+
+int et_pooler(et_handle_t h, const void* packed, const int* cu_seqlens, void* pooled_out, int batch_size,
+              int seq_len, void* stream) {
+  ET_TRY
+  if (h == nullptr) return ET_INVALID_ARGUMENT;
+  int rc = check_shape(h, batch_size, seq_len, h->cfg.head_num, h->cfg.size_per_head);
+  if (rc != ET_OK) return rc;
+  if (packed == nullptr || pooled_out == nullptr) return set_error(h, ET_INVALID_ARGUMENT, "null tensor pointer");
+  DeviceGuard guard(h->cfg.device);
+  return pooler_impl(h, packed, cu_seqlens ? cu_seqlens : h->ws.cu_seqlens, pooled_out, batch_size,
+                     batch_size * seq_len, static_cast<cudaStream_t>(stream));
+  ET_CATCH(h)
+}
+
+int et_last_packed_output(et_handle_t h, const void** packed, const int** valid_word_num) {
+  if (h == nullptr) return ET_INVALID_ARGUMENT;
+  if (packed) *packed = h->ws.x;
+  if (valid_word_num) *valid_word_num = h->ws.valid_word_num;
+  return ET_OK;
+}
+
 int et_device_status(et_handle_t h, void* stream, int* out_status) {
   ET_TRY
   if (h == nullptr || out_status == nullptr) return ET_INVALID_ARGUMENT;
@@ -847,6 +1125,39 @@ int et_add_bias_input_layernorm(int dtype, void* out, const void* input, const v
                                                             F_(gamma), F_(beta), t_ptr, max_tokens, n, eps, s));
 }
 
+int et_embedding_layernorm(int dtype, const int* input_ids, const int* token_type_ids, const int* batch_idx,
+                           const int* word_idx, const int* t_ptr, const void* word_table, int vocab_size,
+                           const void* type_table, int type_vocab_size, const void* position_table,
+                           const void* gamma, const void* beta, float eps, void* to_tensor, int batch, int seq,
+                           int hidden, void* stream) {
+  if (batch < 0 || seq < 0 || hidden <= 0 || (dtype != ET_FP16 && dtype != ET_FP32)) return ET_INVALID_ARGUMENT;
+  if (batch == 0 || seq == 0) return ET_OK;  // no token, nothing to write
+  if (!input_ids || !batch_idx || !word_idx || !t_ptr || !word_table || !gamma || !beta || !to_tensor ||
+      vocab_size <= 0 || (type_table && type_vocab_size <= 0))
+    return ET_INVALID_ARGUMENT;
+  if (!(eps > 0.f)) eps = 1e-12f;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return ET_DISPATCH(dtype,
+                     launch_embedding_layernorm<__half>(input_ids, token_type_ids, batch_idx, word_idx, t_ptr,
+                                                        H_(word_table), vocab_size, H_(type_table),
+                                                        type_vocab_size, H_(position_table), H_(gamma), H_(beta),
+                                                        static_cast<__half*>(to_tensor), batch, seq, hidden, eps, s),
+                     launch_embedding_layernorm<float>(input_ids, token_type_ids, batch_idx, word_idx, t_ptr,
+                                                       F_(word_table), vocab_size, F_(type_table),
+                                                       type_vocab_size, F_(position_table), F_(gamma), F_(beta),
+                                                       static_cast<float*>(to_tensor), batch, seq, hidden, eps, s));
+}
+
+int et_gather_first_tokens(int dtype, const void* packed, const int* cu_seqlens, void* out, int batch_size,
+                           int max_tokens, int hidden, void* stream) {
+  if (!packed || !cu_seqlens || !out || batch_size < 0 || max_tokens < 0 || hidden <= 0 ||
+      (dtype != ET_FP16 && dtype != ET_FP32))
+    return ET_INVALID_ARGUMENT;
+  return to_status(launch_gather_first_tokens(packed, cu_seqlens, out, batch_size, max_tokens,
+                                              hidden * (dtype == ET_FP16 ? 2 : 4), nullptr,
+                                              static_cast<cudaStream_t>(stream)));
+}
+
 int et_attention(int dtype, const void* q, const void* k, const void* v, long long token_stride,
                  long long head_stride, void* ctx, const int* cu_seqlens, int batch, int max_seq,
                  int max_tokens, int heads, int d, int use_simt, int* status_word, void* stream) {
@@ -890,7 +1201,7 @@ int et_attention_tiles(const void* q, const void* k, const void* v, long long to
 int et_gemm(int dtype, const void* a, const void* w, const void* w_packed, const void* bias, void* c,
             const int* m_ptr, int max_m, int n, int k, int epilogue, int use_simt, int* status_word,
             void* stream) {
-  if (!a || !c || !m_ptr || max_m < 0 || n <= 0 || k <= 0 || epilogue < 0 || epilogue > 2)
+  if (!a || !c || !m_ptr || max_m < 0 || n <= 0 || k <= 0 || epilogue < 0 || epilogue > 3)
     return ET_INVALID_ARGUMENT;
   if (epilogue != 0 && !bias) return ET_INVALID_ARGUMENT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);

@@ -126,6 +126,9 @@ gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ W, const T* __re
         if (epilogue == kEpiBiasGelu) {
 #pragma unroll
           for (int j = 0; j < 4; ++j) o[j] = gelu_tanh(o[j]);
+        } else if (epilogue == kEpiBiasTanh) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) o[j] = tanhf(o[j]);
         }
       }
       Load4<T>::st(C + static_cast<size_t>(r) * N + c, o);

@@ -116,6 +116,10 @@ __device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, __half* ctile
 #pragma unroll
         for (int e = 0; e < 8; ++e) f[e] += fb[e];
       }
+      if (EPI == kEpiBiasTanh) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] = tanhf(f[e]);
+      }
       Vec16 o = VecTraits<__half>::pack(f);
       if (EPI == kEpiBiasGelu) {
         o.x = gelu_tanh_half2(o.x);
@@ -603,6 +607,8 @@ cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const __ha
       return launch_pair_epi<kEpiBias>(ta, tb, bias, c, m_ptr, max_m, n, k, status_word, stream);
     case kEpiBiasGelu:
       return launch_pair_epi<kEpiBiasGelu>(ta, tb, bias, c, m_ptr, max_m, n, k, status_word, stream);
+    case kEpiBiasTanh:
+      return launch_pair_epi<kEpiBiasTanh>(ta, tb, bias, c, m_ptr, max_m, n, k, status_word, stream);
     default:
       return cudaErrorInvalidValue;
   }
@@ -640,6 +646,8 @@ cudaError_t launch_bn(const CUtensorMap& ta, const CUtensorMap& tb, const __half
       return launch_bn_epi<BN, kEpiBias>(ta, tb, bias, c, m_ptr, max_m, n, k, status_word, stream);
     case kEpiBiasGelu:
       return launch_bn_epi<BN, kEpiBiasGelu>(ta, tb, bias, c, m_ptr, max_m, n, k, status_word, stream);
+    case kEpiBiasTanh:
+      return launch_bn_epi<BN, kEpiBiasTanh>(ta, tb, bias, c, m_ptr, max_m, n, k, status_word, stream);
     default:
       return cudaErrorInvalidValue;
   }

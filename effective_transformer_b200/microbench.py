@@ -104,6 +104,18 @@ def main() -> None:
         return lambda: lib.et_gemm(dt, P(a), P(w), P(wp), P(bias), P(gemm_out), P(tn), n_pos, nn, kk, epi, simt,
                                    P(status), st)
 
+    # embedding stage: ids drawn over the full BERT vocabulary, so word rows miss L2 as in production
+    vocab = 30522
+    ids = torch.randint(0, vocab, (b, s), device=dev, generator=g, dtype=torch.int32)
+    types = torch.randint(0, 2, (b, s), device=dev, generator=g, dtype=torch.int32)
+    word_t, type_t, pos_t = rnd(vocab, h), rnd(2, h), rnd(512, h)
+    first_tok = torch.empty(b, h, device=dev, dtype=tdt)
+    w_pool = (rnd(h, h) * 0.02).contiguous()
+    wp_pool = torch.empty(h, h, device=dev, dtype=tdt)
+    assert lib.et_pack_weight(dt, P(w_pool), P(wp_pool), h, h, st) == 0
+    bn = torch.tensor([b], **i32)
+    pooled = torch.empty(b, h, device=dev, dtype=tdt)
+
     plan = torch.zeros(int(lib.et_attention_plan_ints(b, n_pos)), **i32)
     if fp16 and s <= 128:
         assert lib.et_attention_plan(P(cu), b, n_pos, P(plan), st) == 0
@@ -130,6 +142,14 @@ def main() -> None:
                                                            n_pos, heads, 64, P(status), st),
                             "hbm", 4.0 * t * h * e),
         "attention_plan": (lambda: lib.et_attention_plan(P(cu), b, n_pos, P(plan), st), "hbm", 4.0 * b + 8.0 * t),
+        # per valid token: 12 B of ids/indices + one word row read + one packed row written
+        "embedding_layernorm": (lambda: lib.et_embedding_layernorm(
+            dt, P(ids), P(types), P(bidx), P(widx), P(tn), P(word_t), vocab, P(type_t), 2, P(pos_t), P(gamma_h),
+            P(beta_h), 1e-12, P(x_packed), b, s, h, st), "hbm", t * (2.0 * h * e + 16.0)),
+        "gather_first_tokens": (lambda: lib.et_gather_first_tokens(dt, P(x_packed), P(cu), P(first_tok), b, n_pos, h, st),
+                                "hbm", 2.0 * b * h * e),
+        "gemm_pooler": (lambda: lib.et_gemm(dt, P(first_tok), P(w_pool), P(wp_pool), P(bias_h), P(pooled), P(bn), b, h, h,
+                                            3, simt, P(status), st), "tensor", 2.0 * b * h * h),
         "gemm_qkv": (gemm("gemm_qkv", x_packed, bias3, 1), "tensor", 2.0 * t * h * 3 * h),
         "gemm_attn_out": (gemm("gemm_attn_out", x_packed, None, 0), "tensor", 2.0 * t * h * h),
         "gemm_ffn1": (gemm("gemm_ffn1", x_packed, bias_f, 2), "tensor", 2.0 * t * h * f),

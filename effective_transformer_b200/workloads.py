@@ -157,6 +157,45 @@ def make_workload(spec: WorkloadSpec, with_weights: bool = True,
     return Workload(spec, lengths, mask, x, weights)
 
 
+@dataclass
+class ModelHeads:
+    """The pieces of sample/tensorflow/modeling.py's BertModel that sit either
+    side of the encoder stack: token ids and the three embedding tables with
+    their LayerNorm (modeling.py:380-521), and the pooler's dense layer
+    (modeling.py:224-232)."""
+    input_ids: np.ndarray        # int32 [B, S]
+    token_type_ids: np.ndarray   # int32 [B, S]
+    word_table: np.ndarray       # float32 [vocab, H]
+    type_table: np.ndarray       # float32 [type_vocab, H]
+    position_table: np.ndarray   # float32 [max_position, H]
+    ln_gamma: np.ndarray         # float32 [H]
+    ln_beta: np.ndarray          # float32 [H]
+    pooler_kernel: np.ndarray    # float32 [H, H]  ([in, out])
+    pooler_bias: np.ndarray      # float32 [H]
+
+
+def make_model_heads(spec: WorkloadSpec, lengths: np.ndarray, vocab_size: int = 30522,
+                     type_vocab_size: int = 2, max_position: int = 512,
+                     table_scale: float = 0.02) -> ModelHeads:
+    """Seeded ids and tables for the embedding / pooler stages.  Drawn from a
+    RandomState of their own (seed + 7919) so that the encoder-stack draws of
+    ``make_workload`` stay what they are.  Vocabulary, type and position sizes
+    default to sample/tensorflow/bert_config.json; ``table_scale`` is the
+    reference's initializer_range.  Each sequence gets segment 0 then segment 1,
+    split at a random point, as sentence-pair inputs do."""
+    rng = np.random.RandomState(spec.seed + 7919)
+    b, s, h = len(lengths), spec.max_seq_len, spec.shape.hidden
+    ids = rng.randint(0, vocab_size, size=(b, s)).astype(np.int32)
+    split = (rng.rand(b) * (lengths + 1)).astype(np.int32)
+    types = (np.arange(s, dtype=np.int32)[None, :] >= split[:, None]).astype(np.int32)
+    types = np.minimum(types, type_vocab_size - 1).astype(np.int32)
+    t = lambda *shape: (table_scale * rng.randn(*shape)).astype(np.float32)
+    word, typ, pos = t(vocab_size, h), t(type_vocab_size, h), t(max_position, h)
+    gamma = (1.0 + 0.1 * rng.randn(h)).astype(np.float32)
+    beta = (0.1 * rng.randn(h)).astype(np.float32)
+    return ModelHeads(ids, types, word, typ, pos, gamma, beta, t(h, h), t(h))
+
+
 def algorithmic_flops(shape: EncoderShape, lengths: np.ndarray) -> float:
     """FLOPs of one forward pass counted on valid positions only:
     GEMMs 2*T*H*(3H + H + 2F) and attention 4*H*sum(len^2) per layer."""

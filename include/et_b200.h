@@ -177,6 +177,54 @@ int et_forward(et_handle_t handle, const void* from_tensor, const int* mask, voi
 int et_forward_host(et_handle_t handle, const void* from_tensor_host, const int* mask_host,
                     void* out_host, int batch_size, int seq_len, int* valid_word_num_out);
 
+/* ---- the model around the stack: embeddings in front, pooler behind -------
+ * The reference leaves both to TensorFlow (sample/tensorflow/modeling.py:
+ * 380-521 and 224-232) and feeds its input op with the padded embedding output.
+ * Here they run on the packed layout: embedding rows are gathered for valid
+ * tokens only (the placement the reference itself recommends,
+ * tf_op/bert_transformer_op.cu.cc:295-296) and the pooler reads first-token
+ * rows straight from the packed tensor. */
+
+/* Registers the embedding tables (copied; element type = the handle's dtype):
+ * word_table [vocab_size, H]; type_table [type_vocab_size, H] or NULL
+ * (use_token_type = False); position_table [max_position, H] or NULL
+ * (use_position_embeddings = False); LayerNorm gamma/beta [H].
+ * layernorm_eps 0 selects tf.contrib.layers.layer_norm's 1e-12. */
+int et_set_embedding_weights(et_handle_t handle, const void* word_table, int vocab_size,
+                             const void* type_table, int type_vocab_size, const void* position_table,
+                             int max_position, const void* gamma, const void* beta, float layernorm_eps,
+                             int on_host);
+
+/* Registers the pooler's dense layer: kernel [H, H] ([in, out]) and bias [H]. */
+int et_set_pooler_weights(et_handle_t handle, const void* kernel, const void* bias, int on_host);
+
+/* BertModel (sample/tensorflow/modeling.py:107-235) at inference, device
+ * buffers: input_ids / mask int32 [B,S]; token_type_ids int32 [B,S] or NULL
+ * (all zero, modeling.py:159-160).  Outputs, each may be NULL:
+ * sequence_out [B,S,H] (padded rows zero) and pooled_out [B,H] (needs pooler
+ * weights).  A sequence without tokens pools a zero first-token row.  If both
+ * are NULL the packed result stays in the handle (et_last_packed_output).
+ * seq_len > max_position is rejected (tf.assert_less_equal, modeling.py:487).
+ * Asynchronous on `stream`. */
+int et_forward_ids(et_handle_t handle, const int* input_ids, const int* token_type_ids, const int* mask,
+                   void* sequence_out, void* pooled_out, int batch_size, int seq_len, void* stream);
+
+/* Same with HOST buffers; waits for the results.  Only ids and masks go up
+ * (12 bytes per position) and only the requested outputs come back. */
+int et_forward_ids_host(et_handle_t handle, const int* input_ids_host, const int* token_type_ids_host,
+                        const int* mask_host, void* sequence_out_host, void* pooled_out_host,
+                        int batch_size, int seq_len, int* valid_word_num_out);
+
+/* The pooler alone on a packed tensor [T, H] (e.g. the last et_layer output):
+ * pooled_out[b] = tanh(packed[cu_seqlens[b]] * kernel + bias).  cu_seqlens
+ * NULL selects the array of the last et_input/et_forward* call on the handle. */
+int et_pooler(et_handle_t handle, const void* packed, const int* cu_seqlens, void* pooled_out,
+              int batch_size, int seq_len, void* stream);
+
+/* Packed [T, H] result of the last et_forward* call (device pointer, valid
+ * until the next call on the handle) and the device pointer to T. */
+int et_last_packed_output(et_handle_t handle, const void** packed, const int** valid_word_num);
+
 /* Reads the device status word (synchronises `stream`): 0 = no device-side
  * wait expired since the last call.  Non-zero encodes kernel id and wait site;
  * the word is cleared. */
@@ -203,7 +251,9 @@ enum {
   ET_PROF_GEMM_FFN1 = 6,
   ET_PROF_GEMM_FFN2 = 7,
   ET_PROF_RESTORE_PADDING = 8,
-  ET_PROF_NUM = 9
+  ET_PROF_EMBEDDING = 9,
+  ET_PROF_POOLER = 10,
+  ET_PROF_NUM = 11
 };
 int et_set_profiling(et_handle_t handle, int enable);
 int et_get_profile(et_handle_t handle, double* ms_out, long long* launches_out, int reset);
@@ -263,6 +313,26 @@ int et_restore_padding(int dtype, const void* from_tensor, const int* batch_idx,
                        const int* valid_word_num, void* to_tensor, int batch_size, int seq_len,
                        int hidden, void* stream);
 
+/* Embedding lookup + token-type and position rows + LayerNorm
+ * (sample/tensorflow/modeling.py:380-521) for the valid tokens only: packed row
+ * v = (batch_idx[v], word_idx[v]) receives
+ * LN(word_table[input_ids[b,s]] + type_table[token_type_ids[b,s]] + position_table[s]).
+ * token_type_ids NULL = all zero; type_table / position_table NULL = that term
+ * is absent.  An id outside its table contributes a zero row (TensorFlow's GPU
+ * gather / one-hot matmul).  The caller guarantees seq_len <= rows of
+ * position_table. */
+int et_embedding_layernorm(int dtype, const int* input_ids, const int* token_type_ids,
+                           const int* batch_idx, const int* word_idx, const int* valid_word_num,
+                           const void* word_table, int vocab_size, const void* type_table,
+                           int type_vocab_size, const void* position_table, const void* gamma,
+                           const void* beta, float eps, void* to_tensor, int batch_size, int seq_len,
+                           int hidden, void* stream);
+
+/* First-token rows of a packed tensor (sample/tensorflow/modeling.py:228):
+ * out[b] = packed[cu_seqlens[b]], a zero row for a sequence without tokens. */
+int et_gather_first_tokens(int dtype, const void* packed, const int* cu_seqlens, void* out,
+                           int batch_size, int max_tokens, int hidden, void* stream);
+
 /* add_QKV_bias_padding_kernelLauncher (cuda/attention.cu:106-242) without the
  * re-padding: q,k,v packed [T,H] + bias -> head-major packed [3, heads, max_tokens, d]. */
 int et_add_qkv_bias_transpose(int dtype, const void* q, const void* bias_q, const void* k,
@@ -308,7 +378,8 @@ int et_attention_tiles(const void* q, const void* k, const void* v, long long to
 /* cublasGemmEx call sites of the layer functor
  * (tf_op/bert_transformer_op.cu.cc:110-141,200-209,215-225,229-240):
  * C[M,N] = epilogue(A[M,K] * W[K,N] (+ bias)), W row-major [in,out] as the
- * reference passes it.  epilogue: 0 none, 1 +bias, 2 gelu(+bias).  M is read
+ * reference passes it.  epilogue: 0 none, 1 +bias, 2 gelu(+bias), 3 tanh(+bias)
+ * (the pooler's dense layer, sample/tensorflow/modeling.py:229-232).  M is read
  * from the device (`m_ptr`), `max_m` bounds it.  The tcgen05 path needs
  * `w_packed` = the [N,K] K-major copy made by et_pack_weight (w may be NULL);
  * the CUDA-core path (use_simt, always for fp32) reads `w`. */

@@ -100,6 +100,8 @@ def transformer_model(from_tensor, attention_mask, weights: Sequence, heads: int
     flat list of 16 arrays per layer in the order of
     python/effective_transformer/__init__.py:55-74.  Returns [B, S, H]."""
     def prep(a):
+        if isinstance(a, torch.Tensor) and a.dtype == compute_dtype and not round_to_fp16:
+            return a                                         # already in the working precision
         t = _t(a, torch.float32)
         if round_to_fp16:
             t = t.to(torch.float16).to(torch.float32)
@@ -128,6 +130,71 @@ def transformer_model(from_tensor, attention_mask, weights: Sequence, heads: int
             all_layers.append(out.reshape(batch, seq, hidden))
         prev = out
     return prev.reshape(batch, seq, hidden)                  # :890-892
+
+
+def embedding_lookup(input_ids, word_table: torch.Tensor) -> torch.Tensor:
+    """sample/tensorflow/modeling.py:380-422: gather of word_table rows,
+    [B, S] ids -> [B, S, H]."""
+    ids = torch.from_numpy(np.asarray(input_ids).astype(np.int64))
+    return word_table[ids]
+
+
+def embedding_postprocessor(x: torch.Tensor, token_type_ids, type_table: Optional[torch.Tensor],
+                            position_table: Optional[torch.Tensor], gamma: torch.Tensor,
+                            beta: torch.Tensor, eps: float = TF_LAYER_NORM_EPS) -> torch.Tensor:
+    """sample/tensorflow/modeling.py:425-521: + token-type rows (:471-484, the
+    one-hot matmul is a row gather), + the first S position rows (:486-518),
+    then LayerNorm (:520; dropout is the identity at inference)."""
+    b, s, h = x.shape
+    out = x
+    if type_table is not None:
+        tt = torch.from_numpy(np.asarray(token_type_ids).astype(np.int64))
+        out = out + type_table[tt]
+    if position_table is not None:
+        assert s <= position_table.shape[0]                  # :487
+        out = out + position_table[:s].unsqueeze(0)
+    return layer_norm(out, gamma, beta, eps)
+
+
+def pooler(sequence_output: torch.Tensor, kernel: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """sample/tensorflow/modeling.py:224-232: tanh(dense(first token)),
+    [B, S, H] -> [B, H]."""
+    return torch.tanh(dense(sequence_output[:, 0, :], kernel, bias))
+
+
+def bert_model(heads, mask: np.ndarray, weights: Sequence, head_num: int, d: int,
+               compute_dtype=torch.float32, round_to_fp16: bool = False,
+               embedding_eps: float = TF_LAYER_NORM_EPS, ln_eps: float = TF_LAYER_NORM_EPS,
+               zero_padded_rows: bool = False):
+    """BertModel of sample/tensorflow/modeling.py:107-235 at inference:
+    embeddings -> encoder stack -> pooler.  ``heads`` carries the ids and
+    tables (an object with the fields of workloads.ModelHeads).  Returns
+    (embedding_output [B,S,H], sequence_output [B,S,H], pooled_output [B,H]).
+
+    ``zero_padded_rows``: the padding-free ops hand back zeros at padded
+    positions (tf_op/bert_transformer_op.cu.cc:354-360), so a sequence whose
+    first position is padding pools a zero row; set it to state that variant."""
+    def prep(a):
+        t = _t(a, torch.float32)
+        if round_to_fp16:
+            t = t.to(torch.float16).to(torch.float32)
+        return t.to(compute_dtype)
+
+    emb = embedding_lookup(heads.input_ids, prep(heads.word_table))
+    emb = embedding_postprocessor(emb, heads.token_type_ids, prep(heads.type_table),
+                                  prep(heads.position_table), prep(heads.ln_gamma),
+                                  prep(heads.ln_beta), embedding_eps)
+    if round_to_fp16:
+        emb = emb.to(torch.float16).to(compute_dtype)        # the stage's output tensor is fp16
+    b, s = mask.shape
+    am = np.tile(mask, s).reshape(b, s, s)                   # modeling.py:524-555 for a key mask
+    seq_out = transformer_model(emb, am, weights, head_num, d, compute_dtype=compute_dtype,
+                                round_to_fp16=round_to_fp16, ln_eps=ln_eps)
+    pool_in = seq_out
+    if zero_padded_rows:
+        pool_in = seq_out * torch.from_numpy(np.asarray(mask)).to(compute_dtype).unsqueeze(-1)
+    pooled = pooler(pool_in, prep(heads.pooler_kernel), prep(heads.pooler_bias))
+    return emb, seq_out, pooled
 
 
 def valid_rows(y: torch.Tensor, mask: np.ndarray) -> torch.Tensor:

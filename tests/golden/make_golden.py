@@ -33,6 +33,11 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 
 def independent_encoder(wl: W.Workload) -> torch.Tensor:
+    return independent_encoder_from(wl, torch.from_numpy(wl.from_tensor).double())
+
+
+def independent_encoder_from(wl: W.Workload, x: torch.Tensor) -> torch.Tensor:
+    """The independent encoder stack on a given float64 input [B, S, H] and wl.mask."""
     from transformers import BertConfig
     from transformers.models.bert.modeling_bert import BertEncoder
     sh = wl.spec.shape
@@ -54,7 +59,6 @@ def independent_encoder(wl: W.Workload) -> torch.Tensor:
             layer.intermediate.dense.weight.copy_(w[10].T); layer.intermediate.dense.bias.copy_(w[11])
             layer.output.dense.weight.copy_(w[12].T); layer.output.dense.bias.copy_(w[13])
             layer.output.LayerNorm.bias.copy_(w[14]); layer.output.LayerNorm.weight.copy_(w[15])
-        x = torch.from_numpy(wl.from_tensor).double()
         am = torch.from_numpy(W.attention_mask_from_input_mask(wl.mask)).double()
         ext = (1.0 - am[:, None, :, :]) * -10000.0
         return enc(x, attention_mask=ext)[0]

@@ -112,3 +112,53 @@ def test_valid_word_num_last_mask_rule():
     assert P.valid_word_num(np.array([1, 0, 1, 1])) == 3
     assert P.valid_word_num(np.array([1, 0, 1, 0])) == 2
     assert P.valid_word_num(np.array([], dtype=np.int32)) == 0
+
+
+def tiny_model_case():
+    """The case of tests/golden/make_golden_heads.py (sequence 3 emptied)."""
+    spec = W.tiny_spec()
+    wl = W.make_workload(spec, random_gamma_beta=True)
+    lengths = wl.lengths.copy()
+    lengths[3] = 0
+    mask = W.prefix_mask(lengths, spec.max_seq_len)
+    heads = W.make_model_heads(spec, lengths, 1000, 2, 64)
+    return spec, wl, lengths, mask, heads
+
+
+def test_model_heads_oracle_matches_golden_and_independent_implementation():
+    d = np.load(os.path.join(GOLD, "tiny_model_fp64.npz"))
+    spec, wl, lengths, mask, heads = tiny_model_case()
+    assert np.array_equal(mask, d["mask"]) and np.array_equal(heads.input_ids, d["input_ids"])
+    assert np.array_equal(heads.token_type_ids, d["token_type_ids"])
+    e, y, p = O.bert_model(heads, mask, wl.weights, spec.shape.head_num, spec.shape.size_per_head,
+                           compute_dtype=torch.float64)
+    for got, name in ((e.numpy(), "embedding"), (O.valid_rows(y, mask).numpy(), "sequence"), (p.numpy(), "pooled")):
+        assert np.abs(got - d[name + "_oracle64"]).max() < 1e-12, name
+        assert np.abs(got - d[name + "_independent"]).max() < 1e-12, name   # Hugging Face, float64
+
+
+def test_embedding_stage_variants_and_pooler_of_empty_sequence():
+    spec, wl, lengths, mask, heads = tiny_model_case()
+    t = lambda a: torch.from_numpy(a).double()
+    x = O.embedding_lookup(heads.input_ids, t(heads.word_table))
+    full = O.embedding_postprocessor(x, heads.token_type_ids, t(heads.type_table), t(heads.position_table),
+                                     t(heads.ln_gamma), t(heads.ln_beta))
+    # hand-rolled row: word + type + position, then LN
+    b, s = 1, 2
+    row = (heads.word_table[heads.input_ids[b, s]].astype(np.float64)
+           + heads.type_table[heads.token_type_ids[b, s]] + heads.position_table[s])
+    row = (row - row.mean()) / np.sqrt(row.var() + 1e-12) * heads.ln_gamma + heads.ln_beta
+    assert np.abs(full[b, s].numpy() - row).max() < 1e-12
+    # use_token_type = False / use_position_embeddings = False drop exactly that term
+    no_type = O.embedding_postprocessor(x, None, None, t(heads.position_table), t(heads.ln_gamma), t(heads.ln_beta))
+    no_pos = O.embedding_postprocessor(x, heads.token_type_ids, t(heads.type_table), None, t(heads.ln_gamma),
+                                       t(heads.ln_beta))
+    assert not torch.allclose(no_type, full) and not torch.allclose(no_pos, full)
+    # the zero-row variant: an empty sequence pools tanh(bias)
+    _, _, pooled = O.bert_model(heads, mask, wl.weights, spec.shape.head_num, spec.shape.size_per_head,
+                                compute_dtype=torch.float64, zero_padded_rows=True)
+    assert np.abs(pooled[3].numpy() - np.tanh(heads.pooler_bias.astype(np.float64))).max() < 1e-12
+    _, _, pooled_tf = O.bert_model(heads, mask, wl.weights, spec.shape.head_num, spec.shape.size_per_head,
+                                   compute_dtype=torch.float64)
+    keep = lengths > 0
+    assert torch.equal(pooled[keep], pooled_tf[keep])
