@@ -15,6 +15,9 @@ over all ranks.  Prints one JSON line (rank 0).
   e2e       the same through et_forward_host with pinned HOST buffers: the
             host->device copy of the batch and the device->host copy of the
             [B,S,H] result are inside the timed region
+  e2e_from_token_ids  (informational) the same batch given as token ids through
+            et_forward_ids_host: embeddings of the valid tokens, the stack and the
+            pooler; 12 bytes per position go up, the pooled [B,H] rows come back
   roofline  the tcgen05 GEMM (the dominant kernel): algorithmic FLOPs / CUDA-
             event time of its launches inside the timed steps
   cpu_baseline  the CPU oracle (fp32 restatement of the reference's padded TF
@@ -171,6 +174,9 @@ def main():
     ap.add_argument("--cpu-sample", type=int, default=128, help="sequences in the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--graph", action="store_true",
+                    help="time CUDA-graph replays of the pass (et_graph_capture); the per-kernel roofline then comes "
+                         "from a second, eager pass of the same steps")
     args = ap.parse_args()
     spec = W.WORKLOADS[args.workload]
     if args.impl == "reference":
@@ -226,8 +232,13 @@ def main():
         eng.forward(x, mask, out)
     torch.cuda.synchronize()
     assert eng.device_status() == 0, "a device-side wait expired during warm-up"
+    if args.graph:
+        eng.capture(x, mask, out)
+        for _ in range(2):
+            eng.replay()
+        torch.cuda.synchronize()
     eng.get_profile(reset=True)
-    eng.set_profiling(True)
+    eng.set_profiling(not args.graph)
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -237,7 +248,10 @@ def main():
     for i in range(args.steps):
         flush.zero_()                         # evict the previous step's tensors from L2 (untimed)
         starts[i].record()
-        eng.forward(x, mask, out)
+        if args.graph:
+            eng.replay()
+        else:
+            eng.forward(x, mask, out)
         ends[i].record()
     barrier()
     clocks = sampler.stop() if rank == 0 else None
@@ -245,6 +259,17 @@ def main():
     step_ms = [a.elapsed_time(e) for a, e in zip(starts, ends)]
     total_ms = sum(step_ms)
     prof = eng.get_profile(reset=True)
+    if args.graph:
+        # replayed kernels cannot be bracketed by events: per-kernel times from an eager pass of the same steps
+        launches_replayed = {k: v[1] for k, v in prof.items()}
+        eng.set_profiling(True)
+        for i in range(args.steps):
+            flush.zero_()
+            eng.forward(x, mask, out)
+        torch.cuda.synchronize()
+        eng.set_profiling(False)
+        prof = eng.get_profile(reset=True)
+        assert {k: v[1] for k, v in prof.items()} == launches_replayed
     assert eng.device_status() == 0, "a device-side wait expired during the timed steps"
 
     # ---- end to end through the host-buffer entry point -----------------------
@@ -266,16 +291,36 @@ def main():
         e2e_ms = 1000.0 * (time.perf_counter() - t0)
         barrier()
 
+    # ---- the same batch as token ids: embeddings in front, pooler behind ------------
+    # (not the headline: ids + mask go up, only the pooled [B,H] rows come back)
+    ids_ms = None
+    if not args.no_e2e:
+        mh_ = W.make_model_heads(spec, lengths)
+        eng.set_embeddings(mh_.word_table, mh_.type_table, mh_.position_table, mh_.ln_gamma, mh_.ln_beta)
+        eng.set_pooler(mh_.pooler_kernel, mh_.pooler_bias)
+        pin = lambda a: torch.from_numpy(a).pin_memory().numpy()
+        ids_h, types_h, mask_h = pin(mh_.input_ids), pin(mh_.token_type_ids), pin(mask_np)
+        for _ in range(2):
+            eng.forward_ids_host(ids_h, mask_h, types_h, sequence_output=False, pooled_output=True)
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            eng.forward_ids_host(ids_h, mask_h, types_h, sequence_output=False, pooled_output=True)
+        torch.cuda.synchronize()
+        ids_ms = 1000.0 * (time.perf_counter() - t0)
+        barrier()
+
     # ---- reduce over ranks -------------------------------------------------------
-    stats = torch.tensor([total_ms, e2e_ms or 0.0, float(tokens_rank)], dtype=torch.float64, device=dev)
+    stats = torch.tensor([total_ms, e2e_ms or 0.0, float(tokens_rank), ids_ms or 0.0], dtype=torch.float64,
+                         device=dev)
     if world > 1:
         mx = stats.clone()
         dist.all_reduce(mx, op=dist.ReduceOp.MAX)
         sm = stats.clone()
         dist.all_reduce(sm, op=dist.ReduceOp.SUM)
-        total_ms, e2e_total_ms, tokens_all = float(mx[0]), float(mx[1]), float(sm[2])
+        total_ms, e2e_total_ms, tokens_all, ids_total_ms = float(mx[0]), float(mx[1]), float(sm[2]), float(mx[3])
     else:
-        e2e_total_ms, tokens_all = float(stats[1]), float(stats[2])
+        e2e_total_ms, tokens_all, ids_total_ms = float(stats[1]), float(stats[2]), float(stats[3])
 
     if rank == 0:
         peaks, peak_src = read_peaks()
@@ -299,7 +344,9 @@ def main():
             "config": {"workload": spec.name, "sequences_per_gpu": b, "max_seq_len": s,
                        "valid_tokens_rank0": tokens_rank, "valid_tokens_total": int(tokens_all),
                        "layers": sh.num_layers, "hidden": h, "sharding": "sequences, token-balanced, no collective",
-                       "l2": "256 MB buffer written between timed steps (untimed)"},
+                       "l2": "256 MB buffer written between timed steps (untimed)",
+                       "launch": ("cuda-graph replay (et_graph_launch); per-kernel times from a second, eager pass"
+                                  if args.graph else "eager (et_forward), per-kernel events inside the timed steps")},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
                          "frac": (achieved / peak_tf) if (achieved and peak_tf) else None,
                          "traffic": NCU_GEMM_TRAFFIC.get(spec.name),
@@ -317,6 +364,13 @@ def main():
             line["e2e"] = {"value": tokens_all / (e2e_total_ms / args.steps / 1000.0), "unit": UNIT,
                            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                            "ms_per_step": e2e_total_ms / args.steps}
+        if ids_ms is not None:
+            line["e2e_from_token_ids"] = {
+                "value": tokens_all / (ids_total_ms / args.steps / 1000.0), "unit": UNIT,
+                "ms_per_step": ids_total_ms / args.steps, "h2d_bytes_per_step": 3 * b * s * 4,
+                "d2h_bytes_per_step": b * h * x.element_size() + 8,
+                "call": "et_forward_ids_host: ids/types/mask up, embeddings for valid tokens only, "
+                        "stack, pooler; pooled [B,H] down"}
         if world == 1 and not args.no_cpu_baseline:
             tps, dt, toks, threads = cpu_oracle_throughput(spec, args.cpu_sample)
             line["cpu_baseline"] = {

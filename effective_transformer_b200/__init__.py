@@ -264,6 +264,41 @@ class EffectiveTransformer:
                                         batch_size, seq_len, _stream()), self._h)
         return out
 
+    # ---- CUDA-graph replay --------------------------------------------------
+    def capture(self, from_tensor: torch.Tensor, input_mask: torch.Tensor, out: torch.Tensor) -> None:
+        """Records forward(from_tensor, input_mask, out) as a CUDA graph.  The three
+        tensors are the graph's fixed buffers: write each new batch (any mask) into
+        them and call replay().  input_mask must be int32 and contiguous."""
+        self._check_act(from_tensor, "from_tensor")
+        self._check_act(out, "out")
+        if input_mask.dtype != torch.int32 or not input_mask.is_contiguous():
+            raise ValueError("input_mask must be a contiguous int32 tensor (it is a fixed graph buffer)")
+        b, s, _ = from_tensor.shape
+        self._graph_buffers = (from_tensor, input_mask, out)   # keep them alive
+        _capi.check(self._lib.et_graph_capture(self._h, _ptr(from_tensor), _ptr(input_mask), _ptr(out), b, s),
+                    self._h)
+
+    def capture_ids(self, input_ids: torch.Tensor, input_mask: torch.Tensor,
+                    token_type_ids: Optional[torch.Tensor], sequence_out: Optional[torch.Tensor],
+                    pooled_out: Optional[torch.Tensor]) -> None:
+        """Records forward_ids on fixed buffers (all int32 inputs contiguous)."""
+        for t in (input_ids, input_mask, token_type_ids):
+            if t is not None and (t.dtype != torch.int32 or not t.is_contiguous()):
+                raise ValueError("ids and masks must be contiguous int32 tensors (fixed graph buffers)")
+        b, s = input_ids.shape
+        self._graph_buffers = (input_ids, input_mask, token_type_ids, sequence_out, pooled_out)
+        _capi.check(self._lib.et_graph_capture_ids(self._h, _ptr(input_ids), _ptr(token_type_ids),
+                                                   _ptr(input_mask), _ptr(sequence_out), _ptr(pooled_out), b, s),
+                    self._h)
+
+    def replay(self) -> None:
+        """Enqueues the captured pass on the current stream."""
+        _capi.check(self._lib.et_graph_launch(self._h, _stream()), self._h)
+
+    def release_graph(self) -> None:
+        _capi.check(self._lib.et_graph_release(self._h), self._h)
+        self._graph_buffers = None
+
     def set_profiling(self, on: bool) -> None:
         _capi.check(self._lib.et_set_profiling(self._h, 1 if on else 0), self._h)
 

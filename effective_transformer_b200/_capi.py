@@ -74,6 +74,10 @@ SIGNATURES = {
     "et_forward_ids_host": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, ip]),
     "et_pooler": (i32, [vp, vp, vp, vp, i32, i32, vp]),
     "et_last_packed_output": (i32, [vp, C.POINTER(vp), C.POINTER(vp)]),
+    "et_graph_capture": (i32, [vp, vp, vp, vp, i32, i32]),
+    "et_graph_capture_ids": (i32, [vp, vp, vp, vp, vp, vp, i32, i32]),
+    "et_graph_launch": (i32, [vp, vp]),
+    "et_graph_release": (i32, [vp]),
     "et_device_status": (i32, [vp, vp, ip]),
     "et_last_padding_info": (i32, [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.POINTER(vp)]),
     "et_set_profiling": (i32, [vp, i32]),

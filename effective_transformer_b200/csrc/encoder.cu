@@ -128,6 +128,10 @@ struct et_handle_s {
   cudaEvent_t in_done[kMaxChunks] = {}, comp_done[kMaxChunks] = {};
   int host_chunks = 2;
   int* host_pinned = nullptr;  // [2 + kMaxChunks]: valid_word_num, status, per-chunk token counts
+  // one captured forward pass (et_graph_capture*): replayed by et_graph_launch
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t graph_exec = nullptr;
+  long long graph_launches[ET_PROF_NUM] = {};  // kernels per category inside the captured pass
   std::string last_error;
 };
 
@@ -344,6 +348,7 @@ int output_impl(et_handle_t h, const et_output_param_t* p) {
   return ET_OK;
 }
 
+void graph_release(et_handle_t h);
 int stack_impl(et_handle_t h, int batch, int seq, cudaStream_t s);
 int restore_impl(et_handle_t h, void* out, int batch, int seq, cudaStream_t s);
 
@@ -618,6 +623,8 @@ int et_destroy(et_handle_t h) {
   if (h == nullptr) return ET_OK;
   DeviceGuard guard(h->cfg.device);
   cudaDeviceSynchronize();
+  if (h->graph_exec) cudaGraphExecDestroy(h->graph_exec);
+  if (h->graph) cudaGraphDestroy(h->graph);
   for (void* p : h->ws.allocations) cudaFree(p);
   for (void* p : h->model.emb_allocs) cudaFree(p);
   for (void* p : h->model.pool_allocs) cudaFree(p);
@@ -847,6 +854,7 @@ int et_set_embedding_weights(et_handle_t h, const void* word_table, int vocab_si
   ModelWeights& mw = h->model;
   cudaStream_t s = h->own_stream;
   ET_CUDA(h, cudaDeviceSynchronize());  // nothing may still read the tables being replaced
+  graph_release(h);  // a captured pass holds the addresses of the tables being freed
   for (void* p : mw.emb_allocs) cudaFree(p);
   mw.emb_allocs.clear();
   mw.emb_ready = false;
@@ -878,6 +886,7 @@ int et_set_pooler_weights(et_handle_t h, const void* kernel, const void* bias, i
   ModelWeights& mw = h->model;
   cudaStream_t s = h->own_stream;
   ET_CUDA(h, cudaDeviceSynchronize());
+  graph_release(h);
   for (void* p : mw.pool_allocs) cudaFree(p);
   mw.pool_allocs.clear();
   mw.pool_ready = false;
@@ -971,6 +980,104 @@ int et_last_packed_output(et_handle_t h, const void** packed, const int** valid_
   if (h == nullptr) return ET_INVALID_ARGUMENT;
   if (packed) *packed = h->ws.x;
   if (valid_word_num) *valid_word_num = h->ws.valid_word_num;
+  return ET_OK;
+}
+
+}  // extern "C"
+
+namespace {
+
+void graph_release(et_handle_t h) {
+  if (h->graph_exec) cudaGraphExecDestroy(h->graph_exec);
+  if (h->graph) cudaGraphDestroy(h->graph);
+  h->graph_exec = nullptr;
+  h->graph = nullptr;
+}
+
+// Runs `pass` once eagerly (one-time function attributes, driver entry points
+// and tensor-map encodes of first use happen outside the capture), then
+// records the same pass on the handle's own stream into a graph.  The pass only
+// enqueues kernels: the valid-token count stays on the device, so the graph
+// depends on the buffers and on (B, S) but not on the batch's contents.
+template <typename Pass>
+int capture_pass(et_handle_t h, Pass pass) {
+  graph_release(h);
+  cudaStream_t s = h->own_stream;
+  int rc = pass(s);
+  if (rc != ET_OK) return rc;
+  ET_CUDA(h, cudaStreamSynchronize(s));
+  const bool was_profiling = h->prof.enabled;
+  h->prof.enabled = false;  // event pairs inside a capture cannot be timed
+  long long before[ET_PROF_NUM];
+  for (int i = 0; i < ET_PROF_NUM; ++i) before[i] = h->prof.launches[i];
+  cudaError_t e = cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal);
+  if (e != cudaSuccess) {
+    h->prof.enabled = was_profiling;
+    return cuda_fail(h, e, "cudaStreamBeginCapture");
+  }
+  rc = pass(s);
+  cudaGraph_t g = nullptr;
+  e = cudaStreamEndCapture(s, &g);
+  h->prof.enabled = was_profiling;
+  for (int i = 0; i < ET_PROF_NUM; ++i) {
+    h->graph_launches[i] = h->prof.launches[i] - before[i];
+    h->prof.launches[i] = before[i];  // nothing ran yet: launches are counted per replay
+  }
+  if (rc != ET_OK || e != cudaSuccess || g == nullptr) {
+    if (g) cudaGraphDestroy(g);
+    cudaGetLastError();
+    return rc != ET_OK ? rc : cuda_fail(h, e, "cudaStreamEndCapture");
+  }
+  h->graph = g;
+  e = cudaGraphInstantiate(&h->graph_exec, g, 0);
+  if (e != cudaSuccess) {
+    graph_release(h);
+    return cuda_fail(h, e, "cudaGraphInstantiate");
+  }
+  return ET_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int et_graph_capture(et_handle_t h, const void* from_tensor, const int* mask, void* out, int batch_size,
+                     int seq_len) {
+  ET_TRY
+  if (h == nullptr) return ET_INVALID_ARGUMENT;
+  DeviceGuard guard(h->cfg.device);
+  return capture_pass(h, [&](cudaStream_t s) {
+    return forward_impl(h, from_tensor, mask, out, batch_size, seq_len, s);
+  });
+  ET_CATCH(h)
+}
+
+int et_graph_capture_ids(et_handle_t h, const int* input_ids, const int* token_type_ids, const int* mask,
+                         void* sequence_out, void* pooled_out, int batch_size, int seq_len) {
+  ET_TRY
+  if (h == nullptr) return ET_INVALID_ARGUMENT;
+  DeviceGuard guard(h->cfg.device);
+  return capture_pass(h, [&](cudaStream_t s) {
+    return forward_ids_impl(h, input_ids, token_type_ids, mask, sequence_out, pooled_out, batch_size, seq_len, s);
+  });
+  ET_CATCH(h)
+}
+
+int et_graph_launch(et_handle_t h, void* stream) {
+  ET_TRY
+  if (h == nullptr) return ET_INVALID_ARGUMENT;
+  if (h->graph_exec == nullptr) return set_error(h, ET_NOT_READY, "no captured pass: call et_graph_capture first");
+  DeviceGuard guard(h->cfg.device);
+  ET_CUDA(h, cudaGraphLaunch(h->graph_exec, static_cast<cudaStream_t>(stream)));
+  for (int i = 0; i < ET_PROF_NUM; ++i) h->prof.launches[i] += h->graph_launches[i];
+  return ET_OK;
+  ET_CATCH(h)
+}
+
+int et_graph_release(et_handle_t h) {
+  if (h == nullptr) return ET_INVALID_ARGUMENT;
+  DeviceGuard guard(h->cfg.device);
+  graph_release(h);
   return ET_OK;
 }
 

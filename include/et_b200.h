@@ -225,6 +225,27 @@ int et_pooler(et_handle_t handle, const void* packed, const int* cu_seqlens, voi
  * until the next call on the handle) and the device pointer to T. */
 int et_last_packed_output(et_handle_t handle, const void** packed, const int** valid_word_num);
 
+/* ---- CUDA-graph replay ------------------------------------------------------
+ * The valid-token count never leaves the device, so one forward pass is a fixed
+ * sequence of launches for given buffers and (B, S): it can be captured once
+ * and replayed for every batch written into the same buffers, whatever its
+ * mask.  That removes the host's launch cost (about 90 launches per 12-layer
+ * pass), which dominates for small batches.  No reference counterpart.
+ * et_graph_capture runs et_forward(from_tensor, mask, out, B, S) once on a
+ * stream of the handle (so the buffers must hold a valid batch) and records
+ * it; et_graph_capture_ids does the same for et_forward_ids.  A handle holds
+ * one captured pass; capturing again replaces it; registering embedding or
+ * pooler weights discards it.  et_graph_launch enqueues the pass on `stream`.
+ * Per-kernel timing (et_set_profiling) does not see replayed kernels; their
+ * launch counts are added per replay. */
+int et_graph_capture(et_handle_t handle, const void* from_tensor, const int* mask, void* out,
+                     int batch_size, int seq_len);
+int et_graph_capture_ids(et_handle_t handle, const int* input_ids, const int* token_type_ids,
+                         const int* mask, void* sequence_out, void* pooled_out, int batch_size,
+                         int seq_len);
+int et_graph_launch(et_handle_t handle, void* stream);
+int et_graph_release(et_handle_t handle);
+
 /* Reads the device status word (synchronises `stream`): 0 = no device-side
  * wait expired since the last call.  Non-zero encodes kernel id and wait site;
  * the word is cleared. */
