@@ -102,6 +102,28 @@ class EffectiveTransformer:
     def set_debug_simt(self, on: bool) -> None:
         _capi.check(self._lib.et_set_debug_simt(self._h, 1 if on else 0), self._h)
 
+    def set_general_mask(self, on: bool) -> None:
+        """When on, effective_transformer() reads its attention_mask [B,S,S] (dtype of
+        the handle, 1 = attend) through the general-mask attention kernel; when off
+        (default) the mask must be the key-only tile of input_mask and is not read."""
+        _capi.check(self._lib.et_set_general_mask(self._h, 1 if on else 0), self._h)
+
+    def forward_general_mask(self, from_tensor: torch.Tensor, input_mask: torch.Tensor,
+                             attention_mask: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """forward() under a general [B,S,S] attention mask (semantics of the
+        reference op: padded keys take part with K = V = 0)."""
+        self._check_act(from_tensor, "from_tensor")
+        self._check_act(attention_mask, "attention_mask")
+        b, s, _ = from_tensor.shape
+        if tuple(attention_mask.shape) != (b, s, s):
+            raise ValueError("attention_mask must be [B, S, S]")
+        mask = self._i32(input_mask)
+        if out is None:
+            out = torch.empty_like(from_tensor)
+        _capi.check(self._lib.et_forward_general_mask(self._h, _ptr(from_tensor), _ptr(mask), _ptr(attention_mask),
+                                                      _ptr(out), b, s, _stream()), self._h)
+        return out
+
     # ---- the three operators ----------------------------------------------
     def _check_act(self, t: torch.Tensor, name: str) -> None:
         if t.dtype != self.dtype or not t.is_cuda or not t.is_contiguous():

@@ -95,6 +95,10 @@ SIGNATURES = {
                                      i32, i32, i32, vp]),
     "et_gather_first_tokens": (i32, [i32, vp, vp, vp, i32, i32, i32, vp]),
     "et_attention": (i32, [i32, vp, vp, vp, i64, i64, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp]),
+    "et_attention_general_mask": (i32, [i32, vp, vp, vp, i64, i64, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32,
+                                        vp]),
+    "et_set_general_mask": (i32, [vp, i32]),
+    "et_forward_general_mask": (i32, [vp, vp, vp, vp, vp, i32, i32, vp]),
     "et_attention_plan_ints": (C.c_size_t, [i32, i32]),
     "et_attention_plan": (i32, [vp, i32, i32, vp, vp]),
     "et_attention_tiles": (i32, [vp, vp, vp, i64, i64, vp, vp, i32, i32, i32, i32, i32, vp, vp]),

@@ -190,6 +190,16 @@ template <typename T>
 cudaError_t launch_attention_simt(const T* q, const T* k, const T* v, long long token_stride,
                                   long long head_stride, T* ctx, const int* cu_seqlens, int batch,
                                   int max_seq, int heads, int d, cudaStream_t stream);
+// The same under a general [B, S, S] mask with the reference op's semantics
+// (padded keys take part with K = V = 0).  pos_row[b*S+p] = packed row of
+// position p or -1, made by launch_position_rows (a memset and one kernel).
+cudaError_t launch_position_rows(const int* batch_idx, const int* word_idx, const int* t_ptr, int batch,
+                                 int seq, int* pos_row, cudaStream_t stream);
+template <typename T>
+cudaError_t launch_attention_masked_simt(const T* q, const T* k, const T* v, long long token_stride,
+                                         long long head_stride, T* ctx, const T* attr_mask,
+                                         const int* cu_seqlens, const int* word_idx, const int* pos_row,
+                                         int batch, int seq, int heads, int d, cudaStream_t stream);
 // Tensor-core attention (TMA-fed, mma.sync), fp16.  q/k/v hold max_tokens rows.
 cudaError_t launch_attention_tc(const __half* q, const __half* k, const __half* v,
                                 long long token_stride, long long head_stride, __half* ctx,

@@ -84,6 +84,7 @@ struct Workspace {
   int* cu_seqlens = nullptr;  // [B+1]
   int* lens_scratch = nullptr;
   int* attn_plan = nullptr;   // tile plan of the tcgen05 attention (made once per batch)
+  int* pos_row = nullptr;     // [B*S] position -> packed row (general-mask attention)
   int* valid_word_num = nullptr;
   int* status = nullptr;
   std::vector<void*> allocations;
@@ -117,6 +118,10 @@ struct et_handle_s {
   size_t esize = 0;
   float eps = 1e-6f;
   bool use_simt = false;
+  bool general_mask = false;  // et_set_general_mask: et_layer reads attr_mask
+  // general [B,S,S] mask of the pass being enqueued (null: key-only mask, fast kernels)
+  const void* cur_attr_mask = nullptr;
+  const int* cur_word_idx = nullptr;
   std::vector<LayerWeights> layers;
   ModelWeights model;
   Workspace ws;
@@ -207,7 +212,7 @@ size_t workspace_bytes_for(const et_handle_s* h, size_t batch, size_t seq) {
   total += cap * 3 * hid * e;          // qkv
   total += cap * f * e;                // ffn
   total += batch * seq * hid * e * 2;  // staging in/out
-  total += batch * seq * 4 * 7;        // mask / id / type staging + 4 index arrays
+  total += batch * seq * 4 * 8;        // mask / id / type staging + 5 index arrays
   total += round_up(batch, 128) * hid * e * 2;  // first-token rows, pooled output
   total += (batch * 3 + 8) * 4;
   return total;
@@ -275,7 +280,12 @@ int run_layer(et_handle_t h, const LayerWeights& lw, const T* x_in, T* x_out, co
   // Q,K,V projections + bias in one GEMM -> [T, 3H]
   ET_LAUNCH(h, ET_PROF_GEMM_QKV, 1, s, gemm(x_in, lw.wqkv, lw.wqkv_t, lw.bqkv, qkv, 3 * hid, hid, kEpiBias));
   // attention straight from the [T, 3H] buffer to packed context [T, H]
-  if (tc && seq <= 128)
+  if (h->cur_attr_mask != nullptr)
+    ET_LAUNCH(h, ET_PROF_ATTENTION, 1, s,
+              launch_attention_masked_simt<T>(qkv, qkv + hid, qkv + 2 * hid, 3LL * hid, d, ctx,
+                                              B(h->cur_attr_mask), cu_seqlens, h->cur_word_idx, ws.pos_row,
+                                              batch, seq, heads, d, s));
+  else if (tc && seq <= 128)
     ET_LAUNCH(h, ET_PROF_ATTENTION, 1, s,
               launch_attention_tcgen05(reinterpret_cast<const __half*>(qkv),
                                        reinterpret_cast<const __half*>(qkv) + hid,
@@ -386,7 +396,10 @@ int stack_impl(et_handle_t h, int batch, int seq, cudaStream_t s) {
   Workspace& ws = h->ws;
   int rc = ET_OK;
   const int max_m = batch * seq;
-  if (h->cfg.dtype == ET_FP16 && !h->use_simt && seq <= 128 && max_m > 0)
+  if (h->cur_attr_mask != nullptr)
+    ET_LAUNCH(h, ET_PROF_PADDING_OFFSETS, 1, s,
+              launch_position_rows(ws.batch_idx, ws.word_idx, ws.valid_word_num, batch, seq, ws.pos_row, s));
+  else if (h->cfg.dtype == ET_FP16 && !h->use_simt && seq <= 128 && max_m > 0)
     ET_LAUNCH(h, ET_PROF_PADDING_OFFSETS, 1, s,
               launch_attention_plan(ws.cu_seqlens, batch, max_m, ws.attn_plan, s));
   for (int l = 0; l < h->cfg.num_layers; ++l) {
@@ -593,6 +606,7 @@ int et_create(const et_config_t* config, et_handle_t* out_handle) {
       {reinterpret_cast<void**>(&ws.cu_seqlens), (static_cast<size_t>(c.max_batch_size) + 1) * 4},
       {reinterpret_cast<void**>(&ws.lens_scratch), static_cast<size_t>(c.max_batch_size) * 4},
       {reinterpret_cast<void**>(&ws.attn_plan), attention_plan_ints(c.max_batch_size, static_cast<int>(cap)) * 4},
+      {reinterpret_cast<void**>(&ws.pos_row), cap * 4},
       {reinterpret_cast<void**>(&ws.valid_word_num), 4}, {reinterpret_cast<void**>(&ws.status), 4}};
   for (auto& b : bufs)
     if ((rc = ws_alloc(h, b.p, b.bytes)) != ET_OK) return bail(rc);
@@ -753,16 +767,28 @@ int et_layer(et_handle_t h, int layer, const et_encoder_param_t* p, const et_tra
   const int batch = tp->batch_size, seq = tp->from_seq_len, max_m = batch * seq;
   ET_LAUNCH(h, ET_PROF_PADDING_OFFSETS, 1, s, launch_seq_bounds_from_batch_idx(p->batch_idx, p->valid_word_num, batch, max_m,
                                               h->ws.cu_seqlens, s));
-  if (h->cfg.dtype == ET_FP16 && !h->use_simt && seq <= 128 && max_m > 0)
+  if (h->general_mask) {
+    if (p->attr_mask == nullptr)
+      return set_error(h, ET_INVALID_ARGUMENT, "general-mask mode: attr_mask [B,S,S] is required");
+    ET_LAUNCH(h, ET_PROF_PADDING_OFFSETS, 1, s,
+              launch_position_rows(p->batch_idx, p->word_idx, p->valid_word_num, batch, seq, h->ws.pos_row, s));
+    h->cur_attr_mask = p->attr_mask;
+    h->cur_word_idx = p->word_idx;
+  } else if (h->cfg.dtype == ET_FP16 && !h->use_simt && seq <= 128 && max_m > 0) {
     ET_LAUNCH(h, ET_PROF_PADDING_OFFSETS, 1, s,
               launch_attention_plan(h->ws.cu_seqlens, batch, max_m, h->ws.attn_plan, s));
+  }
   if (h->cfg.dtype == ET_FP16)
-    return run_layer<__half>(h, h->layers[layer], static_cast<const __half*>(p->from_tensor),
-                             static_cast<__half*>(p->transformer_out), p->valid_word_num, max_m,
-                             h->ws.cu_seqlens, batch, seq, s);
-  return run_layer<float>(h, h->layers[layer], static_cast<const float*>(p->from_tensor),
+    rc = run_layer<__half>(h, h->layers[layer], static_cast<const __half*>(p->from_tensor),
+                           static_cast<__half*>(p->transformer_out), p->valid_word_num, max_m,
+                           h->ws.cu_seqlens, batch, seq, s);
+  else
+    rc = run_layer<float>(h, h->layers[layer], static_cast<const float*>(p->from_tensor),
                           static_cast<float*>(p->transformer_out), p->valid_word_num, max_m,
                           h->ws.cu_seqlens, batch, seq, s);
+  h->cur_attr_mask = nullptr;
+  h->cur_word_idx = nullptr;
+  return rc;
   ET_CATCH(h)
 }
 
@@ -772,6 +798,27 @@ int et_forward(et_handle_t h, const void* from_tensor, const int* mask, void* ou
   if (h == nullptr) return ET_INVALID_ARGUMENT;
   DeviceGuard guard(h->cfg.device);
   return forward_impl(h, from_tensor, mask, out, batch_size, seq_len, static_cast<cudaStream_t>(stream));
+  ET_CATCH(h)
+}
+
+int et_set_general_mask(et_handle_t h, int enable) {
+  if (h == nullptr) return ET_INVALID_ARGUMENT;
+  h->general_mask = enable != 0;
+  return ET_OK;
+}
+
+int et_forward_general_mask(et_handle_t h, const void* from_tensor, const int* mask, const void* attr_mask,
+                            void* out, int batch_size, int seq_len, void* stream) {
+  ET_TRY
+  if (h == nullptr) return ET_INVALID_ARGUMENT;
+  if (attr_mask == nullptr) return set_error(h, ET_INVALID_ARGUMENT, "attr_mask [B,S,S] is required");
+  DeviceGuard guard(h->cfg.device);
+  h->cur_attr_mask = attr_mask;
+  h->cur_word_idx = h->ws.word_idx;
+  const int rc = forward_impl(h, from_tensor, mask, out, batch_size, seq_len, static_cast<cudaStream_t>(stream));
+  h->cur_attr_mask = nullptr;
+  h->cur_word_idx = nullptr;
+  return rc;
   ET_CATCH(h)
 }
 
@@ -1281,6 +1328,27 @@ int et_attention(int dtype, const void* q, const void* k, const void* v, long lo
                                                    static_cast<__half*>(ctx), cu_seqlens, batch, max_seq, heads, d, s),
                      launch_attention_simt<float>(F_(q), F_(k), F_(v), token_stride, head_stride,
                                                   static_cast<float*>(ctx), cu_seqlens, batch, max_seq, heads, d, s));
+}
+
+int et_attention_general_mask(int dtype, const void* q, const void* k, const void* v, long long token_stride,
+                              long long head_stride, void* ctx, const void* attr_mask, const int* cu_seqlens,
+                              const int* batch_idx, const int* word_idx, const int* t_ptr, int* pos_row_scratch,
+                              int batch, int seq, int heads, int d, void* stream) {
+  if (batch < 0 || seq < 0 || heads <= 0 || d != 64 || (dtype != ET_FP16 && dtype != ET_FP32))
+    return ET_INVALID_ARGUMENT;
+  if (batch == 0 || seq == 0) return ET_OK;
+  if (!q || !k || !v || !ctx || !attr_mask || !cu_seqlens || !batch_idx || !word_idx || !t_ptr || !pos_row_scratch)
+    return ET_INVALID_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int rc = to_status(launch_position_rows(batch_idx, word_idx, t_ptr, batch, seq, pos_row_scratch, s));
+  if (rc != ET_OK) return rc;
+  return ET_DISPATCH(dtype,
+                     launch_attention_masked_simt<__half>(H_(q), H_(k), H_(v), token_stride, head_stride,
+                                                          static_cast<__half*>(ctx), H_(attr_mask), cu_seqlens,
+                                                          word_idx, pos_row_scratch, batch, seq, heads, d, s),
+                     launch_attention_masked_simt<float>(F_(q), F_(k), F_(v), token_stride, head_stride,
+                                                         static_cast<float*>(ctx), F_(attr_mask), cu_seqlens,
+                                                         word_idx, pos_row_scratch, batch, seq, heads, d, s));
 }
 
 size_t et_attention_plan_ints(int batch_size, int max_tokens) {

@@ -170,7 +170,17 @@ int et_output(et_handle_t handle, const et_output_param_t* param);
 int et_forward(et_handle_t handle, const void* from_tensor, const int* mask, void* out,
                int batch_size, int seq_len, void* stream);
 
-/* Same with HOST buffers (pinned or pageable): copies from_tensor and mask to
+/* General attention masks.  By default the layer op does not read attr_mask
+ * (it must be the key-only tile of the input mask, as the reference's sample
+ * builds it, and the fast kernels derive it from the sequence bounds).
+ * et_set_general_mask(handle, 1) makes et_layer read attr_mask [B,S,S]
+ * through et_attention_general_mask's kernel instead;
+ * et_forward_general_mask is et_forward with such a mask. */
+int et_set_general_mask(et_handle_t handle, int enable);
+int et_forward_general_mask(et_handle_t handle, const void* from_tensor, const int* mask,
+                            const void* attr_mask, void* out, int batch_size, int seq_len, void* stream);
+
+/* et_forward with HOST buffers (pinned or pageable): copies from_tensor and mask to
  * the device, runs et_forward, copies the [B,S,H] result back and waits for
  * it, like one sess.run of sample/tensorflow/benchmark.py:114-124.
  * `valid_word_num_out` (may be NULL) receives T. */
@@ -382,6 +392,20 @@ int et_attention(int dtype, const void* q, const void* k, const void* v, long lo
                  long long head_stride, void* ctx, const int* cu_seqlens, int batch_size,
                  int max_seq_len, int max_tokens, int head_num, int size_per_head, int use_simt,
                  int* status_word, void* stream);
+
+/* The attention block under a GENERAL [B,S,S] mask (element type = dtype,
+ * 1 = attend), for callers whose mask is not the key-only tile of the input
+ * mask (causal, banded, per-pair masks).  Semantics of the reference op
+ * (cuda/attention.cu:106-242, 249-382): a query sees all S key positions,
+ * score*1/sqrt(d) + (1 - m)*(-10000); padded key positions take part with
+ * K = V = 0, exactly as the reference's zero-filled padded buffers make them.
+ * CUDA-core kernel, fp32 arithmetic: a correctness fallback, not a fast path.
+ * pos_row_scratch: batch_size*seq_len ints of device memory. */
+int et_attention_general_mask(int dtype, const void* q, const void* k, const void* v, long long token_stride,
+                              long long head_stride, void* ctx, const void* attr_mask, const int* cu_seqlens,
+                              const int* batch_idx, const int* word_idx, const int* valid_word_num,
+                              int* pos_row_scratch, int batch_size, int seq_len, int head_num,
+                              int size_per_head, void* stream);
 
 /* The same attention block on the tcgen05 tensor cores, fp16, for batches whose
  * sequences have at most 128 tokens (max_seq_len <= 128).  A plan packs whole

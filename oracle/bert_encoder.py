@@ -245,11 +245,44 @@ def packed_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqle
     return out
 
 
+def packed_attention_general_mask(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                                  cu_seqlens: np.ndarray, word_idx: np.ndarray, attr_mask: torch.Tensor,
+                                  seq: int, heads: int, d: int) -> torch.Tensor:
+    """The attention block of the reference op under a general [B, S, S] mask:
+    valid rows are scattered into zero-filled padded [B, heads, S, d] buffers
+    (cuda/attention.cu:106-242, memset at tf_op/bert_transformer_op.cu.cc:146),
+    so a padded key takes part with K = V = 0; softmax of
+    score/sqrt(d) + (1 - m) * -10000 over all S keys (cuda/attention.cu:249-382,
+    without the kernel's +1e-6 in the denominator); valid rows gathered back
+    (cuda/attention.cu:388-492).  ``word_idx[v]`` is the position of packed row v."""
+    out = torch.zeros_like(q)
+    scale = 1.0 / math.sqrt(float(d))
+    for b in range(len(cu_seqlens) - 1):
+        lo, hi = int(cu_seqlens[b]), int(cu_seqlens[b + 1])
+        if hi <= lo:
+            continue
+        pos = torch.from_numpy(np.asarray(word_idx[lo:hi]).astype(np.int64))
+        n = hi - lo
+        qb = q[lo:hi].reshape(n, heads, d).permute(1, 0, 2)
+        kp = torch.zeros(heads, seq, d, dtype=q.dtype)
+        vp = torch.zeros(heads, seq, d, dtype=q.dtype)
+        kp[:, pos] = k[lo:hi].reshape(n, heads, d).permute(1, 0, 2)
+        vp[:, pos] = v[lo:hi].reshape(n, heads, d).permute(1, 0, 2)
+        m = attr_mask[b][pos].to(q.dtype)                     # [n, S]: the mask rows of the valid queries
+        scores = torch.matmul(qb, kp.transpose(-1, -2)) * scale + (1.0 - m).unsqueeze(0) * -10000.0
+        p = torch.softmax(scores, dim=-1)
+        out[lo:hi] = torch.matmul(p, vp).permute(1, 0, 2).reshape(n, heads * d)
+    return out
+
+
 def packed_encoder(x_packed, cu_seqlens: np.ndarray, weights: Sequence, heads: int, d: int,
                    compute_dtype=torch.float32, round_to_fp16: bool = False,
-                   ln_eps: float = DEVICE_LAYER_NORM_EPS) -> torch.Tensor:
+                   ln_eps: float = DEVICE_LAYER_NORM_EPS, attr_mask=None, word_idx=None,
+                   seq: Optional[int] = None) -> torch.Tensor:
     """The same stack evaluated on the packed [T, H] layout in the order of the
-    reference's layer functor (tf_op/bert_transformer_op.cu.cc:104-246)."""
+    reference's layer functor (tf_op/bert_transformer_op.cu.cc:104-246).  With
+    ``attr_mask`` [B, S, S] (plus ``word_idx`` and ``seq``) the attention block is
+    packed_attention_general_mask, i.e. the op's behaviour under a general mask."""
     def prep(a):
         t = _t(a, torch.float32)
         if round_to_fp16:
@@ -260,7 +293,11 @@ def packed_encoder(x_packed, cu_seqlens: np.ndarray, weights: Sequence, heads: i
     for l in range(len(weights) // 16):
         w = [prep(a) for a in weights[l * 16:(l + 1) * 16]]
         q, k, v = dense(x, w[0], w[1]), dense(x, w[2], w[3]), dense(x, w[4], w[5])
-        ctx = packed_attention(q, k, v, cu_seqlens, heads, d)
+        if attr_mask is None:
+            ctx = packed_attention(q, k, v, cu_seqlens, heads, d)
+        else:
+            ctx = packed_attention_general_mask(q, k, v, cu_seqlens, word_idx, _t(attr_mask, compute_dtype),
+                                                seq, heads, d)
         att = add_bias_input_layernorm(ctx @ w[6], x, w[7], w[9], w[8], ln_eps)
         inter = add_bias_gelu(att @ w[10], w[11])
         x = add_bias_input_layernorm(inter @ w[12], att, w[13], w[15], w[14], ln_eps)
