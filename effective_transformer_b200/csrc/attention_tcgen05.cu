@@ -167,7 +167,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                          const __grid_constant__ CUtensorMap tmap_v, Coords co, __half* __restrict__ ctx,
                          const int* __restrict__ plan, int batch, int max_tokens, int heads,
-                         float scale_log2e, int* status_word) {
+                         float scale_log2e, int* status_word, int reverse) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t base = smem_u32(smem_raw);
   if ((base & 1023u) != 0u) {
@@ -216,7 +216,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
   bool ok = true;
   // Thread 0: the Q, K, V rows of one item -> buffer `b`, completion on its barrier.
   auto issue = [&](int item_idx, int b) {
-    const int tile_i = item_idx / heads, head_i = item_idx - tile_i * heads;
+    const int li = reverse ? total - 1 - item_idx : item_idx;  // last tiles first: freshest in L2
+    const int tile_i = li / heads, head_i = li - tile_i * heads;
     int rows = tile_rows[tile_i];
     rows = rows < 1 ? 1 : (rows > kTileRows ? kTileRows : rows);
     const int boxes = (rows + kBoxRows - 1) / kBoxRows;
@@ -242,7 +243,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
   };
 
   for (int item = blockIdx.x; item < total && ok; item += gridDim.x, ++it_n) {
-    const int tile = item / heads, head = item - tile * heads;
+    const int litem = reverse ? total - 1 - item : item;
+    const int tile = litem / heads, head = litem - tile * heads;
     const int t0 = tile_start[tile];
     int n = tile_rows[tile];
     n = n < 1 ? 1 : (n > kTileRows ? kTileRows : n);
@@ -419,7 +421,7 @@ cudaError_t launch_attention_plan(const int* cu_seqlens, int batch, int max_toke
 cudaError_t launch_attention_tcgen05(const __half* q, const __half* k, const __half* v,
                                      long long token_stride, long long head_stride, __half* ctx,
                                      const int* plan, int batch, int max_tokens, int heads, int d,
-                                     int* status_word, cudaStream_t stream) {
+                                     int* status_word, cudaStream_t stream, bool reverse) {
   if (batch <= 0 || heads <= 0 || max_tokens <= 0) return cudaSuccess;
   if (d != kD || token_stride < kD || (token_stride % 8) != 0 || (head_stride % 8) != 0 || head_stride < 0)
     return cudaErrorInvalidValue;
@@ -457,7 +459,7 @@ cudaError_t launch_attention_tcgen05(const __half* q, const __half* k, const __h
   const long long max_items = static_cast<long long>(batch) * heads;
   if (grid > max_items) grid = max_items;
   attention_tcgen05_kernel<<<static_cast<int>(grid), kThreads, kSmemBytes, stream>>>(
-      tq, tk, tv, co, ctx, plan, batch, max_tokens, heads, scale_log2e, status_word);
+      tq, tk, tv, co, ctx, plan, batch, max_tokens, heads, scale_log2e, status_word, reverse ? 1 : 0);
   return cudaGetLastError();
 }
 

@@ -157,7 +157,7 @@ cudaError_t launch_add_bias_gelu(T* out, const T* bias, const int* t_ptr, int ma
 template <typename T>
 cudaError_t launch_add_bias_input_layernorm(T* out, const T* input, const T* bias, const T* gamma,
                                             const T* beta, const int* t_ptr, int max_tokens, int n,
-                                            float eps, cudaStream_t stream);
+                                            float eps, cudaStream_t stream, bool reverse = false);
 // Embedding rows + LayerNorm for valid tokens only, written packed [T, n].
 // token_type_ids / type_table / pos_table may be null.
 template <typename T>
@@ -213,10 +213,14 @@ cudaError_t launch_attention_plan(const int* cu_seqlens, int batch, int max_toke
 cudaError_t launch_attention_tcgen05(const __half* q, const __half* k, const __half* v,
                                      long long token_stride, long long head_stride, __half* ctx,
                                      const int* plan, int batch, int max_tokens, int heads, int d,
-                                     int* status_word, cudaStream_t stream);
+                                     int* status_word, cudaStream_t stream, bool reverse = false);
 // tcgen05 GEMM, fp16 in / fp32 accumulate / fp16 out.  w_packed is [N,K].
+// reverse_m: row tiles are visited from the last to the first.  A kernel that
+// consumes what the previous kernel has just written finds the rows written
+// last still in L2 if it starts with them, so consecutive kernels of a layer
+// alternate their direction.
 cudaError_t launch_gemm_tcgen05(const __half* a, const __half* w_packed, const __half* bias,
                                 __half* c, const int* m_ptr, int max_m, int n, int k, int epilogue,
-                                int* status_word, cudaStream_t stream);
+                                int* status_word, cudaStream_t stream, bool reverse_m = false);
 
 }  // namespace etb

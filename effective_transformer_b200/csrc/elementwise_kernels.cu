@@ -101,7 +101,7 @@ __global__ void __launch_bounds__(kThreads, (kVPL <= 4 ? 3 : 1))
 add_bias_input_layernorm_kernel(T* __restrict__ out, const T* __restrict__ input,
                                 const T* __restrict__ bias, const T* __restrict__ gamma,
                                 const T* __restrict__ beta, const int* __restrict__ t_ptr,
-                                int max_tokens, int n, float eps) {
+                                int max_tokens, int n, float eps, int reverse) {
   constexpr int E = VecTraits<T>::kElems;
   const int t = clamp_tokens(t_ptr, max_tokens);
   const int lane = threadIdx.x & 31;
@@ -110,7 +110,8 @@ add_bias_input_layernorm_kernel(T* __restrict__ out, const T* __restrict__ input
   const int vpr = n / E;
   const float inv_n = 1.0f / static_cast<float>(n);
 
-  for (int row = warp; row < t; row += nwarps) {
+  for (int r = warp; r < t; r += nwarps) {
+    const int row = reverse ? t - 1 - r : r;  // last rows first: they are the freshest in L2
     T* orow = out + static_cast<size_t>(row) * n;
     const T* irow = input + static_cast<size_t>(row) * n;
     Vec16 vo[kVPL], vi[kVPL];
@@ -233,7 +234,7 @@ cudaError_t launch_add_bias_gelu(T* out, const T* bias, const int* t_ptr, int ma
 template <typename T>
 cudaError_t launch_add_bias_input_layernorm(T* out, const T* input, const T* bias, const T* gamma,
                                             const T* beta, const int* t_ptr, int max_tokens, int n,
-                                            float eps, cudaStream_t stream) {
+                                            float eps, cudaStream_t stream, bool reverse) {
   constexpr int E = VecTraits<T>::kElems;
   if (max_tokens <= 0) return cudaSuccess;
   if (n % E != 0 || n <= 0) return cudaErrorInvalidValue;
@@ -245,7 +246,8 @@ cudaError_t launch_add_bias_input_layernorm(T* out, const T* input, const T* bia
   const int grid = static_cast<int>(ctas);
 #define ETB_LN(V)                                                                         \
   add_bias_input_layernorm_kernel<T, V><<<grid, kThreads, 0, stream>>>(out, input, bias, gamma, \
-                                                                       beta, t_ptr, max_tokens, n, eps)
+                                                                       beta, t_ptr, max_tokens, n, eps, \
+                                                                       reverse ? 1 : 0)
   if (vpl <= 1) ETB_LN(1);
   else if (vpl <= 2) ETB_LN(2);
   else if (vpl <= 3) ETB_LN(3);
@@ -281,7 +283,7 @@ cudaError_t launch_copy_columns(const T* src, T* dst, int rows, int cols, int ds
   template cudaError_t launch_add_bias_gelu<T>(T*, const T*, const int*, int, int, cudaStream_t); \
   template cudaError_t launch_add_bias_input_layernorm<T>(T*, const T*, const T*, const T*,      \
                                                           const T*, const int*, int, int, float, \
-                                                          cudaStream_t);                         \
+                                                          cudaStream_t, bool);                   \
   template cudaError_t launch_transpose<T>(const T*, T*, int, int, cudaStream_t);                \
   template cudaError_t launch_copy_columns<T>(const T*, T*, int, int, int, int, cudaStream_t);
 ETB_INST(float)

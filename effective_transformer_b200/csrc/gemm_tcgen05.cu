@@ -155,7 +155,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b, __half* __restrict__ C,
                     const __half* __restrict__ bias, const int* __restrict__ m_ptr, int max_m, int N,
-                    int K, int* status_word) {
+                    int K, int* status_word, int reverse_m) {
   using cfg = Cfg<BN>;
   constexpr int S = cfg::kStages;
 
@@ -225,7 +225,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       long long issued = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m_tile = tile / n_tiles, n_tile = tile - m_tile * n_tiles;
+        const int m_lin = tile / n_tiles, n_tile = tile - m_lin * n_tiles;
+        const int m_tile = reverse_m ? m_tiles - 1 - m_lin : m_lin;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
             fail(kSiteProducerEmpty);
@@ -309,7 +310,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint32_t bias_s = bias_addr + ew * (kCols * 2);
     int it = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
-      const int m_tile = tile / n_tiles, n_tile = tile - m_tile * n_tiles;
+      const int m_lin = tile / n_tiles, n_tile = tile - m_lin * n_tiles;
+        const int m_tile = reverse_m ? m_tiles - 1 - m_lin : m_lin;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       const int col0 = n_tile * BN + half * kCols;
@@ -376,7 +378,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                          const __grid_constant__ CUtensorMap tmap_b, __half* __restrict__ C,
                          const __half* __restrict__ bias, const int* __restrict__ m_ptr, int max_m,
-                         int N, int K, int* status_word) {
+                         int N, int K, int* status_word, int reverse_m) {
   using cfg = PairCfg;
   constexpr int S = cfg::kStages;
   constexpr int BN = cfg::BN;
@@ -452,7 +454,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       long long issued = 0;
       bool ok = true;
       for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
-        const int m_tile = tile / n_tiles, n_tile = tile - m_tile * n_tiles;
+        const int m_lin = tile / n_tiles, n_tile = tile - m_lin * n_tiles;
+        const int m_tile = reverse_m ? m_tiles - 1 - m_lin : m_lin;
         const int a_row = m_tile * BM2 + static_cast<int>(rank) * BM;
         const int b_row = n_tile * BN + static_cast<int>(rank) * (BN / 2);
         for (int kb = 0; kb < num_kb; ++kb) {
@@ -540,7 +543,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint32_t bias_s = bias_addr + ew * (kCols * 2);
     int it = 0;
     for (int tile = pair_id; tile < num_tiles; tile += num_pairs, ++it) {
-      const int m_tile = tile / n_tiles, n_tile = tile - m_tile * n_tiles;
+      const int m_lin = tile / n_tiles, n_tile = tile - m_lin * n_tiles;
+        const int m_tile = reverse_m ? m_tiles - 1 - m_lin : m_lin;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       const int col0 = n_tile * BN + half * kCols;
@@ -578,7 +582,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
 template <int EPI>
 cudaError_t launch_pair_epi(const CUtensorMap& ta, const CUtensorMap& tb, const __half* bias, __half* c,
-                            const int* m_ptr, int max_m, int n, int k, int* status_word,
+                            const int* m_ptr, int max_m, int n, int k, int* status_word, int reverse_m,
                             cudaStream_t stream) {
   using cfg = PairCfg;
   static std::once_flag once;
@@ -593,22 +597,22 @@ cudaError_t launch_pair_epi(const CUtensorMap& ta, const CUtensorMap& tb, const 
   if (pairs > max_tiles) pairs = max_tiles;
   if (pairs < 1) pairs = 1;
   gemm_tcgen05_pair_kernel<EPI><<<static_cast<int>(2 * pairs), kNumThreads, cfg::kSmemBytes, stream>>>(
-      ta, tb, c, bias, m_ptr, max_m, n, k, status_word);
+      ta, tb, c, bias, m_ptr, max_m, n, k, status_word, reverse_m);
   return cudaGetLastError();
 }
 
 cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const __half* bias, __half* c,
                         const int* m_ptr, int max_m, int n, int k, int epilogue, int* status_word,
-                        cudaStream_t stream) {
+                        int reverse_m, cudaStream_t stream) {
   switch (epilogue) {
     case kEpiNone:
-      return launch_pair_epi<kEpiNone>(ta, tb, bias, c, m_ptr, max_m, n, k, status_word, stream);
+      return launch_pair_epi<kEpiNone>(ta, tb, bias, c, m_ptr, max_m, n, k, status_word, reverse_m, stream);
     case kEpiBias:
-      return launch_pair_epi<kEpiBias>(ta, tb, bias, c, m_ptr, max_m, n, k, status_word, stream);
+      return launch_pair_epi<kEpiBias>(ta, tb, bias, c, m_ptr, max_m, n, k, status_word, reverse_m, stream);
     case kEpiBiasGelu:
-      return launch_pair_epi<kEpiBiasGelu>(ta, tb, bias, c, m_ptr, max_m, n, k, status_word, stream);
+      return launch_pair_epi<kEpiBiasGelu>(ta, tb, bias, c, m_ptr, max_m, n, k, status_word, reverse_m, stream);
     case kEpiBiasTanh:
-      return launch_pair_epi<kEpiBiasTanh>(ta, tb, bias, c, m_ptr, max_m, n, k, status_word, stream);
+      return launch_pair_epi<kEpiBiasTanh>(ta, tb, bias, c, m_ptr, max_m, n, k, status_word, reverse_m, stream);
     default:
       return cudaErrorInvalidValue;
   }
@@ -616,7 +620,7 @@ cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const __ha
 
 template <int BN, int EPI>
 cudaError_t launch_bn_epi(const CUtensorMap& ta, const CUtensorMap& tb, const __half* bias, __half* c,
-                          const int* m_ptr, int max_m, int n, int k, int* status_word,
+                          const int* m_ptr, int max_m, int n, int k, int* status_word, int reverse_m,
                           cudaStream_t stream) {
   using cfg = Cfg<BN>;
   static std::once_flag once;
@@ -631,23 +635,23 @@ cudaError_t launch_bn_epi(const CUtensorMap& ta, const CUtensorMap& tb, const __
   if (grid > max_tiles) grid = max_tiles;
   if (grid < 1) grid = 1;
   gemm_tcgen05_kernel<BN, EPI><<<static_cast<int>(grid), kNumThreads, cfg::kSmemBytes, stream>>>(
-      ta, tb, c, bias, m_ptr, max_m, n, k, status_word);
+      ta, tb, c, bias, m_ptr, max_m, n, k, status_word, reverse_m);
   return cudaGetLastError();
 }
 
 template <int BN>
 cudaError_t launch_bn(const CUtensorMap& ta, const CUtensorMap& tb, const __half* bias, __half* c,
                       const int* m_ptr, int max_m, int n, int k, int epilogue, int* status_word,
-                      cudaStream_t stream) {
+                      int reverse_m, cudaStream_t stream) {
   switch (epilogue) {
     case kEpiNone:
-      return launch_bn_epi<BN, kEpiNone>(ta, tb, bias, c, m_ptr, max_m, n, k, status_word, stream);
+      return launch_bn_epi<BN, kEpiNone>(ta, tb, bias, c, m_ptr, max_m, n, k, status_word, reverse_m, stream);
     case kEpiBias:
-      return launch_bn_epi<BN, kEpiBias>(ta, tb, bias, c, m_ptr, max_m, n, k, status_word, stream);
+      return launch_bn_epi<BN, kEpiBias>(ta, tb, bias, c, m_ptr, max_m, n, k, status_word, reverse_m, stream);
     case kEpiBiasGelu:
-      return launch_bn_epi<BN, kEpiBiasGelu>(ta, tb, bias, c, m_ptr, max_m, n, k, status_word, stream);
+      return launch_bn_epi<BN, kEpiBiasGelu>(ta, tb, bias, c, m_ptr, max_m, n, k, status_word, reverse_m, stream);
     case kEpiBiasTanh:
-      return launch_bn_epi<BN, kEpiBiasTanh>(ta, tb, bias, c, m_ptr, max_m, n, k, status_word, stream);
+      return launch_bn_epi<BN, kEpiBiasTanh>(ta, tb, bias, c, m_ptr, max_m, n, k, status_word, reverse_m, stream);
     default:
       return cudaErrorInvalidValue;
   }
@@ -685,7 +689,7 @@ bool encode_2d_fp16_sw128(CUtensorMap* map, const void* base, uint64_t rows, uin
 
 cudaError_t launch_gemm_tcgen05(const __half* a, const __half* w_packed, const __half* bias,
                                 __half* c, const int* m_ptr, int max_m, int n, int k, int epilogue,
-                                int* status_word, cudaStream_t stream) {
+                                int* status_word, cudaStream_t stream, bool reverse_m) {
   if (max_m <= 0) return cudaSuccess;
   if (n <= 0 || k <= 0 || (n % 128) != 0 || (k % 8) != 0) return cudaErrorInvalidValue;
   if ((reinterpret_cast<uintptr_t>(a) & 15u) || (reinterpret_cast<uintptr_t>(w_packed) & 15u) ||
@@ -705,10 +709,11 @@ cudaError_t launch_gemm_tcgen05(const __half* a, const __half* w_packed, const _
   if (!encode_2d_fp16_sw128(&tb, w_packed, static_cast<uint64_t>(n), static_cast<uint64_t>(k),
                             static_cast<uint64_t>(k), static_cast<uint32_t>(pair ? 128 : bn), BK))
     return cudaErrorInvalidValue;
-  if (pair) return launch_pair(ta, tb, bias, c, m_ptr, max_m, n, k, epilogue, status_word, stream);
+  const int rev = reverse_m ? 1 : 0;
+  if (pair) return launch_pair(ta, tb, bias, c, m_ptr, max_m, n, k, epilogue, status_word, rev, stream);
   if (bn == 256)
-    return launch_bn<256>(ta, tb, bias, c, m_ptr, max_m, n, k, epilogue, status_word, stream);
-  return launch_bn<128>(ta, tb, bias, c, m_ptr, max_m, n, k, epilogue, status_word, stream);
+    return launch_bn<256>(ta, tb, bias, c, m_ptr, max_m, n, k, epilogue, status_word, rev, stream);
+  return launch_bn<128>(ta, tb, bias, c, m_ptr, max_m, n, k, epilogue, status_word, rev, stream);
 }
 
 }  // namespace etb

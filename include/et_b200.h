@@ -268,8 +268,10 @@ int et_last_padding_info(et_handle_t handle, const int** cu_seqlens, const int**
                          const int** padding_offset, const int** prefix_sum);
 
 /* Per-kernel accounting.  Launch counts are always kept; with profiling
- * enabled every launcher call is also bracketed by CUDA events on the stream
- * it is launched on.  et_get_profile waits for the recorded events and
+ * enabled a CUDA event is recorded on the launching stream after every
+ * launcher call (and before the first one of an API call), so a kernel's time
+ * runs from the end of the launch before it to its own end and the categories
+ * add up to the whole call.  et_get_profile waits for the recorded events and
  * returns, per category, the summed device time in ms and the number of
  * kernels launched since the last reset. */
 enum {
