@@ -90,17 +90,17 @@ __device__ __forceinline__ Vec16 ld_shared_v4(uint32_t addr) {
 // warp's swizzled staging buffer -> coalesced global stores (one instruction
 // writes 4 full 128-byte row segments).  `release` runs once all TMEM reads of
 // the warp have completed.  rows_valid = M - (first row of this warp).
-template <int EPI, int kCols, typename Release>
+template <int EPI, typename Release>
 __device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, __half* ctile, int N, int rows_valid,
-                                                   uint32_t bias_s, uint32_t buf, int lane,
+                                                   uint32_t bias_s, uint32_t buf, int lane, int chunks,
                                                    Release release) {
 #pragma unroll 1
-  for (int c = 0; c < kCols / 64; ++c) {
+  for (int c = 0; c < chunks; ++c) {
     uint32_t r[64];
     tmem_ld_32x32b_x32(t_row + c * 64, r);
     tmem_ld_32x32b_x32(t_row + c * 64 + 32, r + 32);
     tmem_ld_wait();
-    if (c == kCols / 64 - 1) {
+    if (c == chunks - 1) {
       // the accumulator now lives in registers: hand the TMEM buffer back
       tc_fence_before();
       release();
@@ -332,8 +332,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t t_row =
           tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN + half * kCols;
       __half* ctile = C + static_cast<size_t>(row0) * N + col0;
-      epilogue_warp_tile<EPI, kCols>(t_row, ctile, N, M - row0, bias_s, buf, lane,
-                                     [&] { mbar_arrive(tmem_empty_bar(acc)); });
+      epilogue_warp_tile<EPI>(t_row, ctile, N, M - row0, bias_s, buf, lane, kCols / 64,
+                              [&] { mbar_arrive(tmem_empty_bar(acc)); });
     }
   }
 
@@ -358,7 +358,34 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 //   tmem_full[a] one per CTA, CTA 0's MMA thread commits to both
 //   tmem_empty[a] lives in CTA 0, one arrival per epilogue warp of both CTAs
 // No load is multicast: each CTA fetches its own operand rows.
+//
+// Work units and the last wave.  Tiles are dealt round-robin to the pairs, so
+// when num_tiles is not a multiple of the number of pairs the last round
+// keeps only `rem` pairs busy for a whole tile time.  If rem is at most half
+// of the pairs, each of those tiles is cut into two 256 x 128 units (MMA with
+// N = 128, each CTA loading 64 W rows): the last round then takes half a tile
+// time.  BERT-base at T = 39 778: 468 tiles of the N = 768 projections on 74
+// pairs = 6.32 rounds -> 6.5 instead of 7.
 // ---------------------------------------------------------------------------
+struct PairUnit {
+  int m_tile;  // 256-row tile
+  int col0;    // first output column
+  int ncols;   // 256 (whole tile) or 128 (half of a last-round tile)
+};
+__device__ __forceinline__ PairUnit pair_unit(int u, int full_tiles, int n_tiles, int m_tiles, int reverse_m) {
+  int tile = u, half = -1;
+  if (u >= full_tiles) {
+    const int r = u - full_tiles;
+    tile = full_tiles + (r >> 1);
+    half = r & 1;
+  }
+  const int m_lin = tile / n_tiles, n_tile = tile - m_lin * n_tiles;
+  PairUnit pu;
+  pu.m_tile = reverse_m ? m_tiles - 1 - m_lin : m_lin;
+  pu.col0 = n_tile * 256 + (half > 0 ? 128 : 0);
+  pu.ncols = half < 0 ? 256 : 128;
+  return pu;
+}
 struct PairCfg {
   static constexpr int BN = 256;
   static constexpr int kStages = 6;
@@ -376,7 +403,8 @@ struct PairCfg {
 template <int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                         const __grid_constant__ CUtensorMap tmap_b, __half* __restrict__ C,
+                         const __grid_constant__ CUtensorMap tmap_b,
+                         const __grid_constant__ CUtensorMap tmap_b_half, __half* __restrict__ C,
                          const __half* __restrict__ bias, const int* __restrict__ m_ptr, int max_m,
                          int N, int K, int* status_word, int reverse_m) {
   using cfg = PairCfg;
@@ -394,6 +422,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   const uint32_t rank = cluster_ctarank();  // 0 issues the MMAs
   const int pair_id = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  // last round cut into half-width units when it occupies at most half of the pairs
+  const int rem = num_tiles % num_pairs;
+  const bool split = rem > 0 && 2 * rem <= num_pairs;
+  const int full_tiles = split ? num_tiles - rem : num_tiles;
+  const int num_units = full_tiles + (split ? 2 * rem : 0);
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t tiles_addr = smem_u32(smem_raw);
@@ -450,14 +483,16 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (lane == 0) {
       prefetch_tensormap(&tmap_a);
       prefetch_tensormap(&tmap_b);
+      if (split) prefetch_tensormap(&tmap_b_half);
       uint32_t stage = 0, phase = 0;
       long long issued = 0;
       bool ok = true;
-      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
-        const int m_lin = tile / n_tiles, n_tile = tile - m_lin * n_tiles;
-        const int m_tile = reverse_m ? m_tiles - 1 - m_lin : m_lin;
-        const int a_row = m_tile * BM2 + static_cast<int>(rank) * BM;
-        const int b_row = n_tile * BN + static_cast<int>(rank) * (BN / 2);
+      for (int u = pair_id; u < num_units && ok; u += num_pairs) {
+        const PairUnit pu = pair_unit(u, full_tiles, n_tiles, m_tiles, reverse_m);
+        const int a_row = pu.m_tile * BM2 + static_cast<int>(rank) * BM;
+        const int b_row = pu.col0 + static_cast<int>(rank) * (pu.ncols / 2);
+        const bool whole = pu.ncols == BN;
+        const uint32_t stage_tx = 2u * (cfg::kABytes + (whole ? cfg::kBBytes : cfg::kBBytes / 2));
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
             fail(kSiteProducerEmpty);
@@ -467,9 +502,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint32_t a_dst = tiles_addr + stage * cfg::kStageBytes;
           const uint32_t b_dst = a_dst + cfg::kABytes;
           const uint32_t full0 = mapa_shared(full_bar(stage), 0);
-          if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * cfg::kStageBytes);
+          if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), stage_tx);
           tma_load_2d_pair(a_dst, &tmap_a, kb * BK, a_row, full0);
-          tma_load_2d_pair(b_dst, &tmap_b, kb * BK, b_row, full0);
+          tma_load_2d_pair(b_dst, whole ? &tmap_b : &tmap_b_half, kb * BK, b_row, full0);
           ++issued;
           if (++stage == S) {
             stage = 0;
@@ -492,11 +527,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   } else if (warp == 1) {
     // ------------------------- MMA issuer (CTA 0 only) -------------------------
     if (lane == 0 && rank == 0) {
-      constexpr uint32_t idesc = make_idesc_f16_f32acc(BM2, BN);
+      constexpr uint32_t idesc_whole = make_idesc_f16_f32acc(BM2, BN);
+      constexpr uint32_t idesc_half = make_idesc_f16_f32acc(BM2, BN / 2);
       uint32_t stage = 0, phase = 0;
       int it = 0;
       bool ok = true;
-      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++it) {
+      for (int u = pair_id; u < num_units && ok; u += num_pairs, ++it) {
+        const uint32_t idesc = u < full_tiles ? idesc_whole : idesc_half;
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag)) {
@@ -542,14 +579,15 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint32_t buf = staging_addr + ew * kStagingPerWarp;
     const uint32_t bias_s = bias_addr + ew * (kCols * 2);
     int it = 0;
-    for (int tile = pair_id; tile < num_tiles; tile += num_pairs, ++it) {
-      const int m_lin = tile / n_tiles, n_tile = tile - m_lin * n_tiles;
-        const int m_tile = reverse_m ? m_tiles - 1 - m_lin : m_lin;
+    for (int u = pair_id; u < num_units; u += num_pairs, ++it) {
+      const PairUnit pu = pair_unit(u, full_tiles, n_tiles, m_tiles, reverse_m);
+      const int m_tile = pu.m_tile;
+      const int wcols = pu.ncols / 2;  // columns of this warp: 128, or 64 in a half-width unit
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
-      const int col0 = n_tile * BN + half * kCols;
+      const int col0 = pu.col0 + half * wcols;
       if (EPI != kEpiNone) {
-        if (lane < kCols / 8) st_shared_v4(bias_s + lane * 16, ld_global_v4(bias + col0 + lane * 8));
+        if (lane < wcols / 8) st_shared_v4(bias_s + lane * 16, ld_global_v4(bias + col0 + lane * 8));
         __syncwarp();
       }
       const bool got = mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag);
@@ -560,10 +598,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       tc_fence_after();
       const int row0 = m_tile * BM2 + static_cast<int>(rank) * BM + quad * 32;
       const uint32_t t_row =
-          tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN + half * kCols;
+          tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN + half * wcols;
       __half* ctile = C + static_cast<size_t>(row0) * N + col0;
       const uint32_t empty0 = mapa_shared(tmem_empty_bar(acc), 0);
-      epilogue_warp_tile<EPI, kCols>(t_row, ctile, N, M - row0, bias_s, buf, lane, [&] {
+      epilogue_warp_tile<EPI>(t_row, ctile, N, M - row0, bias_s, buf, lane, wcols / 64, [&] {
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(empty0);
       });
@@ -581,7 +619,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
 }
 
 template <int EPI>
-cudaError_t launch_pair_epi(const CUtensorMap& ta, const CUtensorMap& tb, const __half* bias, __half* c,
+cudaError_t launch_pair_epi(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tbh,
+                            const __half* bias, __half* c,
                             const int* m_ptr, int max_m, int n, int k, int* status_word, int reverse_m,
                             cudaStream_t stream) {
   using cfg = PairCfg;
@@ -597,22 +636,23 @@ cudaError_t launch_pair_epi(const CUtensorMap& ta, const CUtensorMap& tb, const 
   if (pairs > max_tiles) pairs = max_tiles;
   if (pairs < 1) pairs = 1;
   gemm_tcgen05_pair_kernel<EPI><<<static_cast<int>(2 * pairs), kNumThreads, cfg::kSmemBytes, stream>>>(
-      ta, tb, c, bias, m_ptr, max_m, n, k, status_word, reverse_m);
+      ta, tb, tbh, c, bias, m_ptr, max_m, n, k, status_word, reverse_m);
   return cudaGetLastError();
 }
 
-cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const __half* bias, __half* c,
+cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tbh,
+                        const __half* bias, __half* c,
                         const int* m_ptr, int max_m, int n, int k, int epilogue, int* status_word,
                         int reverse_m, cudaStream_t stream) {
   switch (epilogue) {
     case kEpiNone:
-      return launch_pair_epi<kEpiNone>(ta, tb, bias, c, m_ptr, max_m, n, k, status_word, reverse_m, stream);
+      return launch_pair_epi<kEpiNone>(ta, tb, tbh, bias, c, m_ptr, max_m, n, k, status_word, reverse_m, stream);
     case kEpiBias:
-      return launch_pair_epi<kEpiBias>(ta, tb, bias, c, m_ptr, max_m, n, k, status_word, reverse_m, stream);
+      return launch_pair_epi<kEpiBias>(ta, tb, tbh, bias, c, m_ptr, max_m, n, k, status_word, reverse_m, stream);
     case kEpiBiasGelu:
-      return launch_pair_epi<kEpiBiasGelu>(ta, tb, bias, c, m_ptr, max_m, n, k, status_word, reverse_m, stream);
+      return launch_pair_epi<kEpiBiasGelu>(ta, tb, tbh, bias, c, m_ptr, max_m, n, k, status_word, reverse_m, stream);
     case kEpiBiasTanh:
-      return launch_pair_epi<kEpiBiasTanh>(ta, tb, bias, c, m_ptr, max_m, n, k, status_word, reverse_m, stream);
+      return launch_pair_epi<kEpiBiasTanh>(ta, tb, tbh, bias, c, m_ptr, max_m, n, k, status_word, reverse_m, stream);
     default:
       return cudaErrorInvalidValue;
   }
@@ -710,7 +750,13 @@ cudaError_t launch_gemm_tcgen05(const __half* a, const __half* w_packed, const _
                             static_cast<uint64_t>(k), static_cast<uint32_t>(pair ? 128 : bn), BK))
     return cudaErrorInvalidValue;
   const int rev = reverse_m ? 1 : 0;
-  if (pair) return launch_pair(ta, tb, bias, c, m_ptr, max_m, n, k, epilogue, status_word, rev, stream);
+  if (pair) {
+    CUtensorMap tbh;  // 64 W rows per CTA: the half-width units of the last round
+    if (!encode_2d_fp16_sw128(&tbh, w_packed, static_cast<uint64_t>(n), static_cast<uint64_t>(k),
+                              static_cast<uint64_t>(k), 64, BK))
+      return cudaErrorInvalidValue;
+    return launch_pair(ta, tb, tbh, bias, c, m_ptr, max_m, n, k, epilogue, status_word, rev, stream);
+  }
   if (bn == 256)
     return launch_bn<256>(ta, tb, bias, c, m_ptr, max_m, n, k, epilogue, status_word, rev, stream);
   return launch_bn<128>(ta, tb, bias, c, m_ptr, max_m, n, k, epilogue, status_word, rev, stream);

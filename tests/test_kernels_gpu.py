@@ -210,6 +210,15 @@ def test_gemm_tcgen05_many_tiles_per_cta():
     _gemm_case(torch.float16, 3000, 3000, 1152, 1024, 1, use_simt=False)   # N = 9 * 128: BN = 128 path
 
 
+@pytest.mark.parametrize("epi", [0, 1, 2])
+@pytest.mark.parametrize("m,n,k", [(6500, 768, 768),      # 78 tiles on 74 CTA pairs: 4 tiles left, cut in halves
+                                   (9372, 768, 3072),     # 111 tiles: 37 left = exactly half of the pairs
+                                   (9729, 768, 768),      # 117 tiles: 43 left, more than half: not cut
+                                   (6401, 2304, 768)])    # 234 tiles: 12 left; a one-row last tile
+def test_gemm_tcgen05_last_round_cut_into_half_width_units(m, n, k, epi):
+    _gemm_case(torch.float16, m, m, n, k, epi, use_simt=False)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
 @pytest.mark.parametrize("m,cap,n,k", [(1, 1, 128, 64), (60, 60, 128, 128), (134, 256, 768, 768),
                                        (257, 300, 768, 3072), (300, 300, 2304, 768), (0, 64, 256, 128)])
