@@ -139,7 +139,8 @@ def run_reference(args, spec):
     rank, world, _ = dist_env()
     if rank != 0:
         return
-    sample = args.cpu_sample
+    # a step of the reference arm is a bounded sample, so that K + W steps end within minutes
+    sample = args.cpu_sample if args.cpu_sample > 0 else min(256, spec.batch)
     times, toks, threads = [], 0, 1
     for i in range(args.warmup + args.steps):
         tps, dt, toks, threads = cpu_oracle_throughput(spec, sample)
@@ -171,7 +172,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", type=int, default=2, help="index into the five benchmark configurations")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
-    ap.add_argument("--cpu-sample", type=int, default=128, help="sequences in the CPU-baseline sample")
+    ap.add_argument("--cpu-sample", type=int, default=0,
+                    help="sequences in the CPU sample; 0 = 512 for the cpu_baseline leg (about 5 s on 16 cores), "
+                         "256 per step for --impl reference")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--graph", action="store_true",
@@ -372,10 +375,11 @@ def main():
                 "call": "et_forward_ids_host: ids/types/mask up, embeddings for valid tokens only, "
                         "stack, pooler; pooled [B,H] down"}
         if world == 1 and not args.no_cpu_baseline:
-            tps, dt, toks, threads = cpu_oracle_throughput(spec, args.cpu_sample)
+            n_cpu = args.cpu_sample if args.cpu_sample > 0 else min(512, spec.batch)
+            tps, dt, toks, threads = cpu_oracle_throughput(spec, n_cpu)
             line["cpu_baseline"] = {
                 "value": tps, "unit": UNIT, "cores": threads, "kind": "port",
-                "sample": f"first {args.cpu_sample} of {spec.batch} sequences ({toks} valid tokens), "
+                "sample": f"first {n_cpu} of {spec.batch} sequences ({toks} valid tokens), "
                           f"{sh.num_layers} layers, padded [B,S] fp32 on the host, {dt:.1f} s"}
         print(json.dumps(line), flush=True)
     eng.close()

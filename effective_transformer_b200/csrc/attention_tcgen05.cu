@@ -85,6 +85,8 @@ __host__ __device__ inline size_t plan_ints(int batch, int max_tokens) {
 // labels every token with its sequence's token range.
 __global__ void attention_plan_kernel(const int* __restrict__ cu_seqlens, int batch, int max_tokens,
                                       int* __restrict__ plan) {
+  pdl_wait();
+  pdl_trigger();
   int* tile_start = plan + 4;
   int* tile_rows = plan + 4 + batch;
   int* seq_lo = plan + 4 + 2 * batch;
@@ -168,6 +170,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
                          const __grid_constant__ CUtensorMap tmap_v, Coords co, __half* __restrict__ ctx,
                          const int* __restrict__ plan, int batch, int max_tokens, int heads,
                          float scale_log2e, int* status_word, int reverse) {
+  pdl_wait();     // the plan and the Q/K/V rows come from earlier kernels
+  pdl_trigger();
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t base = smem_u32(smem_raw);
   if ((base & 1023u) != 0u) {
@@ -414,7 +418,9 @@ size_t attention_plan_ints(int batch, int max_tokens) { return plan_ints(batch, 
 cudaError_t launch_attention_plan(const int* cu_seqlens, int batch, int max_tokens, int* plan,
                                   cudaStream_t stream) {
   if (batch <= 0) return cudaSuccess;
-  attention_plan_kernel<<<1, 1024, 0, stream>>>(cu_seqlens, batch, max_tokens, plan);
+  const cudaError_t le = launch_pdl(attention_plan_kernel, dim3(1), dim3(1024), 0, stream, cu_seqlens, batch,
+                                    max_tokens, plan);
+  if (le != cudaSuccess) return le;
   return cudaGetLastError();
 }
 
@@ -458,9 +464,9 @@ cudaError_t launch_attention_tcgen05(const __half* q, const __half* k, const __h
   long long grid = static_cast<long long>(sm_count()) * kCtasPerSm;
   const long long max_items = static_cast<long long>(batch) * heads;
   if (grid > max_items) grid = max_items;
-  attention_tcgen05_kernel<<<static_cast<int>(grid), kThreads, kSmemBytes, stream>>>(
-      tq, tk, tv, co, ctx, plan, batch, max_tokens, heads, scale_log2e, status_word, reverse ? 1 : 0);
-  return cudaGetLastError();
+  return launch_pdl(attention_tcgen05_kernel, dim3(static_cast<int>(grid)), dim3(kThreads), kSmemBytes, stream,
+                    tq, tk, tv, co, ctx, plan, batch, max_tokens, heads, scale_log2e, status_word,
+                    reverse ? 1 : 0);
 }
 
 }  // namespace etb

@@ -5,7 +5,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <cstdlib>
 #include <string>
+#include <utility>
 
 namespace etb {
 
@@ -26,6 +28,46 @@ inline int sm_count() {
       cached = kNumSMsB200;
   }
   return cached;
+}
+
+// ---- programmatic dependent launch ---------------------------------------
+// Consecutive kernels of a pass are launched with the programmatic-stream-
+// serialization attribute: the next kernel's CTAs may be scheduled, and run
+// their set-up (shared-memory carve-up, barrier init, TMEM allocation), while
+// the previous kernel drains.  The contract that makes this safe:
+//   * every CTA of such a kernel executes pdl_wait() before its first access
+//     to global memory and before any exit path (it returns once the previous
+//     kernel has completed and its writes are visible);
+//   * pdl_trigger() only lets the next kernel start being scheduled earlier; it
+//     carries no ordering.
+// Without the launch attribute both instructions are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// ETB_PDL=0 launches everything with full stream serialization (A/B measurements).
+inline bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("ETB_PDL");
+    return !(e != nullptr && e[0] == '0');
+  }();
+  return on;
+}
+
+// kernel<<<grid, block, smem, stream>>>(args...) with the attribute above.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...);
 }
 
 // ---- device status word ---------------------------------------------------

@@ -102,6 +102,8 @@ add_bias_input_layernorm_kernel(T* __restrict__ out, const T* __restrict__ input
                                 const T* __restrict__ bias, const T* __restrict__ gamma,
                                 const T* __restrict__ beta, const int* __restrict__ t_ptr,
                                 int max_tokens, int n, float eps, int reverse) {
+  pdl_wait();
+  pdl_trigger();
   constexpr int E = VecTraits<T>::kElems;
   const int t = clamp_tokens(t_ptr, max_tokens);
   const int lane = threadIdx.x & 31;
@@ -244,10 +246,10 @@ cudaError_t launch_add_bias_input_layernorm(T* out, const T* input, const T* bia
   const long long cap = static_cast<long long>(sm_count()) * kCtasPerSm;
   if (ctas > cap) ctas = cap;
   const int grid = static_cast<int>(ctas);
-#define ETB_LN(V)                                                                         \
-  add_bias_input_layernorm_kernel<T, V><<<grid, kThreads, 0, stream>>>(out, input, bias, gamma, \
-                                                                       beta, t_ptr, max_tokens, n, eps, \
-                                                                       reverse ? 1 : 0)
+  cudaError_t le = cudaSuccess;
+#define ETB_LN(V)                                                                                   \
+  le = launch_pdl(add_bias_input_layernorm_kernel<T, V>, dim3(grid), dim3(kThreads), 0, stream, out, \
+                  input, bias, gamma, beta, t_ptr, max_tokens, n, eps, reverse ? 1 : 0)
   if (vpl <= 1) ETB_LN(1);
   else if (vpl <= 2) ETB_LN(2);
   else if (vpl <= 3) ETB_LN(3);
@@ -256,7 +258,7 @@ cudaError_t launch_add_bias_input_layernorm(T* out, const T* input, const T* bia
   else if (vpl <= 8) ETB_LN(8);
   else return cudaErrorInvalidValue;
 #undef ETB_LN
-  return cudaGetLastError();
+  return le;
 }
 
 template <typename T>

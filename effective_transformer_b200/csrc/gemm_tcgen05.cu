@@ -159,6 +159,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   using cfg = Cfg<BN>;
   constexpr int S = cfg::kStages;
 
+  pdl_wait();     // M and the A rows come from earlier kernels
+  pdl_trigger();
   int M = *m_ptr;
   M = M < 0 ? 0 : (M > max_m ? max_m : M);
   const int m_tiles = (M + BM - 1) / BM;
@@ -412,6 +414,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   constexpr int BN = cfg::BN;
   constexpr int BM2 = 2 * BM;
 
+  pdl_wait();     // M and the A rows come from earlier kernels
+  pdl_trigger();
   int M = *m_ptr;
   M = M < 0 ? 0 : (M > max_m ? max_m : M);
   const int m_tiles = (M + BM2 - 1) / BM2;
@@ -635,9 +639,8 @@ cudaError_t launch_pair_epi(const CUtensorMap& ta, const CUtensorMap& tb, const 
   long long pairs = sm_count() / 2;
   if (pairs > max_tiles) pairs = max_tiles;
   if (pairs < 1) pairs = 1;
-  gemm_tcgen05_pair_kernel<EPI><<<static_cast<int>(2 * pairs), kNumThreads, cfg::kSmemBytes, stream>>>(
-      ta, tb, tbh, c, bias, m_ptr, max_m, n, k, status_word, reverse_m);
-  return cudaGetLastError();
+  return launch_pdl(gemm_tcgen05_pair_kernel<EPI>, dim3(static_cast<int>(2 * pairs)), dim3(kNumThreads),
+                    cfg::kSmemBytes, stream, ta, tb, tbh, c, bias, m_ptr, max_m, n, k, status_word, reverse_m);
 }
 
 cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tbh,
@@ -674,9 +677,8 @@ cudaError_t launch_bn_epi(const CUtensorMap& ta, const CUtensorMap& tb, const __
   long long grid = sm_count();
   if (grid > max_tiles) grid = max_tiles;
   if (grid < 1) grid = 1;
-  gemm_tcgen05_kernel<BN, EPI><<<static_cast<int>(grid), kNumThreads, cfg::kSmemBytes, stream>>>(
-      ta, tb, c, bias, m_ptr, max_m, n, k, status_word, reverse_m);
-  return cudaGetLastError();
+  return launch_pdl(gemm_tcgen05_kernel<BN, EPI>, dim3(static_cast<int>(grid)), dim3(kNumThreads),
+                    cfg::kSmemBytes, stream, ta, tb, c, bias, m_ptr, max_m, n, k, status_word, reverse_m);
 }
 
 template <int BN>

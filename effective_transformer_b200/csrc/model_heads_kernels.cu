@@ -35,6 +35,8 @@ embedding_layernorm_kernel(const int* __restrict__ input_ids, const int* __restr
                            const T* __restrict__ pos_table, const T* __restrict__ gamma,
                            const T* __restrict__ beta, T* __restrict__ out, int max_tokens, int seq,
                            int n, float eps) {
+  pdl_wait();
+  pdl_trigger();
   constexpr int E = VecTraits<T>::kElems;
   const int t = clamp_tokens(t_ptr, max_tokens);
   const int lane = threadIdx.x & 31;
@@ -128,6 +130,8 @@ __global__ void __launch_bounds__(kThreads)
 gather_first_tokens_kernel(const char* __restrict__ packed, const int* __restrict__ cu_seqlens,
                            char* __restrict__ out, int batch, int max_tokens, int row_bytes,
                            int* __restrict__ count_out) {
+  pdl_wait();
+  pdl_trigger();
   if (count_out != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *count_out = batch;
   const int lane = threadIdx.x & 31;
   const int warp = blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
@@ -164,10 +168,11 @@ cudaError_t launch_embedding_layernorm(const int* input_ids, const int* token_ty
   const long long cap = static_cast<long long>(sm_count()) * kCtasPerSm;
   if (ctas > cap) ctas = cap;
   const int grid = static_cast<int>(ctas);
-#define ETB_EMB(V)                                                                               \
-  embedding_layernorm_kernel<T, V><<<grid, kThreads, 0, stream>>>(                               \
-      input_ids, token_type_ids, batch_idx, word_idx, t_ptr, word_table, vocab, type_table,      \
-      type_vocab, pos_table, gamma, beta, out, static_cast<int>(max_tokens), seq, n, eps)
+  cudaError_t le = cudaSuccess;
+#define ETB_EMB(V)                                                                                  \
+  le = launch_pdl(embedding_layernorm_kernel<T, V>, dim3(grid), dim3(kThreads), 0, stream, input_ids, \
+                  token_type_ids, batch_idx, word_idx, t_ptr, word_table, vocab, type_table, type_vocab, \
+                  pos_table, gamma, beta, out, static_cast<int>(max_tokens), seq, n, eps)
   if (vpl <= 1) ETB_EMB(1);
   else if (vpl <= 2) ETB_EMB(2);
   else if (vpl <= 3) ETB_EMB(3);
@@ -176,7 +181,7 @@ cudaError_t launch_embedding_layernorm(const int* input_ids, const int* token_ty
   else if (vpl <= 8) ETB_EMB(8);
   else return cudaErrorInvalidValue;
 #undef ETB_EMB
-  return cudaGetLastError();
+  return le;
 }
 
 cudaError_t launch_gather_first_tokens(const void* packed, const int* cu_seqlens, void* out, int batch,
@@ -187,10 +192,9 @@ cudaError_t launch_gather_first_tokens(const void* packed, const int* cu_seqlens
   long long ctas = (batch + kThreads / 32 - 1) / (kThreads / 32);
   const long long cap = static_cast<long long>(sm_count()) * kCtasPerSm;
   if (ctas > cap) ctas = cap;
-  gather_first_tokens_kernel<<<static_cast<int>(ctas), kThreads, 0, stream>>>(
-      static_cast<const char*>(packed), cu_seqlens, static_cast<char*>(out), batch, max_tokens, row_bytes,
-      count_out);
-  return cudaGetLastError();
+  return launch_pdl(gather_first_tokens_kernel, dim3(static_cast<int>(ctas)), dim3(kThreads), 0, stream,
+                    static_cast<const char*>(packed), cu_seqlens, static_cast<char*>(out), batch, max_tokens,
+                    row_bytes, count_out);
 }
 
 #define ETB_INST(T)                                                                               \

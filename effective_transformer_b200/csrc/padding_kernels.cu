@@ -20,6 +20,8 @@ constexpr int kRowsPerCta = 8;  // one warp per mask row
 __global__ void __launch_bounds__(kRowsPerCta * 32)
 seq_lengths_kernel(const int* __restrict__ mask, int batch, int seq, int* __restrict__ lens,
                    int* __restrict__ seq_len_out) {
+  pdl_wait();
+  pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.x * kRowsPerCta + warp;
   if (b >= batch) return;
@@ -40,6 +42,8 @@ padding_offsets_emit_kernel(const int* __restrict__ mask, const int* __restrict_
                             int seq, int* __restrict__ prefix_sum, int* __restrict__ valid_word_num,
                             int* __restrict__ batch_idx, int* __restrict__ word_idx,
                             int* __restrict__ cu_seqlens, int* __restrict__ padding_offset) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ int s_part[kRowsPerCta];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r0 = blockIdx.x * kRowsPerCta;
@@ -83,6 +87,7 @@ padding_offsets_emit_kernel(const int* __restrict__ mask, const int* __restrict_
 }
 
 __global__ void empty_batch_kernel(int* valid_word_num, int* cu_seqlens) {
+  pdl_wait();
   if (valid_word_num != nullptr) valid_word_num[0] = 0;
   if (cu_seqlens != nullptr) cu_seqlens[0] = 0;
 }
@@ -91,6 +96,8 @@ __global__ void empty_batch_kernel(int* valid_word_num, int* cu_seqlens) {
 // information): packed rows of one sequence are contiguous and ordered by b.
 __global__ void seq_bounds_kernel(const int* __restrict__ batch_idx, const int* __restrict__ t_ptr,
                                   int batch, int max_tokens, int* __restrict__ cu_seqlens) {
+  pdl_wait();
+  pdl_trigger();
   int t = *t_ptr;
   t = t < 0 ? 0 : (t > max_tokens ? max_tokens : t);
   for (int v = blockIdx.x * blockDim.x + threadIdx.x; v <= t; v += gridDim.x * blockDim.x) {
@@ -133,6 +140,8 @@ __global__ void __launch_bounds__(kCopyWarpsPerCta * 32)
 remove_padding_kernel(const char* __restrict__ from, const int* __restrict__ batch_idx,
                       const int* __restrict__ word_idx, const int* __restrict__ t_ptr,
                       char* __restrict__ to, int max_rows, int seq, int row_bytes) {
+  pdl_wait();
+  pdl_trigger();
   int t = *t_ptr;
   t = t < 0 ? 0 : (t > max_rows ? max_rows : t);
   const int lane = threadIdx.x & 31;
@@ -154,6 +163,8 @@ __global__ void __launch_bounds__(kCopyWarpsPerCta * 32)
 restore_padding_kernel(const char* __restrict__ from, const int* __restrict__ batch_idx,
                        const int* __restrict__ word_idx, const int* __restrict__ t_ptr,
                        char* __restrict__ to, int max_rows, int seq, int row_bytes) {
+  pdl_wait();
+  pdl_trigger();
   int t = *t_ptr;
   t = t < 0 ? 0 : (t > max_rows ? max_rows : t);
   const int lane = threadIdx.x & 31;
@@ -181,15 +192,14 @@ cudaError_t launch_padding_offsets(const int* mask, int batch, int seq, int* pre
                                    int* seq_len_out, int* cu_seqlens, int* padding_offset,
                                    int* scratch, cudaStream_t stream) {
   if (batch <= 0 || seq <= 0) {
-    empty_batch_kernel<<<1, 1, 0, stream>>>(valid_word_num, cu_seqlens);
-    return cudaGetLastError();
+    return launch_pdl(empty_batch_kernel, dim3(1), dim3(1), 0, stream, valid_word_num, cu_seqlens);
   }
   const int ctas = (batch + kRowsPerCta - 1) / kRowsPerCta;
-  seq_lengths_kernel<<<ctas, kRowsPerCta * 32, 0, stream>>>(mask, batch, seq, scratch, seq_len_out);
-  padding_offsets_emit_kernel<<<ctas, kRowsPerCta * 32, 0, stream>>>(
-      mask, scratch, batch, seq, prefix_sum, valid_word_num, batch_idx, word_idx, cu_seqlens,
-      padding_offset);
-  return cudaGetLastError();
+  cudaError_t e = launch_pdl(seq_lengths_kernel, dim3(ctas), dim3(kRowsPerCta * 32), 0, stream, mask, batch, seq,
+                             scratch, seq_len_out);
+  if (e != cudaSuccess) return e;
+  return launch_pdl(padding_offsets_emit_kernel, dim3(ctas), dim3(kRowsPerCta * 32), 0, stream, mask, scratch,
+                    batch, seq, prefix_sum, valid_word_num, batch_idx, word_idx, cu_seqlens, padding_offset);
 }
 
 cudaError_t launch_seq_bounds_from_batch_idx(const int* batch_idx, const int* t_ptr, int batch,
@@ -198,8 +208,8 @@ cudaError_t launch_seq_bounds_from_batch_idx(const int* batch_idx, const int* t_
   int ctas = (max_tokens + 1 + threads - 1) / threads;
   const int cap = sm_count() * 8;
   ctas = ctas < 1 ? 1 : (ctas > cap ? cap : ctas);
-  seq_bounds_kernel<<<ctas, threads, 0, stream>>>(batch_idx, t_ptr, batch, max_tokens, cu_seqlens);
-  return cudaGetLastError();
+  return launch_pdl(seq_bounds_kernel, dim3(ctas), dim3(threads), 0, stream, batch_idx, t_ptr, batch, max_tokens,
+                    cu_seqlens);
 }
 
 template <typename T>
@@ -212,10 +222,9 @@ cudaError_t launch_remove_padding(const T* from, const int* batch_idx, const int
   long long ctas = (rows + kCopyWarpsPerCta - 1) / kCopyWarpsPerCta;
   const long long cap = static_cast<long long>(sm_count()) * kCopyCtasPerSm;
   if (ctas > cap) ctas = cap;
-  remove_padding_kernel<<<static_cast<int>(ctas), kCopyWarpsPerCta * 32, 0, stream>>>(
-      reinterpret_cast<const char*>(from), batch_idx, word_idx, t_ptr, reinterpret_cast<char*>(to),
-      static_cast<int>(rows), seq, row_bytes);
-  return cudaGetLastError();
+  return launch_pdl(remove_padding_kernel, dim3(static_cast<int>(ctas)), dim3(kCopyWarpsPerCta * 32), 0, stream,
+                    reinterpret_cast<const char*>(from), batch_idx, word_idx, t_ptr, reinterpret_cast<char*>(to),
+                    static_cast<int>(rows), seq, row_bytes);
 }
 
 template <typename T>
@@ -228,10 +237,9 @@ cudaError_t launch_restore_padding(const T* from, const int* batch_idx, const in
   long long ctas = (rows + 1 + kCopyWarpsPerCta - 1) / kCopyWarpsPerCta;
   const long long cap = static_cast<long long>(sm_count()) * kCopyCtasPerSm;
   if (ctas > cap) ctas = cap;
-  restore_padding_kernel<<<static_cast<int>(ctas), kCopyWarpsPerCta * 32, 0, stream>>>(
-      reinterpret_cast<const char*>(from), batch_idx, word_idx, t_ptr, reinterpret_cast<char*>(to),
-      static_cast<int>(rows), seq, row_bytes);
-  return cudaGetLastError();
+  return launch_pdl(restore_padding_kernel, dim3(static_cast<int>(ctas)), dim3(kCopyWarpsPerCta * 32), 0, stream,
+                    reinterpret_cast<const char*>(from), batch_idx, word_idx, t_ptr, reinterpret_cast<char*>(to),
+                    static_cast<int>(rows), seq, row_bytes);
 }
 
 #define ETB_INST(T)                                                                              \
