@@ -110,6 +110,28 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
+def measure_fp32_gemm_tflops(dev, n: int = 8192, iters: int = 5) -> float:
+    """FP32 rate of the CUDA cores as cuBLAS reaches it (TF32 disabled): the roofline
+    denominator of the fp32 workloads, whose GEMMs do not use tensor cores."""
+    import torch
+    old = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        a = torch.randn(n, n, device=dev, dtype=torch.float32)
+        b = torch.randn(n, n, device=dev, dtype=torch.float32)
+        torch.matmul(a, b)
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(iters):
+            torch.matmul(a, b)
+        t1.record()
+        t1.synchronize()
+        return 2.0 * n ** 3 * iters / (t0.elapsed_time(t1) / 1000.0) / 1e12
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old
+
+
 def dist_env():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -335,7 +357,15 @@ def main():
         gemm_launches = sum(prof[c][1] for c in gemm_cats)
         gemm_flops_step = 2.0 * tokens_rank * h * (3 * h + h + 2 * sh.ffn_dim) * sh.num_layers
         achieved = (gemm_flops_step * args.steps) / (gemm_ms / 1000.0) / 1e12 if gemm_ms > 0 else None
-        peak_tf = peaks["bf16_tflops_sustained"] if fp16 else None
+        if fp16:
+            peak_tf, peak_note = peaks["bf16_tflops_sustained"], peak_src + " bf16_tflops_sustained"
+        else:
+            # the fp32 handle's GEMM takes every fp32 product as three tf32 tensor-core products
+            # (tf32 runs at half the bf16 rate), so its ceiling in fp32 FLOPs is bf16 / 6; the FP32 FMA
+            # rate of the CUDA cores, as cuBLAS SGEMM reaches it, is measured here for comparison
+            peak_tf = peaks["bf16_tflops_sustained"] / 6.0
+            peak_note = peak_src + " bf16_tflops_sustained / 6 (tf32 = bf16 / 2, three products per fp32 product)"
+            sgemm_tf = measure_fp32_gemm_tflops(dev)
         kernels = {k: {"ms_per_step": v[0] / args.steps, "launches_per_step": v[1] / args.steps}
                    for k, v in prof.items()}
         launches = sum(v[1] for v in prof.values())
@@ -350,19 +380,22 @@ def main():
                        "l2": "256 MB buffer written between timed steps (untimed)",
                        "launch": ("cuda-graph replay (et_graph_launch); per-kernel times from a second, eager pass"
                                   if args.graph else "eager (et_forward), per-kernel events inside the timed steps")},
-            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak_tf,
+                         "unit": "TFLOP/s",
                          "frac": (achieved / peak_tf) if (achieved and peak_tf) else None,
                          "traffic": NCU_GEMM_TRAFFIC.get(spec.name),
                          "traffic_note": NCU_GEMM_TRAFFIC_NOTE if spec.name in NCU_GEMM_TRAFFIC else None,
-                         "kernel": "gemm_tcgen05_pair_kernel" if fp16 else "gemm_simt_kernel",
+                         "kernel": "gemm_tcgen05_pair_kernel" if fp16 else "gemm_tf32x3_kernel (+ split_tf32_kernel)",
                          "algorithmic_flops_per_launch": gemm_flops_step / max(gemm_launches / args.steps, 1),
                          "launches_per_step": gemm_launches / args.steps,
                          "avg_launch_ms": gemm_ms / max(gemm_launches, 1),
-                         "peak_source": peak_src + " bf16_tflops_sustained"},
+                         "peak_source": peak_note},
             "kernels": kernels,
             "gpu_launches": launches,
             "clocks": clocks,
         }
+        if not fp16:
+            line["roofline"]["cublas_sgemm_tflops_measured_here"] = sgemm_tf
         if e2e_ms is not None:
             line["e2e"] = {"value": tokens_all / (e2e_total_ms / args.steps / 1000.0), "unit": UNIT,
                            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,

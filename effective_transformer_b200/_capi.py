@@ -104,6 +104,8 @@ SIGNATURES = {
     "et_attention_tiles": (i32, [vp, vp, vp, i64, i64, vp, vp, i32, i32, i32, i32, i32, vp, vp]),
     "et_gemm": (i32, [i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp]),
     "et_pack_weight": (i32, [i32, vp, vp, i32, i32, vp]),
+    "et_split_tf32": (i32, [vp, vp, vp, vp, i32, i32, vp]),
+    "et_gemm_fp32_tensor": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp]),
 }
 
 _lib: Optional[C.CDLL] = None

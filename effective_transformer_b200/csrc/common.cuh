@@ -256,6 +256,14 @@ cudaError_t launch_attention_tcgen05(const __half* q, const __half* k, const __h
                                      long long token_stride, long long head_stride, __half* ctx,
                                      const int* plan, int batch, int max_tokens, int heads, int d,
                                      int* status_word, cudaStream_t stream, bool reverse = false);
+// fp32 GEMM on the tensor cores by the three-product tf32 split (gemm_tf32x3.cu):
+// x = hi + lo with hi = rn_tf32(x); hi/lo may alias x.  rows_ptr null = max_rows.
+cudaError_t launch_split_tf32(const float* x, float* hi, float* lo, const int* rows_ptr, int max_rows, int cols,
+                              cudaStream_t stream);
+// a_hi/a_lo [max_m, K], w_hi/w_lo [N, K] (K-major); C = epi(A * W^T (+ bias)), fp32.
+cudaError_t launch_gemm_tf32x3(const float* a_hi, const float* a_lo, const float* w_hi, const float* w_lo,
+                               const float* bias, float* c, const int* m_ptr, int max_m, int n, int k,
+                               int epilogue, int* status_word, cudaStream_t stream, bool reverse_m = false);
 // tcgen05 GEMM, fp16 in / fp32 accumulate / fp16 out.  w_packed is [N,K].
 // reverse_m: row tiles are visited from the last to the first.  A kernel that
 // consumes what the previous kernel has just written finds the rows written

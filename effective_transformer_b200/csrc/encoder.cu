@@ -34,6 +34,12 @@ struct LayerWeights {
   void* wo_t = nullptr;    // [H, H]
   void* w1_t = nullptr;    // [F, H]
   void* w2_t = nullptr;    // [H, F]
+  // fp32 handles: the K-major copies above hold rn_tf32(W) and these W - rn_tf32(W)
+  // (the two halves of the three-product tf32 split, gemm_tf32x3.cu)
+  void* wqkv_lo = nullptr;
+  void* wo_lo = nullptr;
+  void* w1_lo = nullptr;
+  void* w2_lo = nullptr;
   void* bqkv = nullptr;    // [3H]
   void* bo = nullptr;
   void* ln1_gamma = nullptr;
@@ -86,6 +92,8 @@ struct Workspace {
   int* lens_scratch = nullptr;
   int* attn_plan = nullptr;   // tile plan of the tcgen05 attention (made once per batch)
   int* pos_row = nullptr;     // [B*S] position -> packed row (general-mask attention)
+  float* a_hi = nullptr;      // fp32 handles: [cap, max(H, F)] tf32 halves of a projection's input
+  float* a_lo = nullptr;
   int* valid_word_num = nullptr;
   int* status = nullptr;
   std::vector<void*> allocations;
@@ -245,6 +253,7 @@ size_t workspace_bytes_for(const et_handle_s* h, size_t batch, size_t seq) {
   total += batch * seq * hid * e * 2;  // staging in/out
   total += batch * seq * 4 * 8;        // mask / id / type staging + 5 index arrays
   total += round_up(batch, 128) * hid * e * 2;  // first-token rows, pooled output
+  if (h->cfg.dtype == ET_FP32) total += cap * (f > hid ? f : hid) * 4 * 2;  // tf32 halves of a GEMM input
   total += (batch * 3 + 8) * 4;
   return total;
 }
@@ -266,6 +275,15 @@ int pack_layer(et_handle_t h, LayerWeights& lw, const void* const* w, cudaStream
     ET_CUDA(h, launch_transpose<T>(W(6), static_cast<T*>(lw.wo_t), hid, hid, s));
     ET_CUDA(h, launch_transpose<T>(W(10), static_cast<T*>(lw.w1_t), hid, f, s));
     ET_CUDA(h, launch_transpose<T>(W(12), static_cast<T*>(lw.w2_t), f, hid, s));
+  }
+  if (std::is_same<T, float>::value && lw.wqkv_lo != nullptr) {
+    // in place: the K-major copy keeps rn_tf32(W), the second array gets the remainder
+    struct { void* hi; void* lo; int rows, cols; } parts[] = {
+        {lw.wqkv_t, lw.wqkv_lo, 3 * hid, hid}, {lw.wo_t, lw.wo_lo, hid, hid},
+        {lw.w1_t, lw.w1_lo, f, hid}, {lw.w2_t, lw.w2_lo, hid, f}};
+    for (auto& p : parts)
+      ET_CUDA(h, launch_split_tf32(static_cast<const float*>(p.hi), static_cast<float*>(p.hi),
+                                   static_cast<float*>(p.lo), nullptr, p.rows, p.cols, s));
   }
   for (int j = 0; j < 3; ++j)
     ET_CUDA(h, cudaMemcpyAsync(static_cast<T*>(lw.bqkv) + j * hid, w[2 * j + 1], sizeof(T) * hid,
@@ -298,6 +316,7 @@ int run_layer(et_handle_t h, const LayerWeights& lw, const T* x_in, T* x_out, co
   T* ffn = static_cast<T*>(ws.ffn);
   auto B = [](const void* p) { return static_cast<const T*>(p); };
   const bool tc = std::is_same<T, __half>::value && !h->use_simt;
+  const bool tc32 = std::is_same<T, float>::value && !h->use_simt;  // three-product tf32 split
   // direction for a kernel that can run either way / for one that only runs first-to-last
   auto turn = [&]() {
     const bool reverse = h->snake && h->prev_ascending;
@@ -306,18 +325,27 @@ int run_layer(et_handle_t h, const LayerWeights& lw, const T* x_in, T* x_out, co
   };
   auto forward_only = [&]() { h->prev_ascending = true; };
 
-  auto gemm = [&](const T* a, const void* w_rm, const void* w_t, const void* bias, T* c, int n, int k,
-                  int epi) -> cudaError_t {
+  auto gemm = [&](const T* a, const void* w_rm, const void* w_t, const void* w_lo, const void* bias, T* c,
+                  int n, int k, int epi) -> cudaError_t {
     if (tc)
       return launch_gemm_tcgen05(reinterpret_cast<const __half*>(a), static_cast<const __half*>(w_t),
                                  static_cast<const __half*>(bias), reinterpret_cast<__half*>(c), t_ptr,
                                  max_m, n, k, epi, ws.status, s, turn());
+    if (tc32) {
+      // w_t holds rn_tf32(W), w_lo the remainder; the input is split the same way first
+      cudaError_t e = launch_split_tf32(reinterpret_cast<const float*>(a), ws.a_hi, ws.a_lo, t_ptr, max_m, k, s);
+      if (e != cudaSuccess) return e;
+      forward_only();
+      return launch_gemm_tf32x3(ws.a_hi, ws.a_lo, static_cast<const float*>(w_t), static_cast<const float*>(w_lo),
+                                static_cast<const float*>(bias), reinterpret_cast<float*>(c), t_ptr, max_m, n, k,
+                                epi, ws.status, s, turn());
+    }
     forward_only();
     return launch_gemm_simt<T>(a, B(w_rm), B(bias), c, t_ptr, max_m, n, k, epi, s);
   };
 
   // Q,K,V projections + bias in one GEMM -> [T, 3H]
-  ET_LAUNCH(h, ET_PROF_GEMM_QKV, 1, s, gemm(x_in, lw.wqkv, lw.wqkv_t, lw.bqkv, qkv, 3 * hid, hid, kEpiBias));
+  ET_LAUNCH(h, ET_PROF_GEMM_QKV, tc32 ? 2 : 1, s, gemm(x_in, lw.wqkv, lw.wqkv_t, lw.wqkv_lo, lw.bqkv, qkv, 3 * hid, hid, kEpiBias));
   // attention straight from the [T, 3H] buffer to packed context [T, H]
   if (h->cur_attr_mask != nullptr)
     ET_LAUNCH(h, ET_PROF_ATTENTION, 1, s,
@@ -342,12 +370,12 @@ int run_layer(et_handle_t h, const LayerWeights& lw, const T* x_in, T* x_out, co
                                         batch, seq, heads, d, s));
   if (!(h->cur_attr_mask == nullptr && tc && seq <= 128)) forward_only();
   // attention output projection, then +bias +residual, LayerNorm
-  ET_LAUNCH(h, ET_PROF_GEMM_ATTN_OUT, 1, s, gemm(ctx, lw.wo, lw.wo_t, nullptr, att, hid, hid, kEpiNone));
+  ET_LAUNCH(h, ET_PROF_GEMM_ATTN_OUT, tc32 ? 2 : 1, s, gemm(ctx, lw.wo, lw.wo_t, lw.wo_lo, nullptr, att, hid, hid, kEpiNone));
   ET_LAUNCH(h, ET_PROF_LAYERNORM, 1, s, launch_add_bias_input_layernorm<T>(att, x_in, B(lw.bo), B(lw.ln1_gamma), B(lw.ln1_beta),
                                                 t_ptr, max_m, hid, h->eps, s, turn()));
   // feed-forward: bias + GELU fused into the first GEMM
-  ET_LAUNCH(h, ET_PROF_GEMM_FFN1, 1, s, gemm(att, lw.w1, lw.w1_t, lw.b1, ffn, f, hid, kEpiBiasGelu));
-  ET_LAUNCH(h, ET_PROF_GEMM_FFN2, 1, s, gemm(ffn, lw.w2, lw.w2_t, nullptr, x_out, hid, f, kEpiNone));
+  ET_LAUNCH(h, ET_PROF_GEMM_FFN1, tc32 ? 2 : 1, s, gemm(att, lw.w1, lw.w1_t, lw.w1_lo, lw.b1, ffn, f, hid, kEpiBiasGelu));
+  ET_LAUNCH(h, ET_PROF_GEMM_FFN2, tc32 ? 2 : 1, s, gemm(ffn, lw.w2, lw.w2_t, lw.w2_lo, nullptr, x_out, hid, f, kEpiNone));
   ET_LAUNCH(h, ET_PROF_LAYERNORM, 1, s, launch_add_bias_input_layernorm<T>(x_out, att, B(lw.b2), B(lw.ln2_gamma), B(lw.ln2_beta),
                                                 t_ptr, max_m, hid, h->eps, s, turn()));
   return ET_OK;
@@ -687,7 +715,7 @@ int et_create(const et_config_t* config, et_handle_t* out_handle) {
   h->hidden = hid;
   h->esize = c.dtype == ET_FP16 ? 2 : 4;
   h->eps = c.layernorm_eps > 0.f ? c.layernorm_eps : 1e-6f;
-  h->use_simt = (c.dtype == ET_FP32);
+  h->use_simt = false;
   h->layers.resize(c.num_layers);
   auto bail = [&](int rc) {
     std::string msg = h->last_error;
@@ -705,11 +733,13 @@ int et_create(const et_config_t* config, et_handle_t* out_handle) {
         {&lw.b1, f}, {&lw.b2, H}, {&lw.ln2_gamma, H}, {&lw.ln2_beta, H}};
     for (auto& it : items)
       if ((rc = ws_alloc(h, it.p, it.n * e)) != ET_OK) return bail(rc);
-    if (c.dtype == ET_FP16) {
+    {  // K-major [out, in] copies for the tensor-core GEMMs (fp32: plus the tf32 remainders)
       struct { void** p; size_t n; } packed[] = {
-          {&lw.wqkv_t, 3 * H * H}, {&lw.wo_t, H * H}, {&lw.w1_t, H * f}, {&lw.w2_t, f * H}};
-      for (auto& it : packed)
-        if ((rc = ws_alloc(h, it.p, it.n * e)) != ET_OK) return bail(rc);
+          {&lw.wqkv_t, 3 * H * H}, {&lw.wo_t, H * H}, {&lw.w1_t, H * f}, {&lw.w2_t, f * H},
+          {&lw.wqkv_lo, 3 * H * H}, {&lw.wo_lo, H * H}, {&lw.w1_lo, H * f}, {&lw.w2_lo, f * H}};
+      const int count = c.dtype == ET_FP16 ? 4 : 8;
+      for (int i = 0; i < count; ++i)
+        if ((rc = ws_alloc(h, packed[i].p, packed[i].n * e)) != ET_OK) return bail(rc);
     }
   }
   Workspace& ws = h->ws;
@@ -732,6 +762,8 @@ int et_create(const et_config_t* config, et_handle_t* out_handle) {
       {reinterpret_cast<void**>(&ws.lens_scratch), static_cast<size_t>(c.max_batch_size) * 4},
       {reinterpret_cast<void**>(&ws.attn_plan), attention_plan_ints(c.max_batch_size, static_cast<int>(cap)) * 4},
       {reinterpret_cast<void**>(&ws.pos_row), cap * 4},
+      {reinterpret_cast<void**>(&ws.a_hi), c.dtype == ET_FP32 ? cap * (f > H ? f : H) * 4 : 0},
+      {reinterpret_cast<void**>(&ws.a_lo), c.dtype == ET_FP32 ? cap * (f > H ? f : H) * 4 : 0},
       {reinterpret_cast<void**>(&ws.valid_word_num), 4}, {reinterpret_cast<void**>(&ws.status), 4}};
   for (auto& b : bufs)
     if ((rc = ws_alloc(h, b.p, b.bytes)) != ET_OK) return bail(rc);
@@ -794,7 +826,7 @@ const char* et_last_error(et_handle_t h) {
 
 int et_set_debug_simt(et_handle_t h, int use_simt) {
   if (h == nullptr) return ET_INVALID_ARGUMENT;
-  h->use_simt = (use_simt != 0) || h->cfg.dtype == ET_FP32;
+  h->use_simt = use_simt != 0;
   return ET_OK;
 }
 
@@ -1541,6 +1573,25 @@ int et_gemm(int dtype, const void* a, const void* w, const void* w_packed, const
                                               epilogue, s),
                      launch_gemm_simt<float>(F_(a), F_(w), F_(bias), static_cast<float*>(c), m_ptr, max_m, n, k,
                                              epilogue, s));
+}
+
+int et_split_tf32(const float* x, float* hi, float* lo, const int* rows_ptr, int max_rows, int cols,
+                  void* stream) {
+  if (max_rows < 0 || cols < 0) return ET_INVALID_ARGUMENT;
+  if (max_rows == 0 || cols == 0) return ET_OK;
+  if (!x || !hi || !lo) return ET_INVALID_ARGUMENT;
+  return to_status(launch_split_tf32(x, hi, lo, rows_ptr, max_rows, cols, static_cast<cudaStream_t>(stream)));
+}
+
+int et_gemm_fp32_tensor(const float* a_hi, const float* a_lo, const float* w_hi, const float* w_lo,
+                        const float* bias, float* c, const int* m_ptr, int max_m, int n, int k, int epilogue,
+                        int* status_word, void* stream) {
+  if (!m_ptr || max_m < 0 || n <= 0 || k <= 0 || epilogue < 0 || epilogue > 3) return ET_INVALID_ARGUMENT;
+  if (epilogue != 0 && !bias) return ET_INVALID_ARGUMENT;
+  if (max_m == 0) return ET_OK;
+  if (!a_hi || !a_lo || !w_hi || !w_lo || !c) return ET_INVALID_ARGUMENT;
+  return to_status(launch_gemm_tf32x3(a_hi, a_lo, w_hi, w_lo, bias, c, m_ptr, max_m, n, k, epilogue, status_word,
+                                      static_cast<cudaStream_t>(stream)));
 }
 
 int et_pack_weight(int dtype, const void* w, void* w_packed, int k, int n, void* stream) {

@@ -295,9 +295,10 @@ int et_get_profile(et_handle_t handle, double* ms_out, long long* launches_out, 
  * from device to host on `stream` and waits for it. */
 int et_copy_to_host(void* dst_host, const void* src_device, size_t bytes, void* stream);
 
-/* Selects the GEMM / attention implementation of an fp16 handle:
- * 0 = tcgen05 tensor-core kernels (default), 1 = CUDA-core kernels (the fp32
- * handle always uses these; on fp16 they exist for debugging only). */
+/* 0 (default): tensor-core kernels - tcgen05 GEMMs and attention for an fp16
+ * handle, the tf32-split tcgen05 GEMM for an fp32 handle (its attention is
+ * always the CUDA-core kernel).  1: CUDA-core GEMMs and attention for both
+ * (plain fp32 FMA arithmetic; for debugging and as a second opinion). */
 int et_set_debug_simt(et_handle_t handle, int use_simt);
 
 /* ---- kernel-level entry points (one per reference launcher) --------------
@@ -434,6 +435,20 @@ int et_gemm(int dtype, const void* a, const void* w, const void* w_packed, const
             const int* m_ptr, int max_m, int n, int k, int epilogue, int use_simt, int* status_word,
             void* stream);
 int et_pack_weight(int dtype, const void* w, void* w_packed, int k, int n, void* stream);
+
+/* The same call sites for the FP32 OperationType on the tensor cores, keeping
+ * fp32 accuracy: every operand is split into two tf32 numbers, x = hi + lo with
+ * hi = round_to_tf32(x) (et_split_tf32; hi or lo may be x itself), and the
+ * product is hi*hi + hi*lo + lo*hi accumulated in fp32 - one tcgen05 kind::tf32
+ * GEMM over a K axis three times as long.  a_hi/a_lo are [max_m, K], w_hi/w_lo
+ * the halves of the [N, K] K-major copy made by et_pack_weight; N a multiple of
+ * 128, K of 32; epilogue as for et_gemm.  No reference counterpart (the
+ * reference's fp32 path is cuBLAS SGEMM). */
+int et_split_tf32(const float* x, float* hi, float* lo, const int* rows_ptr, int max_rows, int cols,
+                  void* stream);
+int et_gemm_fp32_tensor(const float* a_hi, const float* a_lo, const float* w_hi, const float* w_lo,
+                        const float* bias, float* c, const int* m_ptr, int max_m, int n, int k, int epilogue,
+                        int* status_word, void* stream);
 
 #ifdef __cplusplus
 }

@@ -351,3 +351,48 @@ def test_attention_full_size_softmax_rows_sum_to_one():
                           3 * h, 64, iptr(ctx), iptr(dev(cu)), len(lens), 64, t, 12, 64, 0, iptr(st), stream()))
     torch.cuda.synchronize()
     assert float((ctx.float() - 1.0).abs().max()) < 2e-3
+
+
+@pytest.mark.parametrize("m,cap,n,k", [(1, 1, 128, 64), (60, 60, 128, 128), (134, 256, 768, 768),
+                                       (300, 384, 2304, 768), (257, 300, 768, 3072), (128, 128, 256, 32),
+                                       (1000, 1000, 3072, 768), (0, 64, 256, 128), (5000, 5000, 1152, 1024)])
+@pytest.mark.parametrize("epi", [0, 1, 2, 3])
+def test_gemm_fp32_on_tensor_cores_keeps_fp32_accuracy(m, cap, n, k, epi):
+    """The three-product tf32 split: same tolerance as the CUDA-core fp32 GEMM against the
+    float64 product, and the split itself is exact (hi + lo == x, hi has 11 significand bits)."""
+    rng = np.random.RandomState(m + n + k + epi)
+    a = dev(rng.randn(cap, k).astype(np.float32))
+    w = dev((rng.randn(k, n) / math.sqrt(k)).astype(np.float32))
+    bias = dev(rng.randn(n).astype(np.float32))
+    c = torch.full((cap, n), 3.0, dtype=torch.float32, device="cuda")
+    w_hi = torch.empty((n, k), dtype=torch.float32, device="cuda")
+    ok(lib().et_pack_weight(_capi.ET_FP32, iptr(w), iptr(w_hi), k, n, stream()))
+    w_lo = torch.empty_like(w_hi)
+    ok(lib().et_split_tf32(iptr(w_hi), iptr(w_hi), iptr(w_lo), None, n, k, stream()))     # in place
+    a_hi, a_lo = torch.empty_like(a), torch.empty_like(a)
+    mt = dev(np.array([m], np.int32))
+    ok(lib().et_split_tf32(iptr(a), iptr(a_hi), iptr(a_lo), iptr(mt), cap, k, stream()))
+    torch.cuda.synchronize()
+    assert torch.equal(a_hi[:m] + a_lo[:m], a[:m])
+    assert torch.equal(w_hi + w_lo, w.t().contiguous())
+    assert bool(((a_hi[:m].view(torch.int32) & 0x1FFF) == 0).all())          # tf32: low 13 bits clear
+    assert bool((a_lo[:m].abs() <= a[:m].abs() * 2.0 ** -11).all())
+    st = status_word()
+    ok(lib().et_gemm_fp32_tensor(iptr(a_hi), iptr(a_lo), iptr(w_hi), iptr(w_lo), iptr(bias) if epi else None,
+                                 iptr(c), iptr(mt), cap, n, k, epi, iptr(st), stream()))
+    torch.cuda.synchronize()
+    assert int(st[0]) == 0, f"device-side wait expired: status 0x{int(st[0]):x}"
+    ref = a[:m].double() @ w.double()
+    if epi >= 1:
+        ref = ref + bias.double()
+    if epi == 2:
+        ref = O.gelu(ref)
+    if epi == 3:
+        ref = torch.tanh(ref)
+    torch.testing.assert_close(c[:m].double(), ref, rtol=1e-5, atol=2e-5)
+    assert torch.all(c[m:] == 3.0), "rows past M were written"
+    if m > 0:
+        # a plain tf32 product (one term) would miss this tolerance by two orders of magnitude
+        one_term = (a_hi[:m].double() @ w_hi.double().t())
+        plain = a[:m].double() @ w.double()
+        assert float((one_term - plain).abs().max()) > 20 * float((c[:m].double() - ref).abs().max()) or k < 128

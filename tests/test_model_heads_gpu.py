@@ -191,7 +191,7 @@ def assert_model_parity(seq, pooled, ref_seq_valid, ref_pooled, mask, fp16):
     assert torch.all(seq.detach().cpu().reshape(b * s, h)[pad] == 0)
 
 
-@pytest.mark.parametrize("dtype,simt", [("fp32", False), ("fp16", True), ("fp16", False)])
+@pytest.mark.parametrize("dtype,simt", [("fp32", False), ("fp32", True), ("fp16", True), ("fp16", False)])
 def test_forward_ids_tiny_against_golden(dtype, simt):
     d = np.load(os.path.join(GOLD, "tiny_model_fp64.npz"))
     spec, wl, lengths, mask, heads = tiny_model_case(dtype)

@@ -68,7 +68,7 @@ def oracle_valid(wl, spec, dtype64=False):
     return O.valid_rows(y, wl.mask)
 
 
-@pytest.mark.parametrize("dtype,simt", [("fp32", False), ("fp16", True), ("fp16", False)])
+@pytest.mark.parametrize("dtype,simt", [("fp32", False), ("fp32", True), ("fp16", True), ("fp16", False)])
 def test_tiny_against_golden(dtype, simt):
     d = np.load(os.path.join(GOLD, "tiny_fp64.npz"))
     spec = W.tiny_spec(dtype=dtype)
