@@ -71,7 +71,8 @@ typedef struct {
  * fields are ignored; otherwise all 16 weight fields must be device pointers
  * and are repacked on `stream` before the layer runs.  attr_mask ([B,S,S]) is
  * accepted for signature compatibility and must be the key-only tile of the
- * input mask (sample/tensorflow/benchmark.py:59-61); it is not read. */
+ * input mask (sample/tensorflow/benchmark.py:59-61); it is not read unless the
+ * handle is in general-mask mode (et_set_general_mask). */
 typedef struct {
   const void* from_tensor;   /* packed [T, H] inside a [B,S,H]-sized buffer */
   const void* to_tensor;     /* must equal from_tensor (self-attention) */
