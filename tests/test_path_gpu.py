@@ -224,3 +224,44 @@ def test_cfg2_full_size_properties():
     d = (y_p.float() - y[torch.from_numpy(perm).cuda()].float()).abs()
     assert float(d.max()) <= FP16_MAX_ABS and float(d.mean()) <= FP16_MEAN_ABS
     eng.close()
+
+
+def test_cfg3_fp32_full_size_both_gemm_paths():
+    """fp32 workload (B=500, S=64, 12 layers) at full size: a sub-batch against the float64
+    oracle, and the tensor-core (tf32 split) and CUDA-core GEMM paths against each other."""
+    spec = W.WORKLOADS[3]
+    wl = W.make_workload(spec)
+    eng = make_engine(spec, wl)
+    y = run_forward(eng, wl)
+    sub = W.Workload(spec, wl.lengths[:16], wl.mask[:16], wl.from_tensor[:16], wl.weights)
+    ref = oracle_valid(sub, spec, dtype64=True)
+    got = O.valid_rows(y[:16].cpu().double(), sub.mask)
+    rms = float(ref.pow(2).mean().sqrt())
+    assert float((got - ref).abs().max()) <= FP32_REL_RMS * rms
+    eng.set_debug_simt(True)
+    y_simt = run_forward(eng, wl)
+    assert float((y - y_simt).abs().max()) <= FP32_REL_RMS * rms
+    pad = torch.from_numpy(wl.mask.ravel() == 0).cuda()
+    assert torch.all(y.reshape(-1, spec.shape.hidden)[pad] == 0)
+    eng.close()
+
+
+def test_cfg4_bert_large_skewed_lengths_full_size():
+    """BERT-large, 24 layers, B=4096, S=128, 90 % short and 10 % long sequences (524 288
+    positions, 82 348 valid): the long sequences and a few short ones against the oracle."""
+    spec = W.WORKLOADS[4]
+    wl = W.make_workload(spec)
+    assert wl.valid_tokens == 82348
+    eng = make_engine(spec, wl)
+    y = run_forward(eng, wl)
+    order = np.argsort(-wl.lengths, kind="stable")
+    pick = np.sort(np.concatenate([order[:3], order[-3:], [0, 1]]))       # longest, shortest, first
+    sub = W.Workload(spec, wl.lengths[pick], wl.mask[pick], wl.from_tensor[pick], wl.weights)
+    ref = oracle_valid(sub, spec)
+    got = O.valid_rows(y[torch.from_numpy(pick).cuda()].cpu().double(), sub.mask)
+    diff = (got - ref.double()).abs()
+    assert float(diff.max()) <= FP16_MAX_ABS and float(diff.mean()) <= FP16_MEAN_ABS, \
+        (float(diff.max()), float(diff.mean()))
+    pad = torch.from_numpy(wl.mask.ravel() == 0).cuda()
+    assert torch.all(y.reshape(-1, spec.shape.hidden)[pad] == 0)
+    eng.close()
