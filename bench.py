@@ -145,6 +145,12 @@ def cpu_oracle_throughput(spec: W.WorkloadSpec, sample_seqs: int):
     tokens, threads)."""
     import torch
     from oracle import bert_encoder as O
+    # all host cores this process may use (torchrun presets OMP_NUM_THREADS=1 for its workers)
+    try:
+        cores = len(os.sched_getaffinity(0))
+    except AttributeError:
+        cores = os.cpu_count() or 1
+    torch.set_num_threads(max(1, cores))
     wl = W.make_workload(spec, batch_override=sample_seqs)
     am = W.attention_mask_from_input_mask(wl.mask)
     warm = W.Workload(spec, wl.lengths[:4], wl.mask[:4], wl.from_tensor[:4], wl.weights)
