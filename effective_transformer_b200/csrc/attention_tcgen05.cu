@@ -151,10 +151,15 @@ __global__ void attention_plan_kernel(const int* __restrict__ cu_seqlens, int ba
     }
   }
   __syncthreads();  // next[] is dead: seq_hi may be written
-  for (int b = threadIdx.x; b < batch; b += blockDim.x) {
+  // one warp per sequence, lanes over its tokens: the label stores are coalesced
+  // (a thread per sequence scatters 32 lines per store instruction and made this
+  // loop the longest part of the kernel)
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for (int b = warp; b < batch; b += nwarps) {
     int lo = cu_seqlens[b], hi = cu_seqlens[b + 1];
+    lo = lo < 0 ? 0 : lo;
     hi = hi > max_tokens ? max_tokens : hi;
-    for (int t = lo; t < hi; ++t) {
+    for (int t = lo + lane; t < hi; t += 32) {
       seq_lo[t] = lo;
       seq_hi[t] = hi;
     }

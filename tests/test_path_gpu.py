@@ -265,3 +265,27 @@ def test_cfg4_bert_large_skewed_lengths_full_size():
     pad = torch.from_numpy(wl.mask.ravel() == 0).cuda()
     assert torch.all(y.reshape(-1, spec.shape.hidden)[pad] == 0)
     eng.close()
+
+
+def test_two_handles_and_two_streams_do_not_share_state():
+    """Two handles with different weights, driven alternately on two streams: each must
+    reproduce what it computes alone (nothing of a pass lives in process-wide state)."""
+    specs = [W.tiny_spec(dtype="fp16", seed=11), W.tiny_spec(dtype="fp16", layers=3, batch=7, max_seq_len=20, seed=12)]
+    wls = [W.make_workload(s, random_gamma_beta=True) for s in specs]
+    engs = [make_engine(s, w) for s, w in zip(specs, wls)]
+    xs = [torch.from_numpy(w.from_tensor).half().cuda() for w in wls]
+    ms = [torch.from_numpy(w.mask).cuda() for w in wls]
+    alone = [e.forward(x, m).clone() for e, x, m in zip(engs, xs, ms)]
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    outs = [[], []]
+    for _ in range(4):
+        for i in (0, 1):
+            with torch.cuda.stream(streams[i]):
+                outs[i].append(engs[i].forward(xs[i], ms[i]))
+    torch.cuda.synchronize()
+    for i in (0, 1):
+        for y in outs[i]:
+            assert torch.equal(y, alone[i])
+        assert engs[i].device_status() == 0
+        engs[i].close()
