@@ -221,7 +221,9 @@ cudaError_t launch_copy_columns(const T* src, T* dst, int rows, int cols, int ds
                                 cudaStream_t stream);
 
 // kEpiBiasTanh is the pooler's activation (sample/tensorflow/modeling.py:224-232).
-enum Epilogue : int { kEpiNone = 0, kEpiBias = 1, kEpiBiasGelu = 2, kEpiBiasTanh = 3 };
+// kEpiBiasResidual adds a [M,N] tensor (the layer's residual input) besides the bias, so that
+// the LayerNorm behind the projection reads one tensor instead of two.
+enum Epilogue : int { kEpiNone = 0, kEpiBias = 1, kEpiBiasGelu = 2, kEpiBiasTanh = 3, kEpiBiasResidual = 4 };
 
 // CUDA-core GEMM: C[M,N] = epi(A[M,K] * W[K,N]); W row-major [K,N].
 template <typename T>
@@ -271,6 +273,7 @@ cudaError_t launch_gemm_tf32x3(const float* a_hi, const float* a_lo, const float
 // alternate their direction.
 cudaError_t launch_gemm_tcgen05(const __half* a, const __half* w_packed, const __half* bias,
                                 __half* c, const int* m_ptr, int max_m, int n, int k, int epilogue,
-                                int* status_word, cudaStream_t stream, bool reverse_m = false);
+                                int* status_word, cudaStream_t stream, bool reverse_m = false,
+                                const __half* residual = nullptr);
 
 }  // namespace etb

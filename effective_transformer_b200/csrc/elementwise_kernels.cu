@@ -92,7 +92,8 @@ add_bias_gelu_kernel(T* __restrict__ out, const T* __restrict__ bias, const int*
   }
 }
 
-// out[row] = LN(out[row] + input[row] + bias) * gamma + beta, one warp per
+// out[row] = LN(out[row] + input[row] + bias) * gamma + beta (input and bias
+// null: LN(out[row]) alone, for a producer that added them itself), one warp per
 // row, the row held in registers (fp32) between the two statistics passes.
 // bias / gamma / beta are re-read per row: they stay L1-resident, and not
 // keeping them in registers doubles the number of resident warps.
@@ -115,14 +116,14 @@ add_bias_input_layernorm_kernel(T* __restrict__ out, const T* __restrict__ input
   for (int r = warp; r < t; r += nwarps) {
     const int row = reverse ? t - 1 - r : r;  // last rows first: they are the freshest in L2
     T* orow = out + static_cast<size_t>(row) * n;
-    const T* irow = input + static_cast<size_t>(row) * n;
+    const T* irow = input != nullptr ? input + static_cast<size_t>(row) * n : nullptr;
     Vec16 vo[kVPL], vi[kVPL];
 #pragma unroll
     for (int j = 0; j < kVPL; ++j) {
       const int c = j * 32 + lane;
       if (c < vpr) {
         vo[j] = ld_global_v4(orow + c * E);
-        vi[j] = ld_global_nc_v4(irow + c * E);
+        if (input != nullptr) vi[j] = ld_global_nc_v4(irow + c * E);
       }
     }
     float x[kVPL][E];
@@ -131,13 +132,18 @@ add_bias_input_layernorm_kernel(T* __restrict__ out, const T* __restrict__ input
     for (int j = 0; j < kVPL; ++j) {
       const int c = j * 32 + lane;
       if (c < vpr) {
-        float fo[E], fi[E], fb[E];
+        float fo[E];
         VecTraits<T>::unpack(vo[j], fo);
-        VecTraits<T>::unpack(vi[j], fi);
-        VecTraits<T>::unpack(ld_global_v4(bias + c * E), fb);
+        if (input != nullptr) {   // uniform: null when the producer has already added residual and bias
+          float fi[E], fb[E];
+          VecTraits<T>::unpack(vi[j], fi);
+          VecTraits<T>::unpack(ld_global_v4(bias + c * E), fb);
+#pragma unroll
+          for (int e = 0; e < E; ++e) fo[e] += fi[e] + fb[e];
+        }
 #pragma unroll
         for (int e = 0; e < E; ++e) {
-          x[j][e] = fo[e] + fi[e] + fb[e];
+          x[j][e] = fo[e];
           sum += x[j][e];
         }
       } else {

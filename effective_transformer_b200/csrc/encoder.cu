@@ -137,6 +137,7 @@ struct et_handle_s {
   // with the rows its producer wrote last finds them in L2.  prev_ascending =
   // the previous kernel of the chain wrote its rows first-to-last.
   bool snake = true;          // ETB_SNAKE=0 switches it off (A/B measurements)
+  bool fuse_residual = true;  // ETB_FUSE_RESIDUAL=0: bias + residual added by the LayerNorm kernel instead
   bool prev_ascending = true;
   // general [B,S,S] mask of the pass being enqueued (null: key-only mask, fast kernels)
   const void* cur_attr_mask = nullptr;
@@ -375,9 +376,25 @@ int run_layer(et_handle_t h, const LayerWeights& lw, const T* x_in, T* x_out, co
                                                 t_ptr, max_m, hid, h->eps, s, turn()));
   // feed-forward: bias + GELU fused into the first GEMM
   ET_LAUNCH(h, ET_PROF_GEMM_FFN1, tc32 ? 2 : 1, s, gemm(att, lw.w1, lw.w1_t, lw.w1_lo, lw.b1, ffn, f, hid, kEpiBiasGelu));
-  ET_LAUNCH(h, ET_PROF_GEMM_FFN2, tc32 ? 2 : 1, s, gemm(ffn, lw.w2, lw.w2_t, lw.w2_lo, nullptr, x_out, hid, f, kEpiNone));
-  ET_LAUNCH(h, ET_PROF_LAYERNORM, 1, s, launch_add_bias_input_layernorm<T>(x_out, att, B(lw.b2), B(lw.ln2_gamma), B(lw.ln2_beta),
-                                                t_ptr, max_m, hid, h->eps, s, turn()));
+  // fp16 tensor-core path: the second FFN projection adds its bias and the residual in its
+  // epilogue (its K = F main loop leaves the epilogue warps idle time), so the LayerNorm
+  // behind it reads one tensor instead of two.  The attention output projection (K = H) has
+  // no such slack: measured, the same fusion there cost the GEMM what the LayerNorm saved.
+  const bool fuse_res = tc && h->fuse_residual;
+  if (fuse_res) {
+    ET_LAUNCH(h, ET_PROF_GEMM_FFN2, 1, s,
+              launch_gemm_tcgen05(reinterpret_cast<const __half*>(ffn), static_cast<const __half*>(lw.w2_t),
+                                  static_cast<const __half*>(lw.b2), reinterpret_cast<__half*>(x_out), t_ptr, max_m,
+                                  hid, f, kEpiBiasResidual, ws.status, s, turn(),
+                                  reinterpret_cast<const __half*>(att)));
+    ET_LAUNCH(h, ET_PROF_LAYERNORM, 1, s,
+              launch_add_bias_input_layernorm<T>(x_out, nullptr, nullptr, B(lw.ln2_gamma), B(lw.ln2_beta), t_ptr,
+                                                 max_m, hid, h->eps, s, turn()));
+  } else {
+    ET_LAUNCH(h, ET_PROF_GEMM_FFN2, tc32 ? 2 : 1, s, gemm(ffn, lw.w2, lw.w2_t, lw.w2_lo, nullptr, x_out, hid, f, kEpiNone));
+    ET_LAUNCH(h, ET_PROF_LAYERNORM, 1, s, launch_add_bias_input_layernorm<T>(x_out, att, B(lw.b2), B(lw.ln2_gamma), B(lw.ln2_beta),
+                                                  t_ptr, max_m, hid, h->eps, s, turn()));
+  }
   return ET_OK;
 }
 
@@ -779,6 +796,7 @@ int et_create(const et_config_t* config, et_handle_t* out_handle) {
         cudaEventCreateWithFlags(&h->comp_done[i], cudaEventDisableTiming) != cudaSuccess)
       return bail(cuda_fail(h, cudaGetLastError(), "cudaEventCreate"));
   if (const char* e = getenv("ETB_SNAKE")) h->snake = !(e[0] == '0');
+  if (const char* e = getenv("ETB_FUSE_RESIDUAL")) h->fuse_residual = !(e[0] == '0');
   if (const char* e = getenv("ETB_HOST_GRAPH")) h->host_graph_enabled = !(e[0] == '0');
   if (const char* e = getenv("ETB_HOST_CHUNKS")) {
     const int n = atoi(e);

@@ -93,7 +93,7 @@ __device__ __forceinline__ Vec16 ld_shared_v4(uint32_t addr) {
 template <int EPI, typename Release>
 __device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, __half* ctile, int N, int rows_valid,
                                                    uint32_t bias_s, uint32_t buf, int lane, int chunks,
-                                                   Release release) {
+                                                   const __half* rtile, Release release) {
 #pragma unroll 1
   for (int c = 0; c < chunks; ++c) {
     uint32_t r[64];
@@ -130,11 +130,35 @@ __device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, __half* ctile
       st_shared_v4(buf + lane * 128 + ((p ^ (lane & 7)) << 4), o);
     }
     __syncwarp();
+    if (EPI == kEpiBiasResidual) {
+      // the residual is added here, where a warp instruction covers four whole 128-byte row
+      // segments (one row per thread, as in the TMEM phase, would scatter 32 lines per load)
+      Vec16 res[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int rr = 4 * i + (lane >> 3), piece = lane & 7;
-      const Vec16 v = ld_shared_v4(buf + rr * 128 + ((piece ^ (rr & 7)) << 4));
-      if (rr < rows_valid) st_global_v4(ctile + static_cast<size_t>(rr) * N + c * 64 + piece * 8, v);
+      for (int i = 0; i < 8; ++i) {
+        const int rr = 4 * i + (lane >> 3), piece = lane & 7;
+        if (rr < rows_valid) res[i] = ld_global_nc_v4(rtile + static_cast<size_t>(rr) * N + c * 64 + piece * 8);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int rr = 4 * i + (lane >> 3), piece = lane & 7;
+        const Vec16 v = ld_shared_v4(buf + rr * 128 + ((piece ^ (rr & 7)) << 4));
+        if (rr < rows_valid) {
+          float fv[8], fr[8];
+          VecTraits<__half>::unpack(v, fv);
+          VecTraits<__half>::unpack(res[i], fr);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) fv[e] += fr[e];
+          st_global_v4(ctile + static_cast<size_t>(rr) * N + c * 64 + piece * 8, VecTraits<__half>::pack(fv));
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int rr = 4 * i + (lane >> 3), piece = lane & 7;
+        const Vec16 v = ld_shared_v4(buf + rr * 128 + ((piece ^ (rr & 7)) << 4));
+        if (rr < rows_valid) st_global_v4(ctile + static_cast<size_t>(rr) * N + c * 64 + piece * 8, v);
+      }
     }
     __syncwarp();  // the staging buffer is rewritten by the next chunk / tile
   }
@@ -154,8 +178,8 @@ template <int BN, int EPI>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b, __half* __restrict__ C,
-                    const __half* __restrict__ bias, const int* __restrict__ m_ptr, int max_m, int N,
-                    int K, int* status_word, int reverse_m) {
+                    const __half* __restrict__ bias, const __half* __restrict__ residual,
+                    const int* __restrict__ m_ptr, int max_m, int N, int K, int* status_word, int reverse_m) {
   using cfg = Cfg<BN>;
   constexpr int S = cfg::kStages;
 
@@ -334,7 +358,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t t_row =
           tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN + half * kCols;
       __half* ctile = C + static_cast<size_t>(row0) * N + col0;
-      epilogue_warp_tile<EPI>(t_row, ctile, N, M - row0, bias_s, buf, lane, kCols / 64,
+      const __half* rtile = EPI == kEpiBiasResidual ? residual + static_cast<size_t>(row0) * N + col0 : nullptr;
+      epilogue_warp_tile<EPI>(t_row, ctile, N, M - row0, bias_s, buf, lane, kCols / 64, rtile,
                               [&] { mbar_arrive(tmem_empty_bar(acc)); });
     }
   }
@@ -407,8 +432,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                          const __grid_constant__ CUtensorMap tmap_b,
                          const __grid_constant__ CUtensorMap tmap_b_half, __half* __restrict__ C,
-                         const __half* __restrict__ bias, const int* __restrict__ m_ptr, int max_m,
-                         int N, int K, int* status_word, int reverse_m) {
+                         const __half* __restrict__ bias, const __half* __restrict__ residual,
+                         const int* __restrict__ m_ptr, int max_m, int N, int K, int* status_word,
+                         int reverse_m) {
   using cfg = PairCfg;
   constexpr int S = cfg::kStages;
   constexpr int BN = cfg::BN;
@@ -605,7 +631,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
           tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN + half * wcols;
       __half* ctile = C + static_cast<size_t>(row0) * N + col0;
       const uint32_t empty0 = mapa_shared(tmem_empty_bar(acc), 0);
-      epilogue_warp_tile<EPI>(t_row, ctile, N, M - row0, bias_s, buf, lane, wcols / 64, [&] {
+      const __half* rtile = EPI == kEpiBiasResidual ? residual + static_cast<size_t>(row0) * N + col0 : nullptr;
+      epilogue_warp_tile<EPI>(t_row, ctile, N, M - row0, bias_s, buf, lane, wcols / 64, rtile, [&] {
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(empty0);
       });
@@ -624,7 +651,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
 template <int EPI>
 cudaError_t launch_pair_epi(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tbh,
-                            const __half* bias, __half* c,
+                            const __half* bias, const __half* residual, __half* c,
                             const int* m_ptr, int max_m, int n, int k, int* status_word, int reverse_m,
                             cudaStream_t stream) {
   using cfg = PairCfg;
@@ -640,29 +667,32 @@ cudaError_t launch_pair_epi(const CUtensorMap& ta, const CUtensorMap& tb, const 
   if (pairs > max_tiles) pairs = max_tiles;
   if (pairs < 1) pairs = 1;
   return launch_pdl(gemm_tcgen05_pair_kernel<EPI>, dim3(static_cast<int>(2 * pairs)), dim3(kNumThreads),
-                    cfg::kSmemBytes, stream, ta, tb, tbh, c, bias, m_ptr, max_m, n, k, status_word, reverse_m);
+                    cfg::kSmemBytes, stream, ta, tb, tbh, c, bias, residual, m_ptr, max_m, n, k, status_word, reverse_m);
 }
 
 cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tbh,
-                        const __half* bias, __half* c,
+                        const __half* bias, const __half* residual, __half* c,
                         const int* m_ptr, int max_m, int n, int k, int epilogue, int* status_word,
                         int reverse_m, cudaStream_t stream) {
   switch (epilogue) {
     case kEpiNone:
-      return launch_pair_epi<kEpiNone>(ta, tb, tbh, bias, c, m_ptr, max_m, n, k, status_word, reverse_m, stream);
+      return launch_pair_epi<kEpiNone>(ta, tb, tbh, bias, residual, c, m_ptr, max_m, n, k, status_word, reverse_m, stream);
     case kEpiBias:
-      return launch_pair_epi<kEpiBias>(ta, tb, tbh, bias, c, m_ptr, max_m, n, k, status_word, reverse_m, stream);
+      return launch_pair_epi<kEpiBias>(ta, tb, tbh, bias, residual, c, m_ptr, max_m, n, k, status_word, reverse_m, stream);
     case kEpiBiasGelu:
-      return launch_pair_epi<kEpiBiasGelu>(ta, tb, tbh, bias, c, m_ptr, max_m, n, k, status_word, reverse_m, stream);
+      return launch_pair_epi<kEpiBiasGelu>(ta, tb, tbh, bias, residual, c, m_ptr, max_m, n, k, status_word, reverse_m, stream);
     case kEpiBiasTanh:
-      return launch_pair_epi<kEpiBiasTanh>(ta, tb, tbh, bias, c, m_ptr, max_m, n, k, status_word, reverse_m, stream);
+      return launch_pair_epi<kEpiBiasTanh>(ta, tb, tbh, bias, residual, c, m_ptr, max_m, n, k, status_word, reverse_m, stream);
+    case kEpiBiasResidual:
+      return launch_pair_epi<kEpiBiasResidual>(ta, tb, tbh, bias, residual, c, m_ptr, max_m, n, k, status_word,
+                                               reverse_m, stream);
     default:
       return cudaErrorInvalidValue;
   }
 }
 
 template <int BN, int EPI>
-cudaError_t launch_bn_epi(const CUtensorMap& ta, const CUtensorMap& tb, const __half* bias, __half* c,
+cudaError_t launch_bn_epi(const CUtensorMap& ta, const CUtensorMap& tb, const __half* bias, const __half* residual, __half* c,
                           const int* m_ptr, int max_m, int n, int k, int* status_word, int reverse_m,
                           cudaStream_t stream) {
   using cfg = Cfg<BN>;
@@ -678,22 +708,25 @@ cudaError_t launch_bn_epi(const CUtensorMap& ta, const CUtensorMap& tb, const __
   if (grid > max_tiles) grid = max_tiles;
   if (grid < 1) grid = 1;
   return launch_pdl(gemm_tcgen05_kernel<BN, EPI>, dim3(static_cast<int>(grid)), dim3(kNumThreads),
-                    cfg::kSmemBytes, stream, ta, tb, c, bias, m_ptr, max_m, n, k, status_word, reverse_m);
+                    cfg::kSmemBytes, stream, ta, tb, c, bias, residual, m_ptr, max_m, n, k, status_word, reverse_m);
 }
 
 template <int BN>
-cudaError_t launch_bn(const CUtensorMap& ta, const CUtensorMap& tb, const __half* bias, __half* c,
+cudaError_t launch_bn(const CUtensorMap& ta, const CUtensorMap& tb, const __half* bias, const __half* residual, __half* c,
                       const int* m_ptr, int max_m, int n, int k, int epilogue, int* status_word,
                       int reverse_m, cudaStream_t stream) {
   switch (epilogue) {
     case kEpiNone:
-      return launch_bn_epi<BN, kEpiNone>(ta, tb, bias, c, m_ptr, max_m, n, k, status_word, reverse_m, stream);
+      return launch_bn_epi<BN, kEpiNone>(ta, tb, bias, residual, c, m_ptr, max_m, n, k, status_word, reverse_m, stream);
     case kEpiBias:
-      return launch_bn_epi<BN, kEpiBias>(ta, tb, bias, c, m_ptr, max_m, n, k, status_word, reverse_m, stream);
+      return launch_bn_epi<BN, kEpiBias>(ta, tb, bias, residual, c, m_ptr, max_m, n, k, status_word, reverse_m, stream);
     case kEpiBiasGelu:
-      return launch_bn_epi<BN, kEpiBiasGelu>(ta, tb, bias, c, m_ptr, max_m, n, k, status_word, reverse_m, stream);
+      return launch_bn_epi<BN, kEpiBiasGelu>(ta, tb, bias, residual, c, m_ptr, max_m, n, k, status_word, reverse_m, stream);
     case kEpiBiasTanh:
-      return launch_bn_epi<BN, kEpiBiasTanh>(ta, tb, bias, c, m_ptr, max_m, n, k, status_word, reverse_m, stream);
+      return launch_bn_epi<BN, kEpiBiasTanh>(ta, tb, bias, residual, c, m_ptr, max_m, n, k, status_word, reverse_m, stream);
+    case kEpiBiasResidual:
+      return launch_bn_epi<BN, kEpiBiasResidual>(ta, tb, bias, residual, c, m_ptr, max_m, n, k, status_word,
+                                                 reverse_m, stream);
     default:
       return cudaErrorInvalidValue;
   }
@@ -731,13 +764,15 @@ bool encode_2d_fp16_sw128(CUtensorMap* map, const void* base, uint64_t rows, uin
 
 cudaError_t launch_gemm_tcgen05(const __half* a, const __half* w_packed, const __half* bias,
                                 __half* c, const int* m_ptr, int max_m, int n, int k, int epilogue,
-                                int* status_word, cudaStream_t stream, bool reverse_m) {
+                                int* status_word, cudaStream_t stream, bool reverse_m, const __half* residual) {
   if (max_m <= 0) return cudaSuccess;
   if (n <= 0 || k <= 0 || (n % 128) != 0 || (k % 8) != 0) return cudaErrorInvalidValue;
   if ((reinterpret_cast<uintptr_t>(a) & 15u) || (reinterpret_cast<uintptr_t>(w_packed) & 15u) ||
       (reinterpret_cast<uintptr_t>(c) & 15u) || (bias && (reinterpret_cast<uintptr_t>(bias) & 15u)))
     return cudaErrorMisalignedAddress;
   if (epilogue != kEpiNone && bias == nullptr) return cudaErrorInvalidValue;
+  if (epilogue == kEpiBiasResidual && (residual == nullptr || (reinterpret_cast<uintptr_t>(residual) & 15u)))
+    return cudaErrorInvalidValue;
   const int bn = (n % 256 == 0) ? 256 : 128;
   static const bool single_cta = [] {
     const char* e = getenv("ETB_GEMM_SINGLE_CTA");   // debugging: force the one-CTA kernel
@@ -757,11 +792,11 @@ cudaError_t launch_gemm_tcgen05(const __half* a, const __half* w_packed, const _
     if (!encode_2d_fp16_sw128(&tbh, w_packed, static_cast<uint64_t>(n), static_cast<uint64_t>(k),
                               static_cast<uint64_t>(k), 64, BK))
       return cudaErrorInvalidValue;
-    return launch_pair(ta, tb, tbh, bias, c, m_ptr, max_m, n, k, epilogue, status_word, rev, stream);
+    return launch_pair(ta, tb, tbh, bias, residual, c, m_ptr, max_m, n, k, epilogue, status_word, rev, stream);
   }
   if (bn == 256)
-    return launch_bn<256>(ta, tb, bias, c, m_ptr, max_m, n, k, epilogue, status_word, rev, stream);
-  return launch_bn<128>(ta, tb, bias, c, m_ptr, max_m, n, k, epilogue, status_word, rev, stream);
+    return launch_bn<256>(ta, tb, bias, residual, c, m_ptr, max_m, n, k, epilogue, status_word, rev, stream);
+  return launch_bn<128>(ta, tb, bias, residual, c, m_ptr, max_m, n, k, epilogue, status_word, rev, stream);
 }
 
 }  // namespace etb
