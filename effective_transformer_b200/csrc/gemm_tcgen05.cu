@@ -12,9 +12,11 @@
 //   warp 1   MMA issuer: tcgen05.mma cta_group::1 kind::f16, M=128, N=BN, K=16,
 //            accumulating into one of two TMEM buffers of BN columns
 //   warps 2-9 epilogue: tcgen05.ld of the finished accumulator (one TMEM lane
-//            quadrant and one half of the columns per warp), bias / GELU in
-//            fp32, staged through shared memory to coalesced stores of C,
-//            overlapping the next tile's main loop
+//            quadrant and one half of the columns per warp), bias in fp32,
+//            optional GELU / tanh / residual add, staged through shared memory
+//            to coalesced stores of C, overlapping the next tile's main loop
+// The kernel every BERT projection uses is the CTA-pair variant further down
+// (N a multiple of 256); this one covers N = 128 (mod 256).
 // M is read from device memory, so no host synchronisation is needed between
 // the padding-offset kernel and the projections.  Every mbarrier wait is
 // bounded; on expiry the kernel records a code in the status word, all roles
