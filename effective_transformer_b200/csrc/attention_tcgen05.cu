@@ -224,23 +224,53 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
   uint32_t mma_phase = 0;
   bool ok = true;
   // Thread 0: the Q, K, V rows of one item -> buffer `b`, completion on its barrier.
-  auto issue = [&](int item_idx, int b) {
-    const int li = reverse ? total - 1 - item_idx : item_idx;  // last tiles first: freshest in L2
-    const int tile_i = li / heads, head_i = li - tile_i * heads;
-    int rows = tile_rows[tile_i];
-    rows = rows < 1 ? 1 : (rows > kTileRows ? kTileRows : rows);
+  auto issue = [&](int head_i, int first_row, int rows, int b) {
     const int boxes = (rows + kBoxRows - 1) / kBoxRows;
     const uint32_t bar = bar_load0 + 8u * b;
     const uint32_t dst = base + b * kBufBytes;
     mbar_arrive_expect_tx(bar, static_cast<uint32_t>(3 * boxes * kBoxBytes));
-    const int x = head_i * co.x_per_head, y = head_i * co.y_per_head + tile_start[tile_i];
+    const int x = head_i * co.x_per_head, y = head_i * co.y_per_head + first_row;
     for (int j = 0; j < boxes; ++j) {
       tma_load_2d(dst + j * kBoxBytes, &tmap_q, x, y + j * kBoxRows, bar);
       tma_load_2d(dst + kTileBytes + j * kBoxBytes, &tmap_k, x, y + j * kBoxRows, bar);
       tma_load_2d(dst + 2 * kTileBytes + j * kBoxBytes, &tmap_v, x, y + j * kBoxRows, bar);
     }
   };
-  if (threadIdx.x == 0) issue(blockIdx.x, 0);
+  // An item's plan entries (tile bounds, then this row's sequence bounds) are two dependent
+  // global loads.  They are fetched one item ahead in two steps, each issued where nothing needs
+  // its result yet: the tile bounds under the wait for S = Q K^T, the sequence bounds under the
+  // wait for O = P V.
+  struct ItemMeta {
+    int head, t0, n, lo, hi;
+  };
+  auto meta_tile = [&](int item_idx, ItemMeta& m) {   // step 1: issues two loads
+    m = ItemMeta{0, 0, 1, 0, 0};
+    if (item_idx >= total) return;
+    const int li = reverse ? total - 1 - item_idx : item_idx;  // last tiles first: freshest in L2
+    const int tile_i = li / heads;
+    m.head = li - tile_i * heads;
+    m.t0 = tile_start[tile_i];
+    m.n = tile_rows[tile_i];
+  };
+  auto meta_row = [&](ItemMeta& m) {                  // step 2: needs step 1's results, issues two loads
+    m.n = m.n < 1 ? 1 : (m.n > kTileRows ? kTileRows : m.n);
+    if (r < m.n) {
+      m.lo = seq_lo[m.t0 + r];
+      m.hi = seq_hi[m.t0 + r];
+    } else {
+      m.lo = m.hi = m.t0;
+    }
+  };
+  auto meta_finish = [&](ItemMeta& m) {               // this row's sequence, relative to the tile
+    int lo = m.lo - m.t0, hi = m.hi - m.t0;
+    m.lo = lo < 0 ? 0 : lo;
+    m.hi = hi > m.n ? m.n : hi;
+  };
+  ItemMeta cur;
+  meta_tile(blockIdx.x, cur);
+  meta_row(cur);
+  meta_finish(cur);
+  if (threadIdx.x == 0) issue(cur.head, cur.t0, cur.n, 0);
   int it_n = 0;
   auto wait_all = [&](uint32_t bar, uint32_t phase, int site) {
     bool got = mbar_wait(bar, phase, abort_flag);
@@ -252,25 +282,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
   };
 
   for (int item = blockIdx.x; item < total && ok; item += gridDim.x, ++it_n) {
-    const int litem = reverse ? total - 1 - item : item;
-    const int tile = litem / heads, head = litem - tile * heads;
-    const int t0 = tile_start[tile];
-    int n = tile_rows[tile];
-    n = n < 1 ? 1 : (n > kTileRows ? kTileRows : n);
+    const int head = cur.head, t0 = cur.t0, n = cur.n;
     const int n16 = (n + 15) & ~15;
     const uint32_t sq = base, sk = sq + kTileBytes, sv = sk + kTileBytes;
     const uint32_t sp = sq;  // P overwrites Q and K after the scores are computed
     const uint32_t bar_load = bar_load0;
     const uint32_t load_phase = static_cast<uint32_t>(it_n & 1);
 
-    // this row's sequence, relative to the tile
-    int lo = 0, hi = 0;
-    if (r < n) {
-      lo = seq_lo[t0 + r] - t0;
-      hi = seq_hi[t0 + r] - t0;
-      lo = lo < 0 ? 0 : lo;
-      hi = hi > n ? n : hi;
-    }
+    const int lo = cur.lo, hi = cur.hi;
     ok = wait_all(bar_load, load_phase, kSiteLoad);
     if (!ok) break;
 
@@ -291,6 +310,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
       for (int k = 0; k < kD / 16; ++k) umma_f16_ss(tmem_base, qd + 2u * k, kd + 2u * k, idesc, k != 0 ? 1u : 0u);
       umma_commit(bar_mma);
     }
+    ItemMeta nxt;
+    meta_tile(item + static_cast<int>(gridDim.x), nxt);
     ok = wait_all(bar_mma, mma_phase, kSiteScores);
     mma_phase ^= 1u;
     if (!ok) break;
@@ -311,16 +332,17 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
       uhi = (uhi + 15) & ~15;
       // (32 columns per TMEM load; a load may run up to 16 columns past n16, into
       // allocated columns whose values the range test discards)
+      // column c belongs to this row's sequence iff lo <= c < hi, i.e. (unsigned)(c - lo) < hi - lo
+      const unsigned span = static_cast<unsigned>(hi - lo);
       float m = -INFINITY;
       for (int c0 = ulo; c0 < uhi; c0 += 32) {
         uint32_t s32[32];
         tmem_ld_32x32b_x32(t_lane + c0, s32);
         tmem_ld_wait();
+        const int rel = c0 - lo;
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int c = c0 + e;
-          if (c >= lo && c < hi) m = fmaxf(m, __uint_as_float(s32[e]));
-        }
+        for (int e = 0; e < 32; ++e)
+          if (static_cast<unsigned>(rel + e) < span) m = fmaxf(m, __uint_as_float(s32[e]));
       }
       const float ms = (r < n && hi > lo) ? -m * scale_log2e : 0.f;
       float l = 0.f;
@@ -334,14 +356,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
           uint32_t s32[32];
           tmem_ld_32x32b_x32(t_lane + c0, s32);
           tmem_ld_wait();
+          const int rel = c0 - lo;
 #pragma unroll
           for (int e = 0; e < 16; ++e) {
             float p2[2];
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
-              const int c = c0 + 2 * e + u;
               const float pe = ex2_approx(fmaf(__uint_as_float(s32[2 * e + u]), scale_log2e, ms));
-              p2[u] = (c >= lo && c < hi) ? pe : 0.f;
+              p2[u] = static_cast<unsigned>(rel + 2 * e + u) < span ? pe : 0.f;
               l += p2[u];
             }
             pk[e] = pack_half2(p2[0], p2[1]);
@@ -371,6 +393,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
       }
       umma_commit(bar_mma);
     }
+    meta_row(nxt);
     ok = wait_all(bar_mma, mma_phase, kSiteContext);
     mma_phase ^= 1u;
     if (!ok) break;
@@ -378,7 +401,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     // Q, K, V and P are dead: the next item's rows stream in under the epilogue
     if (threadIdx.x == 0 && item + static_cast<int>(gridDim.x) < total) {
       fence_proxy_async_smem();
-      issue(item + gridDim.x, 0);
+      issue(nxt.head, nxt.t0, nxt.n, 0);
     }
 
     // ---- epilogue: O / l -> fp16 -> packed context ----
@@ -405,6 +428,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     tc_fence_before();
     __syncthreads();  // TMEM and the tiles are reused by the next item
     if (threadIdx.x == 0) fence_proxy_async_smem();
+    meta_finish(nxt);
+    cur = nxt;
   }
 
   tc_fence_before();
