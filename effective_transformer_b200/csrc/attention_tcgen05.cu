@@ -34,12 +34,18 @@ constexpr int kBoxRows = 32;
 constexpr int kBoxBytes = kBoxRows * kD * 2;        // 4096
 constexpr int kTileBytes = kTileRows * kD * 2;      // 16384: 128 rows of 128 bytes
 constexpr int kThreads = 128;
-constexpr int kTmemCols = 128;   // S: columns [0,128); O takes columns [0,64) once the softmax has read S
-constexpr int kOCol = 0;
+// TMEM columns of a CTA: S in [0,128); the softmax overwrites it in place with P (fp16 pairs,
+// columns [0,64): the pair of keys 2j, 2j+1 lands in column j, which it has already read), and
+// O goes to [64,128) once every row has consumed its scores.
+constexpr int kTmemCols = 128;
+constexpr int kPCol = 0;
+constexpr int kOCol = 64;
 constexpr int kCtasPerSm = 4;    // 4 x 128 TMEM columns, 4 x 48 KB shared memory
-// One {Q, K, V} buffer + barriers.  P (two 64-key atoms) takes the place of
-// the item's Q and K tiles, which are dead once the scores are in TMEM.  Four
-// CTAs per SM keep the phases of four items in flight.
+// One {Q, K, V} buffer + barriers.  P never touches shared memory (it is the TMEM A operand
+// of the second MMA), so the Q and K tiles are free as soon as S = Q K^T has completed and the
+// V tile as soon as O = P V has: the next item's Q/K rows are loaded under this item's softmax
+// and second MMA, its V rows under the epilogue and the next item's first MMA and softmax.
+// Four CTAs per SM keep the phases of four items in flight.
 constexpr int kBufBytes = 3 * kTileBytes;
 constexpr int kSmemBytes = kBufBytes + 64;
 
@@ -53,6 +59,27 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t* r) 
         "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
         "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
+      : "memory");
+}
+// 32 lanes x 16 columns of 32-bit: thread i of the warp writes TMEM lane (lane field) + i.
+__device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (128 rows = lanes, two fp16 per 32-bit column)
+// is read from tensor memory.
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 __device__ __forceinline__ float ex2_approx(float x) {
@@ -223,18 +250,24 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
 
   uint32_t mma_phase = 0;
   bool ok = true;
-  // Thread 0: the Q, K, V rows of one item -> buffer `b`, completion on its barrier.
-  auto issue = [&](int head_i, int first_row, int rows, int b) {
-    const int boxes = (rows + kBoxRows - 1) / kBoxRows;
-    const uint32_t bar = bar_load0 + 8u * b;
-    const uint32_t dst = base + b * kBufBytes;
-    mbar_arrive_expect_tx(bar, static_cast<uint32_t>(3 * boxes * kBoxBytes));
+  // Thread 0: Q and K rows of an item (barrier bar_qk) / its V rows (barrier bar_v).
+  const uint32_t bar_qk = bar_load0, bar_v = bar_load0 + 8u;
+  auto clamp_rows = [](int rows) { return rows < 1 ? 1 : (rows > kTileRows ? kTileRows : rows); };
+  auto issue_qk = [&](int head_i, int first_row, int rows) {
+    const int boxes = (clamp_rows(rows) + kBoxRows - 1) / kBoxRows;
+    mbar_arrive_expect_tx(bar_qk, static_cast<uint32_t>(2 * boxes * kBoxBytes));
     const int x = head_i * co.x_per_head, y = head_i * co.y_per_head + first_row;
     for (int j = 0; j < boxes; ++j) {
-      tma_load_2d(dst + j * kBoxBytes, &tmap_q, x, y + j * kBoxRows, bar);
-      tma_load_2d(dst + kTileBytes + j * kBoxBytes, &tmap_k, x, y + j * kBoxRows, bar);
-      tma_load_2d(dst + 2 * kTileBytes + j * kBoxBytes, &tmap_v, x, y + j * kBoxRows, bar);
+      tma_load_2d(base + j * kBoxBytes, &tmap_q, x, y + j * kBoxRows, bar_qk);
+      tma_load_2d(base + kTileBytes + j * kBoxBytes, &tmap_k, x, y + j * kBoxRows, bar_qk);
     }
+  };
+  auto issue_v = [&](int head_i, int first_row, int rows) {
+    const int boxes = (clamp_rows(rows) + kBoxRows - 1) / kBoxRows;
+    mbar_arrive_expect_tx(bar_v, static_cast<uint32_t>(boxes * kBoxBytes));
+    const int x = head_i * co.x_per_head, y = head_i * co.y_per_head + first_row;
+    for (int j = 0; j < boxes; ++j)
+      tma_load_2d(base + 2 * kTileBytes + j * kBoxBytes, &tmap_v, x, y + j * kBoxRows, bar_v);
   };
   // An item's plan entries (tile bounds, then this row's sequence bounds) are two dependent
   // global loads.  They are fetched one item ahead in two steps, each issued where nothing needs
@@ -270,7 +303,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
   meta_tile(blockIdx.x, cur);
   meta_row(cur);
   meta_finish(cur);
-  if (threadIdx.x == 0) issue(cur.head, cur.t0, cur.n, 0);
+  if (threadIdx.x == 0) {
+    issue_qk(cur.head, cur.t0, cur.n);
+    issue_v(cur.head, cur.t0, cur.n);
+  }
   int it_n = 0;
   auto wait_all = [&](uint32_t bar, uint32_t phase, int site) {
     bool got = mbar_wait(bar, phase, abort_flag);
@@ -285,21 +321,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     const int head = cur.head, t0 = cur.t0, n = cur.n;
     const int n16 = (n + 15) & ~15;
     const uint32_t sq = base, sk = sq + kTileBytes, sv = sk + kTileBytes;
-    const uint32_t sp = sq;  // P overwrites Q and K after the scores are computed
-    const uint32_t bar_load = bar_load0;
     const uint32_t load_phase = static_cast<uint32_t>(it_n & 1);
+    const bool has_next = item + static_cast<int>(gridDim.x) < total;
 
     const int lo = cur.lo, hi = cur.hi;
-    ok = wait_all(bar_load, load_phase, kSiteLoad);
+    ok = wait_all(bar_qk, load_phase, kSiteLoad);
     if (!ok) break;
-
-    // V rows [n, n16) may belong to the next tile or be stale: P is zero there,
-    // so make V finite there too.
-    for (int idx = threadIdx.x; idx < (n16 - n) * 8; idx += kThreads)
-      st_shared_v4(sv + (n + (idx >> 3)) * 128 + ((idx & 7) << 4), 0u, 0u, 0u, 0u);
-    fence_proxy_async_smem();
     tc_fence_before();
-    __syncthreads();
 
     // ---- S = Q K^T ----
     if (threadIdx.x == 0) {
@@ -316,8 +344,21 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     mma_phase ^= 1u;
     if (!ok) break;
     tc_fence_after();
+    // Q and K are dead: the next item's Q/K rows stream in under the softmax and the second MMA
+    if (threadIdx.x == 0 && has_next) issue_qk(nxt.head, nxt.t0, nxt.n);
 
-    // ---- softmax over the row's own sequence; P -> shared memory ----
+    // this item's V rows were requested an item ago.  Rows [n, n16) may belong to the next
+    // tile or be stale: P is zero there, so make V finite there too.
+    bool got_v = mbar_wait(bar_v, load_phase, abort_flag);
+    if (!got_v) {
+      *abort_flag = 1;
+      report_timeout(status_word, kKernelAttnTc, kSiteLoad);
+    }
+    for (int idx = threadIdx.x; idx < (n16 - n) * 8; idx += kThreads)
+      st_shared_v4(sv + (n + (idx >> 3)) * 128 + ((idx & 7) << 4), 0u, 0u, 0u, 0u);
+    fence_proxy_async_smem();
+
+    // ---- softmax over the row's own sequence; P -> tensor memory, over the scores it replaces ----
     const bool warp_has_rows = warp * 32 < n;
     float inv_l = 1.0f;
     if (warp_has_rows) {
@@ -346,8 +387,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
       }
       const float ms = (r < n && hi > lo) ? -m * scale_log2e : 0.f;
       float l = 0.f;
-      const uint32_t prow = sp + r * 128;
-      const uint32_t swz = static_cast<uint32_t>(r & 7);
       for (int c0 = 0; c0 < n16; c0 += 32) {
         uint32_t pk[16];
 #pragma unroll
@@ -369,27 +408,25 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
             pk[e] = pack_half2(p2[0], p2[1]);
           }
         }
-        // 32 keys = four 16-byte chunks of this row inside the 64-key atom
-        const uint32_t atom = prow + static_cast<uint32_t>(c0 >> 6) * kTileBytes;
-        const uint32_t ch = static_cast<uint32_t>((c0 & 63) >> 3);
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          st_shared_v4(atom + (((ch + j) ^ swz) << 4), pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+        // 32 keys = 16 packed columns; they overwrite score columns [c0/2, c0/2 + 16), all of
+        // which this thread has read (c0/2 + 16 <= c0 + 32 and chunks are visited in order)
+        tmem_st_32x32b_x16(t_lane + kPCol + (c0 >> 1), pk);
       }
+      tmem_st_wait();
       inv_l = (l > 0.f) ? 1.0f / l : 0.f;
     }
-    fence_proxy_async_smem();
     tc_fence_before();
-    __syncthreads();
+    ok = __syncthreads_and(got_v) != 0;
+    if (!ok) break;
 
     // ---- O = P V ----
     if (threadIdx.x == 0) {
       tc_fence_after();
       const uint32_t idesc = idesc_f16(kTileRows, kD, true);
       for (int ks = 0; ks < n16 / 16; ++ks) {
-        const uint64_t pd = make_kmajor_sw128_desc(sp + (ks >> 2) * kTileBytes + (ks & 3) * 32);
         const uint64_t vd = make_kmajor_sw128_desc(sv + ks * 2048);  // MN-major: 16 keys = two 8-row groups
-        umma_f16_ss(tmem_base + kOCol, pd, vd, idesc, ks != 0 ? 1u : 0u);
+        // A = P from tensor memory: 16 keys = 8 packed columns per instruction
+        umma_f16_ts(tmem_base + kOCol, tmem_base + kPCol + ks * 8, vd, idesc, ks != 0 ? 1u : 0u);
       }
       umma_commit(bar_mma);
     }
@@ -398,10 +435,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     mma_phase ^= 1u;
     if (!ok) break;
     tc_fence_after();
-    // Q, K, V and P are dead: the next item's rows stream in under the epilogue
-    if (threadIdx.x == 0 && item + static_cast<int>(gridDim.x) < total) {
-      fence_proxy_async_smem();
-      issue(nxt.head, nxt.t0, nxt.n, 0);
+    // V is dead: the next item's V rows stream in under the epilogue and the next first MMA
+    if (threadIdx.x == 0 && has_next) {
+      fence_proxy_async_smem();  // orders the zero-fill stores above before the copy's writes
+      issue_v(nxt.head, nxt.t0, nxt.n);
     }
 
     // ---- epilogue: O / l -> fp16 -> packed context ----
