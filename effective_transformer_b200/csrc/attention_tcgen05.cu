@@ -347,17 +347,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     // Q and K are dead: the next item's Q/K rows stream in under the softmax and the second MMA
     if (threadIdx.x == 0 && has_next) issue_qk(nxt.head, nxt.t0, nxt.n);
 
-    // this item's V rows were requested an item ago.  Rows [n, n16) may belong to the next
-    // tile or be stale: P is zero there, so make V finite there too.
-    bool got_v = mbar_wait(bar_v, load_phase, abort_flag);
-    if (!got_v) {
-      *abort_flag = 1;
-      report_timeout(status_word, kKernelAttnTc, kSiteLoad);
-    }
-    for (int idx = threadIdx.x; idx < (n16 - n) * 8; idx += kThreads)
-      st_shared_v4(sv + (n + (idx >> 3)) * 128 + ((idx & 7) << 4), 0u, 0u, 0u, 0u);
-    fence_proxy_async_smem();
-
     // ---- softmax over the row's own sequence; P -> tensor memory, over the scores it replaces ----
     const bool warp_has_rows = warp * 32 < n;
     float inv_l = 1.0f;
@@ -415,6 +404,16 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
       tmem_st_wait();
       inv_l = (l > 0.f) ? 1.0f / l : 0.f;
     }
+    // this item's V rows were requested an item ago and have had the softmax to arrive.  Rows
+    // [n, n16) may belong to the next tile or be stale: P is zero there, so make V finite there too.
+    bool got_v = mbar_wait(bar_v, load_phase, abort_flag);
+    if (!got_v) {
+      *abort_flag = 1;
+      report_timeout(status_word, kKernelAttnTc, kSiteLoad);
+    }
+    for (int idx = threadIdx.x; idx < (n16 - n) * 8; idx += kThreads)
+      st_shared_v4(sv + (n + (idx >> 3)) * 128 + ((idx & 7) << 4), 0u, 0u, 0u, 0u);
+    fence_proxy_async_smem();
     tc_fence_before();
     ok = __syncthreads_and(got_v) != 0;
     if (!ok) break;
