@@ -202,17 +202,16 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
                          const __grid_constant__ CUtensorMap tmap_v, Coords co, __half* __restrict__ ctx,
                          const int* __restrict__ plan, int batch, int max_tokens, int heads,
                          float scale_log2e, int* status_word, int reverse) {
-  pdl_wait();     // the plan and the Q/K/V rows come from earlier kernels
+  // The prologue (barriers, TMEM) touches no global memory: it runs before the
+  // wait on the preceding kernel, under that kernel's tail.
   pdl_trigger();
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t base = smem_u32(smem_raw);
   if ((base & 1023u) != 0u) {
+    pdl_wait();  // no CTA leaves before the preceding kernel has completed
     if (threadIdx.x == 0) report_timeout(status_word, kKernelAttnTc, kSiteSmemAlign);
     return;
   }
-  const int num_tiles = plan[0];
-  const int total = num_tiles * heads;
-  if (static_cast<int>(blockIdx.x) >= total) return;
   const int* tile_start = plan + 4;
   const int* tile_rows = plan + 4 + batch;
   const int* seq_lo = plan + 4 + 2 * batch;
@@ -247,6 +246,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+
+  pdl_wait();  // the plan and the Q/K/V rows come from earlier kernels
+  const int num_tiles = plan[0];
+  const int total = num_tiles * heads;  // a CTA beyond it runs no item and frees its TMEM below
 
   uint32_t mma_phase = 0;
   bool ok = true;
@@ -303,7 +306,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
   meta_tile(blockIdx.x, cur);
   meta_row(cur);
   meta_finish(cur);
-  if (threadIdx.x == 0) {
+  if (threadIdx.x == 0 && static_cast<int>(blockIdx.x) < total) {
     issue_qk(cur.head, cur.t0, cur.n);
     issue_v(cur.head, cur.t0, cur.n);
   }

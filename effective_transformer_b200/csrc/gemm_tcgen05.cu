@@ -185,19 +185,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   using cfg = Cfg<BN>;
   constexpr int S = cfg::kStages;
 
-  pdl_wait();     // M and the A rows come from earlier kernels
+  // The prologue (barriers, TMEM) touches no global memory: it runs before the
+  // wait on the preceding kernel, under that kernel's tail.
   pdl_trigger();
-  int M = *m_ptr;
-  M = M < 0 ? 0 : (M > max_m ? max_m : M);
-  const int m_tiles = (M + BM - 1) / BM;
-  const int n_tiles = N / BN;
-  const int num_tiles = m_tiles * n_tiles;
-  const int num_kb = (K + BK - 1) / BK;
-  if (num_tiles == 0) return;  // uniform for the whole grid
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t tiles_addr = smem_u32(smem_raw);
   if ((tiles_addr & 1023u) != 0u) {  // the swizzled tiles need 1024-byte alignment
+    pdl_wait();  // no CTA leaves before the preceding kernel has completed
     if (threadIdx.x == 0) report_timeout(status_word, kKernelGemmTc, kSiteSmemAlign);
     return;
   }
@@ -238,6 +233,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+
+  pdl_wait();  // M and the A rows come from earlier kernels
+  int M = *m_ptr;
+  M = M < 0 ? 0 : (M > max_m ? max_m : M);
+  const int m_tiles = (M + BM - 1) / BM;
+  const int n_tiles = N / BN;
+  const int num_tiles = m_tiles * n_tiles;  // 0: every role's loop is empty
+  const int num_kb = (K + BK - 1) / BK;
 
   auto fail = [&](int site) {
     *abort_flag = 1;
@@ -442,27 +445,16 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   constexpr int BN = cfg::BN;
   constexpr int BM2 = 2 * BM;
 
-  pdl_wait();     // M and the A rows come from earlier kernels
+  // The prologue (barriers, TMEM, cluster sync) touches no global memory: it runs
+  // before the wait on the preceding kernel, under that kernel's tail.
   pdl_trigger();
-  int M = *m_ptr;
-  M = M < 0 ? 0 : (M > max_m ? max_m : M);
-  const int m_tiles = (M + BM2 - 1) / BM2;
-  const int n_tiles = N / BN;
-  const int num_tiles = m_tiles * n_tiles;
-  const int num_kb = (K + BK - 1) / BK;
-  if (num_tiles == 0) return;  // uniform for the whole grid
-
   const uint32_t rank = cluster_ctarank();  // 0 issues the MMAs
   const int pair_id = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-  // last round cut into half-width units when it occupies at most half of the pairs
-  const int rem = num_tiles % num_pairs;
-  const bool split = rem > 0 && 2 * rem <= num_pairs;
-  const int full_tiles = split ? num_tiles - rem : num_tiles;
-  const int num_units = full_tiles + (split ? 2 * rem : 0);
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t tiles_addr = smem_u32(smem_raw);
   if ((tiles_addr & 1023u) != 0u) {  // same layout in both CTAs: uniform for the pair
+    pdl_wait();  // no CTA leaves before the preceding kernel has completed
     if (threadIdx.x == 0) report_timeout(status_word, kKernelGemmTc, kSiteSmemAlign);
     return;
   }
@@ -504,6 +496,19 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   cluster_sync_all();  // the peer's barriers are initialised before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+
+  pdl_wait();  // M and the A rows come from earlier kernels
+  int M = *m_ptr;
+  M = M < 0 ? 0 : (M > max_m ? max_m : M);
+  const int m_tiles = (M + BM2 - 1) / BM2;
+  const int n_tiles = N / BN;
+  const int num_tiles = m_tiles * n_tiles;  // 0: every role's loop is empty
+  const int num_kb = (K + BK - 1) / BK;
+  // last round cut into half-width units when it occupies at most half of the pairs
+  const int rem = num_tiles % num_pairs;
+  const bool split = rem > 0 && 2 * rem <= num_pairs;
+  const int full_tiles = split ? num_tiles - rem : num_tiles;
+  const int num_units = full_tiles + (split ? 2 * rem : 0);
 
   auto fail = [&](int site) {
     *abort_flag = 1;

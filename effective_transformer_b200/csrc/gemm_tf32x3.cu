@@ -6,11 +6,10 @@
 // and the product is taken as  hi*hi + hi*lo + lo*hi  with fp32 accumulation in
 // TMEM: the dropped lo*lo term and the rounding of lo are of relative size
 // 2^-22, i.e. the result is as accurate as an fp32 FMA chain (the 1e-4 * RMS
-// gate of the fp32 path needs about 2^-17).  The three partial products are one
-// GEMM over a K axis three times as long:
-//   k-blocks [0, K/32)        A_hi * W_hi
-//   k-blocks [K/32, 2K/32)    A_hi * W_lo
-//   k-blocks [2K/32, 3K/32)   A_lo * W_hi
+// gate of the fp32 path needs about 2^-17).  A stage of the shared-memory ring
+// holds the four operand tiles of one 32-wide k-block (A_hi, A_lo, W_hi, W_lo)
+// and feeds the three products from them: four tiles fetched per three MMA
+// groups instead of six, because the kernel is bound by the L2 -> SM traffic.
 // W_hi / W_lo ([N,K], K-major) are made once when weights are registered; A_hi /
 // A_lo by split_tf32_kernel in front of each projection.  Replaces the fp32
 // cublasGemmEx call sites of the reference's layer functor
@@ -18,9 +17,9 @@
 // FP32 OperationType (common.h:26).
 //
 // Kernel structure as in gemm_tcgen05.cu (one persistent CTA per SM, 320
-// threads: TMA producer warp, MMA issuer warp, eight epilogue warps; 6-stage
-// shared-memory ring of [128 x 32] fp32 A tiles and [128 x 32] W tiles with the
-// 128-byte swizzle), every wait bounded.  The accumulation differs: see the
+// threads: TMA producer warp, MMA issuer warp, eight epilogue warps; 3-stage
+// shared-memory ring, a stage = four [128 x 32] fp32 tiles with the 128-byte
+// swizzle), every wait bounded.  The accumulation differs: see the
 // note on units in front of the kernel.
 #include "common.cuh"
 #include "ptx_sm100.cuh"
@@ -42,10 +41,10 @@ constexpr int kNumThreads = 64 + kEpilogueThreads;
 
 constexpr int BN = 128;    // four TMEM blocks of BN columns hold the units in flight
 struct Cfg {
-  static constexpr int kStages = 6;
+  static constexpr int kStages = 3;
   static constexpr int kABytes = BM * BK * 4;
   static constexpr int kBBytes = BN * BK * 4;
-  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;  // A_hi, A_lo, W_hi, W_lo
   static constexpr int kNumBars = 2 * kStages + 2 * 4 + 1;
   static constexpr int kSmemBytes = kStages * kStageBytes + 256 /*barriers*/;
   static constexpr int kTmemCols = 4 * BN;
@@ -110,15 +109,15 @@ split_tf32_kernel(const float* x, float* hi, float* lo,
   }
 }
 
-// One tile = 128 x BN of C.  Its 3K/32 k-blocks are cut into units of kUnitKb
-// k-blocks; a unit is accumulated from zero in one of four TMEM blocks of BN
-// columns (used round-robin), and the epilogue warps add finished units into
-// fp32 registers.  Reason: the tensor core adds into its fp32 accumulator with
-// truncation, so a single chain over all 3K/8 instructions drifts by about
-// 1e-4 relative at K = 3072; 32-instruction chains summed with round-to-nearest
-// stay at the level of an fp32 FMA loop.  Draining a unit overlaps the MMAs of
+// One tile = 128 x BN of C.  Its K/32 k-blocks are cut into units of kUnitKb
+// k-blocks (three products each); a unit is accumulated from zero in one of four
+// TMEM blocks of BN columns (used round-robin), and the epilogue warps add
+// finished units into fp32 registers.  Reason: the tensor core adds into its fp32
+// accumulator with truncation, so a single chain over all 3K/8 instructions
+// drifts by about 1e-4 relative at K = 3072; 36-instruction chains summed with
+// round-to-nearest stay at the level of an fp32 FMA loop.  Draining a unit overlaps the MMAs of
 // the next ones, so the issuer never waits for the epilogue in steady state.
-constexpr int kUnitKb = 8;
+constexpr int kUnitKb = 3;
 constexpr int kTmemBlocks = 4;
 
 template <int EPI>
@@ -130,21 +129,14 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __grid_c
   using cfg = Cfg;
   constexpr int S = cfg::kStages;
 
-  pdl_wait();     // M and the A rows come from earlier kernels
+  // The prologue (barriers, TMEM) touches no global memory: it runs before the
+  // wait on the preceding kernel, under that kernel's tail.
   pdl_trigger();
-  int M = *m_ptr;
-  M = M < 0 ? 0 : (M > max_m ? max_m : M);
-  const int m_tiles = (M + BM - 1) / BM;
-  const int n_tiles = N / BN;
-  const int num_tiles = m_tiles * n_tiles;
-  const int kb_per_term = K / BK;
-  const int num_kb = 3 * kb_per_term;
-  const int units_per_tile = (num_kb + kUnitKb - 1) / kUnitKb;
-  if (num_tiles == 0) return;  // uniform for the whole grid
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t tiles_addr = smem_u32(smem_raw);
   if ((tiles_addr & 1023u) != 0u) {
+    pdl_wait();  // no CTA leaves before the preceding kernel has completed
     if (threadIdx.x == 0) report_timeout(status_word, kKernelGemmTc, kSiteSmemAlign);
     return;
   }
@@ -183,6 +175,15 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __grid_c
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  pdl_wait();  // M and the A rows come from earlier kernels
+  int M = *m_ptr;
+  M = M < 0 ? 0 : (M > max_m ? max_m : M);
+  const int m_tiles = (M + BM - 1) / BM;
+  const int n_tiles = N / BN;
+  const int num_tiles = m_tiles * n_tiles;  // 0: every role's loop is empty
+  const int num_kb = K / BK;
+  const int units_per_tile = (num_kb + kUnitKb - 1) / kUnitKb;
+
   auto fail = [&](int site) {
     *abort_flag = 1;
     report_timeout(status_word, kKernelGemmTc, site);
@@ -207,12 +208,13 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __grid_c
             ok = false;
             break;
           }
-          const int term = kb / kb_per_term, kk = (kb - term * kb_per_term) * BK;
           const uint32_t a_dst = tiles_addr + stage * cfg::kStageBytes;
-          const uint32_t b_dst = a_dst + cfg::kABytes;
+          const uint32_t b_dst = a_dst + 2 * cfg::kABytes;
           mbar_arrive_expect_tx(full_bar(stage), cfg::kStageBytes);
-          tma_load_2d(a_dst, term == 2 ? &tmap_a_lo : &tmap_a_hi, kk, m_tile * BM, full_bar(stage));
-          tma_load_2d(b_dst, term == 1 ? &tmap_w_lo : &tmap_w_hi, kk, n_tile * BN, full_bar(stage));
+          tma_load_2d(a_dst, &tmap_a_hi, kb * BK, m_tile * BM, full_bar(stage));
+          tma_load_2d(b_dst, &tmap_w_hi, kb * BK, n_tile * BN, full_bar(stage));
+          tma_load_2d(b_dst + cfg::kBBytes, &tmap_w_lo, kb * BK, n_tile * BN, full_bar(stage));
+          tma_load_2d(a_dst + cfg::kABytes, &tmap_a_lo, kb * BK, m_tile * BM, full_bar(stage));
           ++issued;
           if (++stage == S) {
             stage = 0;
@@ -256,11 +258,18 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __grid_c
             }
             tc_fence_after();
             const uint32_t a_addr = tiles_addr + stage * cfg::kStageBytes;
-            const uint64_t adesc = make_kmajor_sw128_desc(a_addr);
-            const uint64_t bdesc = make_kmajor_sw128_desc(a_addr + cfg::kABytes);
+            const uint64_t a_hi = make_kmajor_sw128_desc(a_addr);
+            const uint64_t a_lo = make_kmajor_sw128_desc(a_addr + cfg::kABytes);
+            const uint64_t w_hi = make_kmajor_sw128_desc(a_addr + 2 * cfg::kABytes);
+            const uint64_t w_lo = make_kmajor_sw128_desc(a_addr + 2 * cfg::kABytes + cfg::kBBytes);
+            // 8 fp32 = 32 bytes inside the swizzle row: +2 in the address field
 #pragma unroll
-            for (int k = 0; k < BK / UMMA_K; ++k)  // 8 fp32 = 32 bytes inside the swizzle row: +2 in the address field
-              umma_tf32_ss(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < BK / UMMA_K; ++k)
+              umma_tf32_ss(d_tmem, a_hi + 2u * k, w_hi + 2u * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) umma_tf32_ss(d_tmem, a_hi + 2u * k, w_lo + 2u * k, idesc, 1u);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) umma_tf32_ss(d_tmem, a_lo + 2u * k, w_hi + 2u * k, idesc, 1u);
             umma_commit(empty_bar(stage));
             if (++stage == S) {
               stage = 0;

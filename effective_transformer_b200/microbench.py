@@ -155,6 +155,21 @@ def main() -> None:
         "gemm_ffn1": (gemm("gemm_ffn1", x_packed, bias_f, 2), "tensor", 2.0 * t * h * f),
         "gemm_ffn2": (gemm("gemm_ffn2", ffn, None, 0), "tensor", 2.0 * t * h * f),
     }
+    # The library GEMM (cuBLAS through torch.matmul) on the same T x N x K, without bias or
+    # activation: a comparison figure for the four projections, never part of the product path.
+    lib_out = {name: torch.empty(t, w[3], device=dev, dtype=tdt) for name, w in weights.items()}
+
+    def library_gemm(name, a):
+        w = weights[name][0]
+        rows, out = a[:t], lib_out[name]
+
+        def run():
+            torch.matmul(rows, w, out=out)
+            return 0
+        return run
+
+    for name, a in (("gemm_qkv", x_packed), ("gemm_attn_out", x_packed), ("gemm_ffn1", x_packed), ("gemm_ffn2", ffn)):
+        kernels["library_" + name] = (library_gemm(name, a), "tensor", kernels[name][2])
     if not (fp16 and s <= 128):
         kernels.pop("attention_tiles"), kernels.pop("attention_plan")
     names = list(kernels) if args.kernel == "all" else args.kernel.split(",")
