@@ -78,6 +78,13 @@ __device__ __forceinline__ void report_timeout(int* status_word, int kernel_id, 
   if (status_word != nullptr) atomicCAS(status_word, 0, (kernel_id << 8) | site);
 }
 
+// x rounded to tf32 (11 significand bits, round to nearest), as an fp32 number.
+__device__ __forceinline__ float rn_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+
 // ---- 16-byte vector access ------------------------------------------------
 struct alignas(16) Vec16 {
   uint32_t x, y, z, w;
@@ -157,7 +164,9 @@ struct VecTraits<__half> {
 // (cuda/cuda_kernels.cu:29-37); evaluated in fp32.
 __device__ __forceinline__ float gelu_tanh(float x) {
   const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-  return x * (0.5f * (1.0f + tanhf(u)));
+  // 0.5 (1 + tanh u) = 1 / (1 + exp(-2u)): one exponential and one reciprocal, relative
+  // error of a few 1e-6; exp overflow (x below about -10) gives x / inf = -0, the limit.
+  return __fdividef(x, 1.0f + __expf(-2.0f * u));
 }
 
 __device__ __forceinline__ float warp_sum(float v) {
@@ -229,11 +238,12 @@ enum Epilogue : int { kEpiNone = 0, kEpiBias = 1, kEpiBiasGelu = 2, kEpiBiasTanh
 template <typename T>
 cudaError_t launch_gemm_simt(const T* a, const T* w, const T* bias, T* c, const int* m_ptr,
                              int max_m, int n, int k, int epilogue, cudaStream_t stream);
-// CUDA-core attention on the packed layout.
+// CUDA-core attention on the packed layout.  ctx_lo (fp32 only): the output is
+// written split for the tf32 projection behind it, rn_tf32 half to ctx, remainder to ctx_lo.
 template <typename T>
 cudaError_t launch_attention_simt(const T* q, const T* k, const T* v, long long token_stride,
                                   long long head_stride, T* ctx, const int* cu_seqlens, int batch,
-                                  int max_seq, int heads, int d, cudaStream_t stream);
+                                  int max_seq, int heads, int d, cudaStream_t stream, T* ctx_lo = nullptr);
 // The same under a general [B, S, S] mask with the reference op's semantics
 // (padded keys take part with K = V = 0).  pos_row[b*S+p] = packed row of
 // position p or -1, made by launch_position_rows (a memset and one kernel).
@@ -263,9 +273,11 @@ cudaError_t launch_attention_tcgen05(const __half* q, const __half* k, const __h
 cudaError_t launch_split_tf32(const float* x, float* hi, float* lo, const int* rows_ptr, int max_rows, int cols,
                               cudaStream_t stream);
 // a_hi/a_lo [max_m, K], w_hi/w_lo [N, K] (K-major); C = epi(A * W^T (+ bias)), fp32.
+// c_lo given: the result is written already split, rn_tf32 half to c and remainder to c_lo.
 cudaError_t launch_gemm_tf32x3(const float* a_hi, const float* a_lo, const float* w_hi, const float* w_lo,
                                const float* bias, float* c, const int* m_ptr, int max_m, int n, int k,
-                               int epilogue, int* status_word, cudaStream_t stream, bool reverse_m = false);
+                               int epilogue, int* status_word, cudaStream_t stream, bool reverse_m = false,
+                               float* c_lo = nullptr);
 // tcgen05 GEMM, fp16 in / fp32 accumulate / fp16 out.  w_packed is [N,K].
 // reverse_m: row tiles are visited from the last to the first.  A kernel that
 // consumes what the previous kernel has just written finds the rows written
@@ -275,5 +287,39 @@ cudaError_t launch_gemm_tcgen05(const __half* a, const __half* w_packed, const _
                                 __half* c, const int* m_ptr, int max_m, int n, int k, int epilogue,
                                 int* status_word, cudaStream_t stream, bool reverse_m = false,
                                 const __half* residual = nullptr);
+
+
+// ---- work units of the CTA-pair GEMMs ---------------------------------------
+// Tiles of 256 x 256 are dealt round-robin to the pairs.  When the last round
+// would keep at most half of the pairs busy, each of its tiles is cut into two
+// 256 x 128 units: units [0, full_tiles) are whole tiles, the rest are halves.
+struct PairUnit {
+  int m_tile;  // 256-row tile
+  int col0;    // first output column
+  int ncols;   // 256 (whole tile) or 128 (half of a last-round tile)
+};
+__device__ __forceinline__ PairUnit pair_unit(int u, int full_tiles, int n_tiles, int m_tiles, int reverse_m) {
+  int tile = u, half = -1;
+  if (u >= full_tiles) {
+    const int r = u - full_tiles;
+    tile = full_tiles + (r >> 1);
+    half = r & 1;
+  }
+  const int m_lin = tile / n_tiles, n_tile = tile - m_lin * n_tiles;
+  PairUnit pu;
+  pu.m_tile = reverse_m ? m_tiles - 1 - m_lin : m_lin;
+  pu.col0 = n_tile * 256 + (half > 0 ? 128 : 0);
+  pu.ncols = half < 0 ? 256 : 128;
+  return pu;
+}
+// Splits `num_tiles` for `num_pairs` pairs: returns the number of whole-tile
+// units, *num_units = all units.
+__device__ __forceinline__ int pair_units(int num_tiles, int num_pairs, int* num_units) {
+  const int rem = num_tiles % num_pairs;
+  const bool split = rem > 0 && 2 * rem <= num_pairs;
+  const int full_tiles = split ? num_tiles - rem : num_tiles;
+  *num_units = full_tiles + (split ? 2 * rem : 0);
+  return full_tiles;
+}
 
 }  // namespace etb

@@ -92,8 +92,9 @@ struct Workspace {
   int* lens_scratch = nullptr;
   int* attn_plan = nullptr;   // tile plan of the tcgen05 attention (made once per batch)
   int* pos_row = nullptr;     // [B*S] position -> packed row (general-mask attention)
-  float* a_hi = nullptr;      // fp32 handles: [cap, max(H, F)] tf32 halves of a projection's input
+  float* a_hi = nullptr;      // fp32 handles: [cap, H] tf32 halves of a projection's input
   float* a_lo = nullptr;
+  float* ffn_lo = nullptr;    // fp32 handles: [cap, F] remainder of the GELU output (its tf32 half is in ffn)
   int* valid_word_num = nullptr;
   int* status = nullptr;
   std::vector<void*> allocations;
@@ -326,25 +327,35 @@ int run_layer(et_handle_t h, const LayerWeights& lw, const T* x_in, T* x_out, co
   };
   auto forward_only = [&]() { h->prev_ascending = true; };
 
+  // fp32 tensor path: a_lo_ready = the input already is its tf32 half with the remainder in
+  // a_lo_ready (written so by the kernel before); c_lo = write the output split the same way.
   auto gemm = [&](const T* a, const void* w_rm, const void* w_t, const void* w_lo, const void* bias, T* c,
-                  int n, int k, int epi) -> cudaError_t {
+                  int n, int k, int epi, const float* a_lo_ready = nullptr, float* c_lo = nullptr) -> cudaError_t {
     if (tc)
       return launch_gemm_tcgen05(reinterpret_cast<const __half*>(a), static_cast<const __half*>(w_t),
                                  static_cast<const __half*>(bias), reinterpret_cast<__half*>(c), t_ptr,
                                  max_m, n, k, epi, ws.status, s, turn());
     if (tc32) {
       // w_t holds rn_tf32(W), w_lo the remainder; the input is split the same way first
-      cudaError_t e = launch_split_tf32(reinterpret_cast<const float*>(a), ws.a_hi, ws.a_lo, t_ptr, max_m, k, s);
-      if (e != cudaSuccess) return e;
-      forward_only();
-      return launch_gemm_tf32x3(ws.a_hi, ws.a_lo, static_cast<const float*>(w_t), static_cast<const float*>(w_lo),
+      const float* a_hi = reinterpret_cast<const float*>(a);
+      const float* a_lo = a_lo_ready;
+      if (a_lo == nullptr) {
+        cudaError_t e = launch_split_tf32(a_hi, ws.a_hi, ws.a_lo, t_ptr, max_m, k, s);
+        if (e != cudaSuccess) return e;
+        forward_only();
+        a_hi = ws.a_hi, a_lo = ws.a_lo;
+      }
+      return launch_gemm_tf32x3(a_hi, a_lo, static_cast<const float*>(w_t), static_cast<const float*>(w_lo),
                                 static_cast<const float*>(bias), reinterpret_cast<float*>(c), t_ptr, max_m, n, k,
-                                epi, ws.status, s, turn());
+                                epi, ws.status, s, turn(), c_lo);
     }
     forward_only();
     return launch_gemm_simt<T>(a, B(w_rm), B(bias), c, t_ptr, max_m, n, k, epi, s);
   };
 
+  // fp32 tensor path: the CUDA-core attention writes its output split for the projection behind
+  // it (the halves of the QKV input in a_hi / a_lo are no longer needed by then)
+  T* ctx_lo = (tc32 && h->cur_attr_mask == nullptr) ? reinterpret_cast<T*>(ws.a_lo) : nullptr;
   // Q,K,V projections + bias in one GEMM -> [T, 3H]
   ET_LAUNCH(h, ET_PROF_GEMM_QKV, tc32 ? 2 : 1, s, gemm(x_in, lw.wqkv, lw.wqkv_t, lw.wqkv_lo, lw.bqkv, qkv, 3 * hid, hid, kEpiBias));
   // attention straight from the [T, 3H] buffer to packed context [T, H]
@@ -368,14 +379,17 @@ int run_layer(et_handle_t h, const LayerWeights& lw, const T* x_in, T* x_out, co
                                    ws.status, s));
   else
     ET_LAUNCH(h, ET_PROF_ATTENTION, 1, s, launch_attention_simt<T>(qkv, qkv + hid, qkv + 2 * hid, 3LL * hid, d, ctx, cu_seqlens,
-                                        batch, seq, heads, d, s));
+                                        batch, seq, heads, d, s, ctx_lo));
   if (!(h->cur_attr_mask == nullptr && tc && seq <= 128)) forward_only();
   // attention output projection, then +bias +residual, LayerNorm
-  ET_LAUNCH(h, ET_PROF_GEMM_ATTN_OUT, tc32 ? 2 : 1, s, gemm(ctx, lw.wo, lw.wo_t, lw.wo_lo, nullptr, att, hid, hid, kEpiNone));
+  ET_LAUNCH(h, ET_PROF_GEMM_ATTN_OUT, tc32 && ctx_lo == nullptr ? 2 : 1, s,
+            gemm(ctx, lw.wo, lw.wo_t, lw.wo_lo, nullptr, att, hid, hid, kEpiNone, reinterpret_cast<const float*>(ctx_lo)));
   ET_LAUNCH(h, ET_PROF_LAYERNORM, 1, s, launch_add_bias_input_layernorm<T>(att, x_in, B(lw.bo), B(lw.ln1_gamma), B(lw.ln1_beta),
                                                 t_ptr, max_m, hid, h->eps, s, turn()));
   // feed-forward: bias + GELU fused into the first GEMM
-  ET_LAUNCH(h, ET_PROF_GEMM_FFN1, tc32 ? 2 : 1, s, gemm(att, lw.w1, lw.w1_t, lw.w1_lo, lw.b1, ffn, f, hid, kEpiBiasGelu));
+  // (fp32 tensor path: the GELU output leaves the epilogue split for the second projection)
+  ET_LAUNCH(h, ET_PROF_GEMM_FFN1, tc32 ? 2 : 1, s,
+            gemm(att, lw.w1, lw.w1_t, lw.w1_lo, lw.b1, ffn, f, hid, kEpiBiasGelu, nullptr, tc32 ? ws.ffn_lo : nullptr));
   // fp16 tensor-core path: the second FFN projection adds its bias and the residual in its
   // epilogue (its K = F main loop leaves the epilogue warps idle time), so the LayerNorm
   // behind it reads one tensor instead of two.  The attention output projection (K = H) has
@@ -391,7 +405,8 @@ int run_layer(et_handle_t h, const LayerWeights& lw, const T* x_in, T* x_out, co
               launch_add_bias_input_layernorm<T>(x_out, nullptr, nullptr, B(lw.ln2_gamma), B(lw.ln2_beta), t_ptr,
                                                  max_m, hid, h->eps, s, turn()));
   } else {
-    ET_LAUNCH(h, ET_PROF_GEMM_FFN2, tc32 ? 2 : 1, s, gemm(ffn, lw.w2, lw.w2_t, lw.w2_lo, nullptr, x_out, hid, f, kEpiNone));
+    ET_LAUNCH(h, ET_PROF_GEMM_FFN2, 1, s,
+              gemm(ffn, lw.w2, lw.w2_t, lw.w2_lo, nullptr, x_out, hid, f, kEpiNone, tc32 ? ws.ffn_lo : nullptr));
     ET_LAUNCH(h, ET_PROF_LAYERNORM, 1, s, launch_add_bias_input_layernorm<T>(x_out, att, B(lw.b2), B(lw.ln2_gamma), B(lw.ln2_beta),
                                                   t_ptr, max_m, hid, h->eps, s, turn()));
   }
@@ -779,8 +794,9 @@ int et_create(const et_config_t* config, et_handle_t* out_handle) {
       {reinterpret_cast<void**>(&ws.lens_scratch), static_cast<size_t>(c.max_batch_size) * 4},
       {reinterpret_cast<void**>(&ws.attn_plan), attention_plan_ints(c.max_batch_size, static_cast<int>(cap)) * 4},
       {reinterpret_cast<void**>(&ws.pos_row), cap * 4},
-      {reinterpret_cast<void**>(&ws.a_hi), c.dtype == ET_FP32 ? cap * (f > H ? f : H) * 4 : 0},
-      {reinterpret_cast<void**>(&ws.a_lo), c.dtype == ET_FP32 ? cap * (f > H ? f : H) * 4 : 0},
+      {reinterpret_cast<void**>(&ws.a_hi), c.dtype == ET_FP32 ? cap * H * 4 : 0},
+      {reinterpret_cast<void**>(&ws.a_lo), c.dtype == ET_FP32 ? cap * H * 4 : 0},
+      {reinterpret_cast<void**>(&ws.ffn_lo), c.dtype == ET_FP32 ? cap * f * 4 : 0},
       {reinterpret_cast<void**>(&ws.valid_word_num), 4}, {reinterpret_cast<void**>(&ws.status), 4}};
   for (auto& b : bufs)
     if ((rc = ws_alloc(h, b.p, b.bytes)) != ET_OK) return bail(rc);

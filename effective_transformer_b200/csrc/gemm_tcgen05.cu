@@ -399,25 +399,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 // time.  BERT-base at T = 39 778: 468 tiles of the N = 768 projections on 74
 // pairs = 6.32 rounds -> 6.5 instead of 7.
 // ---------------------------------------------------------------------------
-struct PairUnit {
-  int m_tile;  // 256-row tile
-  int col0;    // first output column
-  int ncols;   // 256 (whole tile) or 128 (half of a last-round tile)
-};
-__device__ __forceinline__ PairUnit pair_unit(int u, int full_tiles, int n_tiles, int m_tiles, int reverse_m) {
-  int tile = u, half = -1;
-  if (u >= full_tiles) {
-    const int r = u - full_tiles;
-    tile = full_tiles + (r >> 1);
-    half = r & 1;
-  }
-  const int m_lin = tile / n_tiles, n_tile = tile - m_lin * n_tiles;
-  PairUnit pu;
-  pu.m_tile = reverse_m ? m_tiles - 1 - m_lin : m_lin;
-  pu.col0 = n_tile * 256 + (half > 0 ? 128 : 0);
-  pu.ncols = half < 0 ? 256 : 128;
-  return pu;
-}
 struct PairCfg {
   static constexpr int BN = 256;
   static constexpr int kStages = 6;
@@ -505,10 +486,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int num_tiles = m_tiles * n_tiles;  // 0: every role's loop is empty
   const int num_kb = (K + BK - 1) / BK;
   // last round cut into half-width units when it occupies at most half of the pairs
-  const int rem = num_tiles % num_pairs;
-  const bool split = rem > 0 && 2 * rem <= num_pairs;
-  const int full_tiles = split ? num_tiles - rem : num_tiles;
-  const int num_units = full_tiles + (split ? 2 * rem : 0);
+  int num_units;
+  const int full_tiles = pair_units(num_tiles, num_pairs, &num_units);
+  const bool split = num_units != full_tiles;
 
   auto fail = [&](int site) {
     *abort_flag = 1;

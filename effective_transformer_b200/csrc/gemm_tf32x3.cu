@@ -24,6 +24,7 @@
 #include "common.cuh"
 #include "ptx_sm100.cuh"
 
+#include <cstdlib>
 #include <mutex>
 
 namespace etb {
@@ -46,7 +47,8 @@ struct Cfg {
   static constexpr int kBBytes = BN * BK * 4;
   static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;  // A_hi, A_lo, W_hi, W_lo
   static constexpr int kNumBars = 2 * kStages + 2 * 4 + 1;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 256 /*barriers*/;
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 8 * 32 * 32 * 4 /*epilogue staging*/;
   static constexpr int kTmemCols = 4 * BN;
 };
 
@@ -78,10 +80,59 @@ __device__ __forceinline__ void umma_tf32_ss(uint32_t tmem_d, uint64_t adesc, ui
       : "memory");
 }
 
-__device__ __forceinline__ float rn_tf32(float x) {
-  uint32_t r;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-  return __uint_as_float(r);
+// Epilogue store of one warp: 32 rows (one per lane) x 32 columns of finished sums.
+// Bias and activation are applied in the row-per-thread layout; the values then
+// pass through a 32 x 32 float staging buffer of the warp (4 KB, 16-byte groups
+// swizzled by row: conflict-free both ways) so that every global store
+// instruction covers whole 128-byte row segments (4 rows x 128 bytes) instead of
+// 32 rows x 16 bytes.  c_lo given: the result is written already split for the
+// projection that reads it next, rn_tf32 half to C and remainder to c_lo.
+constexpr int kStagingFloatsPerWarp = 32 * 32;
+constexpr int kStagingBytes = kEpilogueWarps * kStagingFloatsPerWarp * 4;
+
+template <int EPI>
+__device__ __forceinline__ void store_chunk(float* stage, const float* vals, float* __restrict__ C,
+                                            float* __restrict__ c_lo, const float* __restrict__ bias, int N,
+                                            int row0, int col, int M, int lane) {
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    float f[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) f[e] = vals[g * 4 + e];
+    if (EPI != kEpiNone) {
+      float fb[4];
+      VecTraits<float>::unpack(ld_global_v4(bias + col + g * 4), fb);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) f[e] += fb[e];
+    }
+    if (EPI == kEpiBiasGelu) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) f[e] = gelu_tanh(f[e]);
+    } else if (EPI == kEpiBiasTanh) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) f[e] = tanhf(f[e]);
+    }
+    *reinterpret_cast<float4*>(stage + lane * 32 + ((g ^ (lane & 7)) << 2)) = make_float4(f[0], f[1], f[2], f[3]);
+  }
+  __syncwarp();
+  const int g = lane & 7;
+#pragma unroll
+  for (int t = 0; t < 8; ++t) {
+    const int r = t * 4 + (lane >> 3);
+    const float4 v = *reinterpret_cast<const float4*>(stage + r * 32 + ((g ^ (r & 7)) << 2));
+    const int row = row0 + r;
+    if (row < M) {
+      const size_t off = static_cast<size_t>(row) * N + col + g * 4;
+      if (c_lo == nullptr) {
+        *reinterpret_cast<float4*>(C + off) = v;
+      } else {
+        const float4 hi = make_float4(rn_tf32(v.x), rn_tf32(v.y), rn_tf32(v.z), rn_tf32(v.w));
+        *reinterpret_cast<float4*>(C + off) = hi;
+        *reinterpret_cast<float4*>(c_lo + off) = make_float4(v.x - hi.x, v.y - hi.y, v.z - hi.z, v.w - hi.w);
+      }
+    }
+  }
+  __syncwarp();  // the buffer is reused by the next chunk
 }
 
 // hi = rn_tf32(x), lo = x - hi, four elements per thread and iteration.  hi or lo
@@ -124,8 +175,8 @@ template <int EPI>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __grid_constant__ CUtensorMap tmap_a_lo,
                    const __grid_constant__ CUtensorMap tmap_w_hi, const __grid_constant__ CUtensorMap tmap_w_lo,
-                   float* __restrict__ C, const float* __restrict__ bias, const int* __restrict__ m_ptr,
-                   int max_m, int N, int K, int* status_word, int reverse_m) {
+                   float* __restrict__ C, float* __restrict__ c_lo, const float* __restrict__ bias,
+                   const int* __restrict__ m_ptr, int max_m, int N, int K, int* status_word, int reverse_m) {
   using cfg = Cfg;
   constexpr int S = cfg::kStages;
 
@@ -289,6 +340,8 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __grid_c
     const int quad = warp & 3;
     const int half = (warp - 2) >> 2;
     constexpr int kCols = BN / 2;
+    float* stage = reinterpret_cast<float*>(smem_raw + S * cfg::kStageBytes + cfg::kBarrierBytes) +
+                   (warp - 2) * kStagingFloatsPerWarp;
     uint32_t unit = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
@@ -319,30 +372,9 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __grid_c
         for (int e = 0; e < kCols; ++e) sum[e] += __uint_as_float(r[e]);
       }
       if (!ok) break;
-      const int row = m_tile * BM + quad * 32 + lane;
-      if (row < M) {
-        float* crow = C + static_cast<size_t>(row) * N + col0;
 #pragma unroll
-        for (int p = 0; p < kCols / 4; ++p) {
-          float f[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) f[e] = sum[p * 4 + e];
-          if (EPI != kEpiNone) {
-            float fb[4];
-            VecTraits<float>::unpack(ld_global_v4(bias + col0 + p * 4), fb);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) f[e] += fb[e];
-          }
-          if (EPI == kEpiBiasGelu) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) f[e] = gelu_tanh(f[e]);
-          } else if (EPI == kEpiBiasTanh) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) f[e] = tanhf(f[e]);
-          }
-          st_global_v4(crow + p * 4, VecTraits<float>::pack(f));
-        }
-      }
+      for (int ch = 0; ch < kCols / 32; ++ch)
+        store_chunk<EPI>(stage, sum + ch * 32, C, c_lo, bias, N, m_tile * BM + quad * 32, col0 + ch * 32, M, lane);
     }
   }
 
@@ -352,6 +384,287 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __grid_c
     __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem_base, cfg::kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// CTA-pair variant (N % 256 == 0): a cluster of two CTAs computes a 256 x 256
+// tile with tcgen05.mma cta_group::2.  Per k-block each CTA fetches A_hi / A_lo
+// for its 128 rows and W_hi / W_lo for 128 of the tile's 256 W rows: 64 KB per
+// 3 x 4 instructions of 128 x 256 x 8 per CTA, half of the L2 -> SM traffic per
+// FLOP of the single-CTA kernel, which is what bounds that kernel.  No load is
+// multicast.  The accumulator of a unit is a 256-column TMEM block in each CTA;
+// the 512 columns hold two blocks, drained by the epilogue warps (128 running
+// sums per thread) while the other block accumulates.  Barriers as in the
+// fp16 pair kernel: full[] and tmem_empty[] live in CTA 0, empty[] and
+// tmem_full[] in both (CTA 0's MMA thread commits to both).  The last round of
+// tiles is cut into 256 x 128 units when it would occupy at most half of the
+// pairs (pair_units()).
+// ---------------------------------------------------------------------------
+constexpr int BM2 = 2 * BM;
+constexpr int BN2 = 256;
+constexpr int kPairBlocks = 2;
+struct PairCfg {
+  static constexpr int kStages = 3;
+  static constexpr int kABytes = BM * BK * 4;          // this CTA's 128 rows of A_hi (and of A_lo)
+  static constexpr int kBBytes = (BN2 / 2) * BK * 4;   // this CTA's 128 rows of W_hi (and of W_lo)
+  static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;
+  static constexpr int kNumBars = 2 * kStages + 2 * kPairBlocks + 1;
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 8 * 32 * 32 * 4 /*epilogue staging*/;
+  static constexpr int kTmemCols = kPairBlocks * BN2;
+};
+
+__device__ __forceinline__ void umma_tf32_ss_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                  uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+template <int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
+gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __grid_constant__ CUtensorMap tmap_a_lo,
+                        const __grid_constant__ CUtensorMap tmap_w_hi, const __grid_constant__ CUtensorMap tmap_w_lo,
+                        const __grid_constant__ CUtensorMap tmap_w_hi_half,
+                        const __grid_constant__ CUtensorMap tmap_w_lo_half, float* __restrict__ C,
+                        float* __restrict__ c_lo, const float* __restrict__ bias, const int* __restrict__ m_ptr,
+                        int max_m, int N, int K, int* status_word, int reverse_m) {
+  using cfg = PairCfg;
+  constexpr int S = cfg::kStages;
+
+  // The prologue touches no global memory: it runs before the wait on the preceding kernel.
+  pdl_trigger();
+  const uint32_t rank = cluster_ctarank();  // 0 issues the MMAs
+  const int pair_id = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t tiles_addr = smem_u32(smem_raw);
+  if ((tiles_addr & 1023u) != 0u) {  // same layout in both CTAs: uniform for the pair
+    pdl_wait();  // no CTA leaves before the preceding kernel has completed
+    if (threadIdx.x == 0) report_timeout(status_word, kKernelGemmTc, kSiteSmemAlign);
+    return;
+  }
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + S * cfg::kStageBytes);
+  const uint32_t bar0 = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (S + s); };
+  auto tmem_full_bar = [&](int a) { return bar0 + 8u * (2 * S + a); };
+  auto tmem_empty_bar = [&](int a) { return bar0 + 8u * (2 * S + kPairBlocks + a); };
+  const uint32_t drain_bar = bar0 + 8u * (2 * S + 2 * kPairBlocks);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + cfg::kNumBars);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < kPairBlocks; ++a) {
+      mbar_init(tmem_full_bar(a), 1);
+      mbar_init(tmem_empty_bar(a), 2 * kEpilogueWarps);
+    }
+    mbar_init(drain_bar, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(tmem_slot), cfg::kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers are initialised before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  pdl_wait();  // M and the A rows come from earlier kernels
+  int M = *m_ptr;
+  M = M < 0 ? 0 : (M > max_m ? max_m : M);
+  const int m_tiles = (M + BM2 - 1) / BM2;
+  const int n_tiles = N / BN2;
+  const int num_tiles = m_tiles * n_tiles;  // 0: every role's loop is empty
+  const int num_kb = K / BK;
+  const int units_per_tile = (num_kb + kUnitKb - 1) / kUnitKb;  // accumulation units, not work units
+  int num_units;
+  const int full_tiles = pair_units(num_tiles, num_pairs, &num_units);
+
+  auto fail = [&](int site) {
+    *abort_flag = 1;
+    report_timeout(status_word, kKernelGemmTc, site);
+  };
+
+  if (warp == 0) {
+    // ------------------------- TMA producer (both CTAs) -------------------------
+    if (lane == 0) {
+      prefetch_tensormap(&tmap_a_hi);
+      prefetch_tensormap(&tmap_a_lo);
+      prefetch_tensormap(&tmap_w_hi);
+      prefetch_tensormap(&tmap_w_lo);
+      uint32_t stage = 0, phase = 0;
+      long long issued = 0;
+      bool ok = true;
+      for (int u = pair_id; u < num_units && ok; u += num_pairs) {
+        const PairUnit pu = pair_unit(u, full_tiles, n_tiles, m_tiles, reverse_m);
+        const int a_row = pu.m_tile * BM2 + static_cast<int>(rank) * BM;
+        const int b_row = pu.col0 + static_cast<int>(rank) * (pu.ncols / 2);
+        const bool whole = pu.ncols == BN2;
+        const uint32_t stage_tx = 2u * (2u * cfg::kABytes + (whole ? 2u * cfg::kBBytes : cfg::kBBytes));
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+            fail(kSiteProducerEmpty);
+            ok = false;
+            break;
+          }
+          const uint32_t a_dst = tiles_addr + stage * cfg::kStageBytes;
+          const uint32_t b_dst = a_dst + 2 * cfg::kABytes;
+          const uint32_t full0 = mapa_shared(full_bar(stage), 0);
+          if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), stage_tx);
+          tma_load_2d_pair(a_dst, &tmap_a_hi, kb * BK, a_row, full0);
+          tma_load_2d_pair(b_dst, whole ? &tmap_w_hi : &tmap_w_hi_half, kb * BK, b_row, full0);
+          tma_load_2d_pair(b_dst + cfg::kBBytes, whole ? &tmap_w_lo : &tmap_w_lo_half, kb * BK, b_row, full0);
+          tma_load_2d_pair(a_dst + cfg::kABytes, &tmap_a_lo, kb * BK, a_row, full0);
+          ++issued;
+          if (++stage == S) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (rank == 0) {
+        // full[] counts both CTAs' bytes: once these phases are complete no copy
+        // of the pair is in flight; the peer learns it at the closing cluster barrier.
+        const long long pending = issued < S ? issued : S;
+        for (long long i = 0; i < pending; ++i) {
+          const long long f = issued - 1 - i;
+          if (!mbar_wait(full_bar(static_cast<int>(f % S)), static_cast<uint32_t>((f / S) & 1), abort_flag) &&
+              *abort_flag == 0)
+            fail(kSiteProducerDrain);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------- MMA issuer (CTA 0 only) -------------------------
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc_whole = make_idesc_tf32_f32acc(BM2, BN2);
+      constexpr uint32_t idesc_half = make_idesc_tf32_f32acc(BM2, BN2 / 2);
+      uint32_t stage = 0, phase = 0;
+      uint32_t unit = 0;  // accumulation units over all work units of this pair: TMEM block = unit % 2
+      bool ok = true;
+      for (int u = pair_id; u < num_units && ok; u += num_pairs) {
+        const uint32_t idesc = u < full_tiles ? idesc_whole : idesc_half;
+        for (int kb0 = 0; kb0 < num_kb && ok; kb0 += kUnitKb, ++unit) {
+          const int blk = unit % kPairBlocks;
+          const uint32_t blk_phase = (unit / kPairBlocks) & 1u;
+          if (!mbar_wait(tmem_empty_bar(blk), blk_phase ^ 1u, abort_flag)) {
+            fail(kSiteMmaTmemEmpty);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + blk * BN2;
+          const int kb1 = min(kb0 + kUnitKb, num_kb);
+          for (int kb = kb0; kb < kb1; ++kb) {
+            if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+              fail(kSiteMmaFull);
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint32_t a_addr = tiles_addr + stage * cfg::kStageBytes;
+            const uint64_t a_hi = make_kmajor_sw128_desc(a_addr);
+            const uint64_t a_lo = make_kmajor_sw128_desc(a_addr + cfg::kABytes);
+            const uint64_t w_hi = make_kmajor_sw128_desc(a_addr + 2 * cfg::kABytes);
+            const uint64_t w_lo = make_kmajor_sw128_desc(a_addr + 2 * cfg::kABytes + cfg::kBBytes);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k)
+              umma_tf32_ss_pair(d_tmem, a_hi + 2u * k, w_hi + 2u * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) umma_tf32_ss_pair(d_tmem, a_hi + 2u * k, w_lo + 2u * k, idesc, 1u);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) umma_tf32_ss_pair(d_tmem, a_lo + 2u * k, w_hi + 2u * k, idesc, 1u);
+            umma_commit_pair(empty_bar(stage));
+            umma_commit_pair(mapa_shared(empty_bar(stage), 1));
+            if (++stage == S) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+          if (ok) {
+            umma_commit_pair(tmem_full_bar(blk));
+            umma_commit_pair(mapa_shared(tmem_full_bar(blk), 1));
+          }
+        }
+      }
+      umma_commit_pair(drain_bar);
+      if (!mbar_wait(drain_bar, 0u, abort_flag) && *abort_flag == 0) fail(kSiteMmaDrain);
+    }
+  } else {
+    // ------------------------- epilogue (both CTAs) -------------------------
+    // warp w reads TMEM lanes [32*(w%4), +32) (one output row per thread) and one
+    // half of the unit's columns (128, or 64 in a half-width unit), kept as
+    // running fp32 sums in registers.
+    const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
+    constexpr int kCols = BN2 / 2;
+    float* stage = reinterpret_cast<float*>(smem_raw + S * cfg::kStageBytes + cfg::kBarrierBytes) +
+                   (warp - 2) * kStagingFloatsPerWarp;
+    uint32_t unit = 0;
+    bool ok = true;
+    for (int u = pair_id; u < num_units && ok; u += num_pairs) {
+      const PairUnit pu = pair_unit(u, full_tiles, n_tiles, m_tiles, reverse_m);
+      const int wcols = pu.ncols / 2;        // this warp's columns
+      const int chunks = wcols / 32;
+      const int col0 = pu.col0 + half * wcols;
+      float sum[kCols];
+#pragma unroll
+      for (int e = 0; e < kCols; ++e) sum[e] = 0.f;
+      for (int ui = 0; ui < units_per_tile; ++ui, ++unit) {
+        const int blk = unit % kPairBlocks;
+        const uint32_t blk_phase = (unit / kPairBlocks) & 1u;
+        const bool got = mbar_wait(tmem_full_bar(blk), blk_phase, abort_flag);
+        if (!__all_sync(0xffffffffu, got)) {
+          if (lane == 0) fail(kSiteEpilogueFull);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + blk * BN2 + half * wcols;
+#pragma unroll
+        for (int ch = 0; ch < kCols / 32; ++ch) {
+          if (ch < chunks) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(t_row + ch * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) sum[ch * 32 + e] += __uint_as_float(r[e]);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(mapa_shared(tmem_empty_bar(blk), 0));  // the block goes back to the issuer
+      }
+      if (!ok) break;
+      const int row0 = pu.m_tile * BM2 + static_cast<int>(rank) * BM + quad * 32;
+#pragma unroll
+      for (int ch = 0; ch < kCols / 32; ++ch)
+        if (ch < chunks) store_chunk<EPI>(stage, sum + ch * 32, C, c_lo, bias, N, row0, col0 + ch * 32, M, lane);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA leaves while the other may still touch its barriers or TMEM
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, cfg::kTmemCols);
   }
 }
 
@@ -370,8 +683,8 @@ bool encode_2d_f32_sw128(CUtensorMap* map, const void* base, uint64_t rows, uint
 
 template <int EPI>
 cudaError_t launch_epi(const CUtensorMap& tah, const CUtensorMap& tal, const CUtensorMap& twh, const CUtensorMap& twl,
-                       const float* bias, float* c, const int* m_ptr, int max_m, int n, int k, int* status_word,
-                       int reverse_m, cudaStream_t stream) {
+                       const float* bias, float* c, float* c_lo, const int* m_ptr, int max_m, int n, int k,
+                       int* status_word, int reverse_m, cudaStream_t stream) {
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
@@ -384,7 +697,28 @@ cudaError_t launch_epi(const CUtensorMap& tah, const CUtensorMap& tal, const CUt
   if (grid > max_tiles) grid = max_tiles;
   if (grid < 1) grid = 1;
   return launch_pdl(gemm_tf32x3_kernel<EPI>, dim3(static_cast<int>(grid)), dim3(kNumThreads), Cfg::kSmemBytes, stream,
-                    tah, tal, twh, twl, c, bias, m_ptr, max_m, n, k, status_word, reverse_m);
+                    tah, tal, twh, twl, c, c_lo, bias, m_ptr, max_m, n, k, status_word, reverse_m);
+}
+
+template <int EPI>
+cudaError_t launch_pair_epi(const CUtensorMap& tah, const CUtensorMap& tal, const CUtensorMap& twh,
+                            const CUtensorMap& twl, const CUtensorMap& twhh, const CUtensorMap& twlh, const float* bias,
+                            float* c, float* c_lo, const int* m_ptr, int max_m, int n, int k, int* status_word,
+                            int reverse_m, cudaStream_t stream) {
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(gemm_tf32x3_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    PairCfg::kSmemBytes);
+  });
+  if (attr_err != cudaSuccess) return attr_err;
+  const long long max_tiles = static_cast<long long>((max_m + BM2 - 1) / BM2) * (n / BN2);
+  long long pairs = sm_count() / 2;
+  if (pairs > max_tiles) pairs = max_tiles;
+  if (pairs < 1) pairs = 1;
+  return launch_pdl(gemm_tf32x3_pair_kernel<EPI>, dim3(static_cast<int>(2 * pairs)), dim3(kNumThreads),
+                    PairCfg::kSmemBytes, stream, tah, tal, twh, twl, twhh, twlh, c, c_lo, bias, m_ptr, max_m, n, k,
+                    status_word, reverse_m);
 }
 
 }  // namespace
@@ -403,7 +737,7 @@ cudaError_t launch_split_tf32(const float* x, float* hi, float* lo, const int* r
 
 cudaError_t launch_gemm_tf32x3(const float* a_hi, const float* a_lo, const float* w_hi, const float* w_lo,
                                const float* bias, float* c, const int* m_ptr, int max_m, int n, int k,
-                               int epilogue, int* status_word, cudaStream_t stream, bool reverse_m) {
+                               int epilogue, int* status_word, cudaStream_t stream, bool reverse_m, float* c_lo) {
   if (max_m <= 0) return cudaSuccess;
   if (n <= 0 || k <= 0 || (n % 128) != 0 || (k % BK) != 0) return cudaErrorInvalidValue;
   for (const void* p : {static_cast<const void*>(a_hi), static_cast<const void*>(a_lo),
@@ -411,6 +745,7 @@ cudaError_t launch_gemm_tf32x3(const float* a_hi, const float* a_lo, const float
                         static_cast<const void*>(c)})
     if (p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15u)) return cudaErrorMisalignedAddress;
   if (bias != nullptr && (reinterpret_cast<uintptr_t>(bias) & 15u)) return cudaErrorMisalignedAddress;
+  if (c_lo != nullptr && (reinterpret_cast<uintptr_t>(c_lo) & 15u)) return cudaErrorMisalignedAddress;
   if (epilogue != kEpiNone && bias == nullptr) return cudaErrorInvalidValue;
   CUtensorMap tah, tal, twh, twl;
   if (!encode_2d_f32_sw128(&tah, a_hi, static_cast<uint64_t>(max_m), static_cast<uint64_t>(k), BM) ||
@@ -419,9 +754,36 @@ cudaError_t launch_gemm_tf32x3(const float* a_hi, const float* a_lo, const float
       !encode_2d_f32_sw128(&twl, w_lo, static_cast<uint64_t>(n), static_cast<uint64_t>(k), BN))
     return cudaErrorInvalidValue;
   const int rev = reverse_m ? 1 : 0;
+  static const bool single_cta = [] {
+    const char* e = getenv("ETB_GEMM_SINGLE_CTA");  // debugging: force the one-CTA kernel
+    return e != nullptr && e[0] == '1';
+  }();
+  // The pair kernel needs enough 256 x 256 tiles at capacity to occupy the pairs; below that
+  // the 128 x 128 tiles of the one-CTA kernel spread a small batch over more SMs.
+  const long long pair_tiles = static_cast<long long>((max_m + BM2 - 1) / BM2) * (n / BN2);
+  if ((n % BN2) == 0 && !single_cta && pair_tiles >= sm_count() / 2) {
+    // the W maps above (128-row boxes) serve whole tiles; half-width units take 64 rows per CTA
+    CUtensorMap twhh, twlh;
+    if (!encode_2d_f32_sw128(&twhh, w_hi, static_cast<uint64_t>(n), static_cast<uint64_t>(k), 64) ||
+        !encode_2d_f32_sw128(&twlh, w_lo, static_cast<uint64_t>(n), static_cast<uint64_t>(k), 64))
+      return cudaErrorInvalidValue;
+#define ETB_PAIR_CASE(E) \
+  case E:                \
+    return launch_pair_epi<E>(tah, tal, twh, twl, twhh, twlh, bias, c, c_lo, m_ptr, max_m, n, k, status_word, rev, \
+                              stream)
+    switch (epilogue) {
+      ETB_PAIR_CASE(kEpiNone);
+      ETB_PAIR_CASE(kEpiBias);
+      ETB_PAIR_CASE(kEpiBiasGelu);
+      ETB_PAIR_CASE(kEpiBiasTanh);
+      default:
+        return cudaErrorInvalidValue;
+    }
+#undef ETB_PAIR_CASE
+  }
 #define ETB_CASE(E) \
   case E:           \
-    return launch_epi<E>(tah, tal, twh, twl, bias, c, m_ptr, max_m, n, k, status_word, rev, stream)
+    return launch_epi<E>(tah, tal, twh, twl, bias, c, c_lo, m_ptr, max_m, n, k, status_word, rev, stream)
   switch (epilogue) {
     ETB_CASE(kEpiNone);
     ETB_CASE(kEpiBias);
