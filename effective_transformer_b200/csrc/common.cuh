@@ -205,10 +205,13 @@ cudaError_t launch_add_qkv_bias_transpose(const T* q, const T* bq, const T* k, c
 template <typename T>
 cudaError_t launch_add_bias_gelu(T* out, const T* bias, const int* t_ptr, int max_tokens, int n,
                                  cudaStream_t stream);
+// split_hi / split_lo (fp32 only, both or neither): the normalised rows are also written as
+// rn_tf32 half and remainder, the input format of the fp32 projections on the tensor cores.
 template <typename T>
 cudaError_t launch_add_bias_input_layernorm(T* out, const T* input, const T* bias, const T* gamma,
                                             const T* beta, const int* t_ptr, int max_tokens, int n,
-                                            float eps, cudaStream_t stream, bool reverse = false);
+                                            float eps, cudaStream_t stream, bool reverse = false,
+                                            T* split_hi = nullptr, T* split_lo = nullptr);
 // Embedding rows + LayerNorm for valid tokens only, written packed [T, n].
 // token_type_ids / type_table / pos_table may be null.
 template <typename T>

@@ -102,7 +102,8 @@ __global__ void __launch_bounds__(kThreads, (kVPL <= 4 ? 3 : 1))
 add_bias_input_layernorm_kernel(T* __restrict__ out, const T* __restrict__ input,
                                 const T* __restrict__ bias, const T* __restrict__ gamma,
                                 const T* __restrict__ beta, const int* __restrict__ t_ptr,
-                                int max_tokens, int n, float eps, int reverse) {
+                                int max_tokens, int n, float eps, int reverse, T* __restrict__ split_hi,
+                                T* __restrict__ split_lo) {
   pdl_wait();
   pdl_trigger();
   constexpr int E = VecTraits<T>::kElems;
@@ -175,6 +176,19 @@ add_bias_input_layernorm_kernel(T* __restrict__ out, const T* __restrict__ input
 #pragma unroll
         for (int e = 0; e < E; ++e) y[e] = (x[j][e] - mean) * rstd * fg[e] + fbe[e];
         st_global_v4(orow + c * E, VecTraits<T>::pack(y));
+        if constexpr (sizeof(T) == 4) {
+          if (split_hi != nullptr) {  // fp32 tensor path: the next projection's input, already split
+            float hi[E], lo[E];
+#pragma unroll
+            for (int e = 0; e < E; ++e) {
+              hi[e] = rn_tf32(y[e]);
+              lo[e] = y[e] - hi[e];
+            }
+            const size_t off = static_cast<size_t>(row) * n + c * E;
+            st_global_v4(split_hi + off, VecTraits<T>::pack(hi));
+            st_global_v4(split_lo + off, VecTraits<T>::pack(lo));
+          }
+        }
       }
     }
   }
@@ -242,9 +256,12 @@ cudaError_t launch_add_bias_gelu(T* out, const T* bias, const int* t_ptr, int ma
 template <typename T>
 cudaError_t launch_add_bias_input_layernorm(T* out, const T* input, const T* bias, const T* gamma,
                                             const T* beta, const int* t_ptr, int max_tokens, int n,
-                                            float eps, cudaStream_t stream, bool reverse) {
+                                            float eps, cudaStream_t stream, bool reverse, T* split_hi,
+                                            T* split_lo) {
   constexpr int E = VecTraits<T>::kElems;
   if (max_tokens <= 0) return cudaSuccess;
+  if ((split_hi == nullptr) != (split_lo == nullptr) || (split_hi != nullptr && sizeof(T) != 4))
+    return cudaErrorInvalidValue;
   if (n % E != 0 || n <= 0) return cudaErrorInvalidValue;
   const int vpl = (n / E + 31) / 32;
   const long long rows_per_cta = kThreads / 32;
@@ -255,7 +272,7 @@ cudaError_t launch_add_bias_input_layernorm(T* out, const T* input, const T* bia
   cudaError_t le = cudaSuccess;
 #define ETB_LN(V)                                                                                   \
   le = launch_pdl(add_bias_input_layernorm_kernel<T, V>, dim3(grid), dim3(kThreads), 0, stream, out, \
-                  input, bias, gamma, beta, t_ptr, max_tokens, n, eps, reverse ? 1 : 0)
+                  input, bias, gamma, beta, t_ptr, max_tokens, n, eps, reverse ? 1 : 0, split_hi, split_lo)
   if (vpl <= 1) ETB_LN(1);
   else if (vpl <= 2) ETB_LN(2);
   else if (vpl <= 3) ETB_LN(3);
@@ -291,7 +308,7 @@ cudaError_t launch_copy_columns(const T* src, T* dst, int rows, int cols, int ds
   template cudaError_t launch_add_bias_gelu<T>(T*, const T*, const int*, int, int, cudaStream_t); \
   template cudaError_t launch_add_bias_input_layernorm<T>(T*, const T*, const T*, const T*,      \
                                                           const T*, const int*, int, int, float, \
-                                                          cudaStream_t, bool);                   \
+                                                          cudaStream_t, bool, T*, T*);           \
   template cudaError_t launch_transpose<T>(const T*, T*, int, int, cudaStream_t);                \
   template cudaError_t launch_copy_columns<T>(const T*, T*, int, int, int, int, cudaStream_t);
 ETB_INST(float)

@@ -307,9 +307,13 @@ int pack_layer_any(et_handle_t h, int layer, const void* const* w, cudaStream_t 
 }
 
 // One encoder layer on the packed layout.  x_out may alias x_in.
+// fp32 tensor path only: in_split_ready = the workspace's a_hi / a_lo already hold the tf32
+// halves of x_in (the layer before wrote them); out_split = write those of x_out for the next
+// layer.  Both are false for a layer called on its own, whose input may be anything.
 template <typename T>
 int run_layer(et_handle_t h, const LayerWeights& lw, const T* x_in, T* x_out, const int* t_ptr,
-              int max_m, const int* cu_seqlens, int batch, int seq, cudaStream_t s) {
+              int max_m, const int* cu_seqlens, int batch, int seq, cudaStream_t s,
+              bool in_split_ready = false, bool out_split = false) {
   const int hid = h->hidden, f = h->cfg.ffn_dim, heads = h->cfg.head_num, d = h->cfg.size_per_head;
   Workspace& ws = h->ws;
   T* qkv = static_cast<T*>(ws.qkv);
@@ -357,7 +361,12 @@ int run_layer(et_handle_t h, const LayerWeights& lw, const T* x_in, T* x_out, co
   // it (the halves of the QKV input in a_hi / a_lo are no longer needed by then)
   T* ctx_lo = (tc32 && h->cur_attr_mask == nullptr) ? reinterpret_cast<T*>(ws.a_lo) : nullptr;
   // Q,K,V projections + bias in one GEMM -> [T, 3H]
-  ET_LAUNCH(h, ET_PROF_GEMM_QKV, tc32 ? 2 : 1, s, gemm(x_in, lw.wqkv, lw.wqkv_t, lw.wqkv_lo, lw.bqkv, qkv, 3 * hid, hid, kEpiBias));
+  if (tc32 && in_split_ready)
+    ET_LAUNCH(h, ET_PROF_GEMM_QKV, 1, s,
+              gemm(reinterpret_cast<const T*>(ws.a_hi), lw.wqkv, lw.wqkv_t, lw.wqkv_lo, lw.bqkv, qkv, 3 * hid, hid,
+                   kEpiBias, ws.a_lo));
+  else
+    ET_LAUNCH(h, ET_PROF_GEMM_QKV, tc32 ? 2 : 1, s, gemm(x_in, lw.wqkv, lw.wqkv_t, lw.wqkv_lo, lw.bqkv, qkv, 3 * hid, hid, kEpiBias));
   // attention straight from the [T, 3H] buffer to packed context [T, H]
   if (h->cur_attr_mask != nullptr)
     ET_LAUNCH(h, ET_PROF_ATTENTION, 1, s,
@@ -384,12 +393,16 @@ int run_layer(et_handle_t h, const LayerWeights& lw, const T* x_in, T* x_out, co
   // attention output projection, then +bias +residual, LayerNorm
   ET_LAUNCH(h, ET_PROF_GEMM_ATTN_OUT, tc32 && ctx_lo == nullptr ? 2 : 1, s,
             gemm(ctx, lw.wo, lw.wo_t, lw.wo_lo, nullptr, att, hid, hid, kEpiNone, reinterpret_cast<const float*>(ctx_lo)));
+  // (fp32 tensor path: both LayerNorms also write their rows split for the projection behind them)
+  T* ln_hi = tc32 ? reinterpret_cast<T*>(ws.a_hi) : nullptr;
+  T* ln_lo = tc32 ? reinterpret_cast<T*>(ws.a_lo) : nullptr;
   ET_LAUNCH(h, ET_PROF_LAYERNORM, 1, s, launch_add_bias_input_layernorm<T>(att, x_in, B(lw.bo), B(lw.ln1_gamma), B(lw.ln1_beta),
-                                                t_ptr, max_m, hid, h->eps, s, turn()));
+                                                t_ptr, max_m, hid, h->eps, s, turn(), ln_hi, ln_lo));
   // feed-forward: bias + GELU fused into the first GEMM
   // (fp32 tensor path: the GELU output leaves the epilogue split for the second projection)
-  ET_LAUNCH(h, ET_PROF_GEMM_FFN1, tc32 ? 2 : 1, s,
-            gemm(att, lw.w1, lw.w1_t, lw.w1_lo, lw.b1, ffn, f, hid, kEpiBiasGelu, nullptr, tc32 ? ws.ffn_lo : nullptr));
+  ET_LAUNCH(h, ET_PROF_GEMM_FFN1, 1, s,
+            gemm(tc32 ? reinterpret_cast<const T*>(ws.a_hi) : att, lw.w1, lw.w1_t, lw.w1_lo, lw.b1, ffn, f, hid,
+                 kEpiBiasGelu, tc32 ? ws.a_lo : nullptr, tc32 ? ws.ffn_lo : nullptr));
   // fp16 tensor-core path: the second FFN projection adds its bias and the residual in its
   // epilogue (its K = F main loop leaves the epilogue warps idle time), so the LayerNorm
   // behind it reads one tensor instead of two.  The attention output projection (K = H) has
@@ -407,8 +420,10 @@ int run_layer(et_handle_t h, const LayerWeights& lw, const T* x_in, T* x_out, co
   } else {
     ET_LAUNCH(h, ET_PROF_GEMM_FFN2, 1, s,
               gemm(ffn, lw.w2, lw.w2_t, lw.w2_lo, nullptr, x_out, hid, f, kEpiNone, tc32 ? ws.ffn_lo : nullptr));
+    const bool split2 = tc32 && out_split;
     ET_LAUNCH(h, ET_PROF_LAYERNORM, 1, s, launch_add_bias_input_layernorm<T>(x_out, att, B(lw.b2), B(lw.ln2_gamma), B(lw.ln2_beta),
-                                                  t_ptr, max_m, hid, h->eps, s, turn()));
+                                                  t_ptr, max_m, hid, h->eps, s, turn(), split2 ? ln_hi : nullptr,
+                                                  split2 ? ln_lo : nullptr));
   }
   return ET_OK;
 }
@@ -510,7 +525,8 @@ int stack_impl(et_handle_t h, int batch, int seq, cudaStream_t s) {
                              ws.valid_word_num, max_m, ws.cu_seqlens, batch, seq, s);
     else
       rc = run_layer<float>(h, h->layers[l], static_cast<const float*>(ws.x), static_cast<float*>(ws.x),
-                            ws.valid_word_num, max_m, ws.cu_seqlens, batch, seq, s);
+                            ws.valid_word_num, max_m, ws.cu_seqlens, batch, seq, s, l > 0,
+                            l + 1 < h->cfg.num_layers);
     if (rc != ET_OK) return rc;
   }
   return ET_OK;
