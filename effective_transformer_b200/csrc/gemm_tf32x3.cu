@@ -40,6 +40,9 @@ constexpr int kEpilogueWarps = 8;
 constexpr int kEpilogueThreads = kEpilogueWarps * 32;
 constexpr int kNumThreads = 64 + kEpilogueThreads;
 
+constexpr int kStagingFloatsPerWarp = 32 * 32;  // epilogue staging: 32 rows x 32 columns per warp
+constexpr int kStagingBytes = kEpilogueWarps * kStagingFloatsPerWarp * 4;
+
 constexpr int BN = 128;    // four TMEM blocks of BN columns hold the units in flight
 struct Cfg {
   static constexpr int kStages = 3;
@@ -48,7 +51,7 @@ struct Cfg {
   static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;  // A_hi, A_lo, W_hi, W_lo
   static constexpr int kNumBars = 2 * kStages + 2 * 4 + 1;
   static constexpr int kBarrierBytes = 256;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 8 * 32 * 32 * 4 /*epilogue staging*/;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + kStagingBytes;
   static constexpr int kTmemCols = 4 * BN;
 };
 
@@ -87,8 +90,6 @@ __device__ __forceinline__ void umma_tf32_ss(uint32_t tmem_d, uint64_t adesc, ui
 // instruction covers whole 128-byte row segments (4 rows x 128 bytes) instead of
 // 32 rows x 16 bytes.  c_lo given: the result is written already split for the
 // projection that reads it next, rn_tf32 half to C and remainder to c_lo.
-constexpr int kStagingFloatsPerWarp = 32 * 32;
-constexpr int kStagingBytes = kEpilogueWarps * kStagingFloatsPerWarp * 4;
 
 template <int EPI>
 __device__ __forceinline__ void store_chunk(float* stage, const float* vals, float* __restrict__ C,
@@ -165,10 +166,14 @@ split_tf32_kernel(const float* x, float* hi, float* lo,
 // TMEM blocks of BN columns (used round-robin), and the epilogue warps add
 // finished units into fp32 registers.  Reason: the tensor core adds into its fp32
 // accumulator with truncation, so a single chain over all 3K/8 instructions
-// drifts by about 1e-4 relative at K = 3072; 36-instruction chains summed with
-// round-to-nearest stay at the level of an fp32 FMA loop.  Draining a unit overlaps the MMAs of
+// drifts by about 1e-4 relative at K = 3072; 72-instruction chains summed with
+// round-to-nearest stay at the level of an fp32 FMA loop.  The unit is also the
+// slack of the pipeline: the issuer runs (number of blocks) units ahead of the
+// epilogue warps, which must fit a tile's bias / activation / store phase into
+// that time; with units of 3 k-blocks the issuer waited for TMEM 19-27 % of a
+// K = 768 projection.  Draining a unit overlaps the MMAs of
 // the next ones, so the issuer never waits for the epilogue in steady state.
-constexpr int kUnitKb = 3;
+constexpr int kUnitKb = 6;
 constexpr int kTmemBlocks = 4;
 
 template <int EPI>
@@ -411,7 +416,7 @@ struct PairCfg {
   static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;
   static constexpr int kNumBars = 2 * kStages + 2 * kPairBlocks + 1;
   static constexpr int kBarrierBytes = 256;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 8 * 32 * 32 * 4 /*epilogue staging*/;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + kStagingBytes;
   static constexpr int kTmemCols = kPairBlocks * BN2;
 };
 
