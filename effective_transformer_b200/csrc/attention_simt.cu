@@ -169,14 +169,38 @@ attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
   const int nq = min(kQB, len - q0);
   const int ni = (nq + 15) >> 4;  // row groups in use
 
-  for (int idx = threadIdx.x; idx < kQB * (kD / 4); idx += kThreads) {
-    const int row = idx >> 4, c = (idx & 15) * 4;
-    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (row < nq) {
-      x = load4<T, kVec>(q + static_cast<size_t>(lo + q0 + row) * token_stride + hoff + c);
-      x.x *= scale, x.y *= scale, x.z *= scale, x.w *= scale;
+  // A 64 x 64 tile is 8 accesses of 4 elements per thread.  All loads of a tile are issued
+  // before the first store to shared memory, so that a thread waits for memory once per tile
+  // and not once per access.
+  constexpr int kPerThread = kQB * (kD / 4) / kThreads;
+  auto load_tile = [&](const T* base, int first_row, int nrows, float4 (&buf)[kPerThread]) {
+#pragma unroll
+    for (int it = 0; it < kPerThread; ++it) {
+      const int idx = it * kThreads + threadIdx.x;
+      const int row = idx >> 4, c = (idx & 15) * 4;
+      buf[it] = make_float4(0.f, 0.f, 0.f, 0.f);  // rows past the sequence: finite values
+      if (row < nrows) buf[it] = load4<T, kVec>(base + static_cast<size_t>(first_row + row) * token_stride + hoff + c);
     }
-    *reinterpret_cast<float4*>(&Qs[row][c]) = x;
+  };
+  auto store_tile = [&](float(*dst)[kPad], const float4 (&buf)[kPerThread], float mul) {
+#pragma unroll
+    for (int it = 0; it < kPerThread; ++it) {
+      const int idx = it * kThreads + threadIdx.x;
+      const int row = idx >> 4, c = (idx & 15) * 4;
+      *reinterpret_cast<float4*>(&dst[row][c]) =
+          make_float4(buf[it].x * mul, buf[it].y * mul, buf[it].z * mul, buf[it].w * mul);
+    }
+  };
+  {
+    // Q tile and the first block of K and V: one round trip to memory
+    float4 qb[kPerThread], kb[kPerThread], vb[kPerThread];
+    const int nk0 = min(kKB, len);
+    load_tile(q, lo + q0, nq, qb);
+    load_tile(k, lo, nk0, kb);
+    load_tile(v, lo, nk0, vb);
+    store_tile(Qs, qb, scale);
+    store_tile(Ks, kb, 1.0f);
+    store_tile(Vs, vb, 1.0f);
   }
 
   float o[4][8], m[4], l[4];
@@ -189,19 +213,12 @@ attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
   }
 
   auto load_keys = [&](int k0, int nk) {
-    for (int idx = threadIdx.x; idx < kKB * (kD / 4); idx += kThreads) {
-      const int row = idx >> 4, c = (idx & 15) * 4;
-      float4 kx = make_float4(0.f, 0.f, 0.f, 0.f), vx = kx;  // rows past the sequence: finite values
-      if (row < nk) {
-        const size_t off = static_cast<size_t>(lo + k0 + row) * token_stride + hoff + c;
-        kx = load4<T, kVec>(k + off);
-        vx = load4<T, kVec>(v + off);
-      }
-      *reinterpret_cast<float4*>(&Ks[row][c]) = kx;
-      *reinterpret_cast<float4*>(&Vs[row][c]) = vx;
-    }
+    float4 kb[kPerThread], vb[kPerThread];
+    load_tile(k, lo + k0, nk, kb);
+    load_tile(v, lo + k0, nk, vb);
+    store_tile(Ks, kb, 1.0f);
+    store_tile(Vs, vb, 1.0f);
   };
-  load_keys(0, min(kKB, len));  // together with the Q tile: one round trip to memory
 
   for (int k0 = 0; k0 < len; k0 += kKB) {
     const int nk = min(kKB, len - k0);
