@@ -241,6 +241,12 @@ def _attention_case(dtype, lens, heads, use_simt, layout):
         q, k, v = qkv[:, :h], qkv[:, h:2 * h], qkv[:, 2 * h:]
         qp, kp, vp = qkv.data_ptr(), qkv.data_ptr() + h * qkv.element_size(), qkv.data_ptr() + 2 * h * qkv.element_size()
         tstride, hstride = 3 * h, d
+    elif layout == "unaligned":  # rows of 3H + 1 elements starting one element into the buffer
+        wide = dev(rng.randn(cap, 3 * h + 1).astype(np.float32), dtype)
+        es = wide.element_size()
+        q, k, v = wide[:, 1:h + 1], wide[:, h + 1:2 * h + 1], wide[:, 2 * h + 1:]
+        qp, kp, vp = wide.data_ptr() + es, wide.data_ptr() + (h + 1) * es, wide.data_ptr() + (2 * h + 1) * es
+        tstride, hstride = 3 * h + 1, d
     else:                      # head-major [3, heads, cap, d] as et_add_qkv_bias_transpose writes it
         buf = dev(rng.randn(3, heads, cap, d).astype(np.float32), dtype)
         q, k, v = [buf[i].permute(1, 0, 2).reshape(cap, h) for i in range(3)]
@@ -274,6 +280,13 @@ def test_attention_tensor_core(lens, layout):
 @pytest.mark.parametrize("lens", LEN_CASES)
 def test_attention_simt(dtype, lens):
     _attention_case(dtype, lens, 3, use_simt=True, layout="qkv")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_attention_simt_rows_off_the_vector_boundary(dtype):
+    """Row segments that do not start on a 16-byte (fp32) / 8-byte (fp16) boundary take the
+    element-wise loads of the CUDA-core kernel."""
+    _attention_case(dtype, [20, 23, 70, 8, 1], 3, use_simt=True, layout="unaligned")
 
 
 def _attention_tiles_case(lens, heads, layout, seed=0):
