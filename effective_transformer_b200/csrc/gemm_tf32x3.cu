@@ -136,6 +136,53 @@ __device__ __forceinline__ void store_chunk(float* stage, const float* vals, flo
   __syncwarp();  // the buffer is reused by the next chunk
 }
 
+// The same for 32 rows x 16 columns (2 KB of staging): a store instruction covers
+// 8 rows x 64 bytes.
+template <int EPI>
+__device__ __forceinline__ void store_chunk16(float* stage, const float* vals, float* __restrict__ C,
+                                              float* __restrict__ c_lo, const float* __restrict__ bias, int N,
+                                              int row0, int col, int M, int lane) {
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    float f[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) f[e] = vals[g * 4 + e];
+    if (EPI != kEpiNone) {
+      float fb[4];
+      VecTraits<float>::unpack(ld_global_v4(bias + col + g * 4), fb);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) f[e] += fb[e];
+    }
+    if (EPI == kEpiBiasGelu) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) f[e] = gelu_tanh(f[e]);
+    } else if (EPI == kEpiBiasTanh) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) f[e] = tanhf(f[e]);
+    }
+    *reinterpret_cast<float4*>(stage + lane * 16 + ((g ^ ((lane >> 1) & 3)) << 2)) = make_float4(f[0], f[1], f[2], f[3]);
+  }
+  __syncwarp();
+  const int g = lane & 3;
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const int r = t * 8 + (lane >> 2);
+    const float4 v = *reinterpret_cast<const float4*>(stage + r * 16 + ((g ^ ((r >> 1) & 3)) << 2));
+    const int row = row0 + r;
+    if (row < M) {
+      const size_t off = static_cast<size_t>(row) * N + col + g * 4;
+      if (c_lo == nullptr) {
+        *reinterpret_cast<float4*>(C + off) = v;
+      } else {
+        const float4 hi = make_float4(rn_tf32(v.x), rn_tf32(v.y), rn_tf32(v.z), rn_tf32(v.w));
+        *reinterpret_cast<float4*>(C + off) = hi;
+        *reinterpret_cast<float4*>(c_lo + off) = make_float4(v.x - hi.x, v.y - hi.y, v.z - hi.z, v.w - hi.w);
+      }
+    }
+  }
+  __syncwarp();  // the buffer is reused by the next chunk
+}
+
 // hi = rn_tf32(x), lo = x - hi, four elements per thread and iteration.  hi or lo
 // may be the same array as x (each element is read, then written, by one thread).
 __global__ void __launch_bounds__(256)
@@ -409,6 +456,14 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __grid_c
 constexpr int BM2 = 2 * BM;
 constexpr int BN2 = 256;
 constexpr int kPairBlocks = 2;
+// Sixteen epilogue warps (four per TMEM lane quadrant, a quarter of the columns each): with
+// eight, a thread holds 128 running sums and the bias / GELU / split / store phase of a tile,
+// squeezed into the remaining registers with two warps per scheduler, took about 27 k cycles
+// per tile of the GELU projection, more than the two accumulation units (18 k cycles) the
+// issuer can run ahead.
+constexpr int kPairEpilogueWarps = 16;
+constexpr int kPairThreads = 64 + kPairEpilogueWarps * 32;
+constexpr int kPairStagingFloatsPerWarp = 32 * 16;  // 32 rows x 16 columns
 struct PairCfg {
   static constexpr int kStages = 3;
   static constexpr int kABytes = BM * BK * 4;          // this CTA's 128 rows of A_hi (and of A_lo)
@@ -416,7 +471,7 @@ struct PairCfg {
   static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;
   static constexpr int kNumBars = 2 * kStages + 2 * kPairBlocks + 1;
   static constexpr int kBarrierBytes = 256;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + kStagingBytes;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + kPairEpilogueWarps * kPairStagingFloatsPerWarp * 4;
   static constexpr int kTmemCols = kPairBlocks * BN2;
 };
 
@@ -431,7 +486,7 @@ __device__ __forceinline__ void umma_tf32_ss_pair(uint32_t tmem_d, uint64_t ades
 }
 
 template <int EPI>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __grid_constant__ CUtensorMap tmap_a_lo,
                         const __grid_constant__ CUtensorMap tmap_w_hi, const __grid_constant__ CUtensorMap tmap_w_lo,
                         const __grid_constant__ CUtensorMap tmap_w_hi_half,
@@ -472,7 +527,7 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __g
     }
     for (int a = 0; a < kPairBlocks; ++a) {
       mbar_init(tmem_full_bar(a), 1);
-      mbar_init(tmem_empty_bar(a), 2 * kEpilogueWarps);
+      mbar_init(tmem_empty_bar(a), 2 * kPairEpilogueWarps);
     }
     mbar_init(drain_bar, 1);
     *abort_flag = 0;
@@ -613,20 +668,20 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __g
   } else {
     // ------------------------- epilogue (both CTAs) -------------------------
     // warp w reads TMEM lanes [32*(w%4), +32) (one output row per thread) and one
-    // half of the unit's columns (128, or 64 in a half-width unit), kept as
+    // quarter of the unit's columns (64, or 32 in a half-width unit), kept as
     // running fp32 sums in registers.
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;
-    constexpr int kCols = BN2 / 2;
+    const int part = (warp - 2) >> 2;
+    constexpr int kCols = BN2 / 4;
     float* stage = reinterpret_cast<float*>(smem_raw + S * cfg::kStageBytes + cfg::kBarrierBytes) +
-                   (warp - 2) * kStagingFloatsPerWarp;
+                   (warp - 2) * kPairStagingFloatsPerWarp;
     uint32_t unit = 0;
     bool ok = true;
     for (int u = pair_id; u < num_units && ok; u += num_pairs) {
       const PairUnit pu = pair_unit(u, full_tiles, n_tiles, m_tiles, reverse_m);
-      const int wcols = pu.ncols / 2;        // this warp's columns
-      const int chunks = wcols / 32;
-      const int col0 = pu.col0 + half * wcols;
+      const int wcols = pu.ncols / 4;        // this warp's columns
+      const int chunks = wcols / 16;
+      const int col0 = pu.col0 + part * wcols;
       float sum[kCols];
 #pragma unroll
       for (int e = 0; e < kCols; ++e) sum[e] = 0.f;
@@ -640,17 +695,16 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __g
           break;
         }
         tc_fence_after();
-        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + blk * BN2 + half * wcols;
+        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + blk * BN2 + part * wcols;
 #pragma unroll
-        for (int ch = 0; ch < kCols / 32; ++ch) {
+        for (int ch = 0; ch < kCols / 16; ++ch)
           if (ch < chunks) {
-            uint32_t r[32];
-            tmem_ld_32x32b_x32(t_row + ch * 32, r);
+            uint32_t r[16];
+            tmem_ld_32x32b_x16(t_row + ch * 16, r);
             tmem_ld_wait();
 #pragma unroll
-            for (int e = 0; e < 32; ++e) sum[ch * 32 + e] += __uint_as_float(r[e]);
+            for (int e = 0; e < 16; ++e) sum[ch * 16 + e] += __uint_as_float(r[e]);
           }
-        }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(mapa_shared(tmem_empty_bar(blk), 0));  // the block goes back to the issuer
@@ -658,8 +712,8 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __g
       if (!ok) break;
       const int row0 = pu.m_tile * BM2 + static_cast<int>(rank) * BM + quad * 32;
 #pragma unroll
-      for (int ch = 0; ch < kCols / 32; ++ch)
-        if (ch < chunks) store_chunk<EPI>(stage, sum + ch * 32, C, c_lo, bias, N, row0, col0 + ch * 32, M, lane);
+      for (int ch = 0; ch < kCols / 16; ++ch)
+        if (ch < chunks) store_chunk16<EPI>(stage, sum + ch * 16, C, c_lo, bias, N, row0, col0 + ch * 16, M, lane);
     }
   }
 
@@ -721,7 +775,7 @@ cudaError_t launch_pair_epi(const CUtensorMap& tah, const CUtensorMap& tal, cons
   long long pairs = sm_count() / 2;
   if (pairs > max_tiles) pairs = max_tiles;
   if (pairs < 1) pairs = 1;
-  return launch_pdl(gemm_tf32x3_pair_kernel<EPI>, dim3(static_cast<int>(2 * pairs)), dim3(kNumThreads),
+  return launch_pdl(gemm_tf32x3_pair_kernel<EPI>, dim3(static_cast<int>(2 * pairs)), dim3(kPairThreads),
                     PairCfg::kSmemBytes, stream, tah, tal, twh, twl, twhh, twlh, c, c_lo, bias, m_ptr, max_m, n, k,
                     status_word, reverse_m);
 }
