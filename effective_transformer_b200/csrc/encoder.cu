@@ -152,7 +152,9 @@ struct et_handle_s {
   static constexpr int kMaxChunks = 8;
   cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;
   cudaEvent_t in_done[kMaxChunks] = {}, comp_done[kMaxChunks] = {};
-  int host_chunks = 3;  // shares 1:2:1 (measured best on cfg2; ETB_HOST_CHUNKS overrides)
+  int host_chunks = 3;     // measured best on cfg2 (ETB_HOST_CHUNKS overrides)
+  int host_mid_share = 6;  // share of a middle chunk when the first and the last have 1: 1:6:1
+                           // (measured on cfg2: 2 -> 9.0 ms, 6 -> 8.8 ms, 8 -> 9.0 ms; ETB_HOST_MID_SHARE)
   int* host_pinned = nullptr;  // [2 + kMaxChunks]: valid_word_num, status, per-chunk token counts
   // one captured forward pass (et_graph_capture*): replayed by et_graph_launch
   cudaGraph_t graph = nullptr;
@@ -640,17 +642,18 @@ int upload_array(et_handle_t h, void** dst, const void* src, size_t count, int o
 }
 
 // Cuts a batch into `chunks` runs of whole sequences.  The first and the last
-// run get half the share of the others: the first upload and the last download
-// are the two copies that nothing overlaps.
-std::vector<std::pair<int, int>> plan_host_chunks(int batch, int chunks) {
+// run get share 1, the others `mid_share`: the first upload and the last
+// download are the two copies that nothing overlaps.
+std::vector<std::pair<int, int>> plan_host_chunks(int batch, int chunks, int mid_share) {
   std::vector<std::pair<int, int>> out;
   if (batch <= 0) return out;
   if (chunks > batch) chunks = batch;
   if (chunks < 1) chunks = 1;
-  const int units = chunks <= 2 ? chunks : 2 * (chunks - 1);
+  if (mid_share < 1) mid_share = 1;
+  const int units = chunks <= 2 ? chunks : 2 + mid_share * (chunks - 2);
   int b0 = 0;
   for (int c = 0; c < chunks; ++c) {
-    const int share = (chunks <= 2 || c == 0 || c == chunks - 1) ? 1 : 2;
+    const int share = (chunks <= 2 || c == 0 || c == chunks - 1) ? 1 : mid_share;
     int nb = static_cast<int>((static_cast<long long>(batch) * share + units - 1) / units);
     if (c == chunks - 1 || b0 + nb > batch) nb = batch - b0;
     if (nb <= 0) break;
@@ -833,6 +836,10 @@ int et_create(const et_config_t* config, et_handle_t* out_handle) {
   if (const char* e = getenv("ETB_HOST_CHUNKS")) {
     const int n = atoi(e);
     if (n >= 1 && n <= et_handle_s::kMaxChunks) h->host_chunks = n;
+  }
+  if (const char* e = getenv("ETB_HOST_MID_SHARE")) {
+    const int n = atoi(e);
+    if (n >= 1 && n <= 16) h->host_mid_share = n;
   }
   if (cudaMallocHost(reinterpret_cast<void**>(&h->host_pinned),
                      (2 + et_handle_s::kMaxChunks) * sizeof(int)) != cudaSuccess)
@@ -1053,7 +1060,7 @@ int et_forward_host(et_handle_t h, const void* from_host, const int* mask_host, 
   const size_t seq_bytes = static_cast<size_t>(seq_len) * h->hidden * h->esize;
   int chunks = h->host_chunks;
   if (static_cast<size_t>(batch_size) * seq_bytes < (8u << 20)) chunks = 1;  // too small to be worth it
-  const std::vector<std::pair<int, int>> plan = plan_host_chunks(batch_size, chunks);
+  const std::vector<std::pair<int, int>> plan = plan_host_chunks(batch_size, chunks, h->host_mid_share);
   const int per = static_cast<int>(plan.size());
   int nchunks = 0;
   et_handle_s::HostGraphs& hg = h->host_graphs;
