@@ -369,7 +369,8 @@ def test_attention_full_size_softmax_rows_sum_to_one():
 @pytest.mark.parametrize("m,cap,n,k", [(1, 1, 128, 64), (60, 60, 128, 128), (134, 256, 768, 768),
                                        (300, 384, 2304, 768), (257, 300, 768, 3072), (128, 128, 256, 32),
                                        (1000, 1000, 3072, 768), (0, 64, 256, 128), (5000, 5000, 1152, 1024),
-                                       (5000, 5000, 1024, 512)])   # 80 pair tiles: the last round is cut in halves
+                                       (5000, 5000, 1024, 512),    # 80 pair tiles: the last round is cut in halves
+                                       (9000, 10000, 768, 3072)])  # pair kernel, long K, M below capacity, 108 tiles
 @pytest.mark.parametrize("epi", [0, 1, 2, 3])
 def test_gemm_fp32_on_tensor_cores_keeps_fp32_accuracy(m, cap, n, k, epi):
     """The three-product tf32 split: same tolerance as the CUDA-core fp32 GEMM against the
