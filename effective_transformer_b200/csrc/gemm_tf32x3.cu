@@ -446,7 +446,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __grid_c
 // 3 x 4 instructions of 128 x 256 x 8 per CTA, half of the L2 -> SM traffic per
 // FLOP of the single-CTA kernel, which is what bounds that kernel.  No load is
 // multicast.  The accumulator of a unit is a 256-column TMEM block in each CTA;
-// the 512 columns hold two blocks, drained by the epilogue warps (128 running
+// the 512 columns hold two blocks, drained by the epilogue warps (64 running
 // sums per thread) while the other block accumulates.  Barriers as in the
 // fp16 pair kernel: full[] and tmem_empty[] live in CTA 0, empty[] and
 // tmem_full[] in both (CTA 0's MMA thread commits to both).  The last round of
