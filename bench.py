@@ -8,10 +8,15 @@ A step is one forward pass of the whole path (input op, all encoder layers,
 output op) over one batch of synthetic input with the shapes and value
 distributions of the reference's benchmark script
 (sample/tensorflow/benchmark.py:38-61): BERT-base, 12 layers, fp16, B=1000
-sequences per GPU, Lmax=64, lengths randint(16, 65).  Metric: valid tokens/s
-over all ranks.  Prints one JSON line (rank 0).
+sequences, Lmax=64, lengths randint(16, 65).  Metric: valid tokens/s over all
+ranks.  Prints one JSON line (rank 0).
 
-  value     inputs resident in HBM, per-step CUDA-event time, max over ranks
+With N > 1 the ONE batch of 1000 sequences is sharded by sequence over the N
+ranks, token-balanced, no collective in the forward pass ("scaling": "strong");
+the figure with 1000 sequences per GPU is reported beside it under "weak".
+
+  value     inputs resident in HBM, per-step CUDA-event time, max over ranks; a step is a replay of
+            the pass recorded as a CUDA graph (--launch eager: one et_forward call per step)
   e2e       the same through et_forward_host with pinned HOST buffers: the
             host->device copy of the batch and the device->host copy of the
             [B,S,H] result are inside the timed region
@@ -19,7 +24,12 @@ over all ranks.  Prints one JSON line (rank 0).
             et_forward_ids_host: embeddings of the valid tokens, the stack and the
             pooler; 12 bytes per position go up, the pooled [B,H] rows come back
   roofline  the tcgen05 GEMM (the dominant kernel): algorithmic FLOPs / CUDA-
-            event time of its launches inside the timed steps
+            event time of its launches in an eager pass over the same steps
+  gather    N > 1: the optional gather of the shard outputs to rank 0 over NVLink
+            (NCCL send/recv into a local buffer, then the batch order restored), timed
+            separately and outside `value`
+  other_workloads  N = 1: short passes over the fp32 workload (cfg3) and BERT-large with
+            skewed lengths (cfg4)
   cpu_baseline  the CPU oracle (fp32 restatement of the reference's padded TF
             graph) timed on a bounded sample of the same batch, N=1 only
 """
@@ -43,12 +53,6 @@ from effective_transformer_b200 import workloads as W  # noqa: E402
 
 METRIC = "valid_tokens_per_sec"
 UNIT = "tokens/s"
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
-# captures summarised in profiles/gemm_tcgen05_cfg2_ncu.md: mean of the FFN1 launch (66.1 + 189.2 MB)
-# and the QKV launch (64.9 + 129.4 MB) of the headline workload.
-NCU_GEMM_TRAFFIC = {"cfg2_base_fp16_b1000_s64": 224.8e6}
-NCU_GEMM_TRAFFIC_NOTE = ("bytes per launch, ncu dram read+write, mean of the captured FFN1 and QKV launches; their "
-                         "algorithmic bytes (A + W + C) are 310.2e6 and 247.9e6 (part of C is still in L2 at kernel end)")
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -62,6 +66,20 @@ def read_peaks():
         except Exception:
             pass
     return dict(FALLBACK_PEAKS), "fallback"
+
+
+def read_traffic(workload: str):
+    """DRAM bytes per launch of the dominant kernel from the committed ncu capture, if one is on
+    record for this workload (profiles/traffic.json; written when the capture is refreshed)."""
+    p = os.path.join(ROOT, "profiles", "traffic.json")
+    try:
+        with open(p) as f:
+            rec = json.load(f).get(workload)
+        if rec:
+            return float(rec["bytes_per_launch"]), rec.get("note")
+    except Exception:
+        pass
+    return None, None
 
 
 class ClockSampler:
@@ -110,16 +128,17 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def measure_fp32_gemm_tflops(dev, n: int = 8192, iters: int = 5) -> float:
-    """FP32 rate of the CUDA cores as cuBLAS reaches it (TF32 disabled): the roofline
-    denominator of the fp32 workloads, whose GEMMs do not use tensor cores."""
+def measure_matmul_tflops(dev, tf32: bool, n: int = 8192, iters: int = 8) -> float:
+    """Rate of the library's fp32 GEMM on this GPU, measured in this run: with tf32=True on the
+    tensor cores (kind tf32), with tf32=False on the CUDA cores (SGEMM)."""
     import torch
     old = torch.backends.cuda.matmul.allow_tf32
-    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_tf32 = tf32
     try:
         a = torch.randn(n, n, device=dev, dtype=torch.float32)
         b = torch.randn(n, n, device=dev, dtype=torch.float32)
-        torch.matmul(a, b)
+        for _ in range(2):
+            torch.matmul(a, b)
         torch.cuda.synchronize()
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0.record()
@@ -137,6 +156,24 @@ def dist_env():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     return rank, world, local
+
+
+def bind_to_gpu_cpus(gpu_index: int):
+    """Best effort: run this rank on the host cores next to its GPU (NVML's CPU affinity), so that
+    the pinned host buffers it allocates are first touched on that NUMA node."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(gpu_index)
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
+        cpus = {i * 64 + b for i, w in enumerate(words) for b in range(64) if (w >> b) & 1}
+        allowed = cpus & set(os.sched_getaffinity(0))
+        if allowed:
+            os.sched_setaffinity(0, allowed)
+            return len(allowed)
+    except Exception:
+        pass
+    return None
 
 
 def cpu_oracle_throughput(spec: W.WorkloadSpec, sample_seqs: int):
@@ -179,10 +216,10 @@ def run_reference(args, spec):
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": spec.name, "note": "CPU port of the reference's padded TF-graph encoder "
                    "(TensorFlow is absent, the reference op cannot be built); each step = the first "
-                   f"{sample} sequences of the batch, all layers"},
+                   f"{sample} sequences of the batch, all layers; tokens/s does not depend on the sample size"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
                          "sample": f"first {sample} of {spec.batch} sequences, {toks} valid tokens, "
                                    f"{spec.shape.num_layers} layers, padded [B,S] fp32"},
@@ -192,6 +229,85 @@ def run_reference(args, spec):
     print(json.dumps(line), flush=True)
 
 
+class DevicePass:
+    """An engine with one batch resident on the device, and the timing of its pass."""
+
+    def __init__(self, et, torch, spec, lengths, x_np, weights, dev, local):
+        self.torch, self.spec = torch, spec
+        sh = spec.shape
+        self.fp16 = spec.dtype == "fp16"
+        self.tdt = torch.float16 if self.fp16 else torch.float32
+        self.lengths = lengths.astype(np.int32)
+        self.tokens = int(self.lengths.sum())
+        self.b, self.s, self.h = len(lengths), spec.max_seq_len, sh.hidden
+        self.mask_np = W.prefix_mask(self.lengths, self.s)
+        self.eng = et.EffectiveTransformer(sh.num_layers, sh.head_num, sh.size_per_head, sh.ffn_dim, max(self.b, 1),
+                                           self.s, dtype=self.tdt, device=local)
+        self.eng.set_weights(weights)
+        if x_np is None:    # N(0,1) input drawn on the device (timing passes over the large workloads)
+            gen = torch.Generator(device=dev).manual_seed(spec.seed)
+            self.x = torch.randn((self.b, self.s, self.h), generator=gen, device=dev, dtype=torch.float32).to(self.tdt)
+        else:
+            self.x = torch.from_numpy(np.ascontiguousarray(x_np)).to(self.tdt).to(dev)
+        self.mask = torch.from_numpy(self.mask_np).to(dev)
+        self.out = torch.empty_like(self.x)
+
+    def gemm_flops(self) -> float:
+        sh = self.spec.shape
+        return 2.0 * self.tokens * self.h * (3 * self.h + self.h + 2 * sh.ffn_dim) * sh.num_layers
+
+    def time(self, steps, warmup, launch, flush, barrier, sampler=None):
+        """Returns (sum of step ms, per-kernel profile of an eager pass over the same steps, clocks)."""
+        torch, eng = self.torch, self.eng
+        for _ in range(warmup):
+            eng.forward(self.x, self.mask, self.out)
+        torch.cuda.synchronize()
+        assert eng.device_status() == 0, "a device-side wait expired during warm-up"
+        graph = launch == "graph"
+        if graph:
+            eng.capture(self.x, self.mask, self.out)
+            for _ in range(2):
+                eng.replay()
+            torch.cuda.synchronize()
+        eng.get_profile(reset=True)
+        eng.set_profiling(not graph)
+        if sampler is not None:
+            sampler.start()
+        starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        barrier()
+        for i in range(steps):
+            flush.zero_()                         # evict the previous step's tensors from L2 (untimed)
+            starts[i].record()
+            if graph:
+                eng.replay()
+            else:
+                eng.forward(self.x, self.mask, self.out)
+            ends[i].record()
+        barrier()
+        clocks = sampler.stop() if sampler is not None else None
+        eng.set_profiling(False)
+        total_ms = sum(a.elapsed_time(e) for a, e in zip(starts, ends))
+        prof = eng.get_profile(reset=True)
+        if graph:
+            # replayed kernels cannot be bracketed by events: per-kernel times from an eager pass of the same steps
+            replayed = {k: v[1] for k, v in prof.items()}
+            eng.set_profiling(True)
+            for i in range(steps):
+                flush.zero_()
+                eng.forward(self.x, self.mask, self.out)
+            torch.cuda.synchronize()
+            eng.set_profiling(False)
+            prof = eng.get_profile(reset=True)
+            assert {k: v[1] for k, v in prof.items()} == replayed
+            eng.release_graph()
+        assert eng.device_status() == 0, "a device-side wait expired during the timed steps"
+        return total_ms, prof, clocks
+
+    def close(self):
+        self.eng.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -199,15 +315,22 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", type=int, default=2, help="index into the five benchmark configurations")
-    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
+    ap.add_argument("--scaling", default="auto", choices=["auto", "weak", "strong"],
+                    help="N > 1: strong = the one batch sharded over the ranks (default), weak = a batch per rank")
+    ap.add_argument("--launch", default="graph", choices=["graph", "eager"],
+                    help="a timed step is a CUDA-graph replay of the pass (et_graph_launch) or one et_forward call")
     ap.add_argument("--cpu-sample", type=int, default=0,
                     help="sequences in the CPU sample; 0 = 512 for the cpu_baseline leg (about 5 s on 16 cores), "
                          "256 per step for --impl reference")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--graph", action="store_true",
-                    help="time CUDA-graph replays of the pass (et_graph_capture); the per-kernel roofline then comes "
-                         "from a second, eager pass of the same steps")
+    ap.add_argument("--no-other", action="store_true", help="skip the cfg3 / cfg4 passes (N = 1)")
+    ap.add_argument("--no-gather", action="store_true", help="skip the output gather and the weak figure (N > 1)")
+    ap.add_argument("--shard-of", type=int, default=0,
+                    help="one GPU only: time rank 0's shard of an N-way split of the batch (what one rank of "
+                         "`--gpus N` runs), to study the small-batch regime without N GPUs")
+    ap.add_argument("--split-layernorm", action="store_true",
+                    help="A/B: a LayerNorm kernel behind each projection instead of the LayerNorm inside the GEMMs")
     args = ap.parse_args()
     spec = W.WORKLOADS[args.workload]
     if args.impl == "reference":
@@ -219,44 +342,38 @@ def main():
     import effective_transformer_b200 as et
 
     rank, world, local = dist_env()
+    cpus_bound = bind_to_gpu_cpus(local) if world > 1 else None
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    # Host-buffer path: chunk shares 1:6:1 are the measured best for one process per host; from
-    # four ranks on, the ranks share PCIe switches and host memory, the middle chunk's upload no
-    # longer hides behind the first chunk's pass, and the wider first chunk (1:2:1) is kept, the
-    # setting the 4- and 8-GPU end-to-end figures were measured with.
-    if world >= 4:
-        os.environ.setdefault("ETB_HOST_MID_SHARE", "2")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    scaling = args.scaling if args.scaling != "auto" else ("strong" if world > 1 else "weak")
 
-    # ---- workload: B sequences per GPU (weak) or B in total (strong) ----------
+    # ---- workload: the one batch sharded over the ranks (strong) or a batch per rank (weak) -------
     base = W.make_workload(spec)                      # canonical draw: lengths, input, weights
-    if world == 1:
+    shards = None
+    if world == 1 and args.shard_of > 1:
+        one, _ = W.balanced_shards(base.lengths, args.shard_of)
+        lengths, x_np = base.lengths[one[0]], base.from_tensor[one[0]]
+    elif world == 1:
         lengths, x_np = base.lengths, base.from_tensor
+    elif scaling == "strong":
+        shards, _ = W.balanced_shards(base.lengths, world)
+        lengths, x_np = base.lengths[shards[rank]], base.from_tensor[shards[rank]]
     else:
-        if args.scaling == "weak":
-            g = np.random.RandomState(spec.seed + 101)
-            all_len = np.concatenate([base.lengths] + [W.draw_lengths(spec, g) for _ in range(world - 1)])
-        else:
-            all_len = base.lengths
-        shards, loads = W.balanced_shards(all_len, world)
-        lengths = all_len[shards[rank]].astype(np.int32)
+        g = np.random.RandomState(spec.seed + 101)
+        all_len = np.concatenate([base.lengths] + [W.draw_lengths(spec, g) for _ in range(world - 1)])
+        wshards, _ = W.balanced_shards(all_len, world)
+        lengths = all_len[wshards[rank]].astype(np.int32)
         x_np = np.random.RandomState(spec.seed + 17 + rank).randn(
             len(lengths), spec.max_seq_len, spec.shape.hidden).astype(np.float32)
-    mask_np = W.prefix_mask(lengths, spec.max_seq_len)
-    tokens_rank = int(lengths.sum())
-    b, s, h = len(lengths), spec.max_seq_len, spec.shape.hidden
-    fp16 = spec.dtype == "fp16"
-    tdt, ndt = (torch.float16, np.float16) if fp16 else (torch.float32, np.float32)
-
     sh = spec.shape
-    eng = et.EffectiveTransformer(sh.num_layers, sh.head_num, sh.size_per_head, sh.ffn_dim, b, s, dtype=tdt,
-                                  device=local)
-    eng.set_weights(base.weights)
-    x = torch.from_numpy(x_np).to(tdt).to(dev)
-    mask = torch.from_numpy(mask_np).to(dev)
-    out = torch.empty_like(x)
+    fp16 = spec.dtype == "fp16"
+    main_pass = DevicePass(et, torch, spec, lengths, x_np, base.weights, dev, local)
+    if args.split_layernorm:
+        main_pass.eng.set_fused_layernorm(False)
+    eng, b, s, h = main_pass.eng, main_pass.b, main_pass.s, main_pass.h
+    tokens_rank = main_pass.tokens
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)   # > 126 MB L2
 
     def barrier():
@@ -265,60 +382,22 @@ def main():
         torch.cuda.synchronize()
 
     # ---- device-resident timing ------------------------------------------------
-    for _ in range(args.warmup):
-        eng.forward(x, mask, out)
-    torch.cuda.synchronize()
-    assert eng.device_status() == 0, "a device-side wait expired during warm-up"
-    if args.graph:
-        eng.capture(x, mask, out)
-        for _ in range(2):
-            eng.replay()
-        torch.cuda.synchronize()
-    eng.get_profile(reset=True)
-    eng.set_profiling(not args.graph)
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-    barrier()
-    for i in range(args.steps):
-        flush.zero_()                         # evict the previous step's tensors from L2 (untimed)
-        starts[i].record()
-        if args.graph:
-            eng.replay()
-        else:
-            eng.forward(x, mask, out)
-        ends[i].record()
-    barrier()
-    clocks = sampler.stop() if rank == 0 else None
-    eng.set_profiling(False)
-    step_ms = [a.elapsed_time(e) for a, e in zip(starts, ends)]
-    total_ms = sum(step_ms)
-    prof = eng.get_profile(reset=True)
-    if args.graph:
-        # replayed kernels cannot be bracketed by events: per-kernel times from an eager pass of the same steps
-        launches_replayed = {k: v[1] for k, v in prof.items()}
-        eng.set_profiling(True)
-        for i in range(args.steps):
-            flush.zero_()
-            eng.forward(x, mask, out)
-        torch.cuda.synchronize()
-        eng.set_profiling(False)
-        prof = eng.get_profile(reset=True)
-        assert {k: v[1] for k, v in prof.items()} == launches_replayed
-    assert eng.device_status() == 0, "a device-side wait expired during the timed steps"
+    total_ms, prof, clocks = main_pass.time(args.steps, args.warmup, args.launch, flush, barrier,
+                                            ClockSampler(local) if rank == 0 else None)
 
     # ---- end to end through the host-buffer entry point -----------------------
     e2e_ms = None
-    h2d = b * s * h * x.element_size() + b * s * 4
-    d2h = b * s * h * x.element_size() + 8
+    esz = main_pass.x.element_size()
+    h2d = b * s * h * esz + b * s * 4
+    d2h = b * s * h * esz + 8
+    shares = None
     if not args.no_e2e:
-        x_host = torch.from_numpy(x_np).to(tdt).pin_memory()
-        m_host = torch.from_numpy(mask_np).pin_memory()
+        x_host = torch.from_numpy(np.ascontiguousarray(x_np)).to(main_pass.tdt).pin_memory()
+        m_host = torch.from_numpy(main_pass.mask_np).pin_memory()
         o_host = torch.empty_like(x_host).pin_memory()
         xh, mh, oh = x_host.numpy(), m_host.numpy(), o_host.numpy()
-        for _ in range(2):
+        barrier()
+        for _ in range(3):      # the first call measures copy and compute times, the second records graphs
             eng.forward_host(xh, mh, oh)
         barrier()
         t0 = time.perf_counter()
@@ -327,6 +406,7 @@ def main():
         torch.cuda.synchronize()
         e2e_ms = 1000.0 * (time.perf_counter() - t0)
         barrier()
+        shares = eng.host_chunk_shares()
 
     # ---- the same batch as token ids: embeddings in front, pooler behind ------------
     # (not the headline: ids + mask go up, only the pooled [B,H] rows come back)
@@ -336,7 +416,7 @@ def main():
         eng.set_embeddings(mh_.word_table, mh_.type_table, mh_.position_table, mh_.ln_gamma, mh_.ln_beta)
         eng.set_pooler(mh_.pooler_kernel, mh_.pooler_bias)
         pin = lambda a: torch.from_numpy(a).pin_memory().numpy()
-        ids_h, types_h, mask_h = pin(mh_.input_ids), pin(mh_.token_type_ids), pin(mask_np)
+        ids_h, types_h, mask_h = pin(mh_.input_ids), pin(mh_.token_type_ids), pin(main_pass.mask_np)
         for _ in range(2):
             eng.forward_ids_host(ids_h, mask_h, types_h, sequence_output=False, pooled_output=True)
         barrier()
@@ -346,6 +426,66 @@ def main():
         torch.cuda.synchronize()
         ids_ms = 1000.0 * (time.perf_counter() - t0)
         barrier()
+
+    # ---- N > 1: the optional output gather (timed separately) and the weak figure ----------------
+    gather_info, weak_info = None, None
+    if world > 1 and scaling == "strong" and not args.no_gather:
+        from effective_transformer_b200.sharding import OutputGather
+        eng.forward(main_pass.x, main_pass.mask, main_pass.out)
+        torch.cuda.synchronize()
+        gather = OutputGather(shards, s, h, main_pass.tdt, dev, dst=0)
+        for _ in range(3):
+            full = gather(main_pass.out)
+        g0 = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+        g1 = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+        barrier()
+        for i in range(args.steps):
+            g0[i].record()
+            full = gather(main_pass.out)
+            g1[i].record()
+        barrier()
+        gather_ms = sum(a.elapsed_time(e) for a, e in zip(g0, g1)) / args.steps
+        gm = torch.tensor([gather_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(gm, op=dist.ReduceOp.MAX)
+        # transport check: an exact integer checksum of every rank's block, before and after
+        mine = main_pass.out.view(torch.int16).to(torch.int64).sum().reshape(1)
+        sums = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(sums, mine)
+        # a batch per GPU (the weak-scaling figure); rank 0 runs the unsharded batch itself, which is
+        # also what the gathered tensor is compared with
+        if rank == 0:
+            wl_len, wl_x = base.lengths, base.from_tensor
+        else:
+            rg = np.random.RandomState(spec.seed + 101 + rank)
+            wl_len = W.draw_lengths(spec, rg)
+            wl_x = rg.randn(len(wl_len), spec.max_seq_len, h).astype(np.float32)
+        weak_pass = DevicePass(et, torch, spec, wl_len, wl_x, base.weights, dev, local)
+        w_ms, _, _ = weak_pass.time(args.steps, args.warmup, args.launch, flush, barrier)
+        wstats = torch.tensor([w_ms, float(weak_pass.tokens)], dtype=torch.float64, device=dev)
+        wmx, wsm = wstats.clone(), wstats.clone()
+        dist.all_reduce(wmx, op=dist.ReduceOp.MAX)
+        dist.all_reduce(wsm, op=dist.ReduceOp.SUM)
+        weak_info = {"value": float(wsm[1]) / (float(wmx[0]) / args.steps / 1000.0), "unit": UNIT,
+                     "ms_per_step": float(wmx[0]) / args.steps, "sequences_per_gpu": spec.batch,
+                     "valid_tokens_total": int(wsm[1])}
+        if rank == 0:
+            off = gather.offsets
+            transport_ok = all(
+                int(gather.recv[int(off[r]):int(off[r + 1])].view(torch.int16).to(torch.int64).sum()) == int(sums[r])
+                for r in range(world))
+            y_single = weak_pass.eng.forward(weak_pass.x, weak_pass.mask)
+            torch.cuda.synchronize()
+            valid = torch.from_numpy(base.mask.ravel() > 0).to(dev)
+            d = (full.float() - y_single.float()).abs().reshape(-1, h)[valid]
+            gather_info = {
+                "ms": float(gm[0]), "bytes": gather.bytes_received,
+                "gb_per_s": gather.bytes_received / (float(gm[0]) / 1000.0) / 1e9,
+                "what": "padded [b_r,S,H] outputs of all ranks -> rank 0 (NCCL send/recv into a local buffer), "
+                        "then the batch order restored by a row gather; outside `value`",
+                "transport_bit_exact": bool(transport_ok),
+                "vs_single_gpu_max_abs": float(d.max()), "vs_single_gpu_mean_abs": float(d.mean()),
+                "padding_rows_zero": bool(torch.all(full.reshape(-1, h)[~valid] == 0))}
+        weak_pass.close()
 
     # ---- reduce over ranks -------------------------------------------------------
     stats = torch.tensor([total_ms, e2e_ms or 0.0, float(tokens_rank), ids_ms or 0.0], dtype=torch.float64,
@@ -363,63 +503,76 @@ def main():
         peaks, peak_src = read_peaks()
         ms_per_step = total_ms / args.steps
         value = tokens_all / (ms_per_step / 1000.0)
-        # roofline of the dominant kernel (rank 0's launches)
-        gemm_cats = ["gemm_qkv", "gemm_attn_out", "gemm_ffn1", "gemm_ffn2"]
-        gemm_ms = sum(prof[c][0] for c in gemm_cats)
-        gemm_launches = sum(prof[c][1] for c in gemm_cats)
-        gemm_flops_step = 2.0 * tokens_rank * h * (3 * h + h + 2 * sh.ffn_dim) * sh.num_layers
-        achieved = (gemm_flops_step * args.steps) / (gemm_ms / 1000.0) / 1e12 if gemm_ms > 0 else None
-        if fp16:
-            peak_tf, peak_note = peaks["bf16_tflops_sustained"], peak_src + " bf16_tflops_sustained"
-        else:
-            # the fp32 handle's GEMM takes every fp32 product as three tf32 tensor-core products
-            # (tf32 runs at half the bf16 rate), so its ceiling in fp32 FLOPs is bf16 / 6; the FP32 FMA
-            # rate of the CUDA cores, as cuBLAS SGEMM reaches it, is measured here for comparison
-            peak_tf = peaks["bf16_tflops_sustained"] / 6.0
-            peak_note = peak_src + " bf16_tflops_sustained / 6 (tf32 = bf16 / 2, three products per fp32 product)"
-            sgemm_tf = measure_fp32_gemm_tflops(dev)
-        kernels = {k: {"ms_per_step": v[0] / args.steps, "launches_per_step": v[1] / args.steps}
-                   for k, v in prof.items()}
-        launches = sum(v[1] for v in prof.values())
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": args.scaling, "vs_baseline": None,
+            "scaling": scaling, "vs_baseline": None,
             "dtype": "f16" if fp16 else "f32", "data": "synthetic",
-            "config": {"workload": spec.name, "sequences_per_gpu": b, "max_seq_len": s,
+            "config": {"workload": spec.name, "sequences_rank0": b, "max_seq_len": s,
                        "valid_tokens_rank0": tokens_rank, "valid_tokens_total": int(tokens_all),
-                       "layers": sh.num_layers, "hidden": h, "sharding": "sequences, token-balanced, no collective",
+                       "layers": sh.num_layers, "hidden": h,
+                       "sharding": ("one batch of %d sequences split over %d ranks, token-balanced, no collective "
+                                    "in the forward pass" % (spec.batch, world)) if scaling == "strong" and world > 1
+                                   else "sequences, token-balanced, no collective",
                        "l2": "256 MB buffer written between timed steps (untimed)",
-                       "host_chunk_shares": "1:%s:1" % os.environ.get("ETB_HOST_MID_SHARE", "6"),
+                       "layernorm": "LayerNorm kernels behind the projections" if args.split_layernorm
+                                    else "inside the projection kernels",
                        "launch": ("cuda-graph replay (et_graph_launch); per-kernel times from a second, eager pass"
-                                  if args.graph else "eager (et_forward), per-kernel events inside the timed steps")},
-            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak_tf,
-                         "unit": "TFLOP/s",
-                         "frac": (achieved / peak_tf) if (achieved and peak_tf) else None,
-                         "traffic": NCU_GEMM_TRAFFIC.get(spec.name),
-                         "traffic_note": NCU_GEMM_TRAFFIC_NOTE if spec.name in NCU_GEMM_TRAFFIC else None,
-                         "kernel": "gemm_tcgen05_pair_kernel" if fp16 else "gemm_tf32x3_kernel (+ split_tf32_kernel)",
-                         "algorithmic_flops_per_launch": gemm_flops_step / max(gemm_launches / args.steps, 1),
-                         "launches_per_step": gemm_launches / args.steps,
-                         "avg_launch_ms": gemm_ms / max(gemm_launches, 1),
-                         "peak_source": peak_note},
-            "kernels": kernels,
-            "gpu_launches": launches,
+                                  if args.launch == "graph"
+                                  else "eager (et_forward), per-kernel events inside the timed steps")},
+            "roofline": roofline_of(main_pass, prof, args.steps, peaks, peak_src, dev, spec.name),
+            "kernels": {k: {"ms_per_step": v[0] / args.steps, "launches_per_step": v[1] / args.steps}
+                        for k, v in prof.items()},
+            "gpu_launches": sum(v[1] for v in prof.values()),
             "clocks": clocks,
         }
-        if not fp16:
-            line["roofline"]["cublas_sgemm_tflops_measured_here"] = sgemm_tf
+        if cpus_bound:
+            line["config"]["host_cores_bound_per_rank"] = cpus_bound
+        if args.shard_of > 1:
+            line["config"]["shard_of"] = args.shard_of
         if e2e_ms is not None:
             line["e2e"] = {"value": tokens_all / (e2e_total_ms / args.steps / 1000.0), "unit": UNIT,
                            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                           "ms_per_step": e2e_total_ms / args.steps}
+                           "ms_per_step": e2e_total_ms / args.steps,
+                           "host_chunk_shares": None if shares is None else
+                           {"chunks": shares[0], "shares": "1:%d:1" % shares[1], "measured_by_handle": shares[2]}}
         if ids_ms is not None:
             line["e2e_from_token_ids"] = {
                 "value": tokens_all / (ids_total_ms / args.steps / 1000.0), "unit": UNIT,
                 "ms_per_step": ids_total_ms / args.steps, "h2d_bytes_per_step": 3 * b * s * 4,
-                "d2h_bytes_per_step": b * h * x.element_size() + 8,
+                "d2h_bytes_per_step": b * h * esz + 8,
                 "call": "et_forward_ids_host: ids/types/mask up, embeddings for valid tokens only, "
                         "stack, pooler; pooled [B,H] down"}
+        if gather_info is not None:
+            line["gather"] = gather_info
+        if weak_info is not None:
+            line["weak"] = weak_info
+    main_pass.close()
+
+    # ---- N = 1: the other single-GPU workloads, short passes ---------------------------------------
+    if rank == 0 and world == 1 and not args.no_other and args.workload == 2 and args.shard_of <= 1:
+        del main_pass
+        torch.cuda.empty_cache()
+        other = {}
+        for idx in (3, 4):
+            ospec = W.WORKLOADS[idx]
+            # canonical lengths (same valid-token count and tile packing); weights from the fast float32
+            # generator and the N(0,1) input drawn on the device: same shapes and distributions
+            owl = W.make_workload_fast(ospec, with_input=False)
+            op = DevicePass(et, torch, ospec, owl.lengths, None, owl.weights, dev, local)
+            o_steps = max(3, min(5, args.steps))
+            o_ms, o_prof, _ = op.time(o_steps, 3, args.launch, flush, barrier)
+            other[ospec.name] = {
+                "ms_per_step": o_ms / o_steps, "value": op.tokens / (o_ms / o_steps / 1000.0), "unit": UNIT,
+                "steps": o_steps, "valid_tokens": op.tokens, "dtype": "f16" if ospec.dtype == "fp16" else "f32",
+                "roofline": roofline_of(op, o_prof, o_steps, peaks, peak_src, dev, ospec.name),
+                "kernels_ms_per_step": {k: v[0] / o_steps for k, v in o_prof.items() if v[1]}}
+            op.close()
+            del op, owl
+            torch.cuda.empty_cache()
+        line["other_workloads"] = other
+
+    if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             n_cpu = args.cpu_sample if args.cpu_sample > 0 else min(512, spec.batch)
             tps, dt, toks, threads = cpu_oracle_throughput(spec, n_cpu)
@@ -428,9 +581,37 @@ def main():
                 "sample": f"first {n_cpu} of {spec.batch} sequences ({toks} valid tokens), "
                           f"{sh.num_layers} layers, padded [B,S] fp32 on the host, {dt:.1f} s"}
         print(json.dumps(line), flush=True)
-    eng.close()
     if world > 1:
         dist.destroy_process_group()
+
+
+def roofline_of(p: DevicePass, prof, steps, peaks, peak_src, dev, workload_name):
+    """Roofline of the dominant kernel (the projections' GEMM) from the eager pass's events."""
+    gemm_cats = ["gemm_qkv", "gemm_attn_out", "gemm_ffn1", "gemm_ffn2"]
+    gemm_ms = sum(prof[c][0] for c in gemm_cats)
+    gemm_launches = sum(prof[c][1] for c in gemm_cats)
+    flops_step = p.gemm_flops()
+    achieved = (flops_step * steps) / (gemm_ms / 1000.0) / 1e12 if gemm_ms > 0 else None
+    out = {"bound": "tensor", "achieved": achieved, "unit": "TFLOP/s"}
+    if p.fp16:
+        peak_tf, note = peaks["bf16_tflops_sustained"], peak_src + " bf16_tflops_sustained"
+        traffic, tnote = read_traffic(workload_name)
+        out.update({"traffic": traffic, "traffic_note": tnote,
+                    "kernel": "gemm_tcgen05_pair_kernel (bias / GELU / residual / LayerNorm epilogues)"})
+    else:
+        # every fp32 product is three tf32 tensor-core products, so the ceiling in fp32 FLOPs is the
+        # tf32 rate / 3; the tf32 rate is the library's tf32 GEMM measured in this run on this GPU
+        tf32 = measure_matmul_tflops(dev, tf32=True)
+        peak_tf = tf32 / 3.0
+        note = "tf32 matmul measured in this run (%.0f TFLOP/s) / 3 products per fp32 product" % tf32
+        out.update({"traffic": None, "kernel": "gemm_tf32x3_pair_kernel (+ split_tf32_kernel)",
+                    "tf32_matmul_tflops_measured_here": tf32,
+                    "cublas_sgemm_tflops_measured_here": measure_matmul_tflops(dev, tf32=False, iters=3)})
+    out.update({"peak": peak_tf, "frac": (achieved / peak_tf) if (achieved and peak_tf) else None,
+                "algorithmic_flops_per_launch": flops_step / max(gemm_launches / steps, 1),
+                "launches_per_step": gemm_launches / steps,
+                "avg_launch_ms": gemm_ms / max(gemm_launches, 1), "peak_source": note})
+    return out
 
 
 if __name__ == "__main__":

@@ -102,6 +102,31 @@ class EffectiveTransformer:
     def set_debug_simt(self, on: bool) -> None:
         _capi.check(self._lib.et_set_debug_simt(self._h, 1 if on else 0), self._h)
 
+    def set_fused_layernorm(self, on: bool) -> None:
+        """On (default): bias + residual + LayerNorm run inside the two hidden-wide projection
+        kernels (5 launches per layer); off: a LayerNorm kernel behind each of them (7)."""
+        _capi.check(self._lib.et_set_fused_layernorm(self._h, 1 if on else 0), self._h)
+
+    def workspace_bytes(self, batch_size: int, seq_len: int) -> int:
+        n = C.c_size_t(0)
+        _capi.check(self._lib.et_workspace_bytes(self._h, batch_size, seq_len, C.byref(n)), self._h)
+        return int(n.value)
+
+    def workspace_allocated_bytes(self) -> int:
+        n = C.c_size_t(0)
+        _capi.check(self._lib.et_workspace_allocated_bytes(self._h, C.byref(n)), self._h)
+        return int(n.value)
+
+    def host_chunk_shares(self) -> Tuple[int, int, bool]:
+        """(chunks, share of a middle chunk, whether the share was measured by the handle)."""
+        c, m, f = C.c_int(0), C.c_int(0), C.c_int(0)
+        _capi.check(self._lib.et_host_chunk_shares(self._h, C.byref(c), C.byref(m), C.byref(f)), self._h)
+        return int(c.value), int(m.value), bool(f.value)
+
+    def selftest_wait_timeout(self) -> None:
+        """Launches the failure-detection self-test kernel (a 2 ms bounded wait that runs out)."""
+        _capi.check(self._lib.et_selftest_wait_timeout(self._h, _stream()), self._h)
+
     def set_general_mask(self, on: bool) -> None:
         """When on, effective_transformer() reads its attention_mask [B,S,S] (dtype of
         the handle, 1 = attend) through the general-mask attention kernel; when off

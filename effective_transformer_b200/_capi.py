@@ -84,6 +84,11 @@ SIGNATURES = {
     "et_get_profile": (i32, [vp, C.POINTER(C.c_double), C.POINTER(C.c_longlong), i32]),
     "et_copy_to_host": (i32, [vp, vp, C.c_size_t, vp]),
     "et_set_debug_simt": (i32, [vp, i32]),
+    "et_set_fused_layernorm": (i32, [vp, i32]),
+    "et_host_chunk_shares": (i32, [vp, ip, ip, ip]),
+    "et_selftest_wait_timeout": (i32, [vp, vp]),
+    "et_workspace_allocated_bytes": (i32, [vp, C.POINTER(C.c_size_t)]),
+    "et_gemm_fused": (i32, [vp, vp, vp, vp, vp, vp, C.c_float, vp, vp, vp, i32, i32, i32, i32, vp, vp]),
     "et_padding_offsets": (i32, [vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp]),
     "et_padding_offsets_noalloc": (i32, [vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp]),
     "et_remove_padding": (i32, [i32, vp, vp, vp, vp, vp, i32, i32, i32, vp]),

@@ -468,16 +468,16 @@ cudaError_t launch_attention_simt(const T* q, const T* k, const T* v, long long 
   if (d != kD) return cudaErrorInvalidValue;
   const float scale = 1.0f / sqrtf(static_cast<float>(d));
   if (max_seq <= 0) return cudaSuccess;
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(attention_simt_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  static PerDeviceOnce once;  // function attributes are per device
+  const cudaError_t once_err = once.run([] {
+    cudaError_t attr_err = cudaFuncSetAttribute(attention_simt_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     kSimtSmemBytes);
     if (attr_err == cudaSuccess)
       attr_err = cudaFuncSetAttribute(attention_simt_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       kSimtSmemBytes);
+    return attr_err;
   });
-  if (attr_err != cudaSuccess) return attr_err;
+  if (once_err != cudaSuccess) return once_err;
   // four elements per access when every row segment starts on such a boundary
   const uintptr_t mask = 4 * sizeof(T) - 1;
   const bool vec = ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |

@@ -350,7 +350,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 cudaError_t launch_attention_tc(const __half* q, const __half* k, const __half* v,
                                 long long token_stride, long long head_stride, __half* ctx,
                                 const int* cu_seqlens, int batch, int max_seq, int max_tokens, int heads,
-                                int d, int* status_word, cudaStream_t stream) {
+                                int d, int* status_word, cudaStream_t stream, TensorMapCache* maps) {
   if (batch <= 0 || heads <= 0 || max_tokens <= 0) return cudaSuccess;
   if (d != kD || token_stride < kD || (token_stride % 8) != 0 || (head_stride % 8) != 0 || head_stride < 0)
     return cudaErrorInvalidValue;
@@ -372,17 +372,17 @@ cudaError_t launch_attention_tc(const __half* q, const __half* k, const __half* 
     return cudaErrorInvalidValue;
   }
   CUtensorMap tq, tk, tv;
-  if (!encode_2d_fp16_sw128(&tq, q, rows, cols, static_cast<uint64_t>(token_stride), kBoxRows, kD) ||
-      !encode_2d_fp16_sw128(&tk, k, rows, cols, static_cast<uint64_t>(token_stride), kBoxRows, kD) ||
-      !encode_2d_fp16_sw128(&tv, v, rows, cols, static_cast<uint64_t>(token_stride), kBoxRows, kD))
+  if (!encode_2d_fp16_sw128(&tq, q, rows, cols, static_cast<uint64_t>(token_stride), kBoxRows, kD, maps) ||
+      !encode_2d_fp16_sw128(&tk, k, rows, cols, static_cast<uint64_t>(token_stride), kBoxRows, kD, maps) ||
+      !encode_2d_fp16_sw128(&tv, v, rows, cols, static_cast<uint64_t>(token_stride), kBoxRows, kD, maps))
     return cudaErrorInvalidValue;
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  static PerDeviceOnce once;  // function attributes are per device
+  const cudaError_t once_err = once.run([] {
+    cudaError_t attr_err = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     kSmemBytes);
+    return attr_err;
   });
-  if (attr_err != cudaSuccess) return attr_err;
+  if (once_err != cudaSuccess) return once_err;
   const float scale_log2e = (1.0f / sqrtf(static_cast<float>(d))) * 1.4426950408889634f;
   const long long total = static_cast<long long>(batch) * heads;
   long long grid = static_cast<long long>(sm_count()) * kCtasPerSm;

@@ -486,7 +486,7 @@ cudaError_t launch_attention_plan(const int* cu_seqlens, int batch, int max_toke
 cudaError_t launch_attention_tcgen05(const __half* q, const __half* k, const __half* v,
                                      long long token_stride, long long head_stride, __half* ctx,
                                      const int* plan, int batch, int max_tokens, int heads, int d,
-                                     int* status_word, cudaStream_t stream, bool reverse) {
+                                     int* status_word, cudaStream_t stream, bool reverse, TensorMapCache* maps) {
   if (batch <= 0 || heads <= 0 || max_tokens <= 0) return cudaSuccess;
   if (d != kD || token_stride < kD || (token_stride % 8) != 0 || (head_stride % 8) != 0 || head_stride < 0)
     return cudaErrorInvalidValue;
@@ -507,17 +507,17 @@ cudaError_t launch_attention_tcgen05(const __half* q, const __half* k, const __h
     return cudaErrorInvalidValue;
   }
   CUtensorMap tq, tk, tv;
-  if (!encode_2d_fp16_sw128(&tq, q, rows, cols, static_cast<uint64_t>(token_stride), kBoxRows, kD) ||
-      !encode_2d_fp16_sw128(&tk, k, rows, cols, static_cast<uint64_t>(token_stride), kBoxRows, kD) ||
-      !encode_2d_fp16_sw128(&tv, v, rows, cols, static_cast<uint64_t>(token_stride), kBoxRows, kD))
+  if (!encode_2d_fp16_sw128(&tq, q, rows, cols, static_cast<uint64_t>(token_stride), kBoxRows, kD, maps) ||
+      !encode_2d_fp16_sw128(&tk, k, rows, cols, static_cast<uint64_t>(token_stride), kBoxRows, kD, maps) ||
+      !encode_2d_fp16_sw128(&tv, v, rows, cols, static_cast<uint64_t>(token_stride), kBoxRows, kD, maps))
     return cudaErrorInvalidValue;
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  static PerDeviceOnce once;  // function attributes are per device
+  const cudaError_t once_err = once.run([] {
+    cudaError_t attr_err = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     kSmemBytes);
+    return attr_err;
   });
-  if (attr_err != cudaSuccess) return attr_err;
+  if (once_err != cudaSuccess) return once_err;
   const float scale_log2e = (1.0f / sqrtf(static_cast<float>(d))) * 1.4426950408889634f;
   // every tile holds at least one sequence, so batch * heads bounds the item count
   long long grid = static_cast<long long>(sm_count()) * kCtasPerSm;

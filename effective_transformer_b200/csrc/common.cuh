@@ -5,11 +5,15 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
 #include <cstdlib>
+#include <mutex>
 #include <string>
 #include <utility>
 
 namespace etb {
+
+class TensorMapCache;  // ptx_sm100.cuh: tensor maps a handle keeps between launches
 
 // Text returned by et_last_error(NULL): errors of calls that take no handle.
 void set_global_error(const std::string& msg);
@@ -17,18 +21,50 @@ void set_global_error(const std::string& msg);
 // ---- launch geometry ------------------------------------------------------
 constexpr int kNumSMsB200 = 148;
 
-inline int sm_count() {
-  static int cached = 0;
-  if (cached == 0) {
-    int dev = 0, n = 0;
-    if (cudaGetDevice(&dev) == cudaSuccess &&
-        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
-      cached = n;
-    else
-      cached = kNumSMsB200;
-  }
-  return cached;
+constexpr int kMaxDevices = 64;
+
+// Index of the current device, or -1.
+inline int current_device() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -1;
+  return dev;
 }
+
+// SM count of the current device (cached per device: a process may hold handles on several GPUs).
+inline int sm_count() {
+  static std::atomic<int> cached[kMaxDevices] = {};
+  const int dev = current_device();
+  if (dev < 0) return kNumSMsB200;
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (n == 0) {
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = kNumSMsB200;
+    cached[dev].store(n, std::memory_order_relaxed);
+  }
+  return n;
+}
+
+// One-time set-up per device.  A kernel's function attributes (the opt-in to more than 48 KB of
+// dynamic shared memory) belong to the device that was current when they were set, so a launcher
+// that serves handles on several GPUs of one process has to set them once on each.
+class PerDeviceOnce {
+ public:
+  template <typename F>
+  cudaError_t run(F&& setup) {
+    const int dev = current_device();
+    if (dev < 0) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(mutex_);
+    if (!done_[dev]) {
+      err_[dev] = setup();
+      done_[dev] = true;
+    }
+    return err_[dev];
+  }
+
+ private:
+  std::mutex mutex_;
+  bool done_[kMaxDevices] = {};
+  cudaError_t err_[kMaxDevices] = {};
+};
 
 // ---- programmatic dependent launch ---------------------------------------
 // Consecutive kernels of a pass are launched with the programmatic-stream-
@@ -72,7 +108,7 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
 
 // ---- device status word ---------------------------------------------------
 // A kernel whose bounded wait expires records (kernel id << 8 | site) once.
-enum KernelId : int { kKernelGemmTc = 1, kKernelAttnTc = 2 };
+enum KernelId : int { kKernelGemmTc = 1, kKernelAttnTc = 2, kKernelSelfTest = 15 };
 
 __device__ __forceinline__ void report_timeout(int* status_word, int kernel_id, int site) {
   if (status_word != nullptr) atomicCAS(status_word, 0, (kernel_id << 8) | site);
@@ -95,6 +131,15 @@ __device__ __forceinline__ Vec16 ld_global_nc_v4(const void* p) {
   asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                : "l"(p));
+  return v;
+}
+// Through L2 only: for rows that other CTAs of the same kernel have just written.
+__device__ __forceinline__ Vec16 ld_global_cg_v4(const void* p) {
+  Vec16 v;
+  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
   return v;
 }
 __device__ __forceinline__ Vec16 ld_global_v4(const void* p) {
@@ -235,7 +280,27 @@ cudaError_t launch_copy_columns(const T* src, T* dst, int rows, int cols, int ds
 // kEpiBiasTanh is the pooler's activation (sample/tensorflow/modeling.py:224-232).
 // kEpiBiasResidual adds a [M,N] tensor (the layer's residual input) besides the bias, so that
 // the LayerNorm behind the projection reads one tensor instead of two.
-enum Epilogue : int { kEpiNone = 0, kEpiBias = 1, kEpiBiasGelu = 2, kEpiBiasTanh = 3, kEpiBiasResidual = 4 };
+// kEpiResidualLayerNorm / kEpiLayerNorm (tcgen05 GEMM with N a multiple of 256 up to 1024 only): the
+// bias + residual + LayerNorm behind the projection (cuda/cuda_kernels.cu:157-236) runs inside the
+// GEMM kernel.  The row block of C whose last column tile has just been stored is normalised in
+// place by warps of the same kernel while the rows are still in L2, so no LayerNorm kernel is
+// launched and the pre-LayerNorm tensor is never read back from HBM.  kEpiResidualLayerNorm adds
+// bias and residual in the GEMM epilogue (as kEpiBiasResidual); kEpiLayerNorm leaves the epilogue
+// bare and adds them when the rows are normalised.
+enum Epilogue : int {
+  kEpiNone = 0, kEpiBias = 1, kEpiBiasGelu = 2, kEpiBiasTanh = 3, kEpiBiasResidual = 4,
+  kEpiResidualLayerNorm = 5, kEpiLayerNorm = 6
+};
+
+// LayerNorm parameters of the two fused epilogues.  `counters`: one int per 32 rows of the 256-row
+// tiles that cover C (8 * ceil(max_m / 256) of them), zero before the launch; the kernel leaves
+// them zero again.
+struct GemmLayerNorm {
+  const __half* gamma = nullptr;
+  const __half* beta = nullptr;
+  float eps = 1e-6f;
+  int* counters = nullptr;
+};
 
 // CUDA-core GEMM: C[M,N] = epi(A[M,K] * W[K,N]); W row-major [K,N].
 template <typename T>
@@ -261,7 +326,7 @@ cudaError_t launch_attention_masked_simt(const T* q, const T* k, const T* v, lon
 cudaError_t launch_attention_tc(const __half* q, const __half* k, const __half* v,
                                 long long token_stride, long long head_stride, __half* ctx,
                                 const int* cu_seqlens, int batch, int max_seq, int max_tokens, int heads,
-                                int d, int* status_word, cudaStream_t stream);
+                                int d, int* status_word, cudaStream_t stream, TensorMapCache* maps = nullptr);
 // tcgen05 attention for sequences of at most 128 tokens: a plan (sequences
 // packed into 128-row tiles) made once per batch, then one launch per layer.
 size_t attention_plan_ints(int batch, int max_tokens);
@@ -270,7 +335,8 @@ cudaError_t launch_attention_plan(const int* cu_seqlens, int batch, int max_toke
 cudaError_t launch_attention_tcgen05(const __half* q, const __half* k, const __half* v,
                                      long long token_stride, long long head_stride, __half* ctx,
                                      const int* plan, int batch, int max_tokens, int heads, int d,
-                                     int* status_word, cudaStream_t stream, bool reverse = false);
+                                     int* status_word, cudaStream_t stream, bool reverse = false,
+                                     TensorMapCache* maps = nullptr);
 // fp32 GEMM on the tensor cores by the three-product tf32 split (gemm_tf32x3.cu):
 // x = hi + lo with hi = rn_tf32(x); hi/lo may alias x.  rows_ptr null = max_rows.
 cudaError_t launch_split_tf32(const float* x, float* hi, float* lo, const int* rows_ptr, int max_rows, int cols,
@@ -280,7 +346,7 @@ cudaError_t launch_split_tf32(const float* x, float* hi, float* lo, const int* r
 cudaError_t launch_gemm_tf32x3(const float* a_hi, const float* a_lo, const float* w_hi, const float* w_lo,
                                const float* bias, float* c, const int* m_ptr, int max_m, int n, int k,
                                int epilogue, int* status_word, cudaStream_t stream, bool reverse_m = false,
-                               float* c_lo = nullptr);
+                               float* c_lo = nullptr, TensorMapCache* maps = nullptr);
 // tcgen05 GEMM, fp16 in / fp32 accumulate / fp16 out.  w_packed is [N,K].
 // reverse_m: row tiles are visited from the last to the first.  A kernel that
 // consumes what the previous kernel has just written finds the rows written
@@ -289,8 +355,14 @@ cudaError_t launch_gemm_tf32x3(const float* a_hi, const float* a_lo, const float
 cudaError_t launch_gemm_tcgen05(const __half* a, const __half* w_packed, const __half* bias,
                                 __half* c, const int* m_ptr, int max_m, int n, int k, int epilogue,
                                 int* status_word, cudaStream_t stream, bool reverse_m = false,
-                                const __half* residual = nullptr);
+                                const __half* residual = nullptr, TensorMapCache* maps = nullptr,
+                                const GemmLayerNorm* ln = nullptr);
+// Whether the fused LayerNorm epilogues can serve a projection of n output columns.
+inline bool gemm_layernorm_supported(int n) { return n > 0 && n % 256 == 0 && n <= 1024; }
 
+
+// One CTA whose bounded wait (2 ms) runs out on purpose; it records (kKernelSelfTest << 8 | 1).
+cudaError_t launch_selftest_wait_timeout(int* status_word, cudaStream_t stream);
 
 // ---- work units of the CTA-pair GEMMs ---------------------------------------
 // Tiles of 256 x 256 are dealt round-robin to the pairs.  When the last round

@@ -16,6 +16,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "ptx_sm100.cuh"
 
 using namespace etb;
 
@@ -95,10 +96,45 @@ struct Workspace {
   float* a_hi = nullptr;      // fp32 handles: [cap, H] tf32 halves of a projection's input
   float* a_lo = nullptr;
   float* ffn_lo = nullptr;    // fp32 handles: [cap, F] remainder of the GELU output (its tf32 half is in ffn)
+  int* ln_counters = nullptr; // [cap / 32] column counts of the GEMMs that normalise their own output rows
   int* valid_word_num = nullptr;
   int* status = nullptr;
   std::vector<void*> allocations;
 };
+
+// Every workspace buffer with its size for a (batch, seq) capacity: et_create allocates from this
+// list and et_workspace_bytes adds it up, so the two cannot drift apart.
+struct WsItem {
+  void** slot;
+  size_t bytes;
+};
+// Row counters of the GEMMs that normalise their own output: one per 32 rows of the 256-row tiles
+// that cover `rows` rows.
+inline size_t ln_counter_ints(size_t rows) { return round_up(rows, 256) / 32 + 8; }
+inline size_t ws_round(size_t bytes) { return round_up(bytes == 0 ? 16 : bytes, 256); }
+
+std::vector<WsItem> workspace_items(const et_config_t& c, size_t batch, size_t seq, Workspace& ws) {
+  const size_t H = static_cast<size_t>(c.head_num) * c.size_per_head, f = c.ffn_dim;
+  const size_t e = c.dtype == ET_FP16 ? 2 : 4;
+  const size_t bs = batch * seq, cap = round_up(bs, 128), bpad = round_up(batch, 128);
+  const bool f32 = c.dtype == ET_FP32;
+  auto I = [](int** p) { return reinterpret_cast<void**>(p); };
+  auto F = [](float** p) { return reinterpret_cast<void**>(p); };
+  return {
+      {&ws.x, cap * H * e}, {&ws.qkv, cap * 3 * H * e}, {&ws.ctx, cap * H * e}, {&ws.att, cap * H * e},
+      {&ws.ffn, cap * f * e}, {&ws.stage_in, bs * H * e}, {&ws.stage_out, bs * H * e},
+      {I(&ws.stage_mask), bs * 4}, {I(&ws.stage_ids), bs * 4}, {I(&ws.stage_types), bs * 4},
+      {&ws.first_tok, bpad * H * e}, {&ws.pooled, bpad * H * e}, {I(&ws.pool_m), 4},
+      {I(&ws.batch_idx), cap * 4}, {I(&ws.word_idx), cap * 4}, {I(&ws.padding_offset), cap * 4},
+      {I(&ws.prefix_sum), cap * 4}, {I(&ws.seq_len), batch * 4}, {I(&ws.cu_seqlens), (batch + 1) * 4},
+      {I(&ws.lens_scratch), batch * 4},
+      {I(&ws.attn_plan), attention_plan_ints(static_cast<int>(batch), static_cast<int>(cap)) * 4},
+      {I(&ws.pos_row), cap * 4},
+      {F(&ws.a_hi), f32 ? cap * H * 4 : 0}, {F(&ws.a_lo), f32 ? cap * H * 4 : 0},
+      {F(&ws.ffn_lo), f32 ? cap * f * 4 : 0},
+      {I(&ws.ln_counters), ln_counter_ints(bs) * 4},
+      {I(&ws.valid_word_num), 4}, {I(&ws.status), 4}};
+}
 
 }  // namespace
 
@@ -137,9 +173,11 @@ struct et_handle_s {
   // Row order of consecutive kernels alternates ("snake"): a kernel that starts
   // with the rows its producer wrote last finds them in L2.  prev_ascending =
   // the previous kernel of the chain wrote its rows first-to-last.
-  bool snake = true;          // ETB_SNAKE=0 switches it off (A/B measurements)
-  bool fuse_residual = true;  // ETB_FUSE_RESIDUAL=0: bias + residual added by the LayerNorm kernel instead
   bool prev_ascending = true;
+  // fp16 tensor-core path: bias + residual + LayerNorm run inside the two N = hidden projections
+  // (et_set_fused_layernorm(0): a LayerNorm kernel behind each of them instead)
+  bool fuse_ln = true;
+  TensorMapCache maps;  // TMA descriptors of this handle's launches
   // general [B,S,S] mask of the pass being enqueued (null: key-only mask, fast kernels)
   const void* cur_attr_mask = nullptr;
   const int* cur_word_idx = nullptr;
@@ -155,6 +193,10 @@ struct et_handle_s {
   int host_chunks = 3;     // measured best on cfg2 (ETB_HOST_CHUNKS overrides)
   int host_mid_share = 6;  // share of a middle chunk when the first and the last have 1: 1:6:1
                            // (measured on cfg2: 2 -> 9.0 ms, 6 -> 8.8 ms, 8 -> 9.0 ms; ETB_HOST_MID_SHARE)
+  bool host_share_auto = true;  // pick the middle share from the first call's measured copy and compute times
+  bool host_share_measured = false;
+  cudaEvent_t tune_ev[4] = {};  // upload start/end, compute start/end of the measuring call
+  size_t ws_bytes_allocated = 0;  // sum of the workspace buffers et_create allocated
   int* host_pinned = nullptr;  // [2 + kMaxChunks]: valid_word_num, status, per-chunk token counts
   // one captured forward pass (et_graph_capture*): replayed by et_graph_launch
   cudaGraph_t graph = nullptr;
@@ -165,6 +207,7 @@ struct et_handle_s {
   // fixed, so only the host's launch cost changes.  ETB_HOST_GRAPH=0 disables it.
   struct HostGraphs {
     int batch = -1, seq = -1, per = 0;  // per = number of chunks of the recorded shape
+    int mid_share = 0;                  // chunk shares the graphs were recorded with
     bool simt = false;
     std::vector<cudaGraph_t> graphs;
     std::vector<cudaGraphExec_t> execs;
@@ -194,6 +237,9 @@ int cuda_fail(et_handle_t h, cudaError_t e, const char* what) {
   return set_error(h, ET_CUDA_ERROR,
                    std::string("[ET][ERROR] CUDA runtime error: ") + cudaGetErrorString(e) + " in " + what);
 }
+// A kernel's bounded wait expired (status word != 0, already copied to host_pinned[1]): clear the
+// word and the GEMMs' row counters (an aborted kernel may have left them half counted).
+int device_timeout(et_handle_t h, cudaStream_t s);
 #define ET_CUDA(h, expr)                                   \
   do {                                                     \
     cudaError_t e__ = (expr);                              \
@@ -240,25 +286,31 @@ struct DeviceGuard {
   }
 };
 
+// Clears the general-mask state of a pass on every way out of the call that set it, so that a
+// call that fails half-way cannot leave the handle in general-mask mode for the next one.
+struct MaskScope {
+  et_handle_t h;
+  MaskScope(et_handle_t handle, const void* attr_mask, const int* word_idx) : h(handle) {
+    h->cur_attr_mask = attr_mask;
+    h->cur_word_idx = word_idx;
+  }
+  ~MaskScope() {
+    h->cur_attr_mask = nullptr;
+    h->cur_word_idx = nullptr;
+  }
+};
+
 int ws_alloc(et_handle_t h, void** p, size_t bytes) {
-  bytes = round_up(bytes == 0 ? 16 : bytes, 256);
+  bytes = ws_round(bytes);
   ET_CUDA(h, cudaMalloc(p, bytes));
   h->ws.allocations.push_back(*p);
   return ET_OK;
 }
 
 size_t workspace_bytes_for(const et_handle_s* h, size_t batch, size_t seq) {
-  const size_t cap = round_up(batch * seq, 128);
-  const size_t hid = h->hidden, f = h->cfg.ffn_dim, e = h->esize;
+  Workspace scratch;  // only the sizes are read
   size_t total = 0;
-  total += cap * hid * e * 3;          // x, ctx, att
-  total += cap * 3 * hid * e;          // qkv
-  total += cap * f * e;                // ffn
-  total += batch * seq * hid * e * 2;  // staging in/out
-  total += batch * seq * 4 * 8;        // mask / id / type staging + 5 index arrays
-  total += round_up(batch, 128) * hid * e * 2;  // first-token rows, pooled output
-  if (h->cfg.dtype == ET_FP32) total += cap * (f > hid ? f : hid) * 4 * 2;  // tf32 halves of a GEMM input
-  total += (batch * 3 + 8) * 4;
+  for (const WsItem& it : workspace_items(h->cfg, batch, seq, scratch)) total += ws_round(it.bytes);
   return total;
 }
 
@@ -327,7 +379,7 @@ int run_layer(et_handle_t h, const LayerWeights& lw, const T* x_in, T* x_out, co
   const bool tc32 = std::is_same<T, float>::value && !h->use_simt;  // three-product tf32 split
   // direction for a kernel that can run either way / for one that only runs first-to-last
   auto turn = [&]() {
-    const bool reverse = h->snake && h->prev_ascending;
+    const bool reverse = h->prev_ascending;
     h->prev_ascending = !reverse;
     return reverse;
   };
@@ -340,7 +392,7 @@ int run_layer(et_handle_t h, const LayerWeights& lw, const T* x_in, T* x_out, co
     if (tc)
       return launch_gemm_tcgen05(reinterpret_cast<const __half*>(a), static_cast<const __half*>(w_t),
                                  static_cast<const __half*>(bias), reinterpret_cast<__half*>(c), t_ptr,
-                                 max_m, n, k, epi, ws.status, s, turn());
+                                 max_m, n, k, epi, ws.status, s, turn(), nullptr, &h->maps);
     if (tc32) {
       // w_t holds rn_tf32(W), w_lo the remainder; the input is split the same way first
       const float* a_hi = reinterpret_cast<const float*>(a);
@@ -353,7 +405,7 @@ int run_layer(et_handle_t h, const LayerWeights& lw, const T* x_in, T* x_out, co
       }
       return launch_gemm_tf32x3(a_hi, a_lo, static_cast<const float*>(w_t), static_cast<const float*>(w_lo),
                                 static_cast<const float*>(bias), reinterpret_cast<float*>(c), t_ptr, max_m, n, k,
-                                epi, ws.status, s, turn(), c_lo);
+                                epi, ws.status, s, turn(), c_lo, &h->maps);
     }
     forward_only();
     return launch_gemm_simt<T>(a, B(w_rm), B(bias), c, t_ptr, max_m, n, k, epi, s);
@@ -381,25 +433,42 @@ int run_layer(et_handle_t h, const LayerWeights& lw, const T* x_in, T* x_out, co
                                        reinterpret_cast<const __half*>(qkv) + hid,
                                        reinterpret_cast<const __half*>(qkv) + 2 * hid, 3LL * hid, d,
                                        reinterpret_cast<__half*>(ctx), ws.attn_plan, batch, max_m, heads, d,
-                                       ws.status, s, turn()));
+                                       ws.status, s, turn(), &h->maps));
   else if (tc)
     ET_LAUNCH(h, ET_PROF_ATTENTION, 1, s, launch_attention_tc(reinterpret_cast<const __half*>(qkv),
                                    reinterpret_cast<const __half*>(qkv) + hid,
                                    reinterpret_cast<const __half*>(qkv) + 2 * hid, 3LL * hid, d,
                                    reinterpret_cast<__half*>(ctx), cu_seqlens, batch, seq, max_m, heads, d,
-                                   ws.status, s));
+                                   ws.status, s, &h->maps));
   else
     ET_LAUNCH(h, ET_PROF_ATTENTION, 1, s, launch_attention_simt<T>(qkv, qkv + hid, qkv + 2 * hid, 3LL * hid, d, ctx, cu_seqlens,
                                         batch, seq, heads, d, s, ctx_lo));
   if (!(h->cur_attr_mask == nullptr && tc && seq <= 128)) forward_only();
+  // fp16 tensor-core path: bias + residual + LayerNorm run inside the projection kernels (rows are
+  // normalised in place as soon as their last column tile has been stored), no LayerNorm launch
+  const bool ln_in_gemm = tc && h->fuse_ln && gemm_layernorm_supported(hid);
+  auto H16 = [](const void* p) { return static_cast<const __half*>(p); };
+  GemmLayerNorm gln;
+  gln.eps = h->eps;
+  gln.counters = ws.ln_counters;
   // attention output projection, then +bias +residual, LayerNorm
-  ET_LAUNCH(h, ET_PROF_GEMM_ATTN_OUT, tc32 && ctx_lo == nullptr ? 2 : 1, s,
-            gemm(ctx, lw.wo, lw.wo_t, lw.wo_lo, nullptr, att, hid, hid, kEpiNone, reinterpret_cast<const float*>(ctx_lo)));
   // (fp32 tensor path: both LayerNorms also write their rows split for the projection behind them)
   T* ln_hi = tc32 ? reinterpret_cast<T*>(ws.a_hi) : nullptr;
   T* ln_lo = tc32 ? reinterpret_cast<T*>(ws.a_lo) : nullptr;
-  ET_LAUNCH(h, ET_PROF_LAYERNORM, 1, s, launch_add_bias_input_layernorm<T>(att, x_in, B(lw.bo), B(lw.ln1_gamma), B(lw.ln1_beta),
-                                                t_ptr, max_m, hid, h->eps, s, turn(), ln_hi, ln_lo));
+  if (ln_in_gemm) {
+    gln.gamma = H16(lw.ln1_gamma);
+    gln.beta = H16(lw.ln1_beta);
+    ET_LAUNCH(h, ET_PROF_GEMM_ATTN_OUT, 1, s,
+              launch_gemm_tcgen05(H16(ctx), H16(lw.wo_t), H16(lw.bo), reinterpret_cast<__half*>(att), t_ptr, max_m,
+                                  hid, hid, kEpiLayerNorm, ws.status, s, turn(), H16(x_in), &h->maps, &gln));
+  } else {
+    ET_LAUNCH(h, ET_PROF_GEMM_ATTN_OUT, tc32 && ctx_lo == nullptr ? 2 : 1, s,
+              gemm(ctx, lw.wo, lw.wo_t, lw.wo_lo, nullptr, att, hid, hid, kEpiNone,
+                   reinterpret_cast<const float*>(ctx_lo)));
+    ET_LAUNCH(h, ET_PROF_LAYERNORM, 1, s,
+              launch_add_bias_input_layernorm<T>(att, x_in, B(lw.bo), B(lw.ln1_gamma), B(lw.ln1_beta), t_ptr, max_m,
+                                                 hid, h->eps, s, turn(), ln_hi, ln_lo));
+  }
   // feed-forward: bias + GELU fused into the first GEMM
   // (fp32 tensor path: the GELU output leaves the epilogue split for the second projection)
   ET_LAUNCH(h, ET_PROF_GEMM_FFN1, 1, s,
@@ -408,14 +477,17 @@ int run_layer(et_handle_t h, const LayerWeights& lw, const T* x_in, T* x_out, co
   // fp16 tensor-core path: the second FFN projection adds its bias and the residual in its
   // epilogue (its K = F main loop leaves the epilogue warps idle time), so the LayerNorm
   // behind it reads one tensor instead of two.  The attention output projection (K = H) has
-  // no such slack: measured, the same fusion there cost the GEMM what the LayerNorm saved.
-  const bool fuse_res = tc && h->fuse_residual;
-  if (fuse_res) {
+  // no such slack: there the rows' bias and residual are added where they are normalised.
+  if (ln_in_gemm) {
+    gln.gamma = H16(lw.ln2_gamma);
+    gln.beta = H16(lw.ln2_beta);
     ET_LAUNCH(h, ET_PROF_GEMM_FFN2, 1, s,
-              launch_gemm_tcgen05(reinterpret_cast<const __half*>(ffn), static_cast<const __half*>(lw.w2_t),
-                                  static_cast<const __half*>(lw.b2), reinterpret_cast<__half*>(x_out), t_ptr, max_m,
-                                  hid, f, kEpiBiasResidual, ws.status, s, turn(),
-                                  reinterpret_cast<const __half*>(att)));
+              launch_gemm_tcgen05(H16(ffn), H16(lw.w2_t), H16(lw.b2), reinterpret_cast<__half*>(x_out), t_ptr, max_m,
+                                  hid, f, kEpiResidualLayerNorm, ws.status, s, turn(), H16(att), &h->maps, &gln));
+  } else if (tc) {
+    ET_LAUNCH(h, ET_PROF_GEMM_FFN2, 1, s,
+              launch_gemm_tcgen05(H16(ffn), H16(lw.w2_t), H16(lw.b2), reinterpret_cast<__half*>(x_out), t_ptr, max_m,
+                                  hid, f, kEpiBiasResidual, ws.status, s, turn(), H16(att), &h->maps));
     ET_LAUNCH(h, ET_PROF_LAYERNORM, 1, s,
               launch_add_bias_input_layernorm<T>(x_out, nullptr, nullptr, B(lw.ln2_gamma), B(lw.ln2_beta), t_ptr,
                                                  max_m, hid, h->eps, s, turn()));
@@ -428,6 +500,15 @@ int run_layer(et_handle_t h, const LayerWeights& lw, const T* x_in, T* x_out, co
                                                   split2 ? ln_lo : nullptr));
   }
   return ET_OK;
+}
+
+int device_timeout(et_handle_t h, cudaStream_t s) {
+  char msg[96];
+  snprintf(msg, sizeof msg, "device-side wait expired, status word 0x%x", h->host_pinned[1]);
+  cudaMemsetAsync(h->ws.status, 0, 4, s);
+  cudaMemsetAsync(h->ws.ln_counters, 0, ln_counter_ints(h->ws.cap_tokens) * 4, s);
+  cudaStreamSynchronize(s);
+  return set_error(h, ET_DEVICE_TIMEOUT, msg);
 }
 
 int check_shape(et_handle_t h, int batch, int seq, int heads, int d) {
@@ -567,7 +648,7 @@ int pooler_impl(et_handle_t h, const void* packed, const int* cu_seqlens, void* 
     ET_LAUNCH(h, ET_PROF_POOLER, 1, s,
               launch_gemm_tcgen05(static_cast<const __half*>(ws.first_tok), static_cast<const __half*>(mw.pool_w_t),
                                   static_cast<const __half*>(mw.pool_b), static_cast<__half*>(pooled_out),
-                                  ws.pool_m, batch, hid, hid, kEpiBiasTanh, ws.status, s));
+                                  ws.pool_m, batch, hid, hid, kEpiBiasTanh, ws.status, s, false, nullptr, &h->maps));
   else if (h->cfg.dtype == ET_FP16)
     ET_LAUNCH(h, ET_PROF_POOLER, 1, s,
               launch_gemm_simt<__half>(static_cast<const __half*>(ws.first_tok), static_cast<const __half*>(mw.pool_w),
@@ -721,6 +802,7 @@ void host_graphs_build(et_handle_t h, int batch, int seq, const std::vector<std:
   hg.batch = batch;
   hg.seq = seq;
   hg.per = static_cast<int>(plan.size());
+  hg.mid_share = h->host_mid_share;
   hg.simt = h->use_simt;
 }
 
@@ -752,6 +834,10 @@ int et_create(const et_config_t* config, et_handle_t* out_handle) {
   const int hid = c.head_num * c.size_per_head;
   if (c.ffn_dim <= 0 || (c.ffn_dim % 128) != 0 || (hid % 128) != 0)
     return set_error(nullptr, ET_INVALID_ARGUMENT, "hidden and ffn_dim must be positive multiples of 128");
+  // the LayerNorm and embedding kernels keep a row in the registers of one warp: 8 vectors of 16 bytes per lane
+  if (hid > (c.dtype == ET_FP16 ? 2048 : 1024))
+    return set_error(nullptr, ET_INVALID_ARGUMENT,
+                     "hidden (head_num * size_per_head) is limited to 2048 for ET_FP16 and 1024 for ET_FP32");
   int ndev = 0;
   if (cudaGetDeviceCount(&ndev) != cudaSuccess || c.device < 0 || c.device >= ndev)
     return set_error(nullptr, ET_CUDA_ERROR, "no such CUDA device");
@@ -794,31 +880,13 @@ int et_create(const et_config_t* config, et_handle_t* out_handle) {
     }
   }
   Workspace& ws = h->ws;
-  const size_t bs = static_cast<size_t>(c.max_batch_size) * c.max_seq_len;
-  ws.cap_tokens = round_up(bs, 128);
-  const size_t cap = ws.cap_tokens;
-  struct { void** p; size_t bytes; } bufs[] = {
-      {&ws.x, cap * H * e}, {&ws.qkv, cap * 3 * H * e}, {&ws.ctx, cap * H * e}, {&ws.att, cap * H * e},
-      {&ws.ffn, cap * f * e}, {&ws.stage_in, bs * H * e}, {&ws.stage_out, bs * H * e},
-      {reinterpret_cast<void**>(&ws.stage_mask), bs * 4},
-      {reinterpret_cast<void**>(&ws.stage_ids), bs * 4}, {reinterpret_cast<void**>(&ws.stage_types), bs * 4},
-      {&ws.first_tok, round_up(static_cast<size_t>(c.max_batch_size), 128) * H * e},
-      {&ws.pooled, round_up(static_cast<size_t>(c.max_batch_size), 128) * H * e},
-      {reinterpret_cast<void**>(&ws.pool_m), 4},
-      {reinterpret_cast<void**>(&ws.batch_idx), cap * 4}, {reinterpret_cast<void**>(&ws.word_idx), cap * 4},
-      {reinterpret_cast<void**>(&ws.padding_offset), cap * 4},
-      {reinterpret_cast<void**>(&ws.prefix_sum), cap * 4},
-      {reinterpret_cast<void**>(&ws.seq_len), static_cast<size_t>(c.max_batch_size) * 4},
-      {reinterpret_cast<void**>(&ws.cu_seqlens), (static_cast<size_t>(c.max_batch_size) + 1) * 4},
-      {reinterpret_cast<void**>(&ws.lens_scratch), static_cast<size_t>(c.max_batch_size) * 4},
-      {reinterpret_cast<void**>(&ws.attn_plan), attention_plan_ints(c.max_batch_size, static_cast<int>(cap)) * 4},
-      {reinterpret_cast<void**>(&ws.pos_row), cap * 4},
-      {reinterpret_cast<void**>(&ws.a_hi), c.dtype == ET_FP32 ? cap * H * 4 : 0},
-      {reinterpret_cast<void**>(&ws.a_lo), c.dtype == ET_FP32 ? cap * H * 4 : 0},
-      {reinterpret_cast<void**>(&ws.ffn_lo), c.dtype == ET_FP32 ? cap * f * 4 : 0},
-      {reinterpret_cast<void**>(&ws.valid_word_num), 4}, {reinterpret_cast<void**>(&ws.status), 4}};
-  for (auto& b : bufs)
-    if ((rc = ws_alloc(h, b.p, b.bytes)) != ET_OK) return bail(rc);
+  ws.cap_tokens = round_up(static_cast<size_t>(c.max_batch_size) * c.max_seq_len, 128);
+  for (const WsItem& b : workspace_items(c, static_cast<size_t>(c.max_batch_size),
+                                         static_cast<size_t>(c.max_seq_len), ws))
+    if ((rc = ws_alloc(h, b.slot, b.bytes)) != ET_OK) return bail(rc);
+    else h->ws_bytes_allocated += ws_round(b.bytes);
+  if (cudaMemset(ws.ln_counters, 0, ln_counter_ints(ws.cap_tokens) * 4) != cudaSuccess)
+    return bail(cuda_fail(h, cudaGetLastError(), "cudaMemset"));
   if (cudaMemset(ws.status, 0, 4) != cudaSuccess || cudaMemset(ws.valid_word_num, 0, 4) != cudaSuccess)
     return bail(cuda_fail(h, cudaGetLastError(), "cudaMemset"));
   if (cudaStreamCreateWithFlags(&h->own_stream, cudaStreamNonBlocking) != cudaSuccess)
@@ -830,17 +898,20 @@ int et_create(const et_config_t* config, et_handle_t* out_handle) {
     if (cudaEventCreateWithFlags(&h->in_done[i], cudaEventDisableTiming) != cudaSuccess ||
         cudaEventCreateWithFlags(&h->comp_done[i], cudaEventDisableTiming) != cudaSuccess)
       return bail(cuda_fail(h, cudaGetLastError(), "cudaEventCreate"));
-  if (const char* e = getenv("ETB_SNAKE")) h->snake = !(e[0] == '0');
-  if (const char* e = getenv("ETB_FUSE_RESIDUAL")) h->fuse_residual = !(e[0] == '0');
   if (const char* e = getenv("ETB_HOST_GRAPH")) h->host_graph_enabled = !(e[0] == '0');
   if (const char* e = getenv("ETB_HOST_CHUNKS")) {
     const int n = atoi(e);
     if (n >= 1 && n <= et_handle_s::kMaxChunks) h->host_chunks = n;
   }
-  if (const char* e = getenv("ETB_HOST_MID_SHARE")) {
+  if (const char* e = getenv("ETB_HOST_MID_SHARE")) {  // fixes the shares; otherwise the first call measures
     const int n = atoi(e);
-    if (n >= 1 && n <= 16) h->host_mid_share = n;
+    if (n >= 1 && n <= 16) {
+      h->host_mid_share = n;
+      h->host_share_auto = false;
+    }
   }
+  for (auto& ev : h->tune_ev)
+    if (cudaEventCreate(&ev) != cudaSuccess) return bail(cuda_fail(h, cudaGetLastError(), "cudaEventCreate"));
   if (cudaMallocHost(reinterpret_cast<void**>(&h->host_pinned),
                      (2 + et_handle_s::kMaxChunks) * sizeof(int)) != cudaSuccess)
     return bail(cuda_fail(h, cudaGetLastError(), "cudaMallocHost"));
@@ -869,6 +940,8 @@ int et_destroy(et_handle_t h) {
     if (h->in_done[i]) cudaEventDestroy(h->in_done[i]);
     if (h->comp_done[i]) cudaEventDestroy(h->comp_done[i]);
   }
+  for (cudaEvent_t ev : h->tune_ev)
+    if (ev) cudaEventDestroy(ev);
   if (h->own_stream) cudaStreamDestroy(h->own_stream);
   if (h->h2d_stream) cudaStreamDestroy(h->h2d_stream);
   if (h->d2h_stream) cudaStreamDestroy(h->d2h_stream);
@@ -884,6 +957,32 @@ const char* et_last_error(et_handle_t h) {
 int et_set_debug_simt(et_handle_t h, int use_simt) {
   if (h == nullptr) return ET_INVALID_ARGUMENT;
   h->use_simt = use_simt != 0;
+  return ET_OK;
+}
+
+int et_set_fused_layernorm(et_handle_t h, int enable) {
+  if (h == nullptr) return ET_INVALID_ARGUMENT;
+  if (h->fuse_ln != (enable != 0)) {
+    DeviceGuard guard(h->cfg.device);
+    cudaDeviceSynchronize();
+    graph_release(h);        // recorded passes hold the other kernel sequence
+    host_graphs_release(h);
+  }
+  h->fuse_ln = enable != 0;
+  return ET_OK;
+}
+
+int et_workspace_allocated_bytes(et_handle_t h, size_t* out_bytes) {
+  if (h == nullptr || out_bytes == nullptr) return ET_INVALID_ARGUMENT;
+  *out_bytes = h->ws_bytes_allocated;
+  return ET_OK;
+}
+
+int et_host_chunk_shares(et_handle_t h, int* chunks, int* mid_share, int* measured) {
+  if (h == nullptr) return ET_INVALID_ARGUMENT;
+  if (chunks) *chunks = h->host_chunks;
+  if (mid_share) *mid_share = h->host_mid_share;
+  if (measured) *measured = h->host_share_measured ? 1 : 0;
   return ET_OK;
 }
 
@@ -973,6 +1072,10 @@ int et_layer(et_handle_t h, int layer, const et_encoder_param_t* p, const et_tra
   DeviceGuard guard(h->cfg.device);
   h->prof.chain = nullptr;
   cudaStream_t s = static_cast<cudaStream_t>(p->stream);
+  if (h->general_mask && p->attr_mask == nullptr)
+    return set_error(h, ET_INVALID_ARGUMENT, "general-mask mode: attr_mask [B,S,S] is required");
+  // from here on every return leaves the handle in key-only-mask mode again
+  MaskScope mask_scope(h, h->general_mask ? p->attr_mask : nullptr, h->general_mask ? p->word_idx : nullptr);
   if (p->attr_kernel_Q != nullptr) {
     const void* w[16] = {p->attr_kernel_Q, p->attr_bias_Q, p->attr_kernel_K, p->attr_bias_K,
                          p->attr_kernel_V, p->attr_bias_V, p->attr_output_kernel, p->attr_output_bias,
@@ -988,13 +1091,9 @@ int et_layer(et_handle_t h, int layer, const et_encoder_param_t* p, const et_tra
   const int batch = tp->batch_size, seq = tp->from_seq_len, max_m = batch * seq;
   ET_LAUNCH(h, ET_PROF_PADDING_OFFSETS, 1, s, launch_seq_bounds_from_batch_idx(p->batch_idx, p->valid_word_num, batch, max_m,
                                               h->ws.cu_seqlens, s));
-  if (h->general_mask) {
-    if (p->attr_mask == nullptr)
-      return set_error(h, ET_INVALID_ARGUMENT, "general-mask mode: attr_mask [B,S,S] is required");
+  if (h->cur_attr_mask != nullptr) {
     ET_LAUNCH(h, ET_PROF_PADDING_OFFSETS, 1, s,
               launch_position_rows(p->batch_idx, p->word_idx, p->valid_word_num, batch, seq, h->ws.pos_row, s));
-    h->cur_attr_mask = p->attr_mask;
-    h->cur_word_idx = p->word_idx;
   } else if (h->cfg.dtype == ET_FP16 && !h->use_simt && seq <= 128 && max_m > 0) {
     ET_LAUNCH(h, ET_PROF_PADDING_OFFSETS, 1, s,
               launch_attention_plan(h->ws.cu_seqlens, batch, max_m, h->ws.attn_plan, s));
@@ -1007,8 +1106,6 @@ int et_layer(et_handle_t h, int layer, const et_encoder_param_t* p, const et_tra
     rc = run_layer<float>(h, h->layers[layer], static_cast<const float*>(p->from_tensor),
                           static_cast<float*>(p->transformer_out), p->valid_word_num, max_m,
                           h->ws.cu_seqlens, batch, seq, s);
-  h->cur_attr_mask = nullptr;
-  h->cur_word_idx = nullptr;
   return rc;
   ET_CATCH(h)
 }
@@ -1034,25 +1131,41 @@ int et_forward_general_mask(et_handle_t h, const void* from_tensor, const int* m
   if (h == nullptr) return ET_INVALID_ARGUMENT;
   if (attr_mask == nullptr) return set_error(h, ET_INVALID_ARGUMENT, "attr_mask [B,S,S] is required");
   DeviceGuard guard(h->cfg.device);
-  h->cur_attr_mask = attr_mask;
-  h->cur_word_idx = h->ws.word_idx;
-  const int rc = forward_impl(h, from_tensor, mask, out, batch_size, seq_len, static_cast<cudaStream_t>(stream));
-  h->cur_attr_mask = nullptr;
-  h->cur_word_idx = nullptr;
-  return rc;
+  MaskScope mask_scope(h, attr_mask, h->ws.word_idx);
+  return forward_impl(h, from_tensor, mask, out, batch_size, seq_len, static_cast<cudaStream_t>(stream));
   ET_CATCH(h)
 }
 
-int et_forward_host(et_handle_t h, const void* from_host, const int* mask_host, void* out_host,
-                    int batch_size, int seq_len, int* valid_word_num_out) {
-  ET_TRY
-  if (h == nullptr) return ET_INVALID_ARGUMENT;
-  int rc = check_shape(h, batch_size, seq_len, h->cfg.head_num, h->cfg.size_per_head);
-  if (rc != ET_OK) return rc;
-  if (!from_host || !mask_host || !out_host) return set_error(h, ET_INVALID_ARGUMENT, "null host pointer");
-  DeviceGuard guard(h->cfg.device);
+}  // extern "C"
+
+namespace {
+
+// Best middle share of a 3-chunk host-buffer call from the measured times of one call: `up` ms
+// for the whole upload, `comp` ms for the whole pass (the download is taken to cost what the
+// upload does).  Timeline of shares 1:m:1 -- upload of chunk 0, then its pass while chunk 1 is
+// uploaded, the passes of chunks 1 and 2, the download of chunk 2:
+//   t(m) = up/(m+2) + max(comp/(m+2), up*m/(m+2)) + comp*(m+1)/(m+2) + up/(m+2)
+// A wide middle chunk shortens the two copies nothing overlaps, until its own upload no longer
+// hides behind the first chunk's pass (several processes sharing the host's PCIe switches).
+int best_mid_share(double up, double comp) {
+  int best = 2;
+  double best_t = 1e30;
+  for (int m : {1, 2, 3, 4, 6, 8}) {
+    const double t = up / (m + 2) + std::max(comp / (m + 2), up * m / (m + 2)) + comp * (m + 1) / (m + 2) +
+                     up / (m + 2);
+    if (t < best_t - 1e-9) {
+      best_t = t;
+      best = m;
+    }
+  }
+  return best;
+}
+
+int forward_host_body(et_handle_t h, const void* from_host, const int* mask_host, void* out_host,
+                      int batch_size, int seq_len, int* valid_word_num_out) {
   Workspace& ws = h->ws;
   cudaStream_t s = h->own_stream;
+  int rc = ET_OK;
   // The batch is cut into chunks of whole sequences (they are independent):
   // all uploads are queued on the upload stream at once, chunk i is computed
   // when its upload has landed, and its result goes back on the download
@@ -1066,7 +1179,10 @@ int et_forward_host(et_handle_t h, const void* from_host, const int* mask_host, 
   et_handle_s::HostGraphs& hg = h->host_graphs;
   const bool graphs_allowed = h->host_graph_enabled && !h->prof.enabled && h->cur_attr_mask == nullptr;
   const bool replay = graphs_allowed && hg.batch == batch_size && hg.seq == seq_len && hg.per == per &&
-                      hg.simt == h->use_simt && !hg.execs.empty();
+                      hg.mid_share == h->host_mid_share && hg.simt == h->use_simt && !hg.execs.empty();
+  // the first chunked call measures the copy and compute times that choose the shares of the next ones
+  const bool measure = h->host_share_auto && !h->host_share_measured && per >= 3 && h->tune_ev[0] != nullptr;
+  if (measure) ET_CUDA(h, cudaEventRecord(h->tune_ev[0], h->h2d_stream));
   for (; nchunks < per; ++nchunks) {
     const size_t b0 = plan[nchunks].first, nb = plan[nchunks].second;
     ET_CUDA(h, cudaMemcpyAsync(static_cast<char*>(ws.stage_in) + b0 * seq_bytes,
@@ -1077,10 +1193,13 @@ int et_forward_host(et_handle_t h, const void* from_host, const int* mask_host, 
                                nb * seq_len * 4, cudaMemcpyHostToDevice, h->h2d_stream));
     ET_CUDA(h, cudaEventRecord(h->in_done[nchunks], h->h2d_stream));
   }
+  if (measure) ET_CUDA(h, cudaEventRecord(h->tune_ev[1], h->h2d_stream));
   for (int c = 0; c < per; ++c) {
     const size_t b0 = plan[c].first;
     const int nb = plan[c].second;
     ET_CUDA(h, cudaStreamWaitEvent(s, h->in_done[c], 0));
+    // the middle chunk's pass, from the moment its upload has landed: the compute rate of the batch
+    if (measure && c == 1) ET_CUDA(h, cudaEventRecord(h->tune_ev[2], s));
     if (replay && c < static_cast<int>(hg.execs.size())) {
       ET_CUDA(h, cudaGraphLaunch(hg.execs[c], s));
       for (int i = 0; i < ET_PROF_NUM; ++i) h->prof.launches[i] += hg.launches[c][i];
@@ -1088,11 +1207,9 @@ int et_forward_host(et_handle_t h, const void* from_host, const int* mask_host, 
       rc = forward_impl(h, static_cast<char*>(ws.stage_in) + b0 * seq_bytes,
                         ws.stage_mask + static_cast<size_t>(b0) * seq_len,
                         static_cast<char*>(ws.stage_out) + b0 * seq_bytes, nb, seq_len, s);
-      if (rc != ET_OK) {
-        cudaDeviceSynchronize();
-        return rc;
-      }
+      if (rc != ET_OK) return rc;
     }
+    if (measure && c == 1) ET_CUDA(h, cudaEventRecord(h->tune_ev[3], s));
     ET_CUDA(h, cudaMemcpyAsync(&h->host_pinned[2 + c], ws.valid_word_num, 4, cudaMemcpyDeviceToHost, s));
     ET_CUDA(h, cudaEventRecord(h->comp_done[c], s));
     ET_CUDA(h, cudaStreamWaitEvent(h->d2h_stream, h->comp_done[c], 0));
@@ -1107,20 +1224,49 @@ int et_forward_host(et_handle_t h, const void* from_host, const int* mask_host, 
   int total_tokens = 0;
   for (int i = 0; i < nchunks; ++i) total_tokens += h->host_pinned[2 + i];
   if (valid_word_num_out) *valid_word_num_out = total_tokens;
-  if (h->host_pinned[1] != 0) {
-    char msg[96];
-    snprintf(msg, sizeof msg, "device-side wait expired, status word 0x%x", h->host_pinned[1]);
-    cudaMemsetAsync(ws.status, 0, 4, s);
-    cudaStreamSynchronize(s);
-    return set_error(h, ET_DEVICE_TIMEOUT, msg);
+  if (h->host_pinned[1] != 0) return device_timeout(h, s);
+  if (measure) {
+    float up_ms = 0.f, mid_ms = 0.f;
+    if (cudaEventElapsedTime(&up_ms, h->tune_ev[0], h->tune_ev[1]) == cudaSuccess &&
+        cudaEventElapsedTime(&mid_ms, h->tune_ev[2], h->tune_ev[3]) == cudaSuccess && up_ms > 0.f && mid_ms > 0.f &&
+        plan[1].second > 0) {
+      const double comp_ms = static_cast<double>(mid_ms) * batch_size / plan[1].second;
+      h->host_mid_share = best_mid_share(up_ms, comp_ms);
+    }
+    h->host_share_measured = true;
   }
   // second call in a row with this shape: record its chunks for the calls to come
   if (!replay && graphs_allowed && batch_size > 0 && h->last_host_batch == batch_size &&
-      h->last_host_seq == seq_len)
+      h->last_host_seq == seq_len && !measure)
     host_graphs_build(h, batch_size, seq_len, plan);  // best effort: on failure the eager path stays
   h->last_host_batch = batch_size;
   h->last_host_seq = seq_len;
   return ET_OK;
+}
+
+// Copies of a host-buffer call may still be running when an error is found: nothing of the call
+// may touch the caller's buffers after it has returned.
+void quiesce_host_call(et_handle_t h) {
+  cudaStreamSynchronize(h->own_stream);
+  cudaStreamSynchronize(h->h2d_stream);
+  cudaStreamSynchronize(h->d2h_stream);
+}
+
+}  // namespace
+
+extern "C" {
+
+int et_forward_host(et_handle_t h, const void* from_host, const int* mask_host, void* out_host,
+                    int batch_size, int seq_len, int* valid_word_num_out) {
+  ET_TRY
+  if (h == nullptr) return ET_INVALID_ARGUMENT;
+  int rc = check_shape(h, batch_size, seq_len, h->cfg.head_num, h->cfg.size_per_head);
+  if (rc != ET_OK) return rc;
+  if (!from_host || !mask_host || !out_host) return set_error(h, ET_INVALID_ARGUMENT, "null host pointer");
+  DeviceGuard guard(h->cfg.device);
+  rc = forward_host_body(h, from_host, mask_host, out_host, batch_size, seq_len, valid_word_num_out);
+  if (rc != ET_OK) quiesce_host_call(h);
+  return rc;
   ET_CATCH(h)
 }
 
@@ -1203,28 +1349,23 @@ int et_forward_ids(et_handle_t h, const int* input_ids, const int* token_type_id
   ET_CATCH(h)
 }
 
-int et_forward_ids_host(et_handle_t h, const int* ids_host, const int* types_host, const int* mask_host,
-                        void* sequence_out_host, void* pooled_out_host, int batch_size, int seq_len,
-                        int* valid_word_num_out) {
-  ET_TRY
-  if (h == nullptr) return ET_INVALID_ARGUMENT;
-  int rc = check_shape(h, batch_size, seq_len, h->cfg.head_num, h->cfg.size_per_head);
-  if (rc != ET_OK) return rc;
-  if (!ids_host || !mask_host) return set_error(h, ET_INVALID_ARGUMENT, "null host pointer");
-  DeviceGuard guard(h->cfg.device);
+}  // extern "C"
+
+namespace {
+
+int forward_ids_host_body(et_handle_t h, const int* ids_host, const int* types_host, const int* mask_host,
+                          void* sequence_out_host, void* pooled_out_host, int batch_size, int seq_len,
+                          int* valid_word_num_out) {
   Workspace& ws = h->ws;
   cudaStream_t s = h->own_stream;
   const size_t n = static_cast<size_t>(batch_size) * seq_len;
   ET_CUDA(h, cudaMemcpyAsync(ws.stage_ids, ids_host, n * 4, cudaMemcpyHostToDevice, s));
   ET_CUDA(h, cudaMemcpyAsync(ws.stage_mask, mask_host, n * 4, cudaMemcpyHostToDevice, s));
   if (types_host) ET_CUDA(h, cudaMemcpyAsync(ws.stage_types, types_host, n * 4, cudaMemcpyHostToDevice, s));
-  rc = forward_ids_impl(h, ws.stage_ids, types_host ? ws.stage_types : nullptr, ws.stage_mask,
-                        sequence_out_host ? ws.stage_out : nullptr, pooled_out_host ? ws.pooled : nullptr,
-                        batch_size, seq_len, s);
-  if (rc != ET_OK) {
-    cudaDeviceSynchronize();
-    return rc;
-  }
+  const int rc = forward_ids_impl(h, ws.stage_ids, types_host ? ws.stage_types : nullptr, ws.stage_mask,
+                                  sequence_out_host ? ws.stage_out : nullptr, pooled_out_host ? ws.pooled : nullptr,
+                                  batch_size, seq_len, s);
+  if (rc != ET_OK) return rc;
   if (pooled_out_host)
     ET_CUDA(h, cudaMemcpyAsync(pooled_out_host, ws.pooled, static_cast<size_t>(batch_size) * h->hidden * h->esize,
                                cudaMemcpyDeviceToHost, s));
@@ -1235,14 +1376,27 @@ int et_forward_ids_host(et_handle_t h, const int* ids_host, const int* types_hos
   ET_CUDA(h, cudaMemcpyAsync(&h->host_pinned[1], ws.status, 4, cudaMemcpyDeviceToHost, s));
   ET_CUDA(h, cudaStreamSynchronize(s));
   if (valid_word_num_out) *valid_word_num_out = h->host_pinned[0];
-  if (h->host_pinned[1] != 0) {
-    char msg[96];
-    snprintf(msg, sizeof msg, "device-side wait expired, status word 0x%x", h->host_pinned[1]);
-    cudaMemsetAsync(ws.status, 0, 4, s);
-    cudaStreamSynchronize(s);
-    return set_error(h, ET_DEVICE_TIMEOUT, msg);
-  }
+  if (h->host_pinned[1] != 0) return device_timeout(h, s);
   return ET_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int et_forward_ids_host(et_handle_t h, const int* ids_host, const int* types_host, const int* mask_host,
+                        void* sequence_out_host, void* pooled_out_host, int batch_size, int seq_len,
+                        int* valid_word_num_out) {
+  ET_TRY
+  if (h == nullptr) return ET_INVALID_ARGUMENT;
+  int rc = check_shape(h, batch_size, seq_len, h->cfg.head_num, h->cfg.size_per_head);
+  if (rc != ET_OK) return rc;
+  if (!ids_host || !mask_host) return set_error(h, ET_INVALID_ARGUMENT, "null host pointer");
+  DeviceGuard guard(h->cfg.device);
+  rc = forward_ids_host_body(h, ids_host, types_host, mask_host, sequence_out_host, pooled_out_host, batch_size,
+                             seq_len, valid_word_num_out);
+  if (rc != ET_OK) quiesce_host_call(h);
+  return rc;
   ET_CATCH(h)
 }
 
@@ -1375,6 +1529,8 @@ int et_device_status(et_handle_t h, void* stream, int* out_status) {
   *out_status = h->host_pinned[1];
   if (*out_status != 0) {
     ET_CUDA(h, cudaMemsetAsync(h->ws.status, 0, 4, s));
+    // an aborted GEMM may have left its row counters half counted
+    ET_CUDA(h, cudaMemsetAsync(h->ws.ln_counters, 0, ln_counter_ints(h->ws.cap_tokens) * 4, s));
     ET_CUDA(h, cudaStreamSynchronize(s));
   }
   return ET_OK;
@@ -1630,6 +1786,35 @@ int et_gemm(int dtype, const void* a, const void* w, const void* w_packed, const
                                               epilogue, s),
                      launch_gemm_simt<float>(F_(a), F_(w), F_(bias), static_cast<float*>(c), m_ptr, max_m, n, k,
                                              epilogue, s));
+}
+
+int et_gemm_fused(const void* a, const void* w_packed, const void* bias, const void* residual, const void* gamma,
+                  const void* beta, float eps, int* row_counters, void* c, const int* m_ptr, int max_m, int n,
+                  int k, int epilogue, int* status_word, void* stream) {
+  if (!a || !w_packed || !bias || !residual || !c || !m_ptr || max_m < 0 || n <= 0 || k <= 0)
+    return ET_INVALID_ARGUMENT;
+  if (epilogue != kEpiBiasResidual && epilogue != kEpiResidualLayerNorm && epilogue != kEpiLayerNorm)
+    return ET_INVALID_ARGUMENT;
+  GemmLayerNorm ln;
+  if (epilogue != kEpiBiasResidual) {
+    if (!gamma || !beta || !row_counters || !gemm_layernorm_supported(n)) return ET_INVALID_ARGUMENT;
+    ln.gamma = H_(gamma);
+    ln.beta = H_(beta);
+    ln.eps = eps > 0.f ? eps : 1e-6f;
+    ln.counters = row_counters;
+  }
+  return to_status(launch_gemm_tcgen05(H_(a), H_(w_packed), H_(bias), static_cast<__half*>(c), m_ptr, max_m, n, k,
+                                       epilogue, status_word, static_cast<cudaStream_t>(stream), false,
+                                       H_(residual), nullptr, &ln));
+}
+
+int et_selftest_wait_timeout(et_handle_t h, void* stream) {
+  ET_TRY
+  if (h == nullptr) return ET_INVALID_ARGUMENT;
+  DeviceGuard guard(h->cfg.device);
+  ET_CUDA(h, launch_selftest_wait_timeout(h->ws.status, static_cast<cudaStream_t>(stream)));
+  return ET_OK;
+  ET_CATCH(h)
 }
 
 int et_split_tf32(const float* x, float* hi, float* lo, const int* rows_ptr, int max_rows, int cols,

@@ -42,6 +42,92 @@ constexpr int kNumThreads = 64 + kEpilogueThreads;
 
 constexpr int kStagingPerWarp = 32 * 128;  // 32 rows x 128 bytes (64 fp16 columns)
 
+// ---- LayerNorm inside the GEMM kernel (kEpiResidualLayerNorm, kEpiLayerNorm) -----------------
+// Every epilogue warp counts the columns it has stored for its 32 rows in a global counter of that
+// row block.  The warp whose count completes the row (all N columns, written by up to six warps of
+// three CTA pairs) knows that the whole pre-LayerNorm block is in L2, and posts it to one of the
+// CTA's LayerNorm warps, which normalise it in place off the epilogue's critical path.
+constexpr int kLnWarps = 2;  // each serves the mailboxes of four epilogue warps
+__host__ __device__ constexpr bool has_ln(int epi) { return epi == kEpiResidualLayerNorm || epi == kEpiLayerNorm; }
+// what the accumulator epilogue itself does for an epilogue kind
+__host__ __device__ constexpr int base_epi(int epi) {
+  return epi == kEpiResidualLayerNorm ? kEpiBiasResidual : epi == kEpiLayerNorm ? kEpiNone : epi;
+}
+__host__ __device__ constexpr int threads_of(int epi) { return kNumThreads + (has_ln(epi) ? kLnWarps * 32 : 0); }
+
+// LayerNorm of `nrows` (<= 32) consecutive rows of c [*, n] in place by one warp, n = 256 * VPL:
+// lane l holds the 16-byte vectors j * 32 + l of a row, statistics in fp32 in two passes over the
+// registers, as add_bias_input_layernorm_kernel does (same arithmetic in the same order).
+// ADD: x = c + (residual + bias) first.  Rows are read through L2 (other CTAs wrote them).
+template <int VPL, bool ADD>
+__device__ __forceinline__ void ln_rows(__half* c, const __half* residual, const __half* bias,
+                                          const __half* gamma, const __half* beta, int n, int nrows, float eps,
+                                          int lane) {
+  // rows per batch: about 18 16-byte vectors in flight per lane (the kernel runs 384 threads, so a
+  // thread has 168 registers)
+  constexpr int kFit = (VPL == 4 ? 16 : 18) / (VPL * (ADD ? 2 : 1));
+  constexpr int R = kFit > 8 ? 8 : kFit;
+  const float inv_n = 1.0f / static_cast<float>(n);
+  for (int r0 = 0; r0 < nrows; r0 += R) {
+    Vec16 vc[R][VPL], vr[ADD ? R : 1][VPL];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      if (r0 + r < nrows) {
+#pragma unroll
+        for (int j = 0; j < VPL; ++j) {
+          const size_t off = static_cast<size_t>(r0 + r) * n + (j * 32 + lane) * 8;
+          vc[r][j] = ld_global_cg_v4(c + off);
+          if (ADD) vr[r][j] = ld_global_nc_v4(residual + off);
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      if (r0 + r < nrows) {   // uniform over the warp
+        float x[VPL][8];
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < VPL; ++j) {
+          float fo[8];
+          VecTraits<__half>::unpack(vc[r][j], fo);
+          if (ADD) {
+            float fi[8], fb[8];
+            VecTraits<__half>::unpack(vr[r][j], fi);
+            VecTraits<__half>::unpack(ld_global_v4(bias + (j * 32 + lane) * 8), fb);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) fo[e] += fi[e] + fb[e];
+          }
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            x[j][e] = fo[e];
+            sum += x[j][e];
+          }
+        }
+        const float mean = warp_sum(sum) * inv_n;
+        float sq = 0.f;
+#pragma unroll
+        for (int j = 0; j < VPL; ++j) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float dlt = x[j][e] - mean;
+            sq += dlt * dlt;
+          }
+        }
+        const float rstd = rsqrtf(warp_sum(sq) * inv_n + eps);
+#pragma unroll
+        for (int j = 0; j < VPL; ++j) {
+          float fg[8], fbe[8], y[8];
+          VecTraits<__half>::unpack(ld_global_v4(gamma + (j * 32 + lane) * 8), fg);
+          VecTraits<__half>::unpack(ld_global_v4(beta + (j * 32 + lane) * 8), fbe);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) y[e] = (x[j][e] - mean) * rstd * fg[e] + fbe[e];
+          st_global_v4(c + static_cast<size_t>(r0 + r) * n + (j * 32 + lane) * 8, VecTraits<__half>::pack(y));
+        }
+      }
+    }
+  }
+}
+
 template <int BN>
 struct Cfg {
   static constexpr int kStages = (BN == 256) ? 4 : 6;
@@ -174,6 +260,7 @@ enum Site : int {
   kSiteMmaDrain = 5,
   kSiteEpilogueFull = 6,
   kSiteSmemAlign = 7,
+  kSiteLnMailbox = 8,
 };
 
 template <int BN, int EPI>
@@ -413,14 +500,15 @@ struct PairCfg {
   static constexpr int kTmemCols = 2 * BN;
 };
 
-template <int EPI>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
+// VPL: 16-byte vectors of a C row per lane in the LayerNorm warps (N / 256); 0 for the other epilogues.
+template <int EPI, int VPL>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(threads_of(EPI), 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                          const __grid_constant__ CUtensorMap tmap_b,
                          const __grid_constant__ CUtensorMap tmap_b_half, __half* __restrict__ C,
                          const __half* __restrict__ bias, const __half* __restrict__ residual,
                          const int* __restrict__ m_ptr, int max_m, int N, int K, int* status_word,
-                         int reverse_m) {
+                         int reverse_m, const GemmLayerNorm ln) {
   using cfg = PairCfg;
   constexpr int S = cfg::kStages;
   constexpr int BN = cfg::BN;
@@ -451,6 +539,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const uint32_t drain_bar = bar0 + 8u * (2 * S + 4);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + cfg::kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  // LayerNorm variants: ln_box[e] = first row + 1 of a complete 32-row block posted by epilogue
+  // warp e (0 = empty), ln_done[e] = that warp has left its loop
+  volatile int* ln_box = reinterpret_cast<volatile int*>(tmem_slot + 2);
+  volatile int* ln_done = ln_box + kEpilogueWarps;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -465,6 +557,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     mbar_init(drain_bar, 1);
     *abort_flag = 0;
+    for (int e = 0; e < 2 * kEpilogueWarps; ++e) ln_box[e] = 0;
     fence_mbar_init();
     fence_proxy_async_smem();
   }
@@ -587,8 +680,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       umma_commit_pair(drain_bar);
       if (!mbar_wait(drain_bar, 0u, abort_flag) && *abort_flag == 0) fail(kSiteMmaDrain);
     }
-  } else {
+  } else if (warp < 2 + kEpilogueWarps) {
     // ------------------------- epilogue (both CTAs) -------------------------
+    constexpr int kBase = base_epi(EPI);
     const int quad = warp & 3;
     const int ew = warp - 2;
     const int half = ew >> 2;
@@ -603,7 +697,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       const int col0 = pu.col0 + half * wcols;
-      if (EPI != kEpiNone) {
+      if (kBase != kEpiNone) {
         if (lane < wcols / 8) st_shared_v4(bias_s + lane * 16, ld_global_v4(bias + col0 + lane * 8));
         __syncwarp();
       }
@@ -618,11 +712,88 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
           tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN + half * wcols;
       __half* ctile = C + static_cast<size_t>(row0) * N + col0;
       const uint32_t empty0 = mapa_shared(tmem_empty_bar(acc), 0);
-      const __half* rtile = EPI == kEpiBiasResidual ? residual + static_cast<size_t>(row0) * N + col0 : nullptr;
-      epilogue_warp_tile<EPI>(t_row, ctile, N, M - row0, bias_s, buf, lane, wcols / 64, rtile, [&] {
+      const __half* rtile = kBase == kEpiBiasResidual ? residual + static_cast<size_t>(row0) * N + col0 : nullptr;
+      epilogue_warp_tile<kBase>(t_row, ctile, N, M - row0, bias_s, buf, lane, wcols / 64, rtile, [&] {
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(empty0);
       });
+      if constexpr (has_ln(EPI)) {
+        // Count this warp's columns for its 32 rows.  Release: the stores above are ordered
+        // before the count; acquire: the warp that completes the row block sees all of them.
+        __threadfence();
+        __syncwarp();
+        const int group = row0 >> 5;
+        int before = 0;
+        if (lane == 0) before = atomicAdd(ln.counters + group, wcols);
+        before = __shfl_sync(0xffffffffu, before, 0);
+        if (before + wcols == N) {
+          __threadfence();
+          const int nrows = min(32, M - row0);
+          if (lane == 0) {
+            ln.counters[group] = 0;  // nobody else touches it any more: zero again for the next launch
+            if (nrows > 0) {
+              // hand the block to this warp's LayerNorm warp; its mailbox is empty unless that warp is
+              // still busy with the block posted three or more tiles ago (it never waits for anybody)
+              unsigned long long t0 = 0;
+              bool empty = true;
+              while (ln_box[ew] != 0) {
+                __nanosleep(64);
+                const unsigned long long now = globaltimer_ns();
+                if (t0 == 0) t0 = now;
+                else if (now - t0 > kWaitTimeoutNs) {
+                  fail(kSiteLnMailbox);
+                  empty = false;
+                  break;
+                }
+              }
+              if (empty) {
+                __threadfence_block();
+                ln_box[ew] = row0 + 1;
+              }
+            }
+          }
+          __syncwarp();
+        }
+      }
+    }
+    if constexpr (has_ln(EPI)) {
+      __syncwarp();
+      if (lane == 0) {
+        __threadfence_block();  // a posted block is visible before the flag
+        ln_done[ew] = 1;
+      }
+    }
+  } else if constexpr (has_ln(EPI)) {
+    // ------------------------- LayerNorm warps (both CTAs) -------------------------
+    const int hw = warp - (2 + kEpilogueWarps);
+    unsigned long long t0 = 0;
+    for (;;) {
+      bool any = false, all_done = true;
+      for (int e = hw; e < kEpilogueWarps; e += kLnWarps) {
+        const int done = ln_done[e];  // read before the mailbox: a warp posts before it sets the flag
+        const int v = ln_box[e];
+        if (v != 0) {
+          any = true;
+          __threadfence();  // the poster saw the complete block; order this warp's reads behind that
+          const int row0 = v - 1;
+          if constexpr (VPL > 0)
+            ln_rows<VPL, EPI == kEpiLayerNorm>(C + static_cast<size_t>(row0) * N,
+                                               residual + static_cast<size_t>(row0) * N, bias, ln.gamma, ln.beta, N,
+                                               min(32, M - row0), ln.eps, lane);
+          __syncwarp();
+          if (lane == 0) ln_box[e] = 0;
+        }
+        if (!done) all_done = false;
+      }
+      if (all_done && !any) break;
+      if (!any) {
+        __nanosleep(128);
+        const unsigned long long now = globaltimer_ns();  // bounded like every other wait
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > 4 * kWaitTimeoutNs) break;
+      } else {
+        t0 = 0;
+      }
     }
   }
 
@@ -636,46 +807,72 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
 }
 
-template <int EPI>
+template <int EPI, int VPL>
 cudaError_t launch_pair_epi(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tbh,
                             const __half* bias, const __half* residual, __half* c,
                             const int* m_ptr, int max_m, int n, int k, int* status_word, int reverse_m,
-                            cudaStream_t stream) {
+                            const GemmLayerNorm& ln, cudaStream_t stream) {
   using cfg = PairCfg;
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<EPI>,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize, cfg::kSmemBytes);
+  static PerDeviceOnce once;  // function attributes are per device
+  const cudaError_t once_err = once.run([] {
+    return cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<EPI, VPL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                cfg::kSmemBytes);
   });
-  if (attr_err != cudaSuccess) return attr_err;
+  if (once_err != cudaSuccess) return once_err;
   const long long max_tiles = static_cast<long long>((max_m + 2 * BM - 1) / (2 * BM)) * (n / cfg::BN);
   long long pairs = sm_count() / 2;
   if (pairs > max_tiles) pairs = max_tiles;
   if (pairs < 1) pairs = 1;
-  return launch_pdl(gemm_tcgen05_pair_kernel<EPI>, dim3(static_cast<int>(2 * pairs)), dim3(kNumThreads),
-                    cfg::kSmemBytes, stream, ta, tb, tbh, c, bias, residual, m_ptr, max_m, n, k, status_word, reverse_m);
+  return launch_pdl(gemm_tcgen05_pair_kernel<EPI, VPL>, dim3(static_cast<int>(2 * pairs)), dim3(threads_of(EPI)),
+                    cfg::kSmemBytes, stream, ta, tb, tbh, c, bias, residual, m_ptr, max_m, n, k, status_word, reverse_m,
+                    ln);
+}
+
+// LayerNorm variants: one instantiation per row width (N / 256 vectors per lane).
+template <int EPI>
+cudaError_t launch_pair_ln(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tbh,
+                           const __half* bias, const __half* residual, __half* c, const int* m_ptr, int max_m,
+                           int n, int k, int* status_word, int reverse_m, const GemmLayerNorm& ln,
+                           cudaStream_t stream) {
+#define ETB_LN_CASE(V)                                                                                            \
+  case V:                                                                                                         \
+    return launch_pair_epi<EPI, V>(ta, tb, tbh, bias, residual, c, m_ptr, max_m, n, k, status_word, reverse_m, ln, \
+                                   stream)
+  switch (n >> 8) {
+    ETB_LN_CASE(1);
+    ETB_LN_CASE(2);
+    ETB_LN_CASE(3);
+    ETB_LN_CASE(4);
+    default:
+      return cudaErrorInvalidValue;
+  }
+#undef ETB_LN_CASE
 }
 
 cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tbh,
                         const __half* bias, const __half* residual, __half* c,
                         const int* m_ptr, int max_m, int n, int k, int epilogue, int* status_word,
-                        int reverse_m, cudaStream_t stream) {
+                        int reverse_m, const GemmLayerNorm& ln, cudaStream_t stream) {
+#define ETB_PAIR_CASE(E)                                                                                      \
+  case E:                                                                                                     \
+    return launch_pair_epi<E, 0>(ta, tb, tbh, bias, residual, c, m_ptr, max_m, n, k, status_word, reverse_m, ln, \
+                                 stream)
   switch (epilogue) {
-    case kEpiNone:
-      return launch_pair_epi<kEpiNone>(ta, tb, tbh, bias, residual, c, m_ptr, max_m, n, k, status_word, reverse_m, stream);
-    case kEpiBias:
-      return launch_pair_epi<kEpiBias>(ta, tb, tbh, bias, residual, c, m_ptr, max_m, n, k, status_word, reverse_m, stream);
-    case kEpiBiasGelu:
-      return launch_pair_epi<kEpiBiasGelu>(ta, tb, tbh, bias, residual, c, m_ptr, max_m, n, k, status_word, reverse_m, stream);
-    case kEpiBiasTanh:
-      return launch_pair_epi<kEpiBiasTanh>(ta, tb, tbh, bias, residual, c, m_ptr, max_m, n, k, status_word, reverse_m, stream);
-    case kEpiBiasResidual:
-      return launch_pair_epi<kEpiBiasResidual>(ta, tb, tbh, bias, residual, c, m_ptr, max_m, n, k, status_word,
-                                               reverse_m, stream);
+    ETB_PAIR_CASE(kEpiNone);
+    ETB_PAIR_CASE(kEpiBias);
+    ETB_PAIR_CASE(kEpiBiasGelu);
+    ETB_PAIR_CASE(kEpiBiasTanh);
+    ETB_PAIR_CASE(kEpiBiasResidual);
+    case kEpiResidualLayerNorm:
+      return launch_pair_ln<kEpiResidualLayerNorm>(ta, tb, tbh, bias, residual, c, m_ptr, max_m, n, k, status_word,
+                                                   reverse_m, ln, stream);
+    case kEpiLayerNorm:
+      return launch_pair_ln<kEpiLayerNorm>(ta, tb, tbh, bias, residual, c, m_ptr, max_m, n, k, status_word,
+                                           reverse_m, ln, stream);
     default:
       return cudaErrorInvalidValue;
   }
+#undef ETB_PAIR_CASE
 }
 
 template <int BN, int EPI>
@@ -683,13 +880,13 @@ cudaError_t launch_bn_epi(const CUtensorMap& ta, const CUtensorMap& tb, const __
                           const int* m_ptr, int max_m, int n, int k, int* status_word, int reverse_m,
                           cudaStream_t stream) {
   using cfg = Cfg<BN>;
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI>,
+  static PerDeviceOnce once;  // function attributes are per device
+  const cudaError_t once_err = once.run([] {
+    cudaError_t attr_err = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI>,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, cfg::kSmemBytes);
+    return attr_err;
   });
-  if (attr_err != cudaSuccess) return attr_err;
+  if (once_err != cudaSuccess) return once_err;
   const long long max_tiles = static_cast<long long>((max_m + BM - 1) / BM) * (n / BN);
   long long grid = sm_count();
   if (grid > max_tiles) grid = max_tiles;
@@ -734,8 +931,27 @@ EncodeTiledFn get_encode_tiled() {
   return fn;
 }
 
+const CUtensorMap* TensorMapCache::find(int dtype_tag, const void* base, uint64_t rows, uint64_t cols,
+                                        uint64_t row_stride, uint32_t box_rows, uint32_t box_cols) {
+  const auto it = entries_.find(Key{dtype_tag, base, rows, cols, row_stride, box_rows, box_cols});
+  return it == entries_.end() ? nullptr : &it->second;
+}
+
+void TensorMapCache::insert(int dtype_tag, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride,
+                            uint32_t box_rows, uint32_t box_cols, const CUtensorMap& map) {
+  if (entries_.size() >= kMaxEntries) entries_.clear();
+  entries_[Key{dtype_tag, base, rows, cols, row_stride, box_rows, box_cols}] = map;
+}
+
 bool encode_2d_fp16_sw128(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
-                          uint64_t row_stride_elems, uint32_t box_rows, uint32_t box_cols) {
+                          uint64_t row_stride_elems, uint32_t box_rows, uint32_t box_cols,
+                          TensorMapCache* cache) {
+  if (cache != nullptr) {
+    if (const CUtensorMap* hit = cache->find(2, base, rows, cols, row_stride_elems, box_rows, box_cols)) {
+      *map = *hit;
+      return true;
+    }
+  }
   EncodeTiledFn fn = get_encode_tiled();
   if (fn == nullptr) return false;
   const cuuint64_t dims[2] = {cols, rows};
@@ -746,43 +962,51 @@ bool encode_2d_fp16_sw128(CUtensorMap* map, const void* base, uint64_t rows, uin
                         strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS;
+  if (r != CUDA_SUCCESS) return false;
+  if (cache != nullptr) cache->insert(2, base, rows, cols, row_stride_elems, box_rows, box_cols, *map);
+  return true;
 }
 
 cudaError_t launch_gemm_tcgen05(const __half* a, const __half* w_packed, const __half* bias,
                                 __half* c, const int* m_ptr, int max_m, int n, int k, int epilogue,
-                                int* status_word, cudaStream_t stream, bool reverse_m, const __half* residual) {
+                                int* status_word, cudaStream_t stream, bool reverse_m, const __half* residual,
+                                TensorMapCache* maps, const GemmLayerNorm* ln) {
   if (max_m <= 0) return cudaSuccess;
   if (n <= 0 || k <= 0 || (n % 128) != 0 || (k % 8) != 0) return cudaErrorInvalidValue;
   if ((reinterpret_cast<uintptr_t>(a) & 15u) || (reinterpret_cast<uintptr_t>(w_packed) & 15u) ||
       (reinterpret_cast<uintptr_t>(c) & 15u) || (bias && (reinterpret_cast<uintptr_t>(bias) & 15u)))
     return cudaErrorMisalignedAddress;
   if (epilogue != kEpiNone && bias == nullptr) return cudaErrorInvalidValue;
-  if (epilogue == kEpiBiasResidual && (residual == nullptr || (reinterpret_cast<uintptr_t>(residual) & 15u)))
+  const bool needs_residual =
+      epilogue == kEpiBiasResidual || epilogue == kEpiResidualLayerNorm || epilogue == kEpiLayerNorm;
+  if (needs_residual && (residual == nullptr || (reinterpret_cast<uintptr_t>(residual) & 15u)))
     return cudaErrorInvalidValue;
+  GemmLayerNorm lnp;
+  if (has_ln(epilogue)) {
+    if (ln == nullptr || ln->gamma == nullptr || ln->beta == nullptr || ln->counters == nullptr ||
+        !gemm_layernorm_supported(n))
+      return cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(ln->gamma) & 15u) || (reinterpret_cast<uintptr_t>(ln->beta) & 15u))
+      return cudaErrorMisalignedAddress;
+    lnp = *ln;
+  }
   const int bn = (n % 256 == 0) ? 256 : 128;
-  static const bool single_cta = [] {
-    const char* e = getenv("ETB_GEMM_SINGLE_CTA");   // debugging: force the one-CTA kernel
-    return e != nullptr && e[0] == '1';
-  }();
-  const bool pair = (bn == 256) && !single_cta;
+  const bool pair = bn == 256;
   CUtensorMap ta, tb;
   if (!encode_2d_fp16_sw128(&ta, a, static_cast<uint64_t>(max_m), static_cast<uint64_t>(k),
-                            static_cast<uint64_t>(k), BM, BK))
+                            static_cast<uint64_t>(k), BM, BK, maps))
     return cudaErrorInvalidValue;
   if (!encode_2d_fp16_sw128(&tb, w_packed, static_cast<uint64_t>(n), static_cast<uint64_t>(k),
-                            static_cast<uint64_t>(k), static_cast<uint32_t>(pair ? 128 : bn), BK))
+                            static_cast<uint64_t>(k), static_cast<uint32_t>(pair ? 128 : bn), BK, maps))
     return cudaErrorInvalidValue;
   const int rev = reverse_m ? 1 : 0;
   if (pair) {
     CUtensorMap tbh;  // 64 W rows per CTA: the half-width units of the last round
     if (!encode_2d_fp16_sw128(&tbh, w_packed, static_cast<uint64_t>(n), static_cast<uint64_t>(k),
-                              static_cast<uint64_t>(k), 64, BK))
+                              static_cast<uint64_t>(k), 64, BK, maps))
       return cudaErrorInvalidValue;
-    return launch_pair(ta, tb, tbh, bias, residual, c, m_ptr, max_m, n, k, epilogue, status_word, rev, stream);
+    return launch_pair(ta, tb, tbh, bias, residual, c, m_ptr, max_m, n, k, epilogue, status_word, rev, lnp, stream);
   }
-  if (bn == 256)
-    return launch_bn<256>(ta, tb, bias, residual, c, m_ptr, max_m, n, k, epilogue, status_word, rev, stream);
   return launch_bn<128>(ta, tb, bias, residual, c, m_ptr, max_m, n, k, epilogue, status_word, rev, stream);
 }
 

@@ -727,7 +727,14 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmap_a_hi, const __g
   }
 }
 
-bool encode_2d_f32_sw128(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+bool encode_2d_f32_sw128(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                         TensorMapCache* cache) {
+  if (cache != nullptr) {
+    if (const CUtensorMap* hit = cache->find(4, base, rows, cols, cols, box_rows, BK)) {
+      *map = *hit;
+      return true;
+    }
+  }
   EncodeTiledFn fn = get_encode_tiled();
   if (fn == nullptr) return false;
   const cuuint64_t dims[2] = {cols, rows};
@@ -737,20 +744,22 @@ bool encode_2d_f32_sw128(CUtensorMap* map, const void* base, uint64_t rows, uint
   const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box,
                         elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS;
+  if (r != CUDA_SUCCESS) return false;
+  if (cache != nullptr) cache->insert(4, base, rows, cols, cols, box_rows, BK, *map);
+  return true;
 }
 
 template <int EPI>
 cudaError_t launch_epi(const CUtensorMap& tah, const CUtensorMap& tal, const CUtensorMap& twh, const CUtensorMap& twl,
                        const float* bias, float* c, float* c_lo, const int* m_ptr, int max_m, int n, int k,
                        int* status_word, int reverse_m, cudaStream_t stream) {
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(gemm_tf32x3_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  static PerDeviceOnce once;  // function attributes are per device
+  const cudaError_t once_err = once.run([] {
+    cudaError_t attr_err = cudaFuncSetAttribute(gemm_tf32x3_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     Cfg::kSmemBytes);
+    return attr_err;
   });
-  if (attr_err != cudaSuccess) return attr_err;
+  if (once_err != cudaSuccess) return once_err;
   const long long max_tiles = static_cast<long long>((max_m + BM - 1) / BM) * (n / BN);
   long long grid = sm_count();
   if (grid > max_tiles) grid = max_tiles;
@@ -764,13 +773,13 @@ cudaError_t launch_pair_epi(const CUtensorMap& tah, const CUtensorMap& tal, cons
                             const CUtensorMap& twl, const CUtensorMap& twhh, const CUtensorMap& twlh, const float* bias,
                             float* c, float* c_lo, const int* m_ptr, int max_m, int n, int k, int* status_word,
                             int reverse_m, cudaStream_t stream) {
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(gemm_tf32x3_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  static PerDeviceOnce once;  // function attributes are per device
+  const cudaError_t once_err = once.run([] {
+    cudaError_t attr_err = cudaFuncSetAttribute(gemm_tf32x3_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     PairCfg::kSmemBytes);
+    return attr_err;
   });
-  if (attr_err != cudaSuccess) return attr_err;
+  if (once_err != cudaSuccess) return once_err;
   const long long max_tiles = static_cast<long long>((max_m + BM2 - 1) / BM2) * (n / BN2);
   long long pairs = sm_count() / 2;
   if (pairs > max_tiles) pairs = max_tiles;
@@ -796,7 +805,8 @@ cudaError_t launch_split_tf32(const float* x, float* hi, float* lo, const int* r
 
 cudaError_t launch_gemm_tf32x3(const float* a_hi, const float* a_lo, const float* w_hi, const float* w_lo,
                                const float* bias, float* c, const int* m_ptr, int max_m, int n, int k,
-                               int epilogue, int* status_word, cudaStream_t stream, bool reverse_m, float* c_lo) {
+                               int epilogue, int* status_word, cudaStream_t stream, bool reverse_m, float* c_lo,
+                               TensorMapCache* maps) {
   if (max_m <= 0) return cudaSuccess;
   if (n <= 0 || k <= 0 || (n % 128) != 0 || (k % BK) != 0) return cudaErrorInvalidValue;
   for (const void* p : {static_cast<const void*>(a_hi), static_cast<const void*>(a_lo),
@@ -807,24 +817,20 @@ cudaError_t launch_gemm_tf32x3(const float* a_hi, const float* a_lo, const float
   if (c_lo != nullptr && (reinterpret_cast<uintptr_t>(c_lo) & 15u)) return cudaErrorMisalignedAddress;
   if (epilogue != kEpiNone && bias == nullptr) return cudaErrorInvalidValue;
   CUtensorMap tah, tal, twh, twl;
-  if (!encode_2d_f32_sw128(&tah, a_hi, static_cast<uint64_t>(max_m), static_cast<uint64_t>(k), BM) ||
-      !encode_2d_f32_sw128(&tal, a_lo, static_cast<uint64_t>(max_m), static_cast<uint64_t>(k), BM) ||
-      !encode_2d_f32_sw128(&twh, w_hi, static_cast<uint64_t>(n), static_cast<uint64_t>(k), BN) ||
-      !encode_2d_f32_sw128(&twl, w_lo, static_cast<uint64_t>(n), static_cast<uint64_t>(k), BN))
+  if (!encode_2d_f32_sw128(&tah, a_hi, static_cast<uint64_t>(max_m), static_cast<uint64_t>(k), BM, maps) ||
+      !encode_2d_f32_sw128(&tal, a_lo, static_cast<uint64_t>(max_m), static_cast<uint64_t>(k), BM, maps) ||
+      !encode_2d_f32_sw128(&twh, w_hi, static_cast<uint64_t>(n), static_cast<uint64_t>(k), BN, maps) ||
+      !encode_2d_f32_sw128(&twl, w_lo, static_cast<uint64_t>(n), static_cast<uint64_t>(k), BN, maps))
     return cudaErrorInvalidValue;
   const int rev = reverse_m ? 1 : 0;
-  static const bool single_cta = [] {
-    const char* e = getenv("ETB_GEMM_SINGLE_CTA");  // debugging: force the one-CTA kernel
-    return e != nullptr && e[0] == '1';
-  }();
   // The pair kernel needs enough 256 x 256 tiles at capacity to occupy the pairs; below that
   // the 128 x 128 tiles of the one-CTA kernel spread a small batch over more SMs.
   const long long pair_tiles = static_cast<long long>((max_m + BM2 - 1) / BM2) * (n / BN2);
-  if ((n % BN2) == 0 && !single_cta && pair_tiles >= sm_count() / 2) {
+  if ((n % BN2) == 0 && pair_tiles >= sm_count() / 2) {
     // the W maps above (128-row boxes) serve whole tiles; half-width units take 64 rows per CTA
     CUtensorMap twhh, twlh;
-    if (!encode_2d_f32_sw128(&twhh, w_hi, static_cast<uint64_t>(n), static_cast<uint64_t>(k), 64) ||
-        !encode_2d_f32_sw128(&twlh, w_lo, static_cast<uint64_t>(n), static_cast<uint64_t>(k), 64))
+    if (!encode_2d_f32_sw128(&twhh, w_hi, static_cast<uint64_t>(n), static_cast<uint64_t>(k), 64, maps) ||
+        !encode_2d_f32_sw128(&twlh, w_lo, static_cast<uint64_t>(n), static_cast<uint64_t>(k), 64, maps))
       return cudaErrorInvalidValue;
 #define ETB_PAIR_CASE(E) \
   case E:                \

@@ -272,7 +272,6 @@ namespace {
 
 static __device__ __align__(256) int g_noalloc_row_lengths[ET_NOALLOC_MAX_BATCH];
 
-constexpr int kMaxDevices = 64;
 std::mutex g_noalloc_mutex;
 int* g_noalloc_ptr[kMaxDevices] = {};
 
@@ -297,10 +296,11 @@ cudaError_t noalloc_scratch(int** out) {
 }  // namespace
 }  // namespace etb
 
-extern "C" int et_padding_offsets_noalloc(const int* mask, int batch_size, int seq_len, int* prefix_sum,
-                                          int* valid_word_num, int* batch_idx, int* word_idx,
-                                          int* seq_len_out, int* cu_seqlens, int* padding_offset,
-                                          void* stream) {
+namespace {
+
+int noalloc_impl(const int* mask, int batch_size, int seq_len, int* prefix_sum, int* valid_word_num,
+                 int* batch_idx, int* word_idx, int* seq_len_out, int* cu_seqlens, int* padding_offset,
+                 void* stream) {
   if (batch_size < 0 || seq_len < 0) {
     etb::set_global_error("et_padding_offsets_noalloc: negative batch_size or seq_len");
     return ET_INVALID_ARGUMENT;
@@ -332,4 +332,19 @@ extern "C" int et_padding_offsets_noalloc(const int* mask, int batch_size, int s
     return ET_CUDA_ERROR;
   }
   return ET_OK;
+}
+
+}  // namespace
+
+extern "C" int et_padding_offsets_noalloc(const int* mask, int batch_size, int seq_len, int* prefix_sum,
+                                          int* valid_word_num, int* batch_idx, int* word_idx,
+                                          int* seq_len_out, int* cu_seqlens, int* padding_offset,
+                                          void* stream) {
+  // The error texts are std::strings: no exception (a failed host allocation) may cross the C ABI.
+  try {
+    return noalloc_impl(mask, batch_size, seq_len, prefix_sum, valid_word_num, batch_idx, word_idx, seq_len_out,
+                        cu_seqlens, padding_offset, stream);
+  } catch (...) {
+    return ET_CUDA_ERROR;
+  }
 }

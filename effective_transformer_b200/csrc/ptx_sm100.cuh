@@ -8,6 +8,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <unordered_map>
+
 namespace etb {
 namespace ptx {
 
@@ -52,7 +54,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait.  `abort_flag` is a shared-memory word any role sets when it
 // gives up, so that the others stop waiting too.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait_ns(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                             unsigned long long limit_ns) {
   unsigned long long t0 = 0;
   for (uint32_t spin = 1;; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -60,9 +63,12 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       if (*abort_flag != 0) return false;
       const unsigned long long now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > kWaitTimeoutNs) return false;
+      else if (now - t0 > limit_ns) return false;
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  return mbar_wait_ns(bar, parity, abort_flag, kWaitTimeoutNs);
 }
 
 // ---- TMA --------------------------------------------------------------------
@@ -237,8 +243,48 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn get_encode_tiled();
+// Encoded tensor maps kept by their owner (an encoder handle) so that a launch on the same
+// buffer, shape and box reuses the descriptor instead of calling the driver's encoder again:
+// a pass makes about 150 such look-ups.  Not thread-safe: one cache per handle, and calls on
+// a handle are not re-entrant.
+class TensorMapCache {
+ public:
+  // The cached map for this key, or nullptr when there is none yet (then *slot points at a
+  // fresh entry for the caller to fill; the entry only counts once `commit` has been called).
+  const CUtensorMap* find(int dtype_tag, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride,
+                          uint32_t box_rows, uint32_t box_cols);
+  void insert(int dtype_tag, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride,
+              uint32_t box_rows, uint32_t box_cols, const CUtensorMap& map);
+  void clear() { entries_.clear(); }
+  size_t size() const { return entries_.size(); }
+
+ private:
+  struct Key {
+    int tag;
+    const void* base;
+    uint64_t rows, cols, stride;
+    uint32_t box_rows, box_cols;
+    bool operator==(const Key& o) const {
+      return tag == o.tag && base == o.base && rows == o.rows && cols == o.cols && stride == o.stride &&
+             box_rows == o.box_rows && box_cols == o.box_cols;
+    }
+  };
+  struct KeyHash {
+    size_t operator()(const Key& k) const {
+      uint64_t h = reinterpret_cast<uintptr_t>(k.base) * 0x9E3779B97F4A7C15ull;
+      h ^= (k.rows + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
+      h ^= (k.cols * 1315423911ull + k.stride * 2654435761ull + k.box_rows * 97u + k.box_cols * 31u + k.tag);
+      return static_cast<size_t>(h);
+    }
+  };
+  static constexpr size_t kMaxEntries = 1024;  // caller-owned buffers may change from call to call
+  std::unordered_map<Key, CUtensorMap, KeyHash> entries_;
+};
+
 // fp16 row-major [rows, cols] tensor, box [box_rows, box_cols], 128-byte swizzle.
+// `cache` (optional): the descriptor is taken from / added to it.
 bool encode_2d_fp16_sw128(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
-                          uint64_t row_stride_elems, uint32_t box_rows, uint32_t box_cols);
+                          uint64_t row_stride_elems, uint32_t box_rows, uint32_t box_cols,
+                          TensorMapCache* cache = nullptr);
 
 }  // namespace etb

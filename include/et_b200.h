@@ -148,6 +148,9 @@ int et_set_layer_weights(et_handle_t handle, int layer, const void* const* weigh
 /* Bytes of handle-owned workspace for a [B, S] batch (size_t arithmetic; the
  * reference's int formula overflows, tf_op/bert_transformer_op.cu.cc:75-77). */
 int et_workspace_bytes(et_handle_t handle, int batch_size, int seq_len, size_t* out_bytes);
+/* What et_create allocated for the handle's own (max_batch_size, max_seq_len):
+ * equals et_workspace_bytes at that shape (both are read from one table). */
+int et_workspace_allocated_bytes(et_handle_t handle, size_t* out_bytes);
 
 /* ---- the three operators ------------------------------------------------ */
 
@@ -302,6 +305,27 @@ int et_copy_to_host(void* dst_host, const void* src_device, size_t bytes, void* 
  * (plain fp32 FMA arithmetic; for debugging and as a second opinion). */
 int et_set_debug_simt(et_handle_t handle, int use_simt);
 
+/* 1 (default, fp16 handles with hidden a multiple of 256 up to 1024): the two
+ * add_bias_input_layernorm launches of a layer (tf_op/bert_transformer_op.cu.cc:
+ * 211-213,242-246) run inside the attention-output and second feed-forward
+ * projection kernels: a layer is 5 launches.  0: one LayerNorm kernel behind
+ * each of them (7 launches).  Changing the setting drops recorded graphs. */
+int et_set_fused_layernorm(et_handle_t handle, int enable);
+
+/* Chunking of the host-buffer call (et_forward_host): number of chunks, share of
+ * a middle chunk when the first and the last have 1, and whether that share
+ * comes from the handle's own measurement (the first chunked call times the
+ * upload and a pass, the later calls use the shares that minimise the
+ * unoverlapped copies; ETB_HOST_MID_SHARE fixes the share instead). */
+int et_host_chunk_shares(et_handle_t handle, int* chunks, int* mid_share, int* measured);
+
+/* Failure-detection self-test: launches one CTA whose bounded wait (2 ms, on a
+ * barrier nobody arrives at; no copy or MMA in flight) runs out, so that it
+ * records a code in the handle's status word and returns normally.  The next
+ * et_device_status reports (15 << 8 | 1) and clears the word; the host-buffer
+ * calls map a non-zero word to ET_DEVICE_TIMEOUT.  No reference counterpart. */
+int et_selftest_wait_timeout(et_handle_t handle, void* stream);
+
 /* ---- kernel-level entry points (one per reference launcher) --------------
  * dtype is an et_dtype_t; all pointers are device pointers; `valid_word_num`
  * is a DEVICE pointer to T (row counts are never read back to the host). */
@@ -436,6 +460,24 @@ int et_gemm(int dtype, const void* a, const void* w, const void* w_packed, const
             const int* m_ptr, int max_m, int n, int k, int epilogue, int use_simt, int* status_word,
             void* stream);
 int et_pack_weight(int dtype, const void* w, void* w_packed, int k, int n, void* stream);
+
+/* The tcgen05 GEMM (fp16) with the epilogues that take the layer's residual:
+ *   4  C = A*W + bias + residual                      (the second feed-forward
+ *      projection followed by a separate LayerNorm)
+ *   5  C = LayerNorm(A*W + bias + residual), bias and residual added in the
+ *      accumulator epilogue (tf_op/bert_transformer_op.cu.cc:229-246 in one kernel)
+ *   6  the same result with bias and residual added where the rows are
+ *      normalised (tf_op/bert_transformer_op.cu.cc:200-213 in one kernel)
+ * For 5 and 6 (N a multiple of 256, at most 1024) every 32-row block of C is
+ * normalised in place by the kernel as soon as its last column tile has been
+ * stored: semantics of add_bias_input_layernorm (cuda/cuda_kernels.cu:157-236),
+ * fp32 statistics, eps <= 0 means 1e-6.  `row_counters`: 8 * ceil(max_m / 256)
+ * ints (one per 32 rows of the 256-row tiles), zero before the call; the kernel
+ * leaves them zero.  `residual` is [max_m, N]
+ * and must not alias c. */
+int et_gemm_fused(const void* a, const void* w_packed, const void* bias, const void* residual,
+                  const void* gamma, const void* beta, float eps, int* row_counters, void* c,
+                  const int* m_ptr, int max_m, int n, int k, int epilogue, int* status_word, void* stream);
 
 /* The same call sites for the FP32 OperationType on the tensor cores, keeping
  * fp32 accuracy: every operand is split into two tf32 numbers, x = hi + lo with

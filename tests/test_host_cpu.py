@@ -96,6 +96,21 @@ owned = torch.zeros(spec.batch, dtype=torch.int32)
 owned[torch.from_numpy(shards[rank])] = 1
 dist.all_reduce(owned)
 assert bool(torch.all(owned == 1))
+# the optional output gather: every rank's padded block goes to rank 0, which restores the batch order
+from effective_transformer_b200.sharding import OutputGather, inverse_order
+S, H = 4, 8
+gather = OutputGather(shards, S, H, torch.float32, torch.device("cpu"), dst=0)
+local = torch.from_numpy(shards[rank].astype(np.float32)).reshape(-1, 1, 1).expand(-1, S, H).contiguous()
+for _ in range(2):                      # buffers are reused from call to call
+    full = gather(local)
+if rank == 0:
+    want = torch.arange(spec.batch, dtype=torch.float32).reshape(-1, 1, 1).expand(-1, S, H)
+    assert torch.equal(full, want)
+    assert gather.bytes_received == (spec.batch - len(shards[0])) * S * H * 4
+else:
+    assert full is None
+inv = inverse_order(shards)
+assert np.array_equal(np.concatenate(shards)[inv], np.arange(spec.batch))
 dist.destroy_process_group()
 sys.stdout.write("rank%d-ok\n" % rank)
 sys.stdout.flush()

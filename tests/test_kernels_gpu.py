@@ -411,3 +411,120 @@ def test_gemm_fp32_on_tensor_cores_keeps_fp32_accuracy(m, cap, n, k, epi):
         one_term = (a_hi[:m].double() @ w_hi.double().t())
         plain = a[:m].double() @ w.double()
         assert float((one_term - plain).abs().max()) > 20 * float((c[:m].double() - ref).abs().max()) or k < 128
+
+
+# ---- epilogues that take the layer's residual: bias + residual, and the LayerNorm inside the GEMM -------
+def _gemm_fused_case(m, cap, n, k, epi, seed=0, counters_check=True):
+    """et_gemm_fused against the float64 oracle: C = A W + bias + residual (4), and its LayerNorm
+    (5: bias/residual added in the accumulator epilogue, 6: added where the rows are normalised)."""
+    rng = np.random.RandomState(seed + m + n + k + epi)
+    h = torch.float16
+    a = dev(rng.randn(cap, k).astype(np.float32), h)
+    w = dev((rng.randn(k, n) / math.sqrt(k)).astype(np.float32), h)
+    bias = dev(0.5 * rng.randn(n).astype(np.float32), h)
+    res = dev(rng.randn(cap, n).astype(np.float32), h)
+    gamma = dev((1 + 0.2 * rng.randn(n)).astype(np.float32), h)
+    beta = dev(0.3 * rng.randn(n).astype(np.float32), h)
+    c = torch.full((cap, n), 3.0, dtype=h, device="cuda")
+    wp = torch.empty((n, k), dtype=h, device="cuda")
+    ok(lib().et_pack_weight(DT[h], iptr(w), iptr(wp), k, n, stream()))
+    counters = torch.zeros(8 * ((cap + 255) // 256) + 1, dtype=torch.int32, device="cuda")   # one per 32 rows of the 256-row tiles
+    mt = dev(np.array([m], np.int32))
+    st = status_word()
+    ok(lib().et_gemm_fused(iptr(a), iptr(wp), iptr(bias), iptr(res), iptr(gamma), iptr(beta), 1e-6, iptr(counters),
+                           iptr(c), iptr(mt), cap, n, k, epi, iptr(st), stream()))
+    torch.cuda.synchronize()
+    assert int(st[0]) == 0, f"device-side wait expired: status 0x{int(st[0]):x}"
+    pre = a[:m].double() @ w.double() + bias.double() + res[:m].double()
+    if epi == 4:
+        torch.testing.assert_close(c[:m].double(), pre, rtol=2e-3, atol=4e-3)
+    else:
+        mean = pre.mean(-1, keepdim=True)
+        var = ((pre - mean) ** 2).mean(-1, keepdim=True)
+        ref = (pre - mean) / torch.sqrt(var + 1e-6) * gamma.double() + beta.double()
+        # the pre-LayerNorm sum is stored in fp16 once (as the reference's half kernel adds in half2,
+        # cuda/cuda_kernels.cu:214): one fp16 rounding of an O(1) value in front of the normalisation
+        torch.testing.assert_close(c[:m].double(), ref, rtol=3e-3, atol=6e-3)
+    assert torch.all(c[m:] == 3.0), "rows past M were written"
+    if counters_check:
+        assert int(counters.abs().sum()) == 0, "the row counters must be zero again after the launch"
+
+
+@pytest.mark.parametrize("epi", [4, 5, 6])
+@pytest.mark.parametrize("m,cap,n,k", [(1, 1, 256, 64), (134, 256, 768, 768), (257, 300, 768, 3072),
+                                       (1000, 1000, 1024, 1024), (300, 384, 512, 128), (0, 64, 768, 128),
+                                       (31, 64, 768, 768), (33, 33, 1024, 4096)])
+def test_gemm_tcgen05_residual_and_layernorm_epilogues(m, cap, n, k, epi):
+    _gemm_fused_case(m, cap, n, k, epi)
+
+
+@pytest.mark.parametrize("epi", [4, 5, 6])
+@pytest.mark.parametrize("m,n,k", [(6500, 768, 768),      # last round cut into half-width units
+                                   (9372, 768, 3072),     # 37 tiles left = exactly half of the pairs
+                                   (9729, 768, 768),      # 43 left: not cut
+                                   (20000, 1024, 1024)])  # several rounds per pair: mailboxes are reused
+def test_gemm_tcgen05_residual_and_layernorm_epilogues_many_tiles(m, n, k, epi):
+    _gemm_fused_case(m, m, n, k, epi)
+
+
+def test_gemm_layernorm_epilogue_equals_gemm_then_layernorm_kernel():
+    """The rows the GEMM normalises itself are those of the two-kernel path: epilogue 4 followed by
+    add_bias_input_layernorm on one tensor, and epilogue 0 followed by the kernel with bias and
+    residual, bit for bit (same arithmetic in the same order)."""
+    rng = np.random.RandomState(5)
+    m, n, k = 4973, 768, 768
+    h = torch.float16
+    a = dev(rng.randn(m, k).astype(np.float32), h)
+    w = dev((rng.randn(k, n) / math.sqrt(k)).astype(np.float32), h)
+    bias = dev(0.5 * rng.randn(n).astype(np.float32), h)
+    res = dev(rng.randn(m, n).astype(np.float32), h)
+    gamma = dev((1 + 0.2 * rng.randn(n)).astype(np.float32), h)
+    beta = dev(0.3 * rng.randn(n).astype(np.float32), h)
+    wp = torch.empty((n, k), dtype=h, device="cuda")
+    ok(lib().et_pack_weight(DT[h], iptr(w), iptr(wp), k, n, stream()))
+    mt = dev(np.array([m], np.int32))
+    st = status_word()
+    counters = torch.zeros(8 * ((m + 255) // 256), dtype=torch.int32, device="cuda")
+    zero_bias = torch.zeros_like(bias)
+
+    def fused(epi):
+        c = torch.empty((m, n), dtype=h, device="cuda")
+        ok(lib().et_gemm_fused(iptr(a), iptr(wp), iptr(bias), iptr(res), iptr(gamma), iptr(beta), 1e-6,
+                               iptr(counters), iptr(c), iptr(mt), m, n, k, epi, iptr(st), stream()))
+        return c
+
+    # 5 == (4, then LayerNorm of one tensor)
+    two = fused(4)
+    ok(lib().et_add_bias_input_layernorm(DT[h], iptr(two), iptr(torch.zeros_like(two)), iptr(zero_bias), iptr(gamma),
+                                         iptr(beta), iptr(mt), m, n, 1e-6, stream()))
+    one = fused(5)
+    torch.cuda.synchronize()
+    assert int(st[0]) == 0
+    assert torch.equal(one, two)
+    # 6 == (plain GEMM, then LayerNorm with bias and residual)
+    plain = torch.empty((m, n), dtype=h, device="cuda")
+    ok(lib().et_gemm(DT[h], iptr(a), None, iptr(wp), None, iptr(plain), iptr(mt), m, n, k, 0, 0, iptr(st), stream()))
+    ok(lib().et_add_bias_input_layernorm(DT[h], iptr(plain), iptr(res), iptr(bias), iptr(gamma), iptr(beta), iptr(mt),
+                                         m, n, 1e-6, stream()))
+    one = fused(6)
+    torch.cuda.synchronize()
+    assert int(st[0]) == 0
+    assert torch.equal(one, plain)
+
+
+def test_gemm_fused_rejects_what_it_cannot_do():
+    z = torch.zeros(256, dtype=torch.float16, device="cuda")
+    cnt = torch.zeros(8, dtype=torch.int32, device="cuda")
+    mt = dev(np.array([1], np.int32))
+    bad = _capi.ET_INVALID_ARGUMENT
+    # N not a multiple of 256 / above 1024 for the LayerNorm epilogues, unknown epilogue, missing pointers
+    assert lib().et_gemm_fused(iptr(z), iptr(z), iptr(z), iptr(z), iptr(z), iptr(z), 1e-6, iptr(cnt), iptr(z),
+                               iptr(mt), 1, 128, 64, 5, None, stream()) == bad
+    assert lib().et_gemm_fused(iptr(z), iptr(z), iptr(z), iptr(z), iptr(z), iptr(z), 1e-6, iptr(cnt), iptr(z),
+                               iptr(mt), 1, 1280, 64, 6, None, stream()) == bad
+    assert lib().et_gemm_fused(iptr(z), iptr(z), iptr(z), iptr(z), iptr(z), iptr(z), 1e-6, iptr(cnt), iptr(z),
+                               iptr(mt), 1, 256, 64, 2, None, stream()) == bad
+    assert lib().et_gemm_fused(iptr(z), iptr(z), iptr(z), iptr(z), iptr(z), iptr(z), 1e-6, None, iptr(z),
+                               iptr(mt), 1, 256, 64, 5, None, stream()) == bad
+    assert lib().et_gemm_fused(iptr(z), iptr(z), iptr(z), None, iptr(z), iptr(z), 1e-6, iptr(cnt), iptr(z),
+                               iptr(mt), 1, 256, 64, 4, None, stream()) == bad
