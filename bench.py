@@ -329,8 +329,9 @@ def main():
     ap.add_argument("--shard-of", type=int, default=0,
                     help="one GPU only: time rank 0's shard of an N-way split of the batch (what one rank of "
                          "`--gpus N` runs), to study the small-batch regime without N GPUs")
-    ap.add_argument("--split-layernorm", action="store_true",
-                    help="A/B: a LayerNorm kernel behind each projection instead of the LayerNorm inside the GEMMs")
+    ap.add_argument("--fused-layernorm", action="store_true",
+                    help="A/B: the LayerNorms inside the projection kernels (et_set_fused_layernorm) instead of a "
+                         "LayerNorm kernel behind each projection")
     args = ap.parse_args()
     spec = W.WORKLOADS[args.workload]
     if args.impl == "reference":
@@ -370,8 +371,8 @@ def main():
     sh = spec.shape
     fp16 = spec.dtype == "fp16"
     main_pass = DevicePass(et, torch, spec, lengths, x_np, base.weights, dev, local)
-    if args.split_layernorm:
-        main_pass.eng.set_fused_layernorm(False)
+    if args.fused_layernorm:
+        main_pass.eng.set_fused_layernorm(True)
     eng, b, s, h = main_pass.eng, main_pass.b, main_pass.s, main_pass.h
     tokens_rank = main_pass.tokens
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)   # > 126 MB L2
@@ -515,8 +516,8 @@ def main():
                                     "in the forward pass" % (spec.batch, world)) if scaling == "strong" and world > 1
                                    else "sequences, token-balanced, no collective",
                        "l2": "256 MB buffer written between timed steps (untimed)",
-                       "layernorm": "LayerNorm kernels behind the projections" if args.split_layernorm
-                                    else "inside the projection kernels",
+                       "layernorm": "inside the projection kernels" if args.fused_layernorm
+                                    else "LayerNorm kernels behind the projections",
                        "launch": ("cuda-graph replay (et_graph_launch); per-kernel times from a second, eager pass"
                                   if args.launch == "graph"
                                   else "eager (et_forward), per-kernel events inside the timed steps")},
@@ -535,7 +536,9 @@ def main():
                            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                            "ms_per_step": e2e_total_ms / args.steps,
                            "host_chunk_shares": None if shares is None else
-                           {"chunks": shares[0], "shares": "1:%d:1" % shares[1], "measured_by_handle": shares[2]}}
+                           {"chunks": shares[0] if shares[1] > 0 else 1,
+                            "shares": ("1:%d:1" % shares[1]) if shares[1] > 0 else "one piece",
+                            "measured_by_handle": shares[2]}}
         if ids_ms is not None:
             line["e2e_from_token_ids"] = {
                 "value": tokens_all / (ids_total_ms / args.steps / 1000.0), "unit": UNIT,

@@ -103,8 +103,8 @@ class EffectiveTransformer:
         _capi.check(self._lib.et_set_debug_simt(self._h, 1 if on else 0), self._h)
 
     def set_fused_layernorm(self, on: bool) -> None:
-        """On (default): bias + residual + LayerNorm run inside the two hidden-wide projection
-        kernels (5 launches per layer); off: a LayerNorm kernel behind each of them (7)."""
+        """Off (default): a LayerNorm kernel behind each hidden-wide projection (7 launches per
+        layer); on: bias + residual + LayerNorm run inside those projection kernels (5)."""
         _capi.check(self._lib.et_set_fused_layernorm(self._h, 1 if on else 0), self._h)
 
     def workspace_bytes(self, batch_size: int, seq_len: int) -> int:

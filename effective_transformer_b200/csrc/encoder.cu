@@ -174,9 +174,11 @@ struct et_handle_s {
   // with the rows its producer wrote last finds them in L2.  prev_ascending =
   // the previous kernel of the chain wrote its rows first-to-last.
   bool prev_ascending = true;
-  // fp16 tensor-core path: bias + residual + LayerNorm run inside the two N = hidden projections
-  // (et_set_fused_layernorm(0): a LayerNorm kernel behind each of them instead)
-  bool fuse_ln = true;
+  // fp16 tensor-core path, et_set_fused_layernorm(1): bias + residual + LayerNorm run inside the two
+  // N = hidden projection kernels (5 launches per layer instead of 7).  Off by default: measured, the
+  // LayerNorm arithmetic (about 250 warp instructions per row) takes the eight epilogue warps of a
+  // CTA longer than a LayerNorm kernel with 48 warps per SM takes for the same rows.
+  bool fuse_ln = false;
   TensorMapCache maps;  // TMA descriptors of this handle's launches
   // general [B,S,S] mask of the pass being enqueued (null: key-only mask, fast kernels)
   const void* cur_attr_mask = nullptr;
@@ -195,7 +197,8 @@ struct et_handle_s {
                            // (measured on cfg2: 2 -> 9.0 ms, 6 -> 8.8 ms, 8 -> 9.0 ms; ETB_HOST_MID_SHARE)
   bool host_share_auto = true;  // pick the middle share from the first call's measured copy and compute times
   bool host_share_measured = false;
-  cudaEvent_t tune_ev[4] = {};  // upload start/end, compute start/end of the measuring call
+  int tuned_batch = -1, tuned_seq = -1;  // shape the chunking was measured on (another shape measures again)
+  cudaEvent_t tune_ev[6] = {};  // upload start/end, pass start/end of the first and of the middle chunk
   size_t ws_bytes_allocated = 0;  // sum of the workspace buffers et_create allocated
   int* host_pinned = nullptr;  // [2 + kMaxChunks]: valid_word_num, status, per-chunk token counts
   // one captured forward pass (et_graph_capture*): replayed by et_graph_launch
@@ -1140,19 +1143,23 @@ int et_forward_general_mask(et_handle_t h, const void* from_tensor, const int* m
 
 namespace {
 
-// Best middle share of a 3-chunk host-buffer call from the measured times of one call: `up` ms
-// for the whole upload, `comp` ms for the whole pass (the download is taken to cost what the
-// upload does).  Timeline of shares 1:m:1 -- upload of chunk 0, then its pass while chunk 1 is
-// uploaded, the passes of chunks 1 and 2, the download of chunk 2:
-//   t(m) = up/(m+2) + max(comp/(m+2), up*m/(m+2)) + comp*(m+1)/(m+2) + up/(m+2)
+// Chunking of a host-buffer call from the measured times of one 3-chunk call: `up` ms for the
+// whole upload (the download is taken to cost the same), a pass over a fraction x of the batch
+// costs fixed + slope * x ms (fixed: the ~90 dependent launches of a pass, whatever its size).
+// Timeline of shares 1:m:1 -- upload of chunk 0, then its pass while chunk 1 is uploaded, the
+// passes of chunks 1 and 2, the download of chunk 2:
+//   t(m) = up/(m+2) + max(pass(1/(m+2)), up*m/(m+2)) + pass(m/(m+2)) + pass(1/(m+2)) + up/(m+2)
 // A wide middle chunk shortens the two copies nothing overlaps, until its own upload no longer
 // hides behind the first chunk's pass (several processes sharing the host's PCIe switches).
-int best_mid_share(double up, double comp) {
-  int best = 2;
-  double best_t = 1e30;
+// One chunk costs up + pass(1) + up: better for small batches, where the fixed cost of two more
+// passes outweighs the overlapped copies.  Returns the middle share, or 0 for "do not chunk".
+int best_host_chunking(double up, double fixed, double slope) {
+  auto pass = [&](double x) { return fixed + slope * x; };
+  int best = 0;
+  double best_t = up + pass(1.0) + up;
   for (int m : {1, 2, 3, 4, 6, 8}) {
-    const double t = up / (m + 2) + std::max(comp / (m + 2), up * m / (m + 2)) + comp * (m + 1) / (m + 2) +
-                     up / (m + 2);
+    const double d = m + 2;
+    const double t = up / d + std::max(pass(1 / d), up * m / d) + pass(m / d) + pass(1 / d) + up / d;
     if (t < best_t - 1e-9) {
       best_t = t;
       best = m;
@@ -1172,8 +1179,14 @@ int forward_host_body(et_handle_t h, const void* from_host, const int* mask_host
   // stream while chunk i+1 is being computed.
   const size_t seq_bytes = static_cast<size_t>(seq_len) * h->hidden * h->esize;
   int chunks = h->host_chunks;
+  if (h->host_share_auto && h->host_share_measured && (h->tuned_batch != batch_size || h->tuned_seq != seq_len)) {
+    h->host_share_measured = false;  // another shape: measure again, starting from the default shares
+    h->host_mid_share = 6;
+  }
   if (static_cast<size_t>(batch_size) * seq_bytes < (8u << 20)) chunks = 1;  // too small to be worth it
-  const std::vector<std::pair<int, int>> plan = plan_host_chunks(batch_size, chunks, h->host_mid_share);
+  if (h->host_share_measured && h->host_mid_share == 0) chunks = 1;          // measured: chunking does not pay
+  const std::vector<std::pair<int, int>> plan =
+      plan_host_chunks(batch_size, chunks, h->host_mid_share > 0 ? h->host_mid_share : 1);
   const int per = static_cast<int>(plan.size());
   int nchunks = 0;
   et_handle_s::HostGraphs& hg = h->host_graphs;
@@ -1198,8 +1211,9 @@ int forward_host_body(et_handle_t h, const void* from_host, const int* mask_host
     const size_t b0 = plan[c].first;
     const int nb = plan[c].second;
     ET_CUDA(h, cudaStreamWaitEvent(s, h->in_done[c], 0));
-    // the middle chunk's pass, from the moment its upload has landed: the compute rate of the batch
-    if (measure && c == 1) ET_CUDA(h, cudaEventRecord(h->tune_ev[2], s));
+    // the passes of the first and the middle chunk, each from the moment its upload has landed: two
+    // sizes give the fixed cost of a pass and its cost per sequence
+    if (measure && c <= 1) ET_CUDA(h, cudaEventRecord(h->tune_ev[2 + 2 * c], s));
     if (replay && c < static_cast<int>(hg.execs.size())) {
       ET_CUDA(h, cudaGraphLaunch(hg.execs[c], s));
       for (int i = 0; i < ET_PROF_NUM; ++i) h->prof.launches[i] += hg.launches[c][i];
@@ -1209,7 +1223,7 @@ int forward_host_body(et_handle_t h, const void* from_host, const int* mask_host
                         static_cast<char*>(ws.stage_out) + b0 * seq_bytes, nb, seq_len, s);
       if (rc != ET_OK) return rc;
     }
-    if (measure && c == 1) ET_CUDA(h, cudaEventRecord(h->tune_ev[3], s));
+    if (measure && c <= 1) ET_CUDA(h, cudaEventRecord(h->tune_ev[3 + 2 * c], s));
     ET_CUDA(h, cudaMemcpyAsync(&h->host_pinned[2 + c], ws.valid_word_num, 4, cudaMemcpyDeviceToHost, s));
     ET_CUDA(h, cudaEventRecord(h->comp_done[c], s));
     ET_CUDA(h, cudaStreamWaitEvent(h->d2h_stream, h->comp_done[c], 0));
@@ -1226,14 +1240,21 @@ int forward_host_body(et_handle_t h, const void* from_host, const int* mask_host
   if (valid_word_num_out) *valid_word_num_out = total_tokens;
   if (h->host_pinned[1] != 0) return device_timeout(h, s);
   if (measure) {
-    float up_ms = 0.f, mid_ms = 0.f;
+    float up_ms = 0.f, first_ms = 0.f, mid_ms = 0.f;
+    const double x0 = static_cast<double>(plan[0].second) / batch_size, x1 = static_cast<double>(plan[1].second) / batch_size;
     if (cudaEventElapsedTime(&up_ms, h->tune_ev[0], h->tune_ev[1]) == cudaSuccess &&
-        cudaEventElapsedTime(&mid_ms, h->tune_ev[2], h->tune_ev[3]) == cudaSuccess && up_ms > 0.f && mid_ms > 0.f &&
-        plan[1].second > 0) {
-      const double comp_ms = static_cast<double>(mid_ms) * batch_size / plan[1].second;
-      h->host_mid_share = best_mid_share(up_ms, comp_ms);
+        cudaEventElapsedTime(&first_ms, h->tune_ev[2], h->tune_ev[3]) == cudaSuccess &&
+        cudaEventElapsedTime(&mid_ms, h->tune_ev[4], h->tune_ev[5]) == cudaSuccess && up_ms > 0.f && first_ms > 0.f &&
+        mid_ms > 0.f && x1 > x0) {
+      double slope = (mid_ms - first_ms) / (x1 - x0);
+      if (slope < 0) slope = 0;
+      double fixed = first_ms - slope * x0;
+      if (fixed < 0) fixed = 0;
+      h->host_mid_share = best_host_chunking(up_ms, fixed, slope);
     }
     h->host_share_measured = true;
+    h->tuned_batch = batch_size;
+    h->tuned_seq = seq_len;
   }
   // second call in a row with this shape: record its chunks for the calls to come
   if (!replay && graphs_allowed && batch_size > 0 && h->last_host_batch == batch_size &&

@@ -44,86 +44,102 @@ constexpr int kStagingPerWarp = 32 * 128;  // 32 rows x 128 bytes (64 fp16 colum
 
 // ---- LayerNorm inside the GEMM kernel (kEpiResidualLayerNorm, kEpiLayerNorm) -----------------
 // Every epilogue warp counts the columns it has stored for its 32 rows in a global counter of that
-// row block.  The warp whose count completes the row (all N columns, written by up to six warps of
-// three CTA pairs) knows that the whole pre-LayerNorm block is in L2, and posts it to one of the
-// CTA's LayerNorm warps, which normalise it in place off the epilogue's critical path.
-constexpr int kLnWarps = 2;  // each serves the mailboxes of four epilogue warps
+// row block.  The warp whose count completes the rows (all N columns, written by up to six warps of
+// three CTA pairs) knows that the whole pre-LayerNorm block is in L2 and posts it to its CTA: the
+// eight epilogue warps then normalise four rows of it each, in place, in the time they would
+// otherwise spend waiting for their next accumulator.
 __host__ __device__ constexpr bool has_ln(int epi) { return epi == kEpiResidualLayerNorm || epi == kEpiLayerNorm; }
 // what the accumulator epilogue itself does for an epilogue kind
 __host__ __device__ constexpr int base_epi(int epi) {
   return epi == kEpiResidualLayerNorm ? kEpiBiasResidual : epi == kEpiLayerNorm ? kEpiNone : epi;
 }
-__host__ __device__ constexpr int threads_of(int epi) { return kNumThreads + (has_ln(epi) ? kLnWarps * 32 : 0); }
+constexpr int kLnRowsPerWarp = 32 / kEpilogueWarps;  // a 32-row block is shared out among the epilogue warps
 
-// LayerNorm of `nrows` (<= 32) consecutive rows of c [*, n] in place by one warp, n = 256 * VPL:
-// lane l holds the 16-byte vectors j * 32 + l of a row, statistics in fp32 in two passes over the
-// registers, as add_bias_input_layernorm_kernel does (same arithmetic in the same order).
+// LayerNorm of RB consecutive rows of c [*, n] in place by one warp, n = 256 * VPL: lane l holds
+// the 16-byte vectors j * 32 + l of a row, statistics in fp32 in two passes over the registers,
+// as add_bias_input_layernorm_kernel does (same arithmetic in the same order).  The RB rows are
+// worked on side by side (no branch between them), so that one row's dependent chains -- the
+// running sums, the shuffles -- hide behind the others'.  Only the first nrows (1..RB) rows
+// exist: the others repeat the last one (same values stored to the same place again).
 // ADD: x = c + (residual + bias) first.  Rows are read through L2 (other CTAs wrote them).
-template <int VPL, bool ADD>
+template <int VPL, bool ADD, int RB>
 __device__ __forceinline__ void ln_rows(__half* c, const __half* residual, const __half* bias,
-                                          const __half* gamma, const __half* beta, int n, int nrows, float eps,
-                                          int lane) {
-  // rows per batch: about 18 16-byte vectors in flight per lane (the kernel runs 384 threads, so a
-  // thread has 168 registers)
-  constexpr int kFit = (VPL == 4 ? 16 : 18) / (VPL * (ADD ? 2 : 1));
-  constexpr int R = kFit > 8 ? 8 : kFit;
+                                        const __half* gamma, const __half* beta, int n, int nrows, float eps,
+                                        int lane) {
   const float inv_n = 1.0f / static_cast<float>(n);
-  for (int r0 = 0; r0 < nrows; r0 += R) {
-    Vec16 vc[R][VPL], vr[ADD ? R : 1][VPL];
+  size_t off[RB];
+  float x[RB][VPL][8];
+  {
+    Vec16 vc[RB][VPL], vr[ADD ? RB : 1][VPL];
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-      if (r0 + r < nrows) {
+    for (int r = 0; r < RB; ++r) {
+      off[r] = static_cast<size_t>(r < nrows ? r : nrows - 1) * n + lane * 8;
 #pragma unroll
-        for (int j = 0; j < VPL; ++j) {
-          const size_t off = static_cast<size_t>(r0 + r) * n + (j * 32 + lane) * 8;
-          vc[r][j] = ld_global_cg_v4(c + off);
-          if (ADD) vr[r][j] = ld_global_nc_v4(residual + off);
-        }
+      for (int j = 0; j < VPL; ++j) {
+        vc[r][j] = ld_global_cg_v4(c + off[r] + j * 256);
+        if (ADD) vr[r][j] = ld_global_nc_v4(residual + off[r] + j * 256);
       }
     }
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-      if (r0 + r < nrows) {   // uniform over the warp
-        float x[VPL][8];
-        float sum = 0.f;
+    for (int j = 0; j < VPL; ++j) {
+      float fb[8];
+      if (ADD) VecTraits<__half>::unpack(ld_global_v4(bias + lane * 8 + j * 256), fb);
 #pragma unroll
-        for (int j = 0; j < VPL; ++j) {
-          float fo[8];
-          VecTraits<__half>::unpack(vc[r][j], fo);
-          if (ADD) {
-            float fi[8], fb[8];
-            VecTraits<__half>::unpack(vr[r][j], fi);
-            VecTraits<__half>::unpack(ld_global_v4(bias + (j * 32 + lane) * 8), fb);
+      for (int r = 0; r < RB; ++r) {
+        VecTraits<__half>::unpack(vc[r][j], x[r][j]);
+        if (ADD) {
+          float fi[8];
+          VecTraits<__half>::unpack(vr[r][j], fi);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) fo[e] += fi[e] + fb[e];
-          }
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            x[j][e] = fo[e];
-            sum += x[j][e];
-          }
-        }
-        const float mean = warp_sum(sum) * inv_n;
-        float sq = 0.f;
-#pragma unroll
-        for (int j = 0; j < VPL; ++j) {
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const float dlt = x[j][e] - mean;
-            sq += dlt * dlt;
-          }
-        }
-        const float rstd = rsqrtf(warp_sum(sq) * inv_n + eps);
-#pragma unroll
-        for (int j = 0; j < VPL; ++j) {
-          float fg[8], fbe[8], y[8];
-          VecTraits<__half>::unpack(ld_global_v4(gamma + (j * 32 + lane) * 8), fg);
-          VecTraits<__half>::unpack(ld_global_v4(beta + (j * 32 + lane) * 8), fbe);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) y[e] = (x[j][e] - mean) * rstd * fg[e] + fbe[e];
-          st_global_v4(c + static_cast<size_t>(r0 + r) * n + (j * 32 + lane) * 8, VecTraits<__half>::pack(y));
+          for (int e = 0; e < 8; ++e) x[r][j][e] += fi[e] + fb[e];
         }
       }
+    }
+  }
+  float mean[RB], rstd[RB];
+#pragma unroll
+  for (int r = 0; r < RB; ++r) {
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sum += x[r][j][e];
+    mean[r] = sum;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+    for (int r = 0; r < RB; ++r) mean[r] += __shfl_xor_sync(0xffffffffu, mean[r], o);
+#pragma unroll
+  for (int r = 0; r < RB; ++r) {
+    mean[r] *= inv_n;
+    float sq = 0.f;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float dlt = x[r][j][e] - mean[r];
+        sq += dlt * dlt;
+      }
+    rstd[r] = sq;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+    for (int r = 0; r < RB; ++r) rstd[r] += __shfl_xor_sync(0xffffffffu, rstd[r], o);
+#pragma unroll
+  for (int r = 0; r < RB; ++r) rstd[r] = rsqrtf(rstd[r] * inv_n + eps);
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    float fg[8], fbe[8];
+    VecTraits<__half>::unpack(ld_global_v4(gamma + lane * 8 + j * 256), fg);
+    VecTraits<__half>::unpack(ld_global_v4(beta + lane * 8 + j * 256), fbe);
+#pragma unroll
+    for (int r = 0; r < RB; ++r) {
+      float y[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) y[e] = (x[r][j][e] - mean[r]) * rstd[r] * fg[e] + fbe[e];
+      st_global_v4(c + off[r] + j * 256, VecTraits<__half>::pack(y));
     }
   }
 }
@@ -496,13 +512,17 @@ struct PairCfg {
   static constexpr int kStagingBytes = kEpilogueWarps * kStagingPerWarp;
   static constexpr int kColsPerWarp = BN / 2;
   static constexpr int kBiasBytes = kEpilogueWarps * kColsPerWarp * 2;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + kBiasBytes + 256;
+  // barriers (2 * kStages + 5), the TMEM slot, the abort flag and the 4 x 8 words of the LayerNorm work sharing
+  static constexpr int kControlBytes = 512;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + kBiasBytes + kControlBytes;
+  static_assert(kNumBars * 8 + 8 + 4 * kEpilogueWarps * 4 <= kControlBytes, "control block too small");
+  static_assert(kSmemBytes <= 232448, "more than 227 KB of shared memory");
   static constexpr int kTmemCols = 2 * BN;
 };
 
 // VPL: 16-byte vectors of a C row per lane in the LayerNorm warps (N / 256); 0 for the other epilogues.
 template <int EPI, int VPL>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(threads_of(EPI), 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                          const __grid_constant__ CUtensorMap tmap_b,
                          const __grid_constant__ CUtensorMap tmap_b_half, __half* __restrict__ C,
@@ -539,10 +559,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const uint32_t drain_bar = bar0 + 8u * (2 * S + 4);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + cfg::kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  // LayerNorm variants: ln_box[e] = first row + 1 of a complete 32-row block posted by epilogue
-  // warp e (0 = empty), ln_done[e] = that warp has left its loop
-  volatile int* ln_box = reinterpret_cast<volatile int*>(tmem_slot + 2);
-  volatile int* ln_done = ln_box + kEpilogueWarps;
+  // LayerNorm variants, per epilogue warp e: box_row[e] = first row of the complete 32-row block
+  // it posted last, box_gen[e] = how many it has posted, box_done[e] = how many 4-row shares of
+  // its blocks the warps have normalised, ln_done[e] = it has left its loop
+  volatile int* box_row = reinterpret_cast<volatile int*>(tmem_slot + 2);
+  volatile int* box_gen = box_row + kEpilogueWarps;
+  volatile int* box_done = box_gen + kEpilogueWarps;
+  volatile int* ln_done = box_done + kEpilogueWarps;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -557,7 +580,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     mbar_init(drain_bar, 1);
     *abort_flag = 0;
-    for (int e = 0; e < 2 * kEpilogueWarps; ++e) ln_box[e] = 0;
+    for (int e = 0; e < 4 * kEpilogueWarps; ++e) box_row[e] = 0;
     fence_mbar_init();
     fence_proxy_async_smem();
   }
@@ -680,17 +703,87 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       umma_commit_pair(drain_bar);
       if (!mbar_wait(drain_bar, 0u, abort_flag) && *abort_flag == 0) fail(kSiteMmaDrain);
     }
-  } else if (warp < 2 + kEpilogueWarps) {
+  } else {
     // ------------------------- epilogue (both CTAs) -------------------------
     constexpr int kBase = base_epi(EPI);
+    constexpr bool kLn = has_ln(EPI);
     const int quad = warp & 3;
     const int ew = warp - 2;
     const int half = ew >> 2;
     constexpr int kCols = cfg::kColsPerWarp;
     const uint32_t buf = staging_addr + ew * kStagingPerWarp;
     const uint32_t bias_s = bias_addr + ew * (kCols * 2);
+
+    // ---- LayerNorm work sharing (LayerNorm variants only) ----
+    // A warp owes every posted block its own four rows.  A warp may post its next block only when
+    // all eight shares of its previous one are done, so a warp is never more than one block behind
+    // per poster and one bit per poster records which of its blocks this warp has seen.
+    uint32_t seen_bits = 0;
+    auto ln_poll = [&]() -> bool {
+      bool any = false;
+      if constexpr (kLn) {
+#pragma unroll 1
+        for (int e = 0; e < kEpilogueWarps; ++e) {
+          const uint32_t g = static_cast<uint32_t>(box_gen[e]);  // one shared-memory read for the whole warp
+          if (((g ^ (seen_bits >> e)) & 1u) != 0u) {
+            any = true;
+            __threadfence();  // the poster saw the complete block; order this warp's reads behind that
+            const int first = box_row[e] + ew * kLnRowsPerWarp;
+            const int nrows = min(kLnRowsPerWarp, M - first);
+            if (nrows > 0) {
+              __half* crow = C + static_cast<size_t>(first) * N;
+              const __half* rrow = residual + static_cast<size_t>(first) * N;
+              constexpr int RB = VPL <= 3 ? kLnRowsPerWarp : kLnRowsPerWarp / 2;
+#pragma unroll 1
+              for (int r0 = 0; r0 < nrows; r0 += RB)
+                ln_rows<(VPL > 0 ? VPL : 1), EPI == kEpiLayerNorm, RB>(
+                    crow + static_cast<size_t>(r0) * N, rrow + static_cast<size_t>(r0) * N, bias, ln.gamma, ln.beta,
+                    N, min(RB, nrows - r0), ln.eps, lane);
+            }
+            seen_bits ^= 1u << e;
+            __syncwarp();
+            if (lane == 0) atomicAdd(const_cast<int*>(box_done + e), 1);
+          }
+        }
+      }
+      return any;
+    };
+    // waits (polling the LayerNorm work) for `ready()`; false on abort or after the time limit
+    auto wait_polling = [&](auto ready) -> bool {
+      unsigned long long t0 = 0;
+      for (uint32_t spin = 1;; ++spin) {
+        if (__all_sync(0xffffffffu, ready())) return true;
+        if (ln_poll()) {
+          t0 = 0;
+        } else if ((spin & 63u) == 0u) {
+          bool stop = *abort_flag != 0;
+          const unsigned long long now = globaltimer_ns();
+          if (t0 == 0) t0 = now;
+          else if (now - t0 > kWaitTimeoutNs) stop = true;
+          if (__any_sync(0xffffffffu, stop)) return false;
+        }
+      }
+    };
+    // posts the complete block that starts at `brow0` (this warp made its column count reach N)
+    auto ln_post = [&](int brow0) -> bool {
+      if (lane == 0) ln.counters[brow0 >> 5] = 0;  // nobody else touches it any more: zero for the next launch
+      if (M - brow0 <= 0) return true;             // a row block past the last row: nothing to normalise
+      const bool free_box =
+          wait_polling([&] { return box_done[ew] == kEpilogueWarps * box_gen[ew]; });
+      if (!free_box) return false;
+      if (lane == 0) {
+        box_row[ew] = brow0;
+        __threadfence_block();
+        box_gen[ew] = box_gen[ew] + 1;
+      }
+      __syncwarp();
+      return true;
+    };
+
+    int prev_row0 = -1, prev_wcols = 0;  // the unit before this one: its column count is still to be added
     int it = 0;
-    for (int u = pair_id; u < num_units; u += num_pairs, ++it) {
+    bool ok = true;
+    for (int u = pair_id; u < num_units && ok; u += num_pairs, ++it) {
       const PairUnit pu = pair_unit(u, full_tiles, n_tiles, m_tiles, reverse_m);
       const int m_tile = pu.m_tile;
       const int wcols = pu.ncols / 2;  // columns of this warp: 128, or 64 in a half-width unit
@@ -701,12 +794,26 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (lane < wcols / 8) st_shared_v4(bias_s + lane * 16, ld_global_v4(bias + col0 + lane * 8));
         __syncwarp();
       }
-      const bool got = mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag);
-      if (!__all_sync(0xffffffffu, got)) {
+      bool got;
+      if constexpr (kLn)
+        got = wait_polling([&] { return mbar_test_wait(tmem_full_bar(acc), acc_phase); });
+      else
+        got = __all_sync(0xffffffffu, mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag));
+      if (!got) {
         if (lane == 0) fail(kSiteEpilogueFull);
         break;
       }
       tc_fence_after();
+      // The previous unit's stores are long on their way by now: count its columns for its 32
+      // rows (release: the stores are ordered before the count).  The count's old value is only
+      // looked at behind this unit's epilogue, so its round trip to L2 is not waited for.
+      int before = 0;
+      if constexpr (kLn) {
+        if (prev_row0 >= 0) {
+          __threadfence();
+          if (lane == 0) before = atomicAdd(ln.counters + (prev_row0 >> 5), prev_wcols);
+        }
+      }
       const int row0 = m_tile * BM2 + static_cast<int>(rank) * BM + quad * 32;
       const uint32_t t_row =
           tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN + half * wcols;
@@ -717,82 +824,55 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(empty0);
       });
-      if constexpr (has_ln(EPI)) {
-        // Count this warp's columns for its 32 rows.  Release: the stores above are ordered
-        // before the count; acquire: the warp that completes the row block sees all of them.
-        __threadfence();
-        __syncwarp();
-        const int group = row0 >> 5;
-        int before = 0;
-        if (lane == 0) before = atomicAdd(ln.counters + group, wcols);
-        before = __shfl_sync(0xffffffffu, before, 0);
-        if (before + wcols == N) {
-          __threadfence();
-          const int nrows = min(32, M - row0);
-          if (lane == 0) {
-            ln.counters[group] = 0;  // nobody else touches it any more: zero again for the next launch
-            if (nrows > 0) {
-              // hand the block to this warp's LayerNorm warp; its mailbox is empty unless that warp is
-              // still busy with the block posted three or more tiles ago (it never waits for anybody)
-              unsigned long long t0 = 0;
-              bool empty = true;
-              while (ln_box[ew] != 0) {
-                __nanosleep(64);
-                const unsigned long long now = globaltimer_ns();
-                if (t0 == 0) t0 = now;
-                else if (now - t0 > kWaitTimeoutNs) {
-                  fail(kSiteLnMailbox);
-                  empty = false;
-                  break;
-                }
-              }
-              if (empty) {
-                __threadfence_block();
-                ln_box[ew] = row0 + 1;
-              }
+      if constexpr (kLn) {
+        if (prev_row0 >= 0) {
+          before = __shfl_sync(0xffffffffu, before, 0);
+          if (before + prev_wcols == N) {  // acquire: this warp now sees all columns of those rows
+            __threadfence();
+            if (!ln_post(prev_row0)) {
+              if (lane == 0) fail(kSiteLnMailbox);
+              ok = false;
             }
           }
-          __syncwarp();
         }
+        prev_row0 = row0;
+        prev_wcols = wcols;
       }
     }
-    if constexpr (has_ln(EPI)) {
+    if constexpr (kLn) {
+      if (ok && prev_row0 >= 0) {  // the last unit of this warp
+        __threadfence();
+        int before = 0;
+        if (lane == 0) before = atomicAdd(ln.counters + (prev_row0 >> 5), prev_wcols);
+        before = __shfl_sync(0xffffffffu, before, 0);
+        if (before + prev_wcols == N) {
+          __threadfence();
+          if (!ln_post(prev_row0) && lane == 0) fail(kSiteLnMailbox);
+        }
+      }
       __syncwarp();
       if (lane == 0) {
         __threadfence_block();  // a posted block is visible before the flag
         ln_done[ew] = 1;
       }
-    }
-  } else if constexpr (has_ln(EPI)) {
-    // ------------------------- LayerNorm warps (both CTAs) -------------------------
-    const int hw = warp - (2 + kEpilogueWarps);
-    unsigned long long t0 = 0;
-    for (;;) {
-      bool any = false, all_done = true;
-      for (int e = hw; e < kEpilogueWarps; e += kLnWarps) {
-        const int done = ln_done[e];  // read before the mailbox: a warp posts before it sets the flag
-        const int v = ln_box[e];
-        if (v != 0) {
-          any = true;
-          __threadfence();  // the poster saw the complete block; order this warp's reads behind that
-          const int row0 = v - 1;
-          if constexpr (VPL > 0)
-            ln_rows<VPL, EPI == kEpiLayerNorm>(C + static_cast<size_t>(row0) * N,
-                                               residual + static_cast<size_t>(row0) * N, bias, ln.gamma, ln.beta, N,
-                                               min(32, M - row0), ln.eps, lane);
-          __syncwarp();
-          if (lane == 0) ln_box[e] = 0;
+      // stay until every warp of the CTA has posted its last block and this warp has done its share
+      // of all of them (ln_done is read before the blocks are looked for: a warp posts before it
+      // sets its flag)
+      unsigned long long t0 = 0;
+      for (;;) {
+        int all_done = 1;
+#pragma unroll
+        for (int e = 0; e < kEpilogueWarps; ++e) all_done &= ln_done[e];
+        const bool any = ln_poll();
+        if (all_done != 0 && !any) break;
+        if (any) {
+          t0 = 0;
+          continue;
         }
-        if (!done) all_done = false;
-      }
-      if (all_done && !any) break;
-      if (!any) {
-        __nanosleep(128);
-        const unsigned long long now = globaltimer_ns();  // bounded like every other wait
+        __nanosleep(64);
+        const unsigned long long now = globaltimer_ns();
         if (t0 == 0) t0 = now;
-        else if (now - t0 > 4 * kWaitTimeoutNs) break;
-      } else {
-        t0 = 0;
+        if (__any_sync(0xffffffffu, now - t0 > 2 * kWaitTimeoutNs)) break;
       }
     }
   }
@@ -823,7 +903,7 @@ cudaError_t launch_pair_epi(const CUtensorMap& ta, const CUtensorMap& tb, const 
   long long pairs = sm_count() / 2;
   if (pairs > max_tiles) pairs = max_tiles;
   if (pairs < 1) pairs = 1;
-  return launch_pdl(gemm_tcgen05_pair_kernel<EPI, VPL>, dim3(static_cast<int>(2 * pairs)), dim3(threads_of(EPI)),
+  return launch_pdl(gemm_tcgen05_pair_kernel<EPI, VPL>, dim3(static_cast<int>(2 * pairs)), dim3(kNumThreads),
                     cfg::kSmemBytes, stream, ta, tb, tbh, c, bias, residual, m_ptr, max_m, n, k, status_word, reverse_m,
                     ln);
 }

@@ -305,18 +305,24 @@ int et_copy_to_host(void* dst_host, const void* src_device, size_t bytes, void* 
  * (plain fp32 FMA arithmetic; for debugging and as a second opinion). */
 int et_set_debug_simt(et_handle_t handle, int use_simt);
 
-/* 1 (default, fp16 handles with hidden a multiple of 256 up to 1024): the two
- * add_bias_input_layernorm launches of a layer (tf_op/bert_transformer_op.cu.cc:
- * 211-213,242-246) run inside the attention-output and second feed-forward
- * projection kernels: a layer is 5 launches.  0: one LayerNorm kernel behind
- * each of them (7 launches).  Changing the setting drops recorded graphs. */
+/* 0 (default): one add_bias_input_layernorm kernel behind the attention-output
+ * and the second feed-forward projection, as in the reference
+ * (tf_op/bert_transformer_op.cu.cc:211-213,242-246): 7 launches per layer.
+ * 1 (fp16 handles with hidden a multiple of 256 up to 1024): both LayerNorms run
+ * inside the projection kernels (et_gemm_fused epilogues 6 and 5): 5 launches per
+ * layer and no pre-LayerNorm tensor read back from HBM.  Same results (the same
+ * arithmetic in the same order).  Measured on B200 it is slower at the benchmark
+ * sizes, which is why it is opt-in.  Changing the setting drops recorded graphs. */
 int et_set_fused_layernorm(et_handle_t handle, int enable);
 
 /* Chunking of the host-buffer call (et_forward_host): number of chunks, share of
- * a middle chunk when the first and the last have 1, and whether that share
- * comes from the handle's own measurement (the first chunked call times the
- * upload and a pass, the later calls use the shares that minimise the
- * unoverlapped copies; ETB_HOST_MID_SHARE fixes the share instead). */
+ * a middle chunk when the first and the last have 1 (0: the handle found that
+ * chunking does not pay for the last shape and sends the batch in one piece),
+ * and whether that comes from the handle's own measurement: the first chunked
+ * call on a (batch, seq) shape times the upload and two passes of different
+ * size, and the later calls use the chunking that minimises the copies nothing
+ * overlaps plus the fixed cost of the extra passes.  ETB_HOST_MID_SHARE fixes
+ * the share instead. */
 int et_host_chunk_shares(et_handle_t handle, int* chunks, int* mid_share, int* measured);
 
 /* Failure-detection self-test: launches one CTA whose bounded wait (2 ms, on a
