@@ -92,13 +92,16 @@ add_bias_gelu_kernel(T* __restrict__ out, const T* __restrict__ bias, const int*
   }
 }
 
-// out[row] = LN(out[row] + input[row] + bias) * gamma + beta (input and bias
-// null: LN(out[row]) alone, for a producer that added them itself), one warp per
-// row, the row held in registers (fp32) between the two statistics passes.
+// out[row] = LN(out[row] + input[row] + bias) * gamma + beta (kHasInput false:
+// LN(out[row]) alone, for a producer that added them itself), one warp per row,
+// the row held in registers (fp32) between the two statistics passes.
+// A warp fetches kRows rows at a time before it works on the first: the kernel is
+// bound by the bytes it has in flight (about 35 KB per SM are needed to cover the
+// HBM latency at full bandwidth), and one 1.5 KB row per warp is too few of them.
 // bias / gamma / beta are re-read per row: they stay L1-resident, and not
-// keeping them in registers doubles the number of resident warps.
-template <typename T, int kVPL>
-__global__ void __launch_bounds__(kThreads, (kVPL <= 4 ? 3 : 1))
+// keeping them in registers raises the number of resident warps.
+template <typename T, int kVPL, int kRows, bool kHasInput>
+__global__ void __launch_bounds__(kThreads, (kVPL <= 4 ? 2 : 1))
 add_bias_input_layernorm_kernel(T* __restrict__ out, const T* __restrict__ input,
                                 const T* __restrict__ bias, const T* __restrict__ gamma,
                                 const T* __restrict__ beta, const int* __restrict__ t_ptr,
@@ -114,79 +117,90 @@ add_bias_input_layernorm_kernel(T* __restrict__ out, const T* __restrict__ input
   const int vpr = n / E;
   const float inv_n = 1.0f / static_cast<float>(n);
 
-  for (int r = warp; r < t; r += nwarps) {
-    const int row = reverse ? t - 1 - r : r;  // last rows first: they are the freshest in L2
-    T* orow = out + static_cast<size_t>(row) * n;
-    const T* irow = input != nullptr ? input + static_cast<size_t>(row) * n : nullptr;
-    Vec16 vo[kVPL], vi[kVPL];
+  for (int r0 = warp; r0 < t; r0 += nwarps * kRows) {
+    Vec16 vo[kRows][kVPL], vi[kHasInput ? kRows : 1][kVPL];
+    int rows[kRows];
 #pragma unroll
-    for (int j = 0; j < kVPL; ++j) {
-      const int c = j * 32 + lane;
-      if (c < vpr) {
-        vo[j] = ld_global_v4(orow + c * E);
-        if (input != nullptr) vi[j] = ld_global_nc_v4(irow + c * E);
-      }
-    }
-    float x[kVPL][E];
-    float sum = 0.f;
+    for (int k = 0; k < kRows; ++k) {
+      const int r = r0 + k * nwarps;
+      rows[k] = r < t ? (reverse ? t - 1 - r : r) : -1;  // last rows first: they are the freshest in L2
+      if (rows[k] >= 0) {
+        const T* orow = out + static_cast<size_t>(rows[k]) * n;
 #pragma unroll
-    for (int j = 0; j < kVPL; ++j) {
-      const int c = j * 32 + lane;
-      if (c < vpr) {
-        float fo[E];
-        VecTraits<T>::unpack(vo[j], fo);
-        if (input != nullptr) {   // uniform: null when the producer has already added residual and bias
-          float fi[E], fb[E];
-          VecTraits<T>::unpack(vi[j], fi);
-          VecTraits<T>::unpack(ld_global_v4(bias + c * E), fb);
-#pragma unroll
-          for (int e = 0; e < E; ++e) fo[e] += fi[e] + fb[e];
-        }
-#pragma unroll
-        for (int e = 0; e < E; ++e) {
-          x[j][e] = fo[e];
-          sum += x[j][e];
-        }
-      } else {
-#pragma unroll
-        for (int e = 0; e < E; ++e) x[j][e] = 0.f;
-      }
-    }
-    const float mean = warp_sum(sum) * inv_n;
-    float sq = 0.f;
-#pragma unroll
-    for (int j = 0; j < kVPL; ++j) {
-      const int c = j * 32 + lane;
-      if (c < vpr) {
-#pragma unroll
-        for (int e = 0; e < E; ++e) {
-          const float dlt = x[j][e] - mean;
-          sq += dlt * dlt;
+        for (int j = 0; j < kVPL; ++j) {
+          const int c = j * 32 + lane;
+          if (c < vpr) {
+            vo[k][j] = ld_global_v4(orow + c * E);
+            if (kHasInput) vi[k][j] = ld_global_nc_v4(input + static_cast<size_t>(rows[k]) * n + c * E);
+          }
         }
       }
     }
-    const float rstd = rsqrtf(warp_sum(sq) * inv_n + eps);
 #pragma unroll
-    for (int j = 0; j < kVPL; ++j) {
-      const int c = j * 32 + lane;
-      if (c < vpr) {
-        float fg[E], fbe[E], y[E];
-        VecTraits<T>::unpack(ld_global_v4(gamma + c * E), fg);
-        VecTraits<T>::unpack(ld_global_v4(beta + c * E), fbe);
+    for (int k = 0; k < kRows; ++k) {
+      if (rows[k] < 0) continue;  // uniform over the warp
+      T* orow = out + static_cast<size_t>(rows[k]) * n;
+      float x[kVPL][E];
+      float sum = 0.f;
 #pragma unroll
-        for (int e = 0; e < E; ++e) y[e] = (x[j][e] - mean) * rstd * fg[e] + fbe[e];
-        st_global_v4(orow + c * E, VecTraits<T>::pack(y));
-        if constexpr (sizeof(T) == 4) {
-          if (split_hi != nullptr) {  // fp32 tensor path: the next projection's input, already split
-            float hi[E], lo[E];
+      for (int j = 0; j < kVPL; ++j) {
+        const int c = j * 32 + lane;
+        if (c < vpr) {
+          float fo[E];
+          VecTraits<T>::unpack(vo[k][j], fo);
+          if (kHasInput) {
+            float fi[E], fb[E];
+            VecTraits<T>::unpack(vi[k][j], fi);
+            VecTraits<T>::unpack(ld_global_v4(bias + c * E), fb);
 #pragma unroll
-            for (int e = 0; e < E; ++e) {
-              hi[e] = rn_tf32(y[e]);
-              lo[e] = y[e] - hi[e];
+            for (int e = 0; e < E; ++e) fo[e] += fi[e] + fb[e];
+          }
+#pragma unroll
+          for (int e = 0; e < E; ++e) {
+            x[j][e] = fo[e];
+            sum += x[j][e];
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < E; ++e) x[j][e] = 0.f;
+        }
+      }
+      const float mean = warp_sum(sum) * inv_n;
+      float sq = 0.f;
+#pragma unroll
+      for (int j = 0; j < kVPL; ++j) {
+        const int c = j * 32 + lane;
+        if (c < vpr) {
+#pragma unroll
+          for (int e = 0; e < E; ++e) {
+            const float dlt = x[j][e] - mean;
+            sq += dlt * dlt;
+          }
+        }
+      }
+      const float rstd = rsqrtf(warp_sum(sq) * inv_n + eps);
+#pragma unroll
+      for (int j = 0; j < kVPL; ++j) {
+        const int c = j * 32 + lane;
+        if (c < vpr) {
+          float fg[E], fbe[E], y[E];
+          VecTraits<T>::unpack(ld_global_v4(gamma + c * E), fg);
+          VecTraits<T>::unpack(ld_global_v4(beta + c * E), fbe);
+#pragma unroll
+          for (int e = 0; e < E; ++e) y[e] = (x[j][e] - mean) * rstd * fg[e] + fbe[e];
+          st_global_v4(orow + c * E, VecTraits<T>::pack(y));
+          if constexpr (sizeof(T) == 4) {
+            if (split_hi != nullptr) {  // fp32 tensor path: the next projection's input, already split
+              float hi[E], lo[E];
+#pragma unroll
+              for (int e = 0; e < E; ++e) {
+                hi[e] = rn_tf32(y[e]);
+                lo[e] = y[e] - hi[e];
+              }
+              const size_t off = static_cast<size_t>(rows[k]) * n + c * E;
+              st_global_v4(split_hi + off, VecTraits<T>::pack(hi));
+              st_global_v4(split_lo + off, VecTraits<T>::pack(lo));
             }
-            const size_t off = static_cast<size_t>(row) * n + c * E;
-            st_global_v4(split_hi + off, VecTraits<T>::pack(hi));
-            st_global_v4(split_lo + off, VecTraits<T>::pack(lo));
           }
         }
       }
@@ -269,16 +283,23 @@ cudaError_t launch_add_bias_input_layernorm(T* out, const T* input, const T* bia
   const long long cap = static_cast<long long>(sm_count()) * kCtasPerSm;
   if (ctas > cap) ctas = cap;
   const int grid = static_cast<int>(ctas);
+  const bool has_input = input != nullptr;
+  if (has_input && bias == nullptr) return cudaErrorInvalidValue;
   cudaError_t le = cudaSuccess;
-#define ETB_LN(V)                                                                                   \
-  le = launch_pdl(add_bias_input_layernorm_kernel<T, V>, dim3(grid), dim3(kThreads), 0, stream, out, \
-                  input, bias, gamma, beta, t_ptr, max_tokens, n, eps, reverse ? 1 : 0, split_hi, split_lo)
-  if (vpl <= 1) ETB_LN(1);
-  else if (vpl <= 2) ETB_LN(2);
-  else if (vpl <= 3) ETB_LN(3);
-  else if (vpl <= 4) ETB_LN(4);
-  else if (vpl <= 6) ETB_LN(6);
-  else if (vpl <= 8) ETB_LN(8);
+  // rows a warp has in flight: about 18 vectors of 16 bytes per lane
+#define ETB_LN(V, R_IN, R_NO)                                                                                  \
+  le = has_input ? launch_pdl(add_bias_input_layernorm_kernel<T, V, R_IN, true>, dim3(grid), dim3(kThreads), 0,  \
+                              stream, out, input, bias, gamma, beta, t_ptr, max_tokens, n, eps, reverse ? 1 : 0, \
+                              split_hi, split_lo)                                                              \
+                 : launch_pdl(add_bias_input_layernorm_kernel<T, V, R_NO, false>, dim3(grid), dim3(kThreads), 0, \
+                              stream, out, input, bias, gamma, beta, t_ptr, max_tokens, n, eps, reverse ? 1 : 0, \
+                              split_hi, split_lo)
+  if (vpl <= 1) ETB_LN(1, 4, 8);
+  else if (vpl <= 2) ETB_LN(2, 4, 8);
+  else if (vpl <= 3) ETB_LN(3, 2, 4);
+  else if (vpl <= 4) ETB_LN(4, 2, 4);
+  else if (vpl <= 6) ETB_LN(6, 1, 2);
+  else if (vpl <= 8) ETB_LN(8, 1, 1);
   else return cudaErrorInvalidValue;
 #undef ETB_LN
   return le;

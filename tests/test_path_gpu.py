@@ -410,6 +410,7 @@ def test_bounded_wait_reports_through_the_status_word():
     assert torch.equal(run_forward(eng, wl), want)
     # the first recorded code wins, and the host-buffer call turns it into ET_DEVICE_TIMEOUT
     eng.selftest_wait_timeout()
+    torch.cuda.synchronize()                             # the host-buffer call runs on the handle's own stream
     with pytest.raises(et.EtError) as e:
         eng.forward_host(wl.from_tensor.astype(np.float16), wl.mask)
     assert e.value.code == _capi.ET_DEVICE_TIMEOUT and "0xf01" in str(e.value)
