@@ -278,22 +278,36 @@ cudaError_t launch_add_bias_input_layernorm(T* out, const T* input, const T* bia
     return cudaErrorInvalidValue;
   if (n % E != 0 || n <= 0) return cudaErrorInvalidValue;
   const int vpl = (n / E + 31) / 32;
-  const long long rows_per_cta = kThreads / 32;
-  long long ctas = (max_tokens + rows_per_cta - 1) / rows_per_cta;
-  const long long cap = static_cast<long long>(sm_count()) * kCtasPerSm;
-  if (ctas > cap) ctas = cap;
-  const int grid = static_cast<int>(ctas);
   const bool has_input = input != nullptr;
   if (has_input && bias == nullptr) return cudaErrorInvalidValue;
   cudaError_t le = cudaSuccess;
-  // rows a warp has in flight: about 18 vectors of 16 bytes per lane
-#define ETB_LN(V, R_IN, R_NO)                                                                                  \
-  le = has_input ? launch_pdl(add_bias_input_layernorm_kernel<T, V, R_IN, true>, dim3(grid), dim3(kThreads), 0,  \
-                              stream, out, input, bias, gamma, beta, t_ptr, max_tokens, n, eps, reverse ? 1 : 0, \
-                              split_hi, split_lo)                                                              \
-                 : launch_pdl(add_bias_input_layernorm_kernel<T, V, R_NO, false>, dim3(grid), dim3(kThreads), 0, \
-                              stream, out, input, bias, gamma, beta, t_ptr, max_tokens, n, eps, reverse ? 1 : 0, \
-                              split_hi, split_lo)
+  // One wave of CTAs, as many as are resident at once (the kernel's warps loop over the rows):
+  // with more, the later waves start as the first ones end and the kernel has a long tail.
+  // Rows a warp has in flight: about 18 vectors of 16 bytes per lane.
+#define ETB_LN_ONE(V, R, HAS)                                                                                  \
+  do {                                                                                                         \
+    auto kernel = add_bias_input_layernorm_kernel<T, V, R, HAS>;                                               \
+    static std::atomic<int> resident[kMaxDevices] = {};                                                        \
+    const int dev = current_device();                                                                          \
+    int per_sm = dev >= 0 ? resident[dev].load(std::memory_order_relaxed) : 0;                                 \
+    if (per_sm == 0) {                                                                                         \
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0) != cudaSuccess ||        \
+          per_sm < 1)                                                                                          \
+        per_sm = 1;                                                                                            \
+      if (dev >= 0) resident[dev].store(per_sm, std::memory_order_relaxed);                                    \
+    }                                                                                                          \
+    const long long rows_per_cta = static_cast<long long>(kThreads / 32) * R;                                  \
+    long long ctas = (max_tokens + rows_per_cta - 1) / rows_per_cta;                                           \
+    const long long cap = static_cast<long long>(sm_count()) * per_sm;                                         \
+    if (ctas > cap) ctas = cap;                                                                                \
+    le = launch_pdl(kernel, dim3(static_cast<int>(ctas)), dim3(kThreads), 0, stream, out, input, bias, gamma,  \
+                    beta, t_ptr, max_tokens, n, eps, reverse ? 1 : 0, split_hi, split_lo);                     \
+  } while (0)
+#define ETB_LN(V, R_IN, R_NO)              \
+  do {                                     \
+    if (has_input) ETB_LN_ONE(V, R_IN, true); \
+    else ETB_LN_ONE(V, R_NO, false);       \
+  } while (0)
   if (vpl <= 1) ETB_LN(1, 4, 8);
   else if (vpl <= 2) ETB_LN(2, 4, 8);
   else if (vpl <= 3) ETB_LN(3, 2, 4);
@@ -302,6 +316,7 @@ cudaError_t launch_add_bias_input_layernorm(T* out, const T* input, const T* bia
   else if (vpl <= 8) ETB_LN(8, 1, 1);
   else return cudaErrorInvalidValue;
 #undef ETB_LN
+#undef ETB_LN_ONE
   return le;
 }
 
