@@ -100,6 +100,7 @@ SIGNATURES = {
                                      i32, i32, i32, vp]),
     "et_gather_first_tokens": (i32, [i32, vp, vp, vp, i32, i32, i32, vp]),
     "et_attention": (i32, [i32, vp, vp, vp, i64, i64, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp]),
+    "et_attention_cross": (i32, [i32, vp, i64, vp, vp, i64, i64, vp, vp, vp, i32, i32, i32, i32, i32, vp]),
     "et_attention_general_mask": (i32, [i32, vp, vp, vp, i64, i64, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32,
                                         vp]),
     "et_set_general_mask": (i32, [vp, i32]),

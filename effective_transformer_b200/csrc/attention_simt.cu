@@ -136,6 +136,10 @@ __device__ __forceinline__ void weighted_values(const float (*Ps)[kPad], const f
   }
 }
 
+// cu_seqlens_k null: self-attention (keys and values are the sequence's own rows).  Otherwise
+// cross-attention: sequence b's queries are rows [cu_seqlens[b], cu_seqlens[b+1]) of q and its
+// keys / values rows [cu_seqlens_k[b], cu_seqlens_k[b+1]) of k / v, which have their own row
+// stride (from_seq_len != to_seq_len of sample/tensorflow/modeling.py:558-752 on packed tensors).
 // One CTA per (sequence, head, block of 64 queries), 128 threads.  Thread
 // (ty, tx) = (tid / 8, tid % 8) owns the 4 x 8 block of scores with rows
 // ty + 16 i and keys tx + 8 j, then the 4 x 8 block of the output with the same
@@ -148,7 +152,8 @@ template <typename T, bool kVec>
 __global__ void __launch_bounds__(kThreads, 4)
 attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
                       long long token_stride, long long head_stride, T* __restrict__ ctx, T* __restrict__ ctx_lo,
-                      const int* __restrict__ cu_seqlens, int heads, int max_seq, float scale) {
+                      const int* __restrict__ cu_seqlens, int heads, int max_seq, float scale,
+                      const int* __restrict__ cu_seqlens_k, long long kv_token_stride, int max_seq_k) {
   pdl_wait();
   pdl_trigger();
   const int b = blockIdx.x / heads, head = blockIdx.x % heads;
@@ -157,6 +162,13 @@ attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
   if (len > max_seq) len = max_seq;  // corrupt bounds: stay inside the sequence budget
   const int q0 = blockIdx.y * kQB;
   if (q0 >= len) return;
+  // the keys' rows: the sequence's own, or those of the other tensor
+  int klo = lo, klen = len;
+  if (cu_seqlens_k != nullptr) {
+    klo = cu_seqlens_k[b];
+    klen = cu_seqlens_k[b + 1] - klo;
+    klen = klen < 0 ? 0 : (klen > max_seq_k ? max_seq_k : klen);
+  }
 
   extern __shared__ __align__(16) float simt_smem[];
   float(*Qs)[kPad] = reinterpret_cast<float(*)[kPad]>(simt_smem);
@@ -173,13 +185,13 @@ attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
   // before the first store to shared memory, so that a thread waits for memory once per tile
   // and not once per access.
   constexpr int kPerThread = kQB * (kD / 4) / kThreads;
-  auto load_tile = [&](const T* base, int first_row, int nrows, float4 (&buf)[kPerThread]) {
+  auto load_tile = [&](const T* base, long long stride, int first_row, int nrows, float4 (&buf)[kPerThread]) {
 #pragma unroll
     for (int it = 0; it < kPerThread; ++it) {
       const int idx = it * kThreads + threadIdx.x;
       const int row = idx >> 4, c = (idx & 15) * 4;
       buf[it] = make_float4(0.f, 0.f, 0.f, 0.f);  // rows past the sequence: finite values
-      if (row < nrows) buf[it] = load4<T, kVec>(base + static_cast<size_t>(first_row + row) * token_stride + hoff + c);
+      if (row < nrows) buf[it] = load4<T, kVec>(base + static_cast<size_t>(first_row + row) * stride + hoff + c);
     }
   };
   auto store_tile = [&](float(*dst)[kPad], const float4 (&buf)[kPerThread], float mul) {
@@ -194,10 +206,10 @@ attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
   {
     // Q tile and the first block of K and V: one round trip to memory
     float4 qb[kPerThread], kb[kPerThread], vb[kPerThread];
-    const int nk0 = min(kKB, len);
-    load_tile(q, lo + q0, nq, qb);
-    load_tile(k, lo, nk0, kb);
-    load_tile(v, lo, nk0, vb);
+    const int nk0 = min(kKB, klen);
+    load_tile(q, token_stride, lo + q0, nq, qb);
+    load_tile(k, kv_token_stride, klo, nk0, kb);
+    load_tile(v, kv_token_stride, klo, nk0, vb);
     store_tile(Qs, qb, scale);
     store_tile(Ks, kb, 1.0f);
     store_tile(Vs, vb, 1.0f);
@@ -214,14 +226,14 @@ attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
 
   auto load_keys = [&](int k0, int nk) {
     float4 kb[kPerThread], vb[kPerThread];
-    load_tile(k, lo + k0, nk, kb);
-    load_tile(v, lo + k0, nk, vb);
+    load_tile(k, kv_token_stride, klo + k0, nk, kb);
+    load_tile(v, kv_token_stride, klo + k0, nk, vb);
     store_tile(Ks, kb, 1.0f);
     store_tile(Vs, vb, 1.0f);
   };
 
-  for (int k0 = 0; k0 < len; k0 += kKB) {
-    const int nk = min(kKB, len - k0);
+  for (int k0 = 0; k0 < klen; k0 += kKB) {
+    const int nk = min(kKB, klen - k0);
     const int nj = (nk + 7) >> 3;      // key groups in use
     const int nk4 = (nk + 3) & ~3;
     if (k0 > 0) {
@@ -291,7 +303,7 @@ attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
     sum += __shfl_xor_sync(0xffffffffu, sum, 4);
     const int row = ty + 16 * i;
     if (row < nq) {
-      const float inv = 1.0f / sum;
+      const float inv = sum > 0.f ? 1.0f / sum : 0.f;  // no key at all (cross-attention onto an empty sequence): zeros
       const size_t off = static_cast<size_t>(lo + q0 + row) * hidden + head * kD;
 #pragma unroll
       for (int e = 0; e < 8; ++e) o[i][e] *= inv;
@@ -463,8 +475,13 @@ template cudaError_t launch_attention_masked_simt<__half>(const __half*, const _
 template <typename T>
 cudaError_t launch_attention_simt(const T* q, const T* k, const T* v, long long token_stride,
                                   long long head_stride, T* ctx, const int* cu_seqlens, int batch,
-                                  int max_seq, int heads, int d, cudaStream_t stream, T* ctx_lo) {
+                                  int max_seq, int heads, int d, cudaStream_t stream, T* ctx_lo,
+                                  const int* cu_seqlens_k, long long kv_token_stride, int max_seq_k) {
   if (batch <= 0 || heads <= 0) return cudaSuccess;
+  if (cu_seqlens_k == nullptr) {
+    kv_token_stride = token_stride;
+    max_seq_k = max_seq;
+  }
   if (d != kD) return cudaErrorInvalidValue;
   const float scale = 1.0f / sqrtf(static_cast<float>(d));
   if (max_seq <= 0) return cudaSuccess;
@@ -482,19 +499,21 @@ cudaError_t launch_attention_simt(const T* q, const T* k, const T* v, long long 
   const uintptr_t mask = 4 * sizeof(T) - 1;
   const bool vec = ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
                      reinterpret_cast<uintptr_t>(ctx) | reinterpret_cast<uintptr_t>(ctx_lo)) & mask) == 0 &&
-                   token_stride % 4 == 0 && head_stride % 4 == 0;
+                   token_stride % 4 == 0 && head_stride % 4 == 0 && kv_token_stride % 4 == 0;
   const dim3 grid(batch * heads, (max_seq + kQB - 1) / kQB);
   return vec ? launch_pdl(attention_simt_kernel<T, true>, grid, dim3(kThreads), kSimtSmemBytes, stream, q, k, v,
-                          token_stride, head_stride, ctx, ctx_lo, cu_seqlens, heads, max_seq, scale)
+                          token_stride, head_stride, ctx, ctx_lo, cu_seqlens, heads, max_seq, scale, cu_seqlens_k,
+                          kv_token_stride, max_seq_k)
              : launch_pdl(attention_simt_kernel<T, false>, grid, dim3(kThreads), kSimtSmemBytes, stream, q, k, v,
-                          token_stride, head_stride, ctx, ctx_lo, cu_seqlens, heads, max_seq, scale);
+                          token_stride, head_stride, ctx, ctx_lo, cu_seqlens, heads, max_seq, scale, cu_seqlens_k,
+                          kv_token_stride, max_seq_k);
 }
 
 template cudaError_t launch_attention_simt<float>(const float*, const float*, const float*,
                                                   long long, long long, float*, const int*, int,
-                                                  int, int, int, cudaStream_t, float*);
+                                                  int, int, int, cudaStream_t, float*, const int*, long long, int);
 template cudaError_t launch_attention_simt<__half>(const __half*, const __half*, const __half*,
                                                    long long, long long, __half*, const int*, int,
-                                                   int, int, int, cudaStream_t, __half*);
+                                                   int, int, int, cudaStream_t, __half*, const int*, long long, int);
 
 }  // namespace etb

@@ -308,10 +308,14 @@ cudaError_t launch_gemm_simt(const T* a, const T* w, const T* bias, T* c, const 
                              int max_m, int n, int k, int epilogue, cudaStream_t stream);
 // CUDA-core attention on the packed layout.  ctx_lo (fp32 only): the output is
 // written split for the tf32 projection behind it, rn_tf32 half to ctx, remainder to ctx_lo.
+// cu_seqlens_k given: cross-attention, sequence b's keys / values are rows
+// [cu_seqlens_k[b], cu_seqlens_k[b+1]) of k / v (row stride kv_token_stride, at most max_seq_k of them).
 template <typename T>
 cudaError_t launch_attention_simt(const T* q, const T* k, const T* v, long long token_stride,
                                   long long head_stride, T* ctx, const int* cu_seqlens, int batch,
-                                  int max_seq, int heads, int d, cudaStream_t stream, T* ctx_lo = nullptr);
+                                  int max_seq, int heads, int d, cudaStream_t stream, T* ctx_lo = nullptr,
+                                  const int* cu_seqlens_k = nullptr, long long kv_token_stride = 0,
+                                  int max_seq_k = 0);
 // The same under a general [B, S, S] mask with the reference op's semantics
 // (padded keys take part with K = V = 0).  pos_row[b*S+p] = packed row of
 // position p or -1, made by launch_position_rows (a memset and one kernel).

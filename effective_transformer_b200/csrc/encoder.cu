@@ -1746,6 +1746,24 @@ int et_attention(int dtype, const void* q, const void* k, const void* v, long lo
                                                   static_cast<float*>(ctx), cu_seqlens, batch, max_seq, heads, d, s));
 }
 
+int et_attention_cross(int dtype, const void* q, long long q_token_stride, const void* k, const void* v,
+                       long long kv_token_stride, long long head_stride, void* ctx, const int* cu_seqlens_q,
+                       const int* cu_seqlens_k, int batch, int max_seq_q, int max_seq_k, int heads, int d,
+                       void* stream) {
+  if (batch < 0 || heads <= 0 || d != 64 || max_seq_q < 0 || max_seq_k < 0 || (dtype != ET_FP16 && dtype != ET_FP32))
+    return ET_INVALID_ARGUMENT;
+  if (batch == 0 || max_seq_q == 0) return ET_OK;
+  if (!q || !k || !v || !ctx || !cu_seqlens_q || !cu_seqlens_k) return ET_INVALID_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return ET_DISPATCH(dtype,
+                     launch_attention_simt<__half>(H_(q), H_(k), H_(v), q_token_stride, head_stride,
+                                                   static_cast<__half*>(ctx), cu_seqlens_q, batch, max_seq_q, heads, d,
+                                                   s, nullptr, cu_seqlens_k, kv_token_stride, max_seq_k),
+                     launch_attention_simt<float>(F_(q), F_(k), F_(v), q_token_stride, head_stride,
+                                                  static_cast<float*>(ctx), cu_seqlens_q, batch, max_seq_q, heads, d, s,
+                                                  nullptr, cu_seqlens_k, kv_token_stride, max_seq_k));
+}
+
 int et_attention_general_mask(int dtype, const void* q, const void* k, const void* v, long long token_stride,
                               long long head_stride, void* ctx, const void* attr_mask, const int* cu_seqlens,
                               const int* batch_idx, const int* word_idx, const int* t_ptr, int* pos_row_scratch,

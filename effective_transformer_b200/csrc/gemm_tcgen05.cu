@@ -727,7 +727,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint32_t g = static_cast<uint32_t>(box_gen[e]);  // one shared-memory read for the whole warp
           if (((g ^ (seen_bits >> e)) & 1u) != 0u) {
             any = true;
-            __threadfence();  // the poster saw the complete block; order this warp's reads behind that
+            // The poster saw the complete block (device-scope acquire) before it published it to this CTA
+            // (CTA-scope release); this warp's reads, which go to L2, are ordered behind the publication.
+            __threadfence_block();
             const int first = box_row[e] + ew * kLnRowsPerWarp;
             const int nrows = min(kLnRowsPerWarp, M - first);
             if (nrows > 0) {

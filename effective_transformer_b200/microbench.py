@@ -155,6 +155,19 @@ def main() -> None:
         "gemm_ffn1": (gemm("gemm_ffn1", x_packed, bias_f, 2), "tensor", 2.0 * t * h * f),
         "gemm_ffn2": (gemm("gemm_ffn2", ffn, None, 0), "tensor", 2.0 * t * h * f),
     }
+    if fp16:
+        # the projections that feed a LayerNorm, with the epilogues that take the residual: 4 = bias + residual,
+        # 5 / 6 = the LayerNorm inside the GEMM kernel (bias + residual added in the epilogue / with the rows)
+        counters = torch.zeros(8 * ((n_pos + 255) // 256) + 8, **i32)
+        fused_out = torch.empty(n_pos, h, device=dev, dtype=tdt)
+
+        def fused(name, a, epi):
+            w, wp, kk, nn = weights[name]
+            return lambda: lib.et_gemm_fused(P(a), P(wp), P(bias_h), P(res), P(gamma_h), P(beta_h), 1e-6, P(counters),
+                                             P(fused_out), P(tn), n_pos, nn, kk, epi, P(status), st)
+        kernels["gemm_ffn2_residual"] = (fused("gemm_ffn2", ffn, 4), "tensor", 2.0 * t * h * f)
+        kernels["gemm_ffn2_layernorm"] = (fused("gemm_ffn2", ffn, 5), "tensor", 2.0 * t * h * f)
+        kernels["gemm_attn_out_layernorm"] = (fused("gemm_attn_out", x_packed, 6), "tensor", 2.0 * t * h * h)
     # The library GEMM (cuBLAS through torch.matmul) on the same T x N x K, without bias or
     # activation: a comparison figure for the four projections, never part of the product path.
     lib_out = {name: torch.empty(t, w[3], device=dev, dtype=tdt) for name, w in weights.items()}

@@ -441,6 +441,20 @@ int et_attention_general_mask(int dtype, const void* q, const void* k, const voi
                               int* pos_row_scratch, int batch_size, int seq_len, int head_num,
                               int size_per_head, void* stream);
 
+/* Cross-attention on packed tensors: from_seq_len != to_seq_len of the
+ * sample model's attention_layer (sample/tensorflow/modeling.py:558-752; the
+ * layer op itself rejects it, tf_op/bert_transformer_op.cc:130-131, and so does
+ * et_layer).  Sequence b's queries are rows [cu_seqlens_q[b], cu_seqlens_q[b+1])
+ * of q (row stride q_token_stride), its keys and values rows
+ * [cu_seqlens_k[b], cu_seqlens_k[b+1]) of k / v (row stride kv_token_stride);
+ * head h at column h * head_stride; ctx is packed [Tq, heads * 64].  Softmax over
+ * the to-sequence's own keys (the key-only mask of the to-tensor); a query whose
+ * to-sequence is empty gets a zero row.  CUDA-core kernel, fp32 arithmetic. */
+int et_attention_cross(int dtype, const void* q, long long q_token_stride, const void* k, const void* v,
+                       long long kv_token_stride, long long head_stride, void* ctx, const int* cu_seqlens_q,
+                       const int* cu_seqlens_k, int batch_size, int max_seq_q, int max_seq_k, int head_num,
+                       int size_per_head, void* stream);
+
 /* The same attention block on the tcgen05 tensor cores, fp16, for batches whose
  * sequences have at most 128 tokens (max_seq_len <= 128).  A plan packs whole
  * sequences into tiles of at most 128 token rows; it depends only on

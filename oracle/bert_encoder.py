@@ -245,6 +245,22 @@ def packed_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqle
     return out
 
 
+def cross_attention_padded(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, attention_mask: torch.Tensor,
+                           heads: int, d: int) -> torch.Tensor:
+    """The core of attention_layer with from_tensor != to_tensor (sample/tensorflow/modeling.py:
+    690-745): q is [B, F, heads*d] (already projected), k and v [B, T, heads*d], attention_mask
+    [B, F, T] (1 = attend).  Returns the context [B, F, heads*d]."""
+    b, f, _ = q.shape
+    t = k.shape[1]
+    qh = q.reshape(b, f, heads, d).permute(0, 2, 1, 3)                      # :690-692
+    kh = k.reshape(b, t, heads, d).permute(0, 2, 1, 3)                      # :695-696
+    scores = torch.matmul(qh, kh.transpose(-1, -2)) * (1.0 / math.sqrt(float(d)))   # :701-703
+    scores = scores + (1.0 - attention_mask.unsqueeze(1).to(q.dtype)) * -10000.0    # :705-717
+    probs = torch.softmax(scores, dim=-1)                                    # :721
+    vh = v.reshape(b, t, heads, d).permute(0, 2, 1, 3)                      # :728-733
+    return torch.matmul(probs, vh).permute(0, 2, 1, 3).reshape(b, f, heads * d)     # :736-745
+
+
 def packed_attention_general_mask(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
                                   cu_seqlens: np.ndarray, word_idx: np.ndarray, attr_mask: torch.Tensor,
                                   seq: int, heads: int, d: int) -> torch.Tensor:

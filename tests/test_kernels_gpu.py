@@ -529,3 +529,46 @@ def test_gemm_fused_rejects_what_it_cannot_do():
                                iptr(mt), 1, 256, 64, 5, None, stream()) == bad
     assert lib().et_gemm_fused(iptr(z), iptr(z), iptr(z), None, iptr(z), iptr(z), 1e-6, iptr(cnt), iptr(z),
                                iptr(mt), 1, 256, 64, 4, None, stream()) == bad
+
+
+# ---- cross-attention: from_seq_len != to_seq_len on packed tensors ------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("lens_q,lens_k", [([5, 1, 16, 33], [7, 40, 3, 1]), ([64, 64, 2], [128, 1, 90]),
+                                           ([10, 0, 4], [6, 9, 0]), ([130, 3], [70, 200])])
+def test_cross_attention_against_the_padded_oracle(dtype, lens_q, lens_k):
+    """et_attention_cross vs attention_layer with from_tensor != to_tensor (padded, key-only mask of
+    the to-tensor), compared on the valid query rows.  A query whose to-sequence is empty gets zeros."""
+    rng = np.random.RandomState(sum(lens_q) + 7 * sum(lens_k))
+    heads, d = 3, 64
+    h = heads * d
+    lens_q, lens_k = np.array(lens_q, np.int32), np.array(lens_k, np.int32)
+    b, f, t = len(lens_q), int(max(lens_q.max(), 1)), int(max(lens_k.max(), 1))
+    cu_q = np.zeros(b + 1, np.int32); cu_q[1:] = np.cumsum(lens_q)
+    cu_k = np.zeros(b + 1, np.int32); cu_k[1:] = np.cumsum(lens_k)
+    tq, tk = int(cu_q[-1]), int(cu_k[-1])
+    q = dev(rng.randn(tq + 3, h).astype(np.float32), dtype)
+    kv = dev(rng.randn(tk + 2, 2 * h).astype(np.float32), dtype)       # K and V side by side: their own row stride
+    ctx = torch.full((tq + 3, h), 2.0, dtype=dtype, device="cuda")
+    cu_q_d, cu_k_d = dev(cu_q), dev(cu_k)
+    ok(lib().et_attention_cross(DT[dtype], iptr(q), h, kv.data_ptr(), kv.data_ptr() + h * kv.element_size(), 2 * h, d,
+                                iptr(ctx), iptr(cu_q_d), iptr(cu_k_d), b, f, t, heads, d, stream()))
+    torch.cuda.synchronize()
+    # padded oracle
+    qp = torch.zeros(b, f, h, dtype=torch.float64)
+    kp = torch.zeros(b, t, h, dtype=torch.float64)
+    vp = torch.zeros(b, t, h, dtype=torch.float64)
+    mask = torch.zeros(b, f, t, dtype=torch.float64)
+    for i in range(b):
+        qp[i, :lens_q[i]] = q[cu_q[i]:cu_q[i + 1]].double().cpu()
+        kp[i, :lens_k[i]] = kv[cu_k[i]:cu_k[i + 1], :h].double().cpu()
+        vp[i, :lens_k[i]] = kv[cu_k[i]:cu_k[i + 1], h:].double().cpu()
+        mask[i, :, :lens_k[i]] = 1.0
+    ref = O.cross_attention_padded(qp, kp, vp, mask, heads, d)
+    tol = dict(rtol=3e-3, atol=3e-3) if dtype == torch.float16 else dict(rtol=1e-5, atol=1e-5)
+    for i in range(b):
+        got = ctx[cu_q[i]:cu_q[i + 1]].double().cpu()
+        if lens_k[i] == 0:
+            assert torch.all(got == 0)
+        else:
+            torch.testing.assert_close(got, ref[i, :lens_q[i]], **tol)
+    assert torch.all(ctx[tq:] == 2.0)
