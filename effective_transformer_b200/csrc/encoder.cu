@@ -175,9 +175,10 @@ struct et_handle_s {
   // the previous kernel of the chain wrote its rows first-to-last.
   bool prev_ascending = true;
   // fp16 tensor-core path, et_set_fused_layernorm(1): bias + residual + LayerNorm run inside the two
-  // N = hidden projection kernels (5 launches per layer instead of 7).  Off by default: measured, the
-  // LayerNorm arithmetic (about 250 warp instructions per row) takes the eight epilogue warps of a
-  // CTA longer than a LayerNorm kernel with 48 warps per SM takes for the same rows.
+  // N = hidden projection kernels (5 launches per layer instead of 7).  Off by default: measured on
+  // B200 it breaks even behind the K = ffn_dim projection and loses behind the K = hidden one (the
+  // eight epilogue warps of a CTA hide the LayerNorm's memory latency worse than the 16 warps per SM
+  // of the LayerNorm kernel, and its L2 traffic slows the GEMM's operand loads).
   bool fuse_ln = false;
   TensorMapCache maps;  // TMA descriptors of this handle's launches
   // general [B,S,S] mask of the pass being enqueued (null: key-only mask, fast kernels)

@@ -43,17 +43,24 @@ constexpr int kNumThreads = 64 + kEpilogueThreads;
 constexpr int kStagingPerWarp = 32 * 128;  // 32 rows x 128 bytes (64 fp16 columns)
 
 // ---- LayerNorm inside the GEMM kernel (kEpiResidualLayerNorm, kEpiLayerNorm) -----------------
-// Every epilogue warp counts the columns it has stored for its 32 rows in a global counter of that
-// row block.  The warp whose count completes the rows (all N columns, written by up to six warps of
-// three CTA pairs) knows that the whole pre-LayerNorm block is in L2 and posts it to its CTA: the
-// eight epilogue warps then normalise four rows of it each, in place, in the time they would
-// otherwise spend waiting for their next accumulator.
+// A 32-row block of C can be normalised once all N of its columns are stored, by up to six warps of
+// three CTA pairs.  Roles in a CTA of these variants:
+//   epilogue warps   store their part of a unit, raise a shared-memory flag, go on
+//   counting warp    (one more warp) sees the flags, makes the flagged stores visible to the GPU with
+//                    ONE fence for all of them (a fence costs a round trip to L2: too long for every
+//                    epilogue warp to wait for it per tile), adds each part's columns to the global
+//                    counter of its row block, and publishes the blocks whose count it completed in a
+//                    queue of the CTA
+//   epilogue warps   normalise four rows each of every published block, in place, in the time they
+//                    would otherwise spend waiting for their next accumulator
 __host__ __device__ constexpr bool has_ln(int epi) { return epi == kEpiResidualLayerNorm || epi == kEpiLayerNorm; }
 // what the accumulator epilogue itself does for an epilogue kind
 __host__ __device__ constexpr int base_epi(int epi) {
   return epi == kEpiResidualLayerNorm ? kEpiBiasResidual : epi == kEpiLayerNorm ? kEpiNone : epi;
 }
+__host__ __device__ constexpr int threads_of(int epi) { return kNumThreads + (has_ln(epi) ? 32 : 0); }
 constexpr int kLnRowsPerWarp = 32 / kEpilogueWarps;  // a 32-row block is shared out among the epilogue warps
+constexpr int kLnQueue = 32;                         // published blocks a CTA can hold before the slowest warp has done its rows
 
 // LayerNorm of RB consecutive rows of c [*, n] in place by one warp, n = 256 * VPL: lane l holds
 // the 16-byte vectors j * 32 + l of a row, statistics in fp32 in two passes over the registers,
@@ -512,17 +519,17 @@ struct PairCfg {
   static constexpr int kStagingBytes = kEpilogueWarps * kStagingPerWarp;
   static constexpr int kColsPerWarp = BN / 2;
   static constexpr int kBiasBytes = kEpilogueWarps * kColsPerWarp * 2;
-  // barriers (2 * kStages + 5), the TMEM slot, the abort flag and the 4 x 8 words of the LayerNorm work sharing
+  // barriers (2 * kStages + 5), the TMEM slot, the abort flag and the words of the LayerNorm work sharing
   static constexpr int kControlBytes = 512;
   static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + kBiasBytes + kControlBytes;
-  static_assert(kNumBars * 8 + 8 + 4 * kEpilogueWarps * 4 <= kControlBytes, "control block too small");
+  static_assert(kNumBars * 8 + 8 + (3 * kEpilogueWarps + kLnQueue + 2) * 4 <= kControlBytes, "control block too small");
   static_assert(kSmemBytes <= 232448, "more than 227 KB of shared memory");
   static constexpr int kTmemCols = 2 * BN;
 };
 
 // VPL: 16-byte vectors of a C row per lane in the LayerNorm warps (N / 256); 0 for the other epilogues.
 template <int EPI, int VPL>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(threads_of(EPI), 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                          const __grid_constant__ CUtensorMap tmap_b,
                          const __grid_constant__ CUtensorMap tmap_b_half, __half* __restrict__ C,
@@ -559,14 +566,16 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const uint32_t drain_bar = bar0 + 8u * (2 * S + 4);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + cfg::kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  // LayerNorm variants, per epilogue warp e: box_row[e] = first row of the complete 32-row block
-  // it posted last, box_gen[e] = how many it has posted, box_done[e] = how many 4-row shares of
-  // its blocks the warps have normalised, ln_done[e] = it has left its loop
-  volatile int* box_row = reinterpret_cast<volatile int*>(tmem_slot + 2);
-  volatile int* box_gen = box_row + kEpilogueWarps;
-  volatile int* box_done = box_gen + kEpilogueWarps;
-  volatile int* ln_done = box_done + kEpilogueWarps;
-
+  // LayerNorm variants.  Per epilogue warp e: ep_units[e] = units whose stores it has issued,
+  // ep_final[e] = it has left its loop, ln_seen[e] = published blocks it has done its rows of.
+  // The queue: q_row[i % kLnQueue] = first row of the i-th published block, *q_tail = how many are
+  // published, *q_closed = the counting warp will publish no more.
+  volatile int* ep_units = reinterpret_cast<volatile int*>(tmem_slot + 2);
+  volatile int* ep_final = ep_units + kEpilogueWarps;
+  volatile int* ln_seen = ep_final + kEpilogueWarps;
+  volatile int* q_row = ln_seen + kEpilogueWarps;
+  volatile int* q_tail = q_row + kLnQueue;
+  volatile int* q_closed = q_tail + 1;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
@@ -580,7 +589,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     mbar_init(drain_bar, 1);
     *abort_flag = 0;
-    for (int e = 0; e < 4 * kEpilogueWarps; ++e) box_row[e] = 0;
+    for (int e = 0; e < 3 * kEpilogueWarps + kLnQueue + 2; ++e) ep_units[e] = 0;
     fence_mbar_init();
     fence_proxy_async_smem();
   }
@@ -703,7 +712,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       umma_commit_pair(drain_bar);
       if (!mbar_wait(drain_bar, 0u, abort_flag) && *abort_flag == 0) fail(kSiteMmaDrain);
     }
-  } else {
+  } else if (warp < 2 + kEpilogueWarps) {
     // ------------------------- epilogue (both CTAs) -------------------------
     constexpr int kBase = base_epi(EPI);
     constexpr bool kLn = has_ln(EPI);
@@ -714,78 +723,40 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint32_t buf = staging_addr + ew * kStagingPerWarp;
     const uint32_t bias_s = bias_addr + ew * (kCols * 2);
 
-    // ---- LayerNorm work sharing (LayerNorm variants only) ----
-    // A warp owes every posted block its own four rows.  A warp may post its next block only when
-    // all eight shares of its previous one are done, so a warp is never more than one block behind
-    // per poster and one bit per poster records which of its blocks this warp has seen.
-    uint32_t seen_bits = 0;
+    // ---- LayerNorm variants: this warp's four rows of every published block ----
+    int seen = 0;  // published blocks this warp has done
     auto ln_poll = [&]() -> bool {
       bool any = false;
       if constexpr (kLn) {
+        const int tail = *q_tail;  // one shared-memory read for the whole warp
+        // The counting warp saw the complete block (device scope) before it published it to this
+        // CTA (CTA-scope release); this warp's reads, which go to L2, are ordered behind that.
+        if (seen != tail) __threadfence_block();
+        for (; seen != tail; ++seen) {
+          any = true;
+          const int first = q_row[seen % kLnQueue] + ew * kLnRowsPerWarp;
+          const int nrows = min(kLnRowsPerWarp, M - first);
+          if (nrows > 0) {
+            __half* crow = C + static_cast<size_t>(first) * N;
+            const __half* rrow = residual + static_cast<size_t>(first) * N;
+            constexpr int RB = VPL <= 3 ? kLnRowsPerWarp : kLnRowsPerWarp / 2;
 #pragma unroll 1
-        for (int e = 0; e < kEpilogueWarps; ++e) {
-          const uint32_t g = static_cast<uint32_t>(box_gen[e]);  // one shared-memory read for the whole warp
-          if (((g ^ (seen_bits >> e)) & 1u) != 0u) {
-            any = true;
-            // The poster saw the complete block (device-scope acquire) before it published it to this CTA
-            // (CTA-scope release); this warp's reads, which go to L2, are ordered behind the publication.
-            __threadfence_block();
-            const int first = box_row[e] + ew * kLnRowsPerWarp;
-            const int nrows = min(kLnRowsPerWarp, M - first);
-            if (nrows > 0) {
-              __half* crow = C + static_cast<size_t>(first) * N;
-              const __half* rrow = residual + static_cast<size_t>(first) * N;
-              constexpr int RB = VPL <= 3 ? kLnRowsPerWarp : kLnRowsPerWarp / 2;
-#pragma unroll 1
-              for (int r0 = 0; r0 < nrows; r0 += RB)
-                ln_rows<(VPL > 0 ? VPL : 1), EPI == kEpiLayerNorm, RB>(
-                    crow + static_cast<size_t>(r0) * N, rrow + static_cast<size_t>(r0) * N, bias, ln.gamma, ln.beta,
-                    N, min(RB, nrows - r0), ln.eps, lane);
-            }
-            seen_bits ^= 1u << e;
-            __syncwarp();
-            if (lane == 0) atomicAdd(const_cast<int*>(box_done + e), 1);
+            for (int r0 = 0; r0 < nrows; r0 += RB)
+              ln_rows<(VPL > 0 ? VPL : 1), EPI == kEpiLayerNorm, RB>(
+                  crow + static_cast<size_t>(r0) * N, rrow + static_cast<size_t>(r0) * N, bias, ln.gamma, ln.beta, N,
+                  min(RB, nrows - r0), ln.eps, lane);
           }
+        }
+        if (any) {
+          __syncwarp();
+          if (lane == 0) ln_seen[ew] = seen;  // the queue slot may be reused once every warp is past it
         }
       }
       return any;
     };
-    // waits (polling the LayerNorm work) for `ready()`; false on abort or after the time limit
-    auto wait_polling = [&](auto ready) -> bool {
-      unsigned long long t0 = 0;
-      for (uint32_t spin = 1;; ++spin) {
-        if (__all_sync(0xffffffffu, ready())) return true;
-        if (ln_poll()) {
-          t0 = 0;
-        } else if ((spin & 63u) == 0u) {
-          bool stop = *abort_flag != 0;
-          const unsigned long long now = globaltimer_ns();
-          if (t0 == 0) t0 = now;
-          else if (now - t0 > kWaitTimeoutNs) stop = true;
-          if (__any_sync(0xffffffffu, stop)) return false;
-        }
-      }
-    };
-    // posts the complete block that starts at `brow0` (this warp made its column count reach N)
-    auto ln_post = [&](int brow0) -> bool {
-      if (lane == 0) ln.counters[brow0 >> 5] = 0;  // nobody else touches it any more: zero for the next launch
-      if (M - brow0 <= 0) return true;             // a row block past the last row: nothing to normalise
-      const bool free_box =
-          wait_polling([&] { return box_done[ew] == kEpilogueWarps * box_gen[ew]; });
-      if (!free_box) return false;
-      if (lane == 0) {
-        box_row[ew] = brow0;
-        __threadfence_block();
-        box_gen[ew] = box_gen[ew] + 1;
-      }
-      __syncwarp();
-      return true;
-    };
 
-    int prev_row0 = -1, prev_wcols = 0;  // the unit before this one: its column count is still to be added
     int it = 0;
-    bool ok = true;
-    for (int u = pair_id; u < num_units && ok; u += num_pairs, ++it) {
+    for (int u = pair_id; u < num_units; u += num_pairs, ++it) {
       const PairUnit pu = pair_unit(u, full_tiles, n_tiles, m_tiles, reverse_m);
       const int m_tile = pu.m_tile;
       const int wcols = pu.ncols / 2;  // columns of this warp: 128, or 64 in a half-width unit
@@ -797,25 +768,33 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         __syncwarp();
       }
       bool got;
-      if constexpr (kLn)
-        got = wait_polling([&] { return mbar_test_wait(tmem_full_bar(acc), acc_phase); });
-      else
+      if constexpr (kLn) {
+        // wait for the accumulator, normalising published rows meanwhile
+        got = true;
+        unsigned long long t0 = 0;
+        for (uint32_t spin = 1;; ++spin) {
+          if (__all_sync(0xffffffffu, mbar_test_wait(tmem_full_bar(acc), acc_phase))) break;
+          if (ln_poll()) {
+            t0 = 0;
+          } else if ((spin & 63u) == 0u) {
+            bool stop = *abort_flag != 0;
+            const unsigned long long now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitTimeoutNs) stop = true;
+            if (__any_sync(0xffffffffu, stop)) {
+              got = false;
+              break;
+            }
+          }
+        }
+      } else {
         got = __all_sync(0xffffffffu, mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag));
+      }
       if (!got) {
         if (lane == 0) fail(kSiteEpilogueFull);
         break;
       }
       tc_fence_after();
-      // The previous unit's stores are long on their way by now: count its columns for its 32
-      // rows (release: the stores are ordered before the count).  The count's old value is only
-      // looked at behind this unit's epilogue, so its round trip to L2 is not waited for.
-      int before = 0;
-      if constexpr (kLn) {
-        if (prev_row0 >= 0) {
-          __threadfence();
-          if (lane == 0) before = atomicAdd(ln.counters + (prev_row0 >> 5), prev_wcols);
-        }
-      }
       const int row0 = m_tile * BM2 + static_cast<int>(rank) * BM + quad * 32;
       const uint32_t t_row =
           tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN + half * wcols;
@@ -827,46 +806,25 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (lane == 0) mbar_arrive_cluster(empty0);
       });
       if constexpr (kLn) {
-        if (prev_row0 >= 0) {
-          before = __shfl_sync(0xffffffffu, before, 0);
-          if (before + prev_wcols == N) {  // acquire: this warp now sees all columns of those rows
-            __threadfence();
-            if (!ln_post(prev_row0)) {
-              if (lane == 0) fail(kSiteLnMailbox);
-              ok = false;
-            }
-          }
-        }
-        prev_row0 = row0;
-        prev_wcols = wcols;
+        // this unit's stores are issued: tell the counting warp (CTA-scope release of all lanes' stores)
+        __threadfence_block();
+        __syncwarp();
+        if (lane == 0) ep_units[ew] = it + 1;
       }
     }
     if constexpr (kLn) {
-      if (ok && prev_row0 >= 0) {  // the last unit of this warp
-        __threadfence();
-        int before = 0;
-        if (lane == 0) before = atomicAdd(ln.counters + (prev_row0 >> 5), prev_wcols);
-        before = __shfl_sync(0xffffffffu, before, 0);
-        if (before + prev_wcols == N) {
-          __threadfence();
-          if (!ln_post(prev_row0) && lane == 0) fail(kSiteLnMailbox);
-        }
-      }
       __syncwarp();
       if (lane == 0) {
-        __threadfence_block();  // a posted block is visible before the flag
-        ln_done[ew] = 1;
+        __threadfence_block();
+        ep_final[ew] = 1;
       }
-      // stay until every warp of the CTA has posted its last block and this warp has done its share
-      // of all of them (ln_done is read before the blocks are looked for: a warp posts before it
-      // sets its flag)
+      // stay until the counting warp has published its last block and this warp has done its rows
+      // of all of them (q_closed is read before the queue: a block is published before the flag)
       unsigned long long t0 = 0;
       for (;;) {
-        int all_done = 1;
-#pragma unroll
-        for (int e = 0; e < kEpilogueWarps; ++e) all_done &= ln_done[e];
+        const int closed = *q_closed;
         const bool any = ln_poll();
-        if (all_done != 0 && !any) break;
+        if (closed != 0 && !any) break;
         if (any) {
           t0 = 0;
           continue;
@@ -874,8 +832,90 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         __nanosleep(64);
         const unsigned long long now = globaltimer_ns();
         if (t0 == 0) t0 = now;
-        if (__any_sync(0xffffffffu, now - t0 > 2 * kWaitTimeoutNs)) break;
+        if (__any_sync(0xffffffffu, now - t0 > 2 * kWaitTimeoutNs || *abort_flag != 0)) break;
       }
+    }
+  } else if constexpr (has_ln(EPI)) {
+    // ------------------------- counting warp (both CTAs, LayerNorm variants) -------------------------
+    // Lane e < 8 follows epilogue warp e through the unit schedule, which it can compute itself.
+    const int e = lane & (kEpilogueWarps - 1);
+    const bool tracker = lane < kEpilogueWarps;
+    const int quad = e & 3;  // epilogue warp e is warp e + 2: TMEM lane quadrant (e + 2) & 3
+    const int equad = (e + 2) & 3;
+    (void)quad;
+    int counted = 0;         // units of warp e already added to the row counters
+    int published = 0;       // blocks this CTA has published (same value in every lane)
+    unsigned long long t0 = 0;
+    bool give_up = false;
+    for (;;) {
+      // flags first, then "final": a warp raises its last flag before it sets final
+      const int final_e = tracker ? ep_final[e] : 1;
+      const int units_e = tracker ? ep_units[e] : 0;
+      const bool pending = tracker && units_e > counted;
+      const unsigned pend_mask = __ballot_sync(0xffffffffu, pending);
+      if (pend_mask != 0u) {
+        t0 = 0;
+        // One device-scope fence for every flagged store: the flags were raised behind CTA-scope
+        // fences of the storing warps, so this fence orders those stores before the counts below.
+        __threadfence();
+        int last_row = -1;
+        if (pending) {
+          const int u = pair_id + counted * num_pairs;
+          const PairUnit pu = pair_unit(u, full_tiles, n_tiles, m_tiles, reverse_m);
+          const int row0 = pu.m_tile * BM2 + static_cast<int>(rank) * BM + equad * 32;
+          const int wcols = pu.ncols / 2;
+          const int before = atomicAdd(ln.counters + (row0 >> 5), wcols);
+          if (before + wcols == N) {  // this part completed the 32 rows: every column is in L2
+            ln.counters[row0 >> 5] = 0;  // nobody else touches it any more: zero again for the next launch
+            if (row0 < M) last_row = row0;
+          }
+          ++counted;
+        }
+        // publish the completed blocks, one queue slot each, in lane order
+        const unsigned post_mask = __ballot_sync(0xffffffffu, last_row >= 0);
+        if (post_mask != 0u) {
+          const int nposts = __popc(post_mask);
+          // room in the queue: every epilogue warp must be past the slots about to be overwritten
+          for (;;) {
+            int slowest = tracker ? ln_seen[e] : 0x7fffffff;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) slowest = min(slowest, __shfl_xor_sync(0xffffffffu, slowest, o));
+            if (published + nposts - slowest <= kLnQueue) break;
+            __nanosleep(64);
+            const unsigned long long now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            if (__any_sync(0xffffffffu, now - t0 > kWaitTimeoutNs || *abort_flag != 0)) {
+              give_up = true;
+              break;
+            }
+          }
+          if (give_up) {
+            if (lane == 0) fail(kSiteLnMailbox);
+            break;
+          }
+          t0 = 0;
+          if (last_row >= 0) {
+            const int slot = published + __popc(post_mask & ((1u << lane) - 1u));
+            q_row[slot % kLnQueue] = last_row;
+          }
+          published += nposts;
+          __threadfence_block();  // acquire of the counts above, release of the queue entries
+          __syncwarp();
+          if (lane == 0) *q_tail = published;
+        }
+        continue;
+      }
+      // nothing flagged: finished when every epilogue warp has left its loop (and all its flags are counted)
+      if (__all_sync(0xffffffffu, final_e != 0)) break;
+      __nanosleep(32);
+      const unsigned long long now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      if (__any_sync(0xffffffffu, now - t0 > 4 * kWaitTimeoutNs || *abort_flag != 0)) break;
+    }
+    __syncwarp();
+    if (lane == 0) {
+      __threadfence_block();
+      *q_closed = 1;
     }
   }
 
@@ -905,7 +945,7 @@ cudaError_t launch_pair_epi(const CUtensorMap& ta, const CUtensorMap& tb, const 
   long long pairs = sm_count() / 2;
   if (pairs > max_tiles) pairs = max_tiles;
   if (pairs < 1) pairs = 1;
-  return launch_pdl(gemm_tcgen05_pair_kernel<EPI, VPL>, dim3(static_cast<int>(2 * pairs)), dim3(kNumThreads),
+  return launch_pdl(gemm_tcgen05_pair_kernel<EPI, VPL>, dim3(static_cast<int>(2 * pairs)), dim3(threads_of(EPI)),
                     cfg::kSmemBytes, stream, ta, tb, tbh, c, bias, residual, m_ptr, max_m, n, k, status_word, reverse_m,
                     ln);
 }
