@@ -108,6 +108,7 @@ SIGNATURES = {
     "et_attention_plan_ints": (C.c_size_t, [i32, i32]),
     "et_attention_plan": (i32, [vp, i32, i32, vp, vp]),
     "et_attention_tiles": (i32, [vp, vp, vp, i64, i64, vp, vp, i32, i32, i32, i32, i32, vp, vp]),
+    "et_attention_tiles_general_mask": (i32, [vp, vp, vp, i64, i64, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp]),
     "et_gemm": (i32, [i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp]),
     "et_pack_weight": (i32, [i32, vp, vp, i32, i32, vp]),
     "et_split_tf32": (i32, [vp, vp, vp, vp, i32, i32, vp]),

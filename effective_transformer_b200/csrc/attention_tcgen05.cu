@@ -187,11 +187,24 @@ struct Coords {
   int x_per_head, y_per_head;  // TMA coordinates: x = head * x_per_head, y = head * y_per_head + token
 };
 
+// General [B, S, S] attention mask (kMask kernels): attr_mask[b][q][k] > 0.5 = query position q of
+// sequence b may attend to key position k; batch_idx / word_idx give the sequence and the position of
+// every packed row.  Semantics of the reference op (cuda/attention.cu:106-382): the score of a
+// disallowed key gets -10000, and a PADDED key position takes part with K = V = 0 -- score 0, nothing
+// added to the context, but its weight counts in the softmax denominator when the mask allows it.
+struct MaskArgs {
+  const __half* attr_mask;
+  const int* batch_idx;
+  const int* word_idx;
+  int seq;
+};
+
+template <bool kMask>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                          const __grid_constant__ CUtensorMap tmap_v, Coords co, __half* __restrict__ ctx,
                          const int* __restrict__ plan, int batch, int max_tokens, int heads,
-                         float scale_log2e, int* status_word, int reverse) {
+                         float scale_log2e, int* status_word, int reverse, MaskArgs ma) {
   // The prologue (barriers, TMEM) touches no global memory: it runs before the
   // wait on the preceding kernel, under that kernel's tail.
   pdl_trigger();
@@ -318,6 +331,36 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     const bool has_next = item + static_cast<int>(gridDim.x) < total;
 
     const int lo = cur.lo, hi = cur.hi;
+    // General mask: which of this row's own keys (tile columns lo..hi) it may attend to, one bit per tile
+    // column, and how many PADDED key positions it may attend to (they only weigh in the denominator).
+    // A row that may attend to nothing attends to everything: the same -10000 on every score cancels.
+    uint32_t allow[4] = {0u, 0u, 0u, 0u};
+    float n_pad = 0.f;
+    if constexpr (kMask) {
+      if (r < n && hi > lo) {
+        const int token = t0 + r;
+        const __half* mrow = ma.attr_mask +
+            (static_cast<size_t>(ma.batch_idx[token]) * ma.seq + ma.word_idx[token]) * ma.seq;
+        int total = 0;  // allowed key positions, valid or padded
+        for (int j = 0; j < ma.seq; ++j) total += __half2float(mrow[j]) > 0.5f ? 1 : 0;
+        int valid_allowed = 0;
+        for (int c = lo; c < hi; ++c) {
+          const int kpos = ma.word_idx[t0 + c];
+          const bool a = total == 0 || __half2float(mrow[kpos]) > 0.5f;
+          valid_allowed += a ? 1 : 0;
+          if (a) {
+            // static register indices: pick the word with a select chain
+            const uint32_t bit = 1u << (c & 31);
+            const int w = c >> 5;
+            allow[0] |= w == 0 ? bit : 0u;
+            allow[1] |= w == 1 ? bit : 0u;
+            allow[2] |= w == 2 ? bit : 0u;
+            allow[3] |= w == 3 ? bit : 0u;
+          }
+        }
+        n_pad = static_cast<float>(total == 0 ? ma.seq - (hi - lo) : total - valid_allowed);
+      }
+    }
     ok = wait_all(bar_qk, load_phase, kSiteLoad);
     if (!ok) break;
     tc_fence_before();
@@ -363,9 +406,20 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         tmem_ld_32x32b_x32(t_lane + c0, s32);
         tmem_ld_wait();
         const int rel = c0 - lo;
+        if constexpr (kMask) {
+          const int w = c0 >> 5;
+          const uint32_t aw = w == 0 ? allow[0] : w == 1 ? allow[1] : w == 2 ? allow[2] : allow[3];
 #pragma unroll
-        for (int e = 0; e < 32; ++e)
-          if (static_cast<unsigned>(rel + e) < span) m = fmaxf(m, __uint_as_float(s32[e]));
+          for (int e = 0; e < 32; ++e)
+            if ((aw >> e) & 1u) m = fmaxf(m, __uint_as_float(s32[e]));
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            if (static_cast<unsigned>(rel + e) < span) m = fmaxf(m, __uint_as_float(s32[e]));
+        }
+      }
+      if constexpr (kMask) {
+        if (n_pad > 0.f) m = fmaxf(m, 0.f);  // a padded key the row may attend to has score 0
       }
       const float ms = (r < n && hi > lo) ? -m * scale_log2e : 0.f;
       float l = 0.f;
@@ -378,13 +432,20 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
           tmem_ld_32x32b_x32(t_lane + c0, s32);
           tmem_ld_wait();
           const int rel = c0 - lo;
+          uint32_t aw = 0u;
+          if constexpr (kMask) {
+            const int w = c0 >> 5;
+            aw = w == 0 ? allow[0] : w == 1 ? allow[1] : w == 2 ? allow[2] : allow[3];
+          }
 #pragma unroll
           for (int e = 0; e < 16; ++e) {
             float p2[2];
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
               const float pe = ex2_approx(fmaf(__uint_as_float(s32[2 * e + u]), scale_log2e, ms));
-              p2[u] = static_cast<unsigned>(rel + 2 * e + u) < span ? pe : 0.f;
+              const bool keep = kMask ? ((aw >> (2 * e + u)) & 1u) != 0u
+                                      : static_cast<unsigned>(rel + 2 * e + u) < span;
+              p2[u] = keep ? pe : 0.f;
               l += p2[u];
             }
             pk[e] = pack_half2(p2[0], p2[1]);
@@ -395,6 +456,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         tmem_st_32x32b_x16(t_lane + kPCol + (c0 >> 1), pk);
       }
       tmem_st_wait();
+      if constexpr (kMask) l += n_pad * ex2_approx(ms);  // padded keys: score 0, V = 0
       inv_l = (l > 0.f) ? 1.0f / l : 0.f;
     }
     // this item's V rows were requested an item ago and have had the softmax to arrive.  Rows
@@ -486,7 +548,8 @@ cudaError_t launch_attention_plan(const int* cu_seqlens, int batch, int max_toke
 cudaError_t launch_attention_tcgen05(const __half* q, const __half* k, const __half* v,
                                      long long token_stride, long long head_stride, __half* ctx,
                                      const int* plan, int batch, int max_tokens, int heads, int d,
-                                     int* status_word, cudaStream_t stream, bool reverse, TensorMapCache* maps) {
+                                     int* status_word, cudaStream_t stream, bool reverse, TensorMapCache* maps,
+                                     const __half* attr_mask, const int* batch_idx, const int* word_idx, int seq) {
   if (batch <= 0 || heads <= 0 || max_tokens <= 0) return cudaSuccess;
   if (d != kD || token_stride < kD || (token_stride % 8) != 0 || (head_stride % 8) != 0 || head_stride < 0)
     return cudaErrorInvalidValue;
@@ -513,19 +576,29 @@ cudaError_t launch_attention_tcgen05(const __half* q, const __half* k, const __h
     return cudaErrorInvalidValue;
   static PerDeviceOnce once;  // function attributes are per device
   const cudaError_t once_err = once.run([] {
-    cudaError_t attr_err = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    kSmemBytes);
+    cudaError_t attr_err = cudaFuncSetAttribute(attention_tcgen05_kernel<false>,
+                                                cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (attr_err == cudaSuccess)
+      attr_err = cudaFuncSetAttribute(attention_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      kSmemBytes);
     return attr_err;
   });
   if (once_err != cudaSuccess) return once_err;
+  const bool masked = attr_mask != nullptr;
+  if (masked && (batch_idx == nullptr || word_idx == nullptr || seq <= 0 || seq > kTileRows))
+    return cudaErrorInvalidValue;
+  const MaskArgs ma{attr_mask, batch_idx, word_idx, seq};
   const float scale_log2e = (1.0f / sqrtf(static_cast<float>(d))) * 1.4426950408889634f;
   // every tile holds at least one sequence, so batch * heads bounds the item count
   long long grid = static_cast<long long>(sm_count()) * kCtasPerSm;
   const long long max_items = static_cast<long long>(batch) * heads;
   if (grid > max_items) grid = max_items;
-  return launch_pdl(attention_tcgen05_kernel, dim3(static_cast<int>(grid)), dim3(kThreads), kSmemBytes, stream,
-                    tq, tk, tv, co, ctx, plan, batch, max_tokens, heads, scale_log2e, status_word,
-                    reverse ? 1 : 0);
+  return masked ? launch_pdl(attention_tcgen05_kernel<true>, dim3(static_cast<int>(grid)), dim3(kThreads), kSmemBytes,
+                             stream, tq, tk, tv, co, ctx, plan, batch, max_tokens, heads, scale_log2e, status_word,
+                             reverse ? 1 : 0, ma)
+                : launch_pdl(attention_tcgen05_kernel<false>, dim3(static_cast<int>(grid)), dim3(kThreads), kSmemBytes,
+                             stream, tq, tk, tv, co, ctx, plan, batch, max_tokens, heads, scale_log2e, status_word,
+                             reverse ? 1 : 0, ma);
 }
 
 }  // namespace etb

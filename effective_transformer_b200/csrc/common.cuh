@@ -333,6 +333,8 @@ cudaError_t launch_attention_tc(const __half* q, const __half* k, const __half* 
                                 int d, int* status_word, cudaStream_t stream, TensorMapCache* maps = nullptr);
 // tcgen05 attention for sequences of at most 128 tokens: a plan (sequences
 // packed into 128-row tiles) made once per batch, then one launch per layer.
+// attr_mask given ([B, seq, seq], 1 = attend; with batch_idx / word_idx of the packed rows): a
+// general mask with the reference op's semantics (padded keys take part with K = V = 0).
 size_t attention_plan_ints(int batch, int max_tokens);
 cudaError_t launch_attention_plan(const int* cu_seqlens, int batch, int max_tokens, int* plan,
                                   cudaStream_t stream);
@@ -340,7 +342,8 @@ cudaError_t launch_attention_tcgen05(const __half* q, const __half* k, const __h
                                      long long token_stride, long long head_stride, __half* ctx,
                                      const int* plan, int batch, int max_tokens, int heads, int d,
                                      int* status_word, cudaStream_t stream, bool reverse = false,
-                                     TensorMapCache* maps = nullptr);
+                                     TensorMapCache* maps = nullptr, const __half* attr_mask = nullptr,
+                                     const int* batch_idx = nullptr, const int* word_idx = nullptr, int seq = 0);
 // fp32 GEMM on the tensor cores by the three-product tf32 split (gemm_tf32x3.cu):
 // x = hi + lo with hi = rn_tf32(x); hi/lo may alias x.  rows_ptr null = max_rows.
 cudaError_t launch_split_tf32(const float* x, float* hi, float* lo, const int* rows_ptr, int max_rows, int cols,

@@ -184,6 +184,7 @@ struct et_handle_s {
   // general [B,S,S] mask of the pass being enqueued (null: key-only mask, fast kernels)
   const void* cur_attr_mask = nullptr;
   const int* cur_word_idx = nullptr;
+  const int* cur_batch_idx = nullptr;
   std::vector<LayerWeights> layers;
   ModelWeights model;
   Workspace ws;
@@ -294,12 +295,14 @@ struct DeviceGuard {
 // call that fails half-way cannot leave the handle in general-mask mode for the next one.
 struct MaskScope {
   et_handle_t h;
-  MaskScope(et_handle_t handle, const void* attr_mask, const int* word_idx) : h(handle) {
+  MaskScope(et_handle_t handle, const void* attr_mask, const int* batch_idx, const int* word_idx) : h(handle) {
     h->cur_attr_mask = attr_mask;
+    h->cur_batch_idx = batch_idx;
     h->cur_word_idx = word_idx;
   }
   ~MaskScope() {
     h->cur_attr_mask = nullptr;
+    h->cur_batch_idx = nullptr;
     h->cur_word_idx = nullptr;
   }
 };
@@ -426,7 +429,18 @@ int run_layer(et_handle_t h, const LayerWeights& lw, const T* x_in, T* x_out, co
   else
     ET_LAUNCH(h, ET_PROF_GEMM_QKV, tc32 ? 2 : 1, s, gemm(x_in, lw.wqkv, lw.wqkv_t, lw.wqkv_lo, lw.bqkv, qkv, 3 * hid, hid, kEpiBias));
   // attention straight from the [T, 3H] buffer to packed context [T, H]
-  if (h->cur_attr_mask != nullptr)
+  const bool masked = h->cur_attr_mask != nullptr;
+  if (masked && tc && seq <= 128)
+    // general mask on the tensor cores: the packed-tile kernel with the mask read per (query, key)
+    ET_LAUNCH(h, ET_PROF_ATTENTION, 1, s,
+              launch_attention_tcgen05(reinterpret_cast<const __half*>(qkv),
+                                       reinterpret_cast<const __half*>(qkv) + hid,
+                                       reinterpret_cast<const __half*>(qkv) + 2 * hid, 3LL * hid, d,
+                                       reinterpret_cast<__half*>(ctx), ws.attn_plan, batch, max_m, heads, d,
+                                       ws.status, s, turn(), &h->maps,
+                                       static_cast<const __half*>(h->cur_attr_mask), h->cur_batch_idx,
+                                       h->cur_word_idx, seq));
+  else if (masked)
     ET_LAUNCH(h, ET_PROF_ATTENTION, 1, s,
               launch_attention_masked_simt<T>(qkv, qkv + hid, qkv + 2 * hid, 3LL * hid, d, ctx,
                                               B(h->cur_attr_mask), cu_seqlens, h->cur_word_idx, ws.pos_row,
@@ -447,7 +461,7 @@ int run_layer(et_handle_t h, const LayerWeights& lw, const T* x_in, T* x_out, co
   else
     ET_LAUNCH(h, ET_PROF_ATTENTION, 1, s, launch_attention_simt<T>(qkv, qkv + hid, qkv + 2 * hid, 3LL * hid, d, ctx, cu_seqlens,
                                         batch, seq, heads, d, s, ctx_lo));
-  if (!(h->cur_attr_mask == nullptr && tc && seq <= 128)) forward_only();
+  if (!(tc && seq <= 128)) forward_only();
   // fp16 tensor-core path: bias + residual + LayerNorm run inside the projection kernels (rows are
   // normalised in place as soon as their last column tile has been stored), no LayerNorm launch
   const bool ln_in_gemm = tc && h->fuse_ln && gemm_layernorm_supported(hid);
@@ -600,12 +614,13 @@ int stack_impl(et_handle_t h, int batch, int seq, cudaStream_t s) {
   int rc = ET_OK;
   h->prev_ascending = true;  // remove-padding / the embedding kernel write rows first-to-last
   const int max_m = batch * seq;
-  if (h->cur_attr_mask != nullptr)
-    ET_LAUNCH(h, ET_PROF_PADDING_OFFSETS, 1, s,
-              launch_position_rows(ws.batch_idx, ws.word_idx, ws.valid_word_num, batch, seq, ws.pos_row, s));
-  else if (h->cfg.dtype == ET_FP16 && !h->use_simt && seq <= 128 && max_m > 0)
+  const bool tiles = h->cfg.dtype == ET_FP16 && !h->use_simt && seq <= 128 && max_m > 0;
+  if (tiles)  // the packed-tile attention serves key-only and general masks
     ET_LAUNCH(h, ET_PROF_PADDING_OFFSETS, 1, s,
               launch_attention_plan(ws.cu_seqlens, batch, max_m, ws.attn_plan, s));
+  else if (h->cur_attr_mask != nullptr)
+    ET_LAUNCH(h, ET_PROF_PADDING_OFFSETS, 1, s,
+              launch_position_rows(ws.batch_idx, ws.word_idx, ws.valid_word_num, batch, seq, ws.pos_row, s));
   for (int l = 0; l < h->cfg.num_layers; ++l) {
     if (h->cfg.dtype == ET_FP16)
       rc = run_layer<__half>(h, h->layers[l], static_cast<const __half*>(ws.x), static_cast<__half*>(ws.x),
@@ -1079,7 +1094,8 @@ int et_layer(et_handle_t h, int layer, const et_encoder_param_t* p, const et_tra
   if (h->general_mask && p->attr_mask == nullptr)
     return set_error(h, ET_INVALID_ARGUMENT, "general-mask mode: attr_mask [B,S,S] is required");
   // from here on every return leaves the handle in key-only-mask mode again
-  MaskScope mask_scope(h, h->general_mask ? p->attr_mask : nullptr, h->general_mask ? p->word_idx : nullptr);
+  MaskScope mask_scope(h, h->general_mask ? p->attr_mask : nullptr, h->general_mask ? p->batch_idx : nullptr,
+                       h->general_mask ? p->word_idx : nullptr);
   if (p->attr_kernel_Q != nullptr) {
     const void* w[16] = {p->attr_kernel_Q, p->attr_bias_Q, p->attr_kernel_K, p->attr_bias_K,
                          p->attr_kernel_V, p->attr_bias_V, p->attr_output_kernel, p->attr_output_bias,
@@ -1095,12 +1111,12 @@ int et_layer(et_handle_t h, int layer, const et_encoder_param_t* p, const et_tra
   const int batch = tp->batch_size, seq = tp->from_seq_len, max_m = batch * seq;
   ET_LAUNCH(h, ET_PROF_PADDING_OFFSETS, 1, s, launch_seq_bounds_from_batch_idx(p->batch_idx, p->valid_word_num, batch, max_m,
                                               h->ws.cu_seqlens, s));
-  if (h->cur_attr_mask != nullptr) {
-    ET_LAUNCH(h, ET_PROF_PADDING_OFFSETS, 1, s,
-              launch_position_rows(p->batch_idx, p->word_idx, p->valid_word_num, batch, seq, h->ws.pos_row, s));
-  } else if (h->cfg.dtype == ET_FP16 && !h->use_simt && seq <= 128 && max_m > 0) {
+  if (h->cfg.dtype == ET_FP16 && !h->use_simt && seq <= 128 && max_m > 0) {
     ET_LAUNCH(h, ET_PROF_PADDING_OFFSETS, 1, s,
               launch_attention_plan(h->ws.cu_seqlens, batch, max_m, h->ws.attn_plan, s));
+  } else if (h->cur_attr_mask != nullptr) {
+    ET_LAUNCH(h, ET_PROF_PADDING_OFFSETS, 1, s,
+              launch_position_rows(p->batch_idx, p->word_idx, p->valid_word_num, batch, seq, h->ws.pos_row, s));
   }
   if (h->cfg.dtype == ET_FP16)
     rc = run_layer<__half>(h, h->layers[layer], static_cast<const __half*>(p->from_tensor),
@@ -1135,7 +1151,7 @@ int et_forward_general_mask(et_handle_t h, const void* from_tensor, const int* m
   if (h == nullptr) return ET_INVALID_ARGUMENT;
   if (attr_mask == nullptr) return set_error(h, ET_INVALID_ARGUMENT, "attr_mask [B,S,S] is required");
   DeviceGuard guard(h->cfg.device);
-  MaskScope mask_scope(h, attr_mask, h->ws.word_idx);
+  MaskScope mask_scope(h, attr_mask, h->ws.batch_idx, h->ws.word_idx);
   return forward_impl(h, from_tensor, mask, out, batch_size, seq_len, static_cast<cudaStream_t>(stream));
   ET_CATCH(h)
 }
@@ -1806,6 +1822,20 @@ int et_attention_tiles(const void* q, const void* k, const void* v, long long to
   return to_status(launch_attention_tcgen05(H_(q), H_(k), H_(v), token_stride, head_stride,
                                             static_cast<__half*>(ctx), plan, batch_size, max_tokens, head_num,
                                             size_per_head, status_word, static_cast<cudaStream_t>(stream)));
+}
+
+int et_attention_tiles_general_mask(const void* q, const void* k, const void* v, long long token_stride,
+                                    long long head_stride, void* ctx, const int* plan, const void* attr_mask,
+                                    const int* batch_idx, const int* word_idx, int batch_size, int seq_len,
+                                    int max_tokens, int head_num, int size_per_head, int* status_word,
+                                    void* stream) {
+  if (!q || !k || !v || !ctx || !plan || !attr_mask || !batch_idx || !word_idx || batch_size < 0 || head_num <= 0 ||
+      size_per_head != 64 || seq_len <= 0 || seq_len > 128 || max_tokens < 0)
+    return ET_INVALID_ARGUMENT;
+  return to_status(launch_attention_tcgen05(H_(q), H_(k), H_(v), token_stride, head_stride,
+                                            static_cast<__half*>(ctx), plan, batch_size, max_tokens, head_num,
+                                            size_per_head, status_word, static_cast<cudaStream_t>(stream), false,
+                                            nullptr, H_(attr_mask), batch_idx, word_idx, seq_len));
 }
 
 int et_gemm(int dtype, const void* a, const void* w, const void* w_packed, const void* bias, void* c,

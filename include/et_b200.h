@@ -467,6 +467,18 @@ int et_attention_plan(const int* cu_seqlens, int batch_size, int max_tokens, int
 int et_attention_tiles(const void* q, const void* k, const void* v, long long token_stride,
                        long long head_stride, void* ctx, const int* plan, int batch_size, int max_seq_len,
                        int max_tokens, int head_num, int size_per_head, int* status_word, void* stream);
+/* The same kernel under a general attention mask attr_mask [B, seq_len, seq_len]
+ * (fp16, 1 = attend), semantics of the reference op's masked softmax
+ * (cuda/attention.cu:106-382: disallowed keys get -10000; a padded key position
+ * takes part with K = V = 0, i.e. it weighs in the denominator when the mask
+ * allows it).  batch_idx / word_idx: sequence and position of every packed row
+ * (outputs of et_padding_offsets).  seq_len <= 128.  A query that may attend to
+ * nothing gets the softmax over all seq_len keys (the TF graph's result). */
+int et_attention_tiles_general_mask(const void* q, const void* k, const void* v, long long token_stride,
+                                    long long head_stride, void* ctx, const int* plan, const void* attr_mask,
+                                    const int* batch_idx, const int* word_idx, int batch_size, int seq_len,
+                                    int max_tokens, int head_num, int size_per_head, int* status_word,
+                                    void* stream);
 
 /* cublasGemmEx call sites of the layer functor
  * (tf_op/bert_transformer_op.cu.cc:110-141,200-209,215-225,229-240):

@@ -163,3 +163,48 @@ def test_whole_path_under_a_general_mask(dtype):
     eng.set_general_mask(False)
     assert torch.equal(et.get_sequence_output(cfg, b, s, None, m, x, wl.weights, engine=eng), eng.forward(x, m))
     eng.close()
+
+
+@pytest.mark.parametrize("prefix", [True, False], ids=["prefix_mask", "mask_with_holes"])
+@pytest.mark.parametrize("seq", [64, 128, 40])
+def test_general_mask_attention_on_tensor_cores(prefix, seq):
+    """et_attention_tiles_general_mask (the packed-tile tcgen05 kernel reading the mask per query and
+    key) against the oracle's restatement of the reference op's masked attention, for every kind of
+    mask, and against the CUDA-core general-mask kernel."""
+    batch, heads, d = 9, 3, 64
+    h = heads * d
+    rng = np.random.RandomState(5 + seq + int(prefix))
+    if prefix:
+        lens = rng.randint(1, seq + 1, size=batch).astype(np.int32)
+        lens[2] = 0
+        lens[5] = seq
+        mask_np = W.prefix_mask(lens, seq)
+    else:
+        mask_np = (rng.rand(batch, seq) < 0.7).astype(np.int32)
+    idx = padding_offsets(dev(mask_np))
+    t = int(idx["valid_word_num"][0])
+    cu, widx = idx["cu_seqlens"].cpu().numpy(), idx["word_idx"].cpu().numpy()
+    dtype = torch.float16
+    qkv = dev(rng.randn(t + 5, 3 * h).astype(np.float32), dtype)
+    q, k, v = qkv[:, :h], qkv[:, h:2 * h], qkv[:, 2 * h:]
+    cap = t + 5
+    plan = torch.zeros(int(lib().et_attention_plan_ints(batch, cap)), dtype=torch.int32, device="cuda")
+    ok(lib().et_attention_plan(iptr(idx["cu_seqlens"]), batch, cap, iptr(plan), stream()))
+    e = qkv.element_size()
+    for name, m_np in general_masks(mask_np, rng).items():
+        attr = dev(m_np, dtype)
+        ctx = torch.full((cap, h), 2.0, dtype=dtype, device="cuda")
+        st = torch.zeros(1, dtype=torch.int32, device="cuda")
+        ok(lib().et_attention_tiles_general_mask(qkv.data_ptr(), qkv.data_ptr() + h * e, qkv.data_ptr() + 2 * h * e,
+                                                 3 * h, 64, iptr(ctx), iptr(plan), iptr(attr), iptr(idx["batch_idx"]),
+                                                 iptr(idx["word_idx"]), batch, seq, cap, heads, 64, iptr(st), stream()))
+        torch.cuda.synchronize()
+        assert int(st[0]) == 0
+        want = O.packed_attention_general_mask(q[:t].double().cpu(), k[:t].double().cpu(), v[:t].double().cpu(), cu,
+                                               widx, torch.from_numpy(m_np).double(), seq, heads, d)
+        torch.testing.assert_close(ctx[:t].double().cpu(), want, rtol=4e-3, atol=4e-3,
+                                   msg=lambda s: f"{name}: tensor-core kernel vs oracle\n{s}")
+        assert torch.all(ctx[t:] == 2.0)
+        simt = run_ours(dtype, q[:t].contiguous(), k[:t].contiguous(), v[:t].contiguous(), attr, idx, batch, seq, heads)
+        torch.testing.assert_close(ctx[:t].float(), simt.float(), rtol=4e-3, atol=4e-3,
+                                   msg=lambda s: f"{name}: tensor-core vs CUDA-core kernel\n{s}")
