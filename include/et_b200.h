@@ -433,8 +433,9 @@ int et_attention(int dtype, const void* q, const void* k, const void* v, long lo
  * (cuda/attention.cu:106-242, 249-382): a query sees all S key positions,
  * score*1/sqrt(d) + (1 - m)*(-10000); padded key positions take part with
  * K = V = 0, exactly as the reference's zero-filled padded buffers make them.
- * CUDA-core kernel, fp32 arithmetic: a correctness fallback, not a fast path.
- * pos_row_scratch: batch_size*seq_len ints of device memory. */
+ * CUDA-core kernel, fp32 arithmetic, any dtype and sequence length; fp16 with
+ * seq_len <= 128 has a tensor-core form, et_attention_tiles_general_mask, which
+ * the handle uses by itself.  pos_row_scratch: batch_size*seq_len ints. */
 int et_attention_general_mask(int dtype, const void* q, const void* k, const void* v, long long token_stride,
                               long long head_stride, void* ctx, const void* attr_mask, const int* cu_seqlens,
                               const int* batch_idx, const int* word_idx, const int* valid_word_num,
