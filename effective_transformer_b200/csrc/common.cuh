@@ -316,6 +316,11 @@ cudaError_t launch_attention_simt(const T* q, const T* k, const T* v, long long 
                                   int max_seq, int heads, int d, cudaStream_t stream, T* ctx_lo = nullptr,
                                   const int* cu_seqlens_k = nullptr, long long kv_token_stride = 0,
                                   int max_seq_k = 0);
+// Self-attention of the fp32 handle on tensor cores at fp32 accuracy (mma.sync tf32, three products
+// per fp32 product); same layout and arguments as launch_attention_simt<float>.
+cudaError_t launch_attention_tf32x3(const float* q, const float* k, const float* v, long long token_stride,
+                                    long long head_stride, float* ctx, const int* cu_seqlens, int batch,
+                                    int max_seq, int heads, int d, cudaStream_t stream, float* ctx_lo = nullptr);
 // The same under a general [B, S, S] mask with the reference op's semantics
 // (padded keys take part with K = V = 0).  pos_row[b*S+p] = packed row of
 // position p or -1, made by launch_position_rows (a memset and one kernel).

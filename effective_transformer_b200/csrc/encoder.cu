@@ -458,6 +458,13 @@ int run_layer(et_handle_t h, const LayerWeights& lw, const T* x_in, T* x_out, co
                                    reinterpret_cast<const __half*>(qkv) + 2 * hid, 3LL * hid, d,
                                    reinterpret_cast<__half*>(ctx), cu_seqlens, batch, seq, max_m, heads, d,
                                    ws.status, s, &h->maps));
+  else if (tc32)
+    // fp32 handle: tensor cores at fp32 accuracy (three tf32 products per product), as its projections
+    ET_LAUNCH(h, ET_PROF_ATTENTION, 1, s,
+              launch_attention_tf32x3(reinterpret_cast<const float*>(qkv), reinterpret_cast<const float*>(qkv) + hid,
+                                      reinterpret_cast<const float*>(qkv) + 2 * hid, 3LL * hid, d,
+                                      reinterpret_cast<float*>(ctx), cu_seqlens, batch, seq, heads, d, s,
+                                      reinterpret_cast<float*>(ctx_lo)));
   else
     ET_LAUNCH(h, ET_PROF_ATTENTION, 1, s, launch_attention_simt<T>(qkv, qkv + hid, qkv + 2 * hid, 3LL * hid, d, ctx, cu_seqlens,
                                         batch, seq, heads, d, s, ctx_lo));
@@ -1756,6 +1763,9 @@ int et_attention(int dtype, const void* q, const void* k, const void* v, long lo
     return to_status(launch_attention_tc(H_(q), H_(k), H_(v), token_stride, head_stride,
                                          static_cast<__half*>(ctx), cu_seqlens, batch, max_seq, max_tokens,
                                          heads, d, status_word, s));
+  if (dtype == ET_FP32 && !use_simt)
+    return to_status(launch_attention_tf32x3(F_(q), F_(k), F_(v), token_stride, head_stride, static_cast<float*>(ctx),
+                                             cu_seqlens, batch, max_seq, heads, d, s));
   return ET_DISPATCH(dtype,
                      launch_attention_simt<__half>(H_(q), H_(k), H_(v), token_stride, head_stride,
                                                    static_cast<__half*>(ctx), cu_seqlens, batch, max_seq, heads, d, s),

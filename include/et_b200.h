@@ -300,8 +300,8 @@ int et_get_profile(et_handle_t handle, double* ms_out, long long* launches_out, 
 int et_copy_to_host(void* dst_host, const void* src_device, size_t bytes, void* stream);
 
 /* 0 (default): tensor-core kernels - tcgen05 GEMMs and attention for an fp16
- * handle, the tf32-split tcgen05 GEMM for an fp32 handle (its attention is
- * always the CUDA-core kernel).  1: CUDA-core GEMMs and attention for both
+ * handle, the tf32-split tcgen05 GEMM and the tf32-split mma.sync attention
+ * for an fp32 handle.  1: CUDA-core GEMMs and attention for both
  * (plain fp32 FMA arithmetic; for debugging and as a second opinion). */
 int et_set_debug_simt(et_handle_t handle, int use_simt);
 
@@ -421,7 +421,9 @@ int et_add_bias_input_layernorm(int dtype, void* out, const void* input, const v
  * by side inside a token row ([T, 3H] as the fused projection writes it) or
  * one [max_tokens, d] block per head; ctx is packed [T, heads*d].  q/k/v/ctx
  * hold max_tokens rows (rows past T are never needed, reads past max_tokens
- * never happen).  use_simt selects the CUDA-core kernel (always for fp32). */
+ * never happen).  use_simt = 0: tensor cores (fp16: TMA-fed mma.sync, any
+ * length; fp32: mma.sync with tf32 operands, three products per fp32 product,
+ * fp32 accuracy); use_simt = 1: the CUDA-core kernel (plain fp32 FMA). */
 int et_attention(int dtype, const void* q, const void* k, const void* v, long long token_stride,
                  long long head_stride, void* ctx, const int* cu_seqlens, int batch_size,
                  int max_seq_len, int max_tokens, int head_num, int size_per_head, int use_simt,

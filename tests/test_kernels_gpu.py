@@ -276,6 +276,14 @@ def test_attention_tensor_core(lens, layout):
     _attention_case(torch.float16, lens, 2, use_simt=False, layout=layout)
 
 
+@pytest.mark.parametrize("lens", LEN_CASES)
+@pytest.mark.parametrize("layout", ["qkv", "headmajor", "unaligned"])
+def test_attention_fp32_on_tensor_cores_keeps_fp32_accuracy(lens, layout):
+    """The fp32 handle's attention: mma.sync with tf32 operands, three products per fp32 product,
+    held to the tolerance of the CUDA-core fp32 kernel (1e-5 against the float64 oracle)."""
+    _attention_case(torch.float32, lens, 3, use_simt=False, layout=layout)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
 @pytest.mark.parametrize("lens", LEN_CASES)
 def test_attention_simt(dtype, lens):
