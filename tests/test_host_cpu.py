@@ -1,12 +1,13 @@
 """CPU tests of the host-side logic: the C-ABI library loads and exports every
 symbol the header declares, the synthetic workloads, the token-balanced shard
-planner, and the multi-rank bookkeeping over gloo (world size 2)."""
+planner, and the multi-rank bookkeeping over gloo (world sizes 2 and 8)."""
 import os
 import re
 import subprocess
 import sys
 
 import numpy as np
+import pytest
 
 from effective_transformer_b200 import _capi
 from effective_transformer_b200 import workloads as W
@@ -79,7 +80,7 @@ sys.path.insert(0, sys.argv[1])
 from effective_transformer_b200 import workloads as W
 dist.init_process_group("gloo")
 rank, world = dist.get_rank(), dist.get_world_size()
-spec = W.WORKLOADS[1]
+spec = W.WORKLOADS[int(sys.argv[2])]
 lens = W.draw_lengths(spec, np.random.RandomState(spec.seed))
 shards, loads = W.balanced_shards(lens, world)
 mine = lens[shards[rank]]
@@ -117,15 +118,18 @@ sys.stdout.flush()
 '''
 
 
-def test_two_rank_sharding_over_gloo(tmp_path):
+@pytest.mark.parametrize("world,cfg,port", [(2, 1, 29533), (8, 2, 29534)])
+def test_sharding_over_gloo(tmp_path, world, cfg, port):
+    """Two ranks on the small configuration, eight on the B=1000 benchmark batch."""
     script = tmp_path / "rank.py"
     script.write_text(RANK_SCRIPT)
-    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29533")
-    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
-                        "--master-addr", "127.0.0.1", "--master-port", "29533", str(script), ROOT],
-                       capture_output=True, text=True, env=env, timeout=300)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=%d" % world,
+                        "--master-addr", "127.0.0.1", "--master-port", str(port), str(script), ROOT, str(cfg)],
+                       capture_output=True, text=True, env=env, timeout=600)
     assert r.returncode == 0, r.stdout + r.stderr
-    assert r.stdout.count("rank0-ok") == 1 and r.stdout.count("rank1-ok") == 1, r.stdout
+    for k in range(world):
+        assert r.stdout.count("rank%d-ok" % k) == 1, r.stdout
 
 
 def test_reference_arm_prints_contract_line():
