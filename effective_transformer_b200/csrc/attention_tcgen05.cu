@@ -398,25 +398,29 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
       uhi = (uhi + 15) & ~15;
       // (32 columns per TMEM load; a load may run up to 16 columns past n16, into
       // allocated columns whose values the range test discards)
-      // column c belongs to this row's sequence iff lo <= c < hi, i.e. (unsigned)(c - lo) < hi - lo
-      const unsigned span = static_cast<unsigned>(hi - lo);
+      // Which of the 32 columns from c0 on this row attends to, one bit per column: the columns of its own
+      // sequence (lo <= c < hi), or the bits the general mask left of them.  One bit test per element is
+      // cheaper than a range test, and the kernel is bound by its instruction count as much as by HBM.
+      auto chunk_bits = [&](int c0) -> uint32_t {
+        if constexpr (kMask) {
+          const int w = c0 >> 5;
+          return w == 0 ? allow[0] : w == 1 ? allow[1] : w == 2 ? allow[2] : allow[3];
+        } else {
+          const int a = max(lo - c0, 0), b = min(hi - c0, 32);
+          if (b <= a) return 0u;
+          const uint32_t below_b = b >= 32 ? 0xffffffffu : (1u << b) - 1u;
+          return below_b & ~((1u << a) - 1u);  // a < b <= 32, so a <= 31
+        }
+      };
       float m = -INFINITY;
       for (int c0 = ulo; c0 < uhi; c0 += 32) {
         uint32_t s32[32];
         tmem_ld_32x32b_x32(t_lane + c0, s32);
         tmem_ld_wait();
-        const int rel = c0 - lo;
-        if constexpr (kMask) {
-          const int w = c0 >> 5;
-          const uint32_t aw = w == 0 ? allow[0] : w == 1 ? allow[1] : w == 2 ? allow[2] : allow[3];
+        const uint32_t aw = chunk_bits(c0);
 #pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if ((aw >> e) & 1u) m = fmaxf(m, __uint_as_float(s32[e]));
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if (static_cast<unsigned>(rel + e) < span) m = fmaxf(m, __uint_as_float(s32[e]));
-        }
+        for (int e = 0; e < 32; ++e)
+          if ((aw >> e) & 1u) m = fmaxf(m, __uint_as_float(s32[e]));
       }
       if constexpr (kMask) {
         if (n_pad > 0.f) m = fmaxf(m, 0.f);  // a padded key the row may attend to has score 0
@@ -431,21 +435,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
           uint32_t s32[32];
           tmem_ld_32x32b_x32(t_lane + c0, s32);
           tmem_ld_wait();
-          const int rel = c0 - lo;
-          uint32_t aw = 0u;
-          if constexpr (kMask) {
-            const int w = c0 >> 5;
-            aw = w == 0 ? allow[0] : w == 1 ? allow[1] : w == 2 ? allow[2] : allow[3];
-          }
+          const uint32_t aw = chunk_bits(c0);
 #pragma unroll
           for (int e = 0; e < 16; ++e) {
             float p2[2];
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
               const float pe = ex2_approx(fmaf(__uint_as_float(s32[2 * e + u]), scale_log2e, ms));
-              const bool keep = kMask ? ((aw >> (2 * e + u)) & 1u) != 0u
-                                      : static_cast<unsigned>(rel + 2 * e + u) < span;
-              p2[u] = keep ? pe : 0.f;
+              p2[u] = ((aw >> (2 * e + u)) & 1u) != 0u ? pe : 0.f;
               l += p2[u];
             }
             pk[e] = pack_half2(p2[0], p2[1]);
