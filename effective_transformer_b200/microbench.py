@@ -85,7 +85,7 @@ def main() -> None:
     bias_f = rnd(f)
     qkv = rnd(n_pos, 3 * h)
     q, k, v = rnd(n_pos, h), rnd(n_pos, h), rnd(n_pos, h)
-    qkv_t = torch.empty(3 * heads * n_pos * 64, device=dev, dtype=tdt)
+    qkv_t = rnd(3 * heads * n_pos * 64)
     ctx = torch.empty(n_pos, h, device=dev, dtype=tdt)
     ffn = rnd(n_pos, f)
     bias3 = rnd(3 * h)
@@ -141,6 +141,11 @@ def main() -> None:
                                                            qkv.data_ptr() + 2 * h * e, 3 * h, 64, P(ctx), P(plan), b, s,
                                                            n_pos, heads, 64, P(status), st),
                             "hbm", 4.0 * t * h * e),
+        # the same kernel reading the head-major [3, heads, positions, 64] layout of et_add_qkv_bias_transpose:
+        # every TMA box is one contiguous 4 KB piece instead of 32 pieces of 128 bytes a row apart
+        "attention_tiles_head_major": (lambda: lib.et_attention_tiles(
+            qkv_t.data_ptr(), qkv_t.data_ptr() + heads * n_pos * 64 * e, qkv_t.data_ptr() + 2 * heads * n_pos * 64 * e,
+            64, n_pos * 64, P(ctx), P(plan), b, s, n_pos, heads, 64, P(status), st), "hbm", 4.0 * t * h * e),
         "attention_plan": (lambda: lib.et_attention_plan(P(cu), b, n_pos, P(plan), st), "hbm", 4.0 * b + 8.0 * t),
         # per valid token: 12 B of ids/indices + one word row read + one packed row written
         "embedding_layernorm": (lambda: lib.et_embedding_layernorm(
@@ -184,7 +189,7 @@ def main() -> None:
     for name, a in (("gemm_qkv", x_packed), ("gemm_attn_out", x_packed), ("gemm_ffn1", x_packed), ("gemm_ffn2", ffn)):
         kernels["library_" + name] = (library_gemm(name, a), "tensor", kernels[name][2])
     if not (fp16 and s <= 128):
-        kernels.pop("attention_tiles"), kernels.pop("attention_plan")
+        kernels.pop("attention_tiles"), kernels.pop("attention_plan"), kernels.pop("attention_tiles_head_major")
     names = list(kernels) if args.kernel == "all" else args.kernel.split(",")
     pk, src = peaks()
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
