@@ -95,7 +95,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.FIELDS,
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "25"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except Exception:
@@ -103,18 +103,23 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.monotonic(), [c.strip() for c in line.split(",")]))
 
-    def stop(self):
+    def stop(self, t_begin=None, t_end=None):
+        """Summary of the samples that arrived between t_begin and t_end (time.monotonic(); the
+        sampler is started ahead of the timed region because nvidia-smi takes a while to come up)."""
         if self.proc is not None:
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=5)
             except Exception:
                 pass
+        rows = [r for t, r in self.rows if (t_begin is None or t >= t_begin) and (t_end is None or t <= t_end)]
+        if not rows:
+            rows = [r for _, r in self.rows]
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        for r in rows:
             try:
                 sm.append(float(r[0])); mx.append(float(r[1]))
             except Exception:
@@ -259,6 +264,8 @@ class DevicePass:
     def time(self, steps, warmup, launch, flush, barrier, sampler=None):
         """Returns (sum of step ms, per-kernel profile of an eager pass over the same steps, clocks)."""
         torch, eng = self.torch, self.eng
+        if sampler is not None:
+            sampler.start()
         for _ in range(warmup):
             eng.forward(self.x, self.mask, self.out)
         torch.cuda.synchronize()
@@ -271,11 +278,10 @@ class DevicePass:
             torch.cuda.synchronize()
         eng.get_profile(reset=True)
         eng.set_profiling(not graph)
-        if sampler is not None:
-            sampler.start()
         starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
         ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
         barrier()
+        t_begin = time.monotonic()
         for i in range(steps):
             flush.zero_()                         # evict the previous step's tensors from L2 (untimed)
             starts[i].record()
@@ -285,7 +291,7 @@ class DevicePass:
                 eng.forward(self.x, self.mask, self.out)
             ends[i].record()
         barrier()
-        clocks = sampler.stop() if sampler is not None else None
+        clocks = sampler.stop(t_begin, time.monotonic()) if sampler is not None else None
         eng.set_profiling(False)
         total_ms = sum(a.elapsed_time(e) for a, e in zip(starts, ends))
         prof = eng.get_profile(reset=True)
