@@ -68,15 +68,22 @@ def read_peaks():
     return dict(FALLBACK_PEAKS), "fallback"
 
 
-def read_traffic(workload: str):
+def read_traffic(workload: str, tokens: int):
     """DRAM bytes per launch of the dominant kernel from the committed ncu capture, if one is on
-    record for this workload (profiles/traffic.json; written when the capture is refreshed)."""
+    record for this workload (profiles/traffic.json; written when the capture is refreshed).  A pass
+    over a shard of the workload gets the capture's bytes scaled by the rows it processes: operand
+    and output rows grow with the tokens, only the weights (3-5 MB of the 190-255 MB) do not."""
     p = os.path.join(ROOT, "profiles", "traffic.json")
     try:
         with open(p) as f:
             rec = json.load(f).get(workload)
         if rec:
-            return float(rec["bytes_per_launch"]), rec.get("note")
+            full, note = float(rec["bytes_per_launch"]), rec.get("note")
+            captured = int(rec.get("valid_tokens", tokens))
+            if captured != tokens:
+                return full * tokens / captured, (note or "") + "; scaled by %d / %d tokens for this shard" % (
+                    tokens, captured)
+            return full, note
     except Exception:
         pass
     return None, None
@@ -604,7 +611,7 @@ def roofline_of(p: DevicePass, prof, steps, peaks, peak_src, dev, workload_name)
     out = {"bound": "tensor", "achieved": achieved, "unit": "TFLOP/s"}
     if p.fp16:
         peak_tf, note = peaks["bf16_tflops_sustained"], peak_src + " bf16_tflops_sustained"
-        traffic, tnote = read_traffic(workload_name)
+        traffic, tnote = read_traffic(workload_name, p.tokens)
         out.update({"traffic": traffic, "traffic_note": tnote,
                     "kernel": "gemm_tcgen05_pair_kernel (bias / GELU / residual / LayerNorm epilogues)"})
     else:
