@@ -108,6 +108,27 @@ def test_cfg1_fp16_twelve_layers(simt):
     eng.close()
 
 
+@pytest.mark.parametrize("ranks", [2, 8])
+def test_sharded_batch_reassembled_equals_the_oracle(ranks):
+    """The multi-GPU split, emulated on one GPU: the batch is dealt to `ranks` shards by the planner
+    the multi-rank benchmark uses, every shard runs through an engine of its own, and the outputs,
+    put back in batch order by the gather's inverse permutation, meet the oracle of the whole batch."""
+    from effective_transformer_b200.sharding import inverse_order
+    spec = W.WORKLOADS[1]
+    wl = W.make_workload(spec)
+    shards, loads = W.balanced_shards(wl.lengths, ranks)
+    assert int(loads.sum()) == wl.valid_tokens
+    blocks = []
+    for idx in shards:
+        part = W.Workload(spec, wl.lengths[idx], wl.mask[idx], wl.from_tensor[idx], wl.weights)
+        eng = make_engine(spec, part)
+        blocks.append(run_forward(eng, part).cpu())
+        eng.close()
+    whole = torch.cat(blocks, dim=0)[torch.from_numpy(inverse_order(shards))]
+    assert whole.shape[0] == spec.batch
+    assert_parity(whole, oracle_valid(wl, spec), wl.mask, fp16=True)
+
+
 def test_operator_api_matches_forward_and_reference_wiring():
     """get_sequence_output wires the three operators exactly like
     python/effective_transformer/__init__.py:42-82 and equals et_forward."""
