@@ -89,6 +89,8 @@ SIGNATURES = {
     "et_selftest_wait_timeout": (i32, [vp, vp]),
     "et_workspace_allocated_bytes": (i32, [vp, C.POINTER(C.c_size_t)]),
     "et_gemm_fused": (i32, [vp, vp, vp, vp, vp, vp, C.c_float, vp, vp, vp, i32, i32, i32, i32, vp, vp]),
+    "et_fold_layernorm": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32, vp]),
+    "et_gemm_deferred_norm": (i32, [vp, vp, vp, vp, vp, vp, vp, C.c_float, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp]),
     "et_padding_offsets": (i32, [vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp]),
     "et_padding_offsets_noalloc": (i32, [vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp]),
     "et_remove_padding": (i32, [i32, vp, vp, vp, vp, vp, i32, i32, i32, vp]),

@@ -287,21 +287,47 @@ cudaError_t launch_copy_columns(const T* src, T* dst, int rows, int cols, int ds
 // launched and the pre-LayerNorm tensor is never read back from HBM.  kEpiResidualLayerNorm adds
 // bias and residual in the GEMM epilogue (as kEpiBiasResidual); kEpiLayerNorm leaves the epilogue
 // bare and adds them when the rows are normalised.
+//
+// kEpiNormIn / kEpiNormInGelu / kEpiNormResidual: the LayerNorm is never materialised.  A projection
+// whose input is LN(x) = (x - mu) * rstd * gamma + beta runs on the un-normalised x with gamma folded
+// into its weights (W' = diag(gamma) W): LN(x) W + b = rstd * (x W' - mu * colsum(W')) + (beta W + b),
+// and the row's mu, rstd come from partial sums the producer of x left beside it.
+//   kEpiNormIn(Gelu)   C = act(rstd[r] * (acc - mu[r] * csum[n]) + bias[n])
+//   kEpiNormResidual   C = acc + bias[n] + ((res[r,n] - mu[r]) * rstd[r] * gamma[n] + beta[n]), i.e. the residual
+//                      is the LayerNorm of `residual`, taken on the fly; and the kernel leaves the sum and
+//                      the sum of squares of every 64-column piece of every row of C (as stored, after
+//                      rounding) in `stats_out`, for the consumers of LN(C).
 enum Epilogue : int {
   kEpiNone = 0, kEpiBias = 1, kEpiBiasGelu = 2, kEpiBiasTanh = 3, kEpiBiasResidual = 4,
-  kEpiResidualLayerNorm = 5, kEpiLayerNorm = 6
+  kEpiResidualLayerNorm = 5, kEpiLayerNorm = 6, kEpiNormIn = 7, kEpiNormInGelu = 8, kEpiNormResidual = 9
 };
 
 // LayerNorm parameters of the two fused epilogues.  `counters`: one int per 32 rows of the 256-row
 // tiles that cover C (8 * ceil(max_m / 256) of them), zero before the launch; the kernel leaves
 // them zero again.
+// Deferred variants (kEpiNorm*): `stats_in` [rows, 2 * stat_slots] holds (sum, sum of squares) per
+// 64-column piece of the rows of the normalised tensor (stat_slots = its width / 64; rows rounded up
+// to the 256-row tile), null = the tensor is used as it is (mu = 0, rstd = 1); `csum` [N] = column
+// sums of the folded weights; `stats_out` [rows, 2 * N / 64]; gamma / beta null = ones / zeros.
 struct GemmLayerNorm {
   const __half* gamma = nullptr;
   const __half* beta = nullptr;
   float eps = 1e-6f;
   int* counters = nullptr;
+  const float* stats_in = nullptr;
+  int stat_slots = 0;
+  const __half* csum = nullptr;
+  float* stats_out = nullptr;
 };
+__host__ __device__ constexpr bool is_deferred_norm(int epi) {
+  return epi == kEpiNormIn || epi == kEpiNormInGelu || epi == kEpiNormResidual;
+}
 
+// LayerNorm parameters folded into the projection that consumes it (kEpiNormIn): w_packed [N,K]
+// K-major -> w_folded = w * gamma[k], csum[n] = sum_k w_folded, bias_folded = bias + beta W.
+cudaError_t launch_fold_layernorm(const __half* w_packed, const __half* bias, const __half* gamma,
+                                  const __half* beta, __half* w_folded, __half* csum, __half* bias_folded, int n,
+                                  int k, cudaStream_t stream);
 // CUDA-core GEMM: C[M,N] = epi(A[M,K] * W[K,N]); W row-major [K,N].
 template <typename T>
 cudaError_t launch_gemm_simt(const T* a, const T* w, const T* bias, T* c, const int* m_ptr,

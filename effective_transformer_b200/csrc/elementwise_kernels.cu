@@ -241,6 +241,38 @@ inline int grid_for(long long work_items) {
   return ctas < 1 ? 1 : static_cast<int>(ctas);
 }
 
+
+// LayerNorm folded into the projection behind it: for LN(x) = (x - mu) * rstd * gamma + beta and
+// y = LN(x) W + b,   y = rstd * (x W' - mu * csum) + b'   with W' = diag(gamma) W, csum = column sums
+// of W' as stored (fp16), b' = b + beta W.  W is the packed [N, K] K-major copy; one CTA per row n.
+__global__ void __launch_bounds__(256)
+fold_layernorm_kernel(const __half* __restrict__ w, const __half* __restrict__ bias,
+                      const __half* __restrict__ gamma, const __half* __restrict__ beta, __half* __restrict__ wf,
+                      __half* __restrict__ csum, __half* __restrict__ bias_f, int k) {
+  const int n = blockIdx.x;
+  const __half* wrow = w + static_cast<size_t>(n) * k;
+  __half* frow = wf + static_cast<size_t>(n) * k;
+  float s = 0.f, bw = 0.f;
+  for (int j = threadIdx.x; j < k; j += blockDim.x) {
+    const float wv = __half2float(wrow[j]);
+    const __half f = __float2half_rn(wv * __half2float(gamma[j]));
+    frow[j] = f;
+    s += __half2float(f);
+    bw += __half2float(beta[j]) * wv;
+  }
+  __shared__ float red[2][8];
+  s = warp_sum(s);
+  bw = warp_sum(bw);
+  if ((threadIdx.x & 31) == 0) red[0][threadIdx.x >> 5] = s, red[1][threadIdx.x >> 5] = bw;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float ts = 0.f, tb = 0.f;
+    for (int i = 0; i < 8; ++i) ts += red[0][i], tb += red[1][i];
+    csum[n] = __float2half_rn(ts);
+    bias_f[n] = __float2half_rn(__half2float(bias[n]) + tb);
+  }
+}
+
 }  // namespace
 
 template <typename T>
@@ -350,5 +382,13 @@ cudaError_t launch_copy_columns(const T* src, T* dst, int rows, int cols, int ds
 ETB_INST(float)
 ETB_INST(__half)
 #undef ETB_INST
+
+cudaError_t launch_fold_layernorm(const __half* w_packed, const __half* bias, const __half* gamma,
+                                  const __half* beta, __half* w_folded, __half* csum, __half* bias_folded, int n,
+                                  int k, cudaStream_t stream) {
+  if (n <= 0 || k <= 0) return cudaErrorInvalidValue;
+  fold_layernorm_kernel<<<n, 256, 0, stream>>>(w_packed, bias, gamma, beta, w_folded, csum, bias_folded, k);
+  return cudaGetLastError();
+}
 
 }  // namespace etb

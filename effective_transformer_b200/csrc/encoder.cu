@@ -1888,6 +1888,34 @@ int et_gemm_fused(const void* a, const void* w_packed, const void* bias, const v
                                        H_(residual), nullptr, &ln));
 }
 
+int et_fold_layernorm(const void* w_packed, const void* bias, const void* gamma, const void* beta, void* w_folded,
+                      void* csum, void* bias_folded, int n, int k, void* stream) {
+  if (!w_packed || !bias || !gamma || !beta || !w_folded || !csum || !bias_folded || n <= 0 || k <= 0)
+    return ET_INVALID_ARGUMENT;
+  return to_status(launch_fold_layernorm(H_(w_packed), H_(bias), H_(gamma), H_(beta), static_cast<__half*>(w_folded),
+                                         static_cast<__half*>(csum), static_cast<__half*>(bias_folded), n, k,
+                                         static_cast<cudaStream_t>(stream)));
+}
+
+int et_gemm_deferred_norm(const void* a, const void* w_packed, const void* bias, const void* csum,
+                          const void* residual, const void* gamma, const void* beta, float eps,
+                          const float* stats_in, float* stats_out, void* c, const int* m_ptr, int max_m, int n,
+                          int k, int epilogue, int* status_word, void* stream) {
+  if (!a || !w_packed || !bias || !c || !m_ptr || max_m < 0 || n <= 0 || k <= 0) return ET_INVALID_ARGUMENT;
+  if (!is_deferred_norm(epilogue)) return ET_INVALID_ARGUMENT;
+  GemmLayerNorm ln;
+  ln.eps = eps > 0.f ? eps : 1e-6f;
+  ln.stats_in = stats_in;
+  ln.stat_slots = (epilogue == kEpiNormResidual ? n : k) / 64;
+  ln.csum = H_(csum);
+  ln.gamma = H_(gamma);
+  ln.beta = H_(beta);
+  ln.stats_out = stats_out;
+  return to_status(launch_gemm_tcgen05(H_(a), H_(w_packed), H_(bias), static_cast<__half*>(c), m_ptr, max_m, n, k,
+                                       epilogue, status_word, static_cast<cudaStream_t>(stream), false,
+                                       H_(residual), nullptr, &ln));
+}
+
 int et_selftest_wait_timeout(et_handle_t h, void* stream) {
   ET_TRY
   if (h == nullptr) return ET_INVALID_ARGUMENT;

@@ -195,6 +195,50 @@ __device__ __forceinline__ Vec16 ld_shared_v4(uint32_t addr) {
   return v;
 }
 
+// What the deferred-LayerNorm epilogues need beside the accumulator.
+struct NormCtx {
+  // kEpiNormIn(Gelu), one row per thread: C = rstd * acc + nm * csum[n] + bias[n], nm = -rstd * mu
+  float rstd = 1.f, nm = 0.f;
+  const __half* csum = nullptr;   // at the warp's first column
+  // kEpiNormResidual, rows 4 i + (lane >> 3) of the coalesced phase
+  float mu_i[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  float rstd_i[8] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f};
+  const __half* gamma = nullptr;  // at the warp's first column; null: ones / zeros
+  const __half* beta = nullptr;
+  float* stats = nullptr;         // stats_out at (first row of the warp, first 64-column piece of the warp)
+  int s2 = 0;                     // floats per row of stats_out
+};
+
+// Row statistics from the partial sums a producer left: (sum, sum of squares) per 64-column piece.
+__device__ __forceinline__ void row_stats(const float* __restrict__ stats, int slots, int width, float eps,
+                                          float& mu, float& rstd) {
+  float s1 = 0.f, s2 = 0.f;
+  for (int j = 0; j < slots; j += 2) {  // slots is even: widths are multiples of 128
+    const float4 v = *reinterpret_cast<const float4*>(stats + 2 * j);
+    s1 += v.x + v.z;
+    s2 += v.y + v.w;
+  }
+  const float inv = 1.0f / static_cast<float>(width);
+  mu = s1 * inv;
+  const float var = fmaxf(s2 * inv - mu * mu, 0.f);
+  rstd = rsqrtf(var + eps);
+}
+
+// v[i] summed over the 8 lanes of a group (lanes 8g .. 8g+7): afterwards v[0] of the lane with
+// piece p (= lane & 7) holds the total of index p.  7 shuffles instead of 24.
+__device__ __forceinline__ void group_transpose_sum(float (&v)[8], int piece) {
+#pragma unroll
+  for (int h = 4; h >= 1; h >>= 1) {
+    const bool upper = (piece & h) != 0;
+#pragma unroll
+    for (int j = 0; j < h; ++j) {
+      const float send = upper ? v[j] : v[j + h];
+      const float keep = upper ? v[j + h] : v[j];
+      v[j] = keep + __shfl_xor_sync(0xffffffffu, send, h);
+    }
+  }
+}
+
 // Epilogue of one warp for one finished accumulator: its 32 rows (TMEM lanes
 // starting at the lane field of t_row) x kCols columns.  Per 64-column chunk:
 // TMEM -> registers (one row per thread) -> bias/GELU in fp32 -> fp16 -> the
@@ -204,7 +248,7 @@ __device__ __forceinline__ Vec16 ld_shared_v4(uint32_t addr) {
 template <int EPI, typename Release>
 __device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, __half* ctile, int N, int rows_valid,
                                                    uint32_t bias_s, uint32_t buf, int lane, int chunks,
-                                                   const __half* rtile, Release release) {
+                                                   const __half* rtile, Release release, const NormCtx& nc = NormCtx()) {
 #pragma unroll 1
   for (int c = 0; c < chunks; ++c) {
     uint32_t r[64];
@@ -221,7 +265,13 @@ __device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, __half* ctile
       float f[8];
 #pragma unroll
       for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[p * 8 + e]);
-      if (EPI != kEpiNone) {
+      if (EPI == kEpiNormIn || EPI == kEpiNormInGelu) {
+        float fb[8], fc[8];
+        VecTraits<__half>::unpack(ld_shared_v4(bias_s + (c * 64 + p * 8) * 2), fb);
+        VecTraits<__half>::unpack(ld_global_nc_v4(nc.csum + c * 64 + p * 8), fc);  // same address in every lane
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] = fmaf(f[e], nc.rstd, fmaf(nc.nm, fc[e], fb[e]));
+      } else if (EPI != kEpiNone) {
         float fb[8];
         VecTraits<__half>::unpack(ld_shared_v4(bias_s + (c * 64 + p * 8) * 2), fb);
 #pragma unroll
@@ -232,7 +282,7 @@ __device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, __half* ctile
         for (int e = 0; e < 8; ++e) f[e] = tanhf(f[e]);
       }
       Vec16 o = VecTraits<__half>::pack(f);
-      if (EPI == kEpiBiasGelu) {
+      if (EPI == kEpiBiasGelu || EPI == kEpiNormInGelu) {
         o.x = gelu_tanh_half2(o.x);
         o.y = gelu_tanh_half2(o.y);
         o.z = gelu_tanh_half2(o.z);
@@ -241,7 +291,54 @@ __device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, __half* ctile
       st_shared_v4(buf + lane * 128 + ((p ^ (lane & 7)) << 4), o);
     }
     __syncwarp();
-    if (EPI == kEpiBiasResidual) {
+    if (EPI == kEpiNormResidual) {
+      // The residual is LN(rtile), taken here where a warp instruction covers four whole 128-byte row
+      // segments; the statistics of the rows as they are stored go out beside them.
+      const int piece = lane & 7, g = lane >> 3;
+      Vec16 res[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int rr = 4 * i + g;
+        if (rr < rows_valid) res[i] = ld_global_nc_v4(rtile + static_cast<size_t>(rr) * N + c * 64 + piece * 8);
+      }
+      float fg[8], fbeta[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) fg[e] = 1.f, fbeta[e] = 0.f;
+      if (nc.gamma != nullptr) {
+        VecTraits<__half>::unpack(ld_global_nc_v4(nc.gamma + c * 64 + piece * 8), fg);
+        VecTraits<__half>::unpack(ld_global_nc_v4(nc.beta + c * 64 + piece * 8), fbeta);
+      }
+      float s1[8], s2[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int rr = 4 * i + g;
+        const Vec16 v = ld_shared_v4(buf + rr * 128 + ((piece ^ (rr & 7)) << 4));
+        s1[i] = 0.f, s2[i] = 0.f;
+        if (rr < rows_valid) {
+          float fv[8], fr[8], fx[8];
+          VecTraits<__half>::unpack(v, fv);
+          VecTraits<__half>::unpack(res[i], fr);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float t = nc.rstd_i[i] * fg[e];
+            fv[e] += fmaf(fr[e], t, fmaf(-nc.mu_i[i], t, fbeta[e]));
+          }
+          const Vec16 o = VecTraits<__half>::pack(fv);
+          st_global_v4(ctile + static_cast<size_t>(rr) * N + c * 64 + piece * 8, o);
+          VecTraits<__half>::unpack(o, fx);  // the statistics are those of the stored values
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            s1[i] += fx[e];
+            s2[i] = fmaf(fx[e], fx[e], s2[i]);
+          }
+        }
+      }
+      group_transpose_sum(s1, piece);
+      group_transpose_sum(s2, piece);
+      const int rr = 4 * piece + g;  // the row whose totals this lane now holds
+      if (rr < rows_valid)
+        *reinterpret_cast<float2*>(nc.stats + static_cast<size_t>(rr) * nc.s2 + 2 * c) = make_float2(s1[0], s2[0]);
+    } else if (EPI == kEpiBiasResidual) {
       // the residual is added here, where a warp instruction covers four whole 128-byte row
       // segments (one row per thread, as in the TMEM phase, would scatter 32 lines per load)
       Vec16 res[8];
@@ -800,11 +897,42 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
           tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN + half * wcols;
       __half* ctile = C + static_cast<size_t>(row0) * N + col0;
       const uint32_t empty0 = mapa_shared(tmem_empty_bar(acc), 0);
-      const __half* rtile = kBase == kEpiBiasResidual ? residual + static_cast<size_t>(row0) * N + col0 : nullptr;
+      const __half* rtile = (kBase == kEpiBiasResidual || kBase == kEpiNormResidual)
+                                ? residual + static_cast<size_t>(row0) * N + col0
+                                : nullptr;
+      NormCtx nc;
+      if constexpr (kBase == kEpiNormIn || kBase == kEpiNormInGelu) {
+        // this thread's row of A is normalised on the way out: its statistics, once per tile
+        const int row = row0 + lane;
+        float mu = 0.f, rstd = 1.f;
+        if (ln.stats_in != nullptr && row < M)
+          row_stats(ln.stats_in + static_cast<size_t>(row) * (2 * ln.stat_slots), ln.stat_slots, K, ln.eps, mu, rstd);
+        nc.rstd = rstd;
+        nc.nm = -rstd * mu;
+        nc.csum = ln.csum + col0;
+      }
+      if constexpr (kBase == kEpiNormResidual) {
+        // lane (g, piece) works out the statistics of residual row 4 * piece + g; the coalesced phase
+        // needs those of rows 4 i + g, which the lanes of its own group hold
+        const int rr = 4 * (lane & 7) + (lane >> 3);
+        float mu = 0.f, rstd = 1.f;
+        if (ln.stats_in != nullptr && row0 + rr < M)
+          row_stats(ln.stats_in + static_cast<size_t>(row0 + rr) * (2 * ln.stat_slots), ln.stat_slots, N, ln.eps, mu,
+                    rstd);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          nc.mu_i[i] = __shfl_sync(0xffffffffu, mu, (lane & ~7) + i);
+          nc.rstd_i[i] = __shfl_sync(0xffffffffu, rstd, (lane & ~7) + i);
+        }
+        nc.gamma = ln.gamma != nullptr ? ln.gamma + col0 : nullptr;
+        nc.beta = ln.beta != nullptr ? ln.beta + col0 : nullptr;
+        nc.s2 = 2 * (N / 64);
+        nc.stats = ln.stats_out + static_cast<size_t>(row0) * nc.s2 + 2 * (col0 / 64);
+      }
       epilogue_warp_tile<kBase>(t_row, ctile, N, M - row0, bias_s, buf, lane, wcols / 64, rtile, [&] {
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(empty0);
-      });
+      }, nc);
       if constexpr (kLn) {
         // this unit's stores are issued: tell the counting warp (CTA-scope release of all lanes' stores)
         __threadfence_block();
@@ -985,6 +1113,9 @@ cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUte
     ETB_PAIR_CASE(kEpiBiasGelu);
     ETB_PAIR_CASE(kEpiBiasTanh);
     ETB_PAIR_CASE(kEpiBiasResidual);
+    ETB_PAIR_CASE(kEpiNormIn);
+    ETB_PAIR_CASE(kEpiNormInGelu);
+    ETB_PAIR_CASE(kEpiNormResidual);
     case kEpiResidualLayerNorm:
       return launch_pair_ln<kEpiResidualLayerNorm>(ta, tb, tbh, bias, residual, c, m_ptr, max_m, n, k, status_word,
                                                    reverse_m, ln, stream);
@@ -1099,8 +1230,8 @@ cudaError_t launch_gemm_tcgen05(const __half* a, const __half* w_packed, const _
       (reinterpret_cast<uintptr_t>(c) & 15u) || (bias && (reinterpret_cast<uintptr_t>(bias) & 15u)))
     return cudaErrorMisalignedAddress;
   if (epilogue != kEpiNone && bias == nullptr) return cudaErrorInvalidValue;
-  const bool needs_residual =
-      epilogue == kEpiBiasResidual || epilogue == kEpiResidualLayerNorm || epilogue == kEpiLayerNorm;
+  const bool needs_residual = epilogue == kEpiBiasResidual || epilogue == kEpiResidualLayerNorm ||
+                              epilogue == kEpiLayerNorm || epilogue == kEpiNormResidual;
   if (needs_residual && (residual == nullptr || (reinterpret_cast<uintptr_t>(residual) & 15u)))
     return cudaErrorInvalidValue;
   GemmLayerNorm lnp;
@@ -1110,6 +1241,24 @@ cudaError_t launch_gemm_tcgen05(const __half* a, const __half* w_packed, const _
       return cudaErrorInvalidValue;
     if ((reinterpret_cast<uintptr_t>(ln->gamma) & 15u) || (reinterpret_cast<uintptr_t>(ln->beta) & 15u))
       return cudaErrorMisalignedAddress;
+    lnp = *ln;
+  }
+  if (is_deferred_norm(epilogue)) {
+    // the pair kernel only; statistics in 64-column pieces of rows whose width is a multiple of 128
+    if (ln == nullptr || (n % 256) != 0) return cudaErrorInvalidValue;
+    const int width = epilogue == kEpiNormResidual ? n : k;  // of the tensor the statistics describe
+    if (ln->stats_in != nullptr &&
+        (ln->stat_slots != width / 64 || (width % 128) != 0 || (reinterpret_cast<uintptr_t>(ln->stats_in) & 15u)))
+      return cudaErrorInvalidValue;
+    if (epilogue == kEpiNormResidual) {
+      if (ln->stats_out == nullptr || (reinterpret_cast<uintptr_t>(ln->stats_out) & 7u)) return cudaErrorInvalidValue;
+      if ((ln->gamma == nullptr) != (ln->beta == nullptr)) return cudaErrorInvalidValue;
+      if (ln->gamma != nullptr &&
+          ((reinterpret_cast<uintptr_t>(ln->gamma) & 15u) || (reinterpret_cast<uintptr_t>(ln->beta) & 15u)))
+        return cudaErrorMisalignedAddress;
+    } else {
+      if (ln->csum == nullptr || (reinterpret_cast<uintptr_t>(ln->csum) & 15u)) return cudaErrorInvalidValue;
+    }
     lnp = *ln;
   }
   const int bn = (n % 256 == 0) ? 256 : 128;

@@ -514,6 +514,32 @@ int et_gemm_fused(const void* a, const void* w_packed, const void* bias, const v
                   const void* gamma, const void* beta, float eps, int* row_counters, void* c,
                   const int* m_ptr, int max_m, int n, int k, int epilogue, int* status_word, void* stream);
 
+/* The LayerNorm that is never materialised.  A projection whose input is
+ * LN(x) = (x - mu) * rstd * gamma + beta can run on x itself with gamma folded
+ * into its weights: LN(x) W + b = rstd * (x W' - mu * colsum(W')) + (beta W + b),
+ * W' = diag(gamma) W.  No counterpart in the reference, which runs
+ * add_bias_input_layernorm (cuda/cuda_kernels.cu:157-271) as a kernel of its own
+ * between the projections (tf_op/bert_transformer_op.cu.cc:211-213,242-246);
+ * the handle uses these inside et_forward* when et_set_deferred_layernorm is on.
+ * et_fold_layernorm: w_packed [N,K] (et_pack_weight), bias [N], gamma / beta [K]
+ * -> w_folded [N,K], csum [N], bias_folded [N] (fp16).
+ * et_gemm_deferred_norm (fp16, n % 256 == 0): epilogue
+ *   7  C = rstd[r] * (A W' - mu[r] * csum[n]) + bias[n]          (bias = bias_folded)
+ *   8  the same, then GELU
+ *   9  C = A W + bias[n] + LN(residual)[r,n], LN taken on the fly from `residual`
+ *      [M,N] with gamma / beta [N] (NULL: ones / zeros); and stats_out
+ *      [rows, 2 * N/64] receives (sum, sum of squares) of every 64-column piece
+ *      of every stored row of C.
+ * stats_in: such statistics of A's rows (7, 8: [rows, 2 * K/64]) or of
+ * residual's rows (9: [rows, 2 * N/64]); NULL: mu = 0, rstd = 1.  Rows of the
+ * statistics buffers: max_m rounded up to a multiple of 256. */
+int et_fold_layernorm(const void* w_packed, const void* bias, const void* gamma, const void* beta, void* w_folded,
+                      void* csum, void* bias_folded, int n, int k, void* stream);
+int et_gemm_deferred_norm(const void* a, const void* w_packed, const void* bias, const void* csum,
+                          const void* residual, const void* gamma, const void* beta, float eps,
+                          const float* stats_in, float* stats_out, void* c, const int* m_ptr, int max_m, int n,
+                          int k, int epilogue, int* status_word, void* stream);
+
 /* The same call sites for the FP32 OperationType on the tensor cores, keeping
  * fp32 accuracy: every operand is split into two tf32 numbers, x = hi + lo with
  * hi = round_to_tf32(x) (et_split_tf32; hi or lo may be x itself), and the

@@ -521,6 +521,115 @@ def test_gemm_layernorm_epilogue_equals_gemm_then_layernorm_kernel():
     assert int((one != plain).sum()) <= m * n // 5000 and float((one.float() - plain.float()).abs().max()) <= 4e-3
 
 
+# ---- the LayerNorm that is never materialised: folded into the consumer, statistics from the producer -----
+def _row_stat_pieces(x16: torch.Tensor) -> torch.Tensor:
+    """(sum, sum of squares) of every 64-column piece of every row, as the producer epilogue leaves them."""
+    rows, width = x16.shape
+    xs = x16.float().reshape(rows, width // 64, 64)
+    return torch.stack([xs.sum(-1), (xs * xs).sum(-1)], dim=-1).reshape(rows, 2 * (width // 64)).contiguous()
+
+
+def _deferred_consumer_case(m, cap, n, k, gelu, with_stats, seed=0):
+    """epilogues 7 / 8: the projection of LN(x) computed from x, folded weights and x's row statistics."""
+    rng = np.random.RandomState(seed + m + n + k)
+    h = torch.float16
+    x = dev((1.5 * rng.randn(cap, k) + 0.3).astype(np.float32), h)        # un-normalised rows with a mean
+    w = dev((rng.randn(k, n) / math.sqrt(k)).astype(np.float32), h)
+    bias = dev(0.5 * rng.randn(n).astype(np.float32), h)
+    gamma = dev((1 + 0.2 * rng.randn(k)).astype(np.float32), h)
+    beta = dev(0.3 * rng.randn(k).astype(np.float32), h)
+    wp = torch.empty((n, k), dtype=h, device="cuda")
+    ok(lib().et_pack_weight(DT[h], iptr(w), iptr(wp), k, n, stream()))
+    wf, csum, bf = torch.empty_like(wp), torch.empty(n, dtype=h, device="cuda"), torch.empty(n, dtype=h, device="cuda")
+    ok(lib().et_fold_layernorm(iptr(wp), iptr(bias), iptr(gamma), iptr(beta), iptr(wf), iptr(csum), iptr(bf), n, k,
+                               stream()))
+    torch.cuda.synchronize()
+    # the fold itself
+    wf_ref = (wp.float() * gamma.float()[None, :]).half()
+    assert torch.equal(wf, wf_ref)
+    torch.testing.assert_close(csum.float(), wf_ref.float().sum(-1), rtol=2e-3, atol=2e-3)
+    torch.testing.assert_close(bf.double(), bias.double() + beta.double() @ w.double(), rtol=2e-3, atol=2e-3)
+    rows_cap = (cap + 255) // 256 * 256
+    stats = torch.zeros(rows_cap, 2 * (k // 64), dtype=torch.float32, device="cuda")
+    stats[:cap] = _row_stat_pieces(x)
+    c = torch.full((cap, n), 3.0, dtype=h, device="cuda")
+    mt = dev(np.array([m], np.int32))
+    st = status_word()
+    ok(lib().et_gemm_deferred_norm(iptr(x), iptr(wf if with_stats else wp), iptr(bf if with_stats else bias),
+                                   iptr(csum), None, None, None, 1e-6, iptr(stats) if with_stats else None, None,
+                                   iptr(c), iptr(mt), cap, n, k, 8 if gelu else 7, iptr(st), stream()))
+    torch.cuda.synchronize()
+    assert int(st[0]) == 0
+    xd = x[:m].double()
+    if with_stats:
+        mean = xd.mean(-1, keepdim=True)
+        var = ((xd - mean) ** 2).mean(-1, keepdim=True)
+        y = (xd - mean) / torch.sqrt(var + 1e-6) * gamma.double() + beta.double()
+    else:
+        y = xd                                                             # no statistics: x is used as it is
+    ref = y @ w.double() + bias.double()
+    if gelu:
+        ref = O.gelu(ref)
+    torch.testing.assert_close(c[:m].double(), ref, rtol=4e-3, atol=8e-3)
+    assert torch.all(c[m:] == 3.0), "rows past M were written"
+
+
+@pytest.mark.parametrize("gelu", [False, True])
+@pytest.mark.parametrize("with_stats", [True, False])
+@pytest.mark.parametrize("m,cap,n,k", [(1, 1, 256, 128), (134, 256, 2304, 768), (257, 300, 3072, 768),
+                                       (1000, 1000, 1024, 1024), (0, 64, 768, 128), (6500, 6500, 768, 768)])
+def test_gemm_tcgen05_projection_of_a_layernorm_that_is_not_materialised(m, cap, n, k, gelu, with_stats):
+    _deferred_consumer_case(m, cap, n, k, gelu, with_stats)
+
+
+def _deferred_producer_case(m, cap, n, k, with_norm, seed=0):
+    """epilogue 9: C = A W + bias + LN(residual) with the LayerNorm taken on the fly, and the statistics
+    of the stored rows of C."""
+    rng = np.random.RandomState(seed + m + n + k + 9)
+    h = torch.float16
+    a = dev(rng.randn(cap, k).astype(np.float32), h)
+    w = dev((rng.randn(k, n) / math.sqrt(k)).astype(np.float32), h)
+    bias = dev(0.5 * rng.randn(n).astype(np.float32), h)
+    res = dev((1.5 * rng.randn(cap, n) + 0.3).astype(np.float32), h)
+    gamma = dev((1 + 0.2 * rng.randn(n)).astype(np.float32), h)
+    beta = dev(0.3 * rng.randn(n).astype(np.float32), h)
+    wp = torch.empty((n, k), dtype=h, device="cuda")
+    ok(lib().et_pack_weight(DT[h], iptr(w), iptr(wp), k, n, stream()))
+    rows_cap = (cap + 255) // 256 * 256
+    stats_in = torch.zeros(rows_cap, 2 * (n // 64), dtype=torch.float32, device="cuda")
+    stats_in[:cap] = _row_stat_pieces(res)
+    stats_out = torch.full((rows_cap, 2 * (n // 64)), -7.0, dtype=torch.float32, device="cuda")
+    c = torch.full((cap, n), 3.0, dtype=h, device="cuda")
+    mt = dev(np.array([m], np.int32))
+    st = status_word()
+    ok(lib().et_gemm_deferred_norm(iptr(a), iptr(wp), iptr(bias), None, iptr(res),
+                                   iptr(gamma) if with_norm else None, iptr(beta) if with_norm else None, 1e-6,
+                                   iptr(stats_in) if with_norm else None, iptr(stats_out), iptr(c), iptr(mt), cap, n,
+                                   k, 9, iptr(st), stream()))
+    torch.cuda.synchronize()
+    assert int(st[0]) == 0
+    rd = res[:m].double()
+    if with_norm:
+        mean = rd.mean(-1, keepdim=True)
+        var = ((rd - mean) ** 2).mean(-1, keepdim=True)
+        rd = (rd - mean) / torch.sqrt(var + 1e-6) * gamma.double() + beta.double()
+    ref = a[:m].double() @ w.double() + bias.double() + rd
+    torch.testing.assert_close(c[:m].double(), ref, rtol=3e-3, atol=6e-3)
+    assert torch.all(c[m:] == 3.0), "rows past M were written"
+    # the statistics describe the rows as they were stored
+    want = _row_stat_pieces(c[:m])
+    torch.testing.assert_close(stats_out[:m], want, rtol=1e-5, atol=1e-4)
+    assert torch.all(stats_out[m:] == -7.0), "statistics of rows past M were written"
+
+
+@pytest.mark.parametrize("with_norm", [True, False])
+@pytest.mark.parametrize("m,cap,n,k", [(1, 1, 256, 64), (134, 256, 768, 768), (257, 300, 768, 3072),
+                                       (1000, 1000, 1024, 4096), (0, 64, 768, 128), (6500, 6500, 768, 768),
+                                       (9372, 9372, 768, 3072)])
+def test_gemm_tcgen05_residual_is_a_layernorm_taken_on_the_fly(m, cap, n, k, with_norm):
+    _deferred_producer_case(m, cap, n, k, with_norm)
+
+
 def test_gemm_fused_rejects_what_it_cannot_do():
     z = torch.zeros(256, dtype=torch.float16, device="cuda")
     cnt = torch.zeros(8, dtype=torch.int32, device="cuda")
