@@ -342,6 +342,8 @@ def main():
     ap.add_argument("--shard-of", type=int, default=0,
                     help="one GPU only: time rank 0's shard of an N-way split of the batch (what one rank of "
                          "`--gpus N` runs), to study the small-batch regime without N GPUs")
+    ap.add_argument("--deferred-layernorm", type=int, default=-1,
+                    help="A/B: 1 / 0 = et_set_deferred_layernorm on / off (default: the library's default)")
     ap.add_argument("--fused-layernorm", action="store_true",
                     help="A/B: the LayerNorms inside the projection kernels (et_set_fused_layernorm) instead of a "
                          "LayerNorm kernel behind each projection")
@@ -386,6 +388,8 @@ def main():
     main_pass = DevicePass(et, torch, spec, lengths, x_np, base.weights, dev, local)
     if args.fused_layernorm:
         main_pass.eng.set_fused_layernorm(True)
+    if args.deferred_layernorm >= 0:
+        main_pass.eng.set_deferred_layernorm(bool(args.deferred_layernorm))
     eng, b, s, h = main_pass.eng, main_pass.b, main_pass.s, main_pass.h
     tokens_rank = main_pass.tokens
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)   # > 126 MB L2

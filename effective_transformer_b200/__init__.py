@@ -107,6 +107,11 @@ class EffectiveTransformer:
         layer); on: bias + residual + LayerNorm run inside those projection kernels (5)."""
         _capi.check(self._lib.et_set_fused_layernorm(self._h, 1 if on else 0), self._h)
 
+    def set_deferred_layernorm(self, on: bool) -> None:
+        """On: the whole-stack calls materialise no LayerNorm between the projections (producers
+        leave row statistics, consumers run on folded weights); only the last one runs as a kernel."""
+        _capi.check(self._lib.et_set_deferred_layernorm(self._h, 1 if on else 0), self._h)
+
     def workspace_bytes(self, batch_size: int, seq_len: int) -> int:
         n = C.c_size_t(0)
         _capi.check(self._lib.et_workspace_bytes(self._h, batch_size, seq_len, C.byref(n)), self._h)

@@ -85,6 +85,7 @@ SIGNATURES = {
     "et_copy_to_host": (i32, [vp, vp, C.c_size_t, vp]),
     "et_set_debug_simt": (i32, [vp, i32]),
     "et_set_fused_layernorm": (i32, [vp, i32]),
+    "et_set_deferred_layernorm": (i32, [vp, i32]),
     "et_host_chunk_shares": (i32, [vp, ip, ip, ip]),
     "et_selftest_wait_timeout": (i32, [vp, vp]),
     "et_workspace_allocated_bytes": (i32, [vp, C.POINTER(C.c_size_t)]),

@@ -49,6 +49,15 @@ struct LayerWeights {
   void* b2 = nullptr;
   void* ln2_gamma = nullptr;
   void* ln2_beta = nullptr;
+  // fp16 handles, deferred LayerNorm: the two projections that consume a LayerNorm, with its gamma
+  // folded into their weights (K-major [out, in]), the column sums of the folded weights, and
+  // bias + beta W.  wqkv_f folds the LayerNorm that closes the layer BEFORE this one.
+  void* wqkv_f = nullptr;
+  void* cqkv = nullptr;
+  void* bqkv_f = nullptr;
+  void* w1_f = nullptr;
+  void* c1 = nullptr;
+  void* b1_f = nullptr;
   bool ready = false;
 };
 
@@ -97,6 +106,8 @@ struct Workspace {
   float* a_lo = nullptr;
   float* ffn_lo = nullptr;    // fp32 handles: [cap, F] remainder of the GELU output (its tf32 half is in ffn)
   int* ln_counters = nullptr; // [cap / 32] column counts of the GEMMs that normalise their own output rows
+  float* stats_x = nullptr;   // deferred LayerNorm: (sum, sum of squares) per 64-column piece of the rows of x
+  float* stats_att = nullptr; // ... and of att
   int* valid_word_num = nullptr;
   int* status = nullptr;
   std::vector<void*> allocations;
@@ -112,6 +123,13 @@ struct WsItem {
 // that cover `rows` rows.
 inline size_t ln_counter_ints(size_t rows) { return round_up(rows, 256) / 32 + 8; }
 inline size_t ws_round(size_t bytes) { return round_up(bytes == 0 ? 16 : bytes, 256); }
+
+// The LayerNorm can be deferred into the projections around it (fp16 tensor-core path, every
+// projection on the CTA-pair kernel, statistics in 64-column pieces of rows of 128 * j columns).
+bool defer_eligible(const et_config_t& c) {
+  const int H = c.head_num * c.size_per_head;
+  return c.dtype == ET_FP16 && H % 256 == 0 && c.ffn_dim % 256 == 0 && c.num_layers > 0;
+}
 
 std::vector<WsItem> workspace_items(const et_config_t& c, size_t batch, size_t seq, Workspace& ws) {
   const size_t H = static_cast<size_t>(c.head_num) * c.size_per_head, f = c.ffn_dim;
@@ -133,6 +151,8 @@ std::vector<WsItem> workspace_items(const et_config_t& c, size_t batch, size_t s
       {F(&ws.a_hi), f32 ? cap * H * 4 : 0}, {F(&ws.a_lo), f32 ? cap * H * 4 : 0},
       {F(&ws.ffn_lo), f32 ? cap * f * 4 : 0},
       {I(&ws.ln_counters), ln_counter_ints(bs) * 4},
+      {F(&ws.stats_x), defer_eligible(c) ? round_up(bs, 256) * (H / 64) * 2 * 4 : 0},
+      {F(&ws.stats_att), defer_eligible(c) ? round_up(bs, 256) * (H / 64) * 2 * 4 : 0},
       {I(&ws.valid_word_num), 4}, {I(&ws.status), 4}};
 }
 
@@ -180,6 +200,13 @@ struct et_handle_s {
   // eight epilogue warps of a CTA hide the LayerNorm's memory latency worse than the 16 warps per SM
   // of the LayerNorm kernel, and its L2 traffic slows the GEMM's operand loads).
   bool fuse_ln = false;
+  // et_set_deferred_layernorm: inside a whole-stack call no LayerNorm between the projections is
+  // materialised; producers leave row statistics, consumers run on folded weights (gemm_tcgen05.cu,
+  // kEpiNorm*).  folded_ready: the folded weights match the layers' current weights.
+  // defer_active: the stack being enqueued runs that way (set by stack_impl for run_layer).
+  bool defer_ln = false;
+  bool folded_ready = false;
+  bool defer_active = false;
   TensorMapCache maps;  // TMA descriptors of this handle's launches
   // general [B,S,S] mask of the pass being enqueued (null: key-only mask, fast kernels)
   const void* cur_attr_mask = nullptr;
@@ -367,6 +394,29 @@ int pack_layer_any(et_handle_t h, int layer, const void* const* w, cudaStream_t 
   return h->cfg.dtype == ET_FP16 ? pack_layer<__half>(h, lw, w, s) : pack_layer<float>(h, lw, w, s);
 }
 
+// Folded weights of every layer (deferred LayerNorm), once all layers have their weights.
+int fold_all(et_handle_t h, cudaStream_t s) {
+  h->folded_ready = false;
+  if (!defer_eligible(h->cfg)) return ET_OK;
+  for (const auto& lw : h->layers)
+    if (!lw.ready) return ET_OK;
+  const int hid = h->hidden, f = h->cfg.ffn_dim;
+  auto H16 = [](const void* p) { return static_cast<const __half*>(p); };
+  auto M16 = [](void* p) { return static_cast<__half*>(p); };
+  for (size_t l = 0; l < h->layers.size(); ++l) {
+    LayerWeights& lw = h->layers[l];
+    ET_CUDA(h, launch_fold_layernorm(H16(lw.w1_t), H16(lw.b1), H16(lw.ln1_gamma), H16(lw.ln1_beta), M16(lw.w1_f),
+                                     M16(lw.c1), M16(lw.b1_f), f, hid, s));
+    if (l > 0) {
+      const LayerWeights& prev = h->layers[l - 1];
+      ET_CUDA(h, launch_fold_layernorm(H16(lw.wqkv_t), H16(lw.bqkv), H16(prev.ln2_gamma), H16(prev.ln2_beta),
+                                       M16(lw.wqkv_f), M16(lw.cqkv), M16(lw.bqkv_f), 3 * hid, hid, s));
+    }
+  }
+  h->folded_ready = true;
+  return ET_OK;
+}
+
 // One encoder layer on the packed layout.  x_out may alias x_in.
 // fp32 tensor path only: in_split_ready = the workspace's a_hi / a_lo already hold the tf32
 // halves of x_in (the layer before wrote them); out_split = write those of x_out for the next
@@ -374,7 +424,7 @@ int pack_layer_any(et_handle_t h, int layer, const void* const* w, cudaStream_t 
 template <typename T>
 int run_layer(et_handle_t h, const LayerWeights& lw, const T* x_in, T* x_out, const int* t_ptr,
               int max_m, const int* cu_seqlens, int batch, int seq, cudaStream_t s,
-              bool in_split_ready = false, bool out_split = false) {
+              bool in_split_ready = false, bool out_split = false, int layer_index = -1) {
   const int hid = h->hidden, f = h->cfg.ffn_dim, heads = h->cfg.head_num, d = h->cfg.size_per_head;
   Workspace& ws = h->ws;
   T* qkv = static_cast<T*>(ws.qkv);
@@ -422,7 +472,21 @@ int run_layer(et_handle_t h, const LayerWeights& lw, const T* x_in, T* x_out, co
   // it (the halves of the QKV input in a_hi / a_lo are no longer needed by then)
   T* ctx_lo = (tc32 && h->cur_attr_mask == nullptr) ? reinterpret_cast<T*>(ws.a_lo) : nullptr;
   // Q,K,V projections + bias in one GEMM -> [T, 3H]
-  if (tc32 && in_split_ready)
+  // Deferred LayerNorm (inside a whole-stack call): x_in holds the un-normalised sum the layer before
+  // left, with its row statistics in ws.stats_x; no LayerNorm kernel runs between the projections.
+  const bool deferred = tc && h->defer_active && layer_index >= 0;
+  auto H16 = [](const void* p) { return static_cast<const __half*>(p); };
+  const int stat_slots = hid / 64;
+  if (deferred && layer_index > 0) {
+    GemmLayerNorm nin;
+    nin.eps = h->eps;
+    nin.stats_in = ws.stats_x;
+    nin.stat_slots = stat_slots;
+    nin.csum = H16(lw.cqkv);
+    ET_LAUNCH(h, ET_PROF_GEMM_QKV, 1, s,
+              launch_gemm_tcgen05(H16(x_in), H16(lw.wqkv_f), H16(lw.bqkv_f), reinterpret_cast<__half*>(qkv), t_ptr,
+                                  max_m, 3 * hid, hid, kEpiNormIn, ws.status, s, turn(), nullptr, &h->maps, &nin));
+  } else if (tc32 && in_split_ready)
     ET_LAUNCH(h, ET_PROF_GEMM_QKV, 1, s,
               gemm(reinterpret_cast<const T*>(ws.a_hi), lw.wqkv, lw.wqkv_t, lw.wqkv_lo, lw.bqkv, qkv, 3 * hid, hid,
                    kEpiBias, ws.a_lo));
@@ -471,8 +535,45 @@ int run_layer(et_handle_t h, const LayerWeights& lw, const T* x_in, T* x_out, co
   if (!(tc && seq <= 128)) forward_only();
   // fp16 tensor-core path: bias + residual + LayerNorm run inside the projection kernels (rows are
   // normalised in place as soon as their last column tile has been stored), no LayerNorm launch
+  if (deferred) {
+    // attention output projection: + bias + LN(x_in) taken on the fly (the layer input itself in the
+    // first layer); leaves the sum in att and its row statistics in ws.stats_att
+    GemmLayerNorm n1;
+    n1.eps = h->eps;
+    n1.stat_slots = stat_slots;
+    if (layer_index > 0) {
+      const LayerWeights& prev = h->layers[layer_index - 1];
+      n1.stats_in = ws.stats_x;
+      n1.gamma = H16(prev.ln2_gamma);
+      n1.beta = H16(prev.ln2_beta);
+    }
+    n1.stats_out = ws.stats_att;
+    ET_LAUNCH(h, ET_PROF_GEMM_ATTN_OUT, 1, s,
+              launch_gemm_tcgen05(H16(ctx), H16(lw.wo_t), H16(lw.bo), reinterpret_cast<__half*>(att), t_ptr, max_m,
+                                  hid, hid, kEpiNormResidual, ws.status, s, turn(), H16(x_in), &h->maps, &n1));
+    // first feed-forward projection of LN1(att): folded weights, statistics, GELU
+    GemmLayerNorm n2;
+    n2.eps = h->eps;
+    n2.stats_in = ws.stats_att;
+    n2.stat_slots = stat_slots;
+    n2.csum = H16(lw.c1);
+    ET_LAUNCH(h, ET_PROF_GEMM_FFN1, 1, s,
+              launch_gemm_tcgen05(H16(att), H16(lw.w1_f), H16(lw.b1_f), reinterpret_cast<__half*>(ffn), t_ptr, max_m,
+                                  f, hid, kEpiNormInGelu, ws.status, s, turn(), nullptr, &h->maps, &n2));
+    // second: + bias + LN1(att) on the fly; leaves the sum in x_out and its statistics in ws.stats_x
+    GemmLayerNorm n3;
+    n3.eps = h->eps;
+    n3.stats_in = ws.stats_att;
+    n3.stat_slots = stat_slots;
+    n3.gamma = H16(lw.ln1_gamma);
+    n3.beta = H16(lw.ln1_beta);
+    n3.stats_out = ws.stats_x;
+    ET_LAUNCH(h, ET_PROF_GEMM_FFN2, 1, s,
+              launch_gemm_tcgen05(H16(ffn), H16(lw.w2_t), H16(lw.b2), reinterpret_cast<__half*>(x_out), t_ptr, max_m,
+                                  hid, f, kEpiNormResidual, ws.status, s, turn(), H16(att), &h->maps, &n3));
+    return ET_OK;
+  }
   const bool ln_in_gemm = tc && h->fuse_ln && gemm_layernorm_supported(hid);
-  auto H16 = [](const void* p) { return static_cast<const __half*>(p); };
   GemmLayerNorm gln;
   gln.eps = h->eps;
   gln.counters = ws.ln_counters;
@@ -628,15 +729,32 @@ int stack_impl(et_handle_t h, int batch, int seq, cudaStream_t s) {
   else if (h->cur_attr_mask != nullptr)
     ET_LAUNCH(h, ET_PROF_PADDING_OFFSETS, 1, s,
               launch_position_rows(ws.batch_idx, ws.word_idx, ws.valid_word_num, batch, seq, ws.pos_row, s));
+  // No LayerNorm between the projections: x holds un-normalised sums from the first layer's end on,
+  // and the last layer's LayerNorm is the one kernel that runs, behind the loop.
+  h->defer_active = h->defer_ln && h->folded_ready && !h->use_simt && defer_eligible(h->cfg) && max_m > 0;
   for (int l = 0; l < h->cfg.num_layers; ++l) {
     if (h->cfg.dtype == ET_FP16)
       rc = run_layer<__half>(h, h->layers[l], static_cast<const __half*>(ws.x), static_cast<__half*>(ws.x),
-                             ws.valid_word_num, max_m, ws.cu_seqlens, batch, seq, s);
+                             ws.valid_word_num, max_m, ws.cu_seqlens, batch, seq, s, false, false, l);
     else
       rc = run_layer<float>(h, h->layers[l], static_cast<const float*>(ws.x), static_cast<float*>(ws.x),
                             ws.valid_word_num, max_m, ws.cu_seqlens, batch, seq, s, l > 0,
                             l + 1 < h->cfg.num_layers);
-    if (rc != ET_OK) return rc;
+    if (rc != ET_OK) {
+      h->defer_active = false;
+      return rc;
+    }
+  }
+  if (h->defer_active) {
+    h->defer_active = false;
+    const LayerWeights& last = h->layers.back();
+    const bool reverse = h->prev_ascending;
+    h->prev_ascending = !reverse;
+    ET_LAUNCH(h, ET_PROF_LAYERNORM, 1, s,
+              launch_add_bias_input_layernorm<__half>(static_cast<__half*>(ws.x), nullptr, nullptr,
+                                                      static_cast<const __half*>(last.ln2_gamma),
+                                                      static_cast<const __half*>(last.ln2_beta), ws.valid_word_num,
+                                                      max_m, h->hidden, h->eps, s, reverse));
   }
   return ET_OK;
 }
@@ -904,6 +1022,12 @@ int et_create(const et_config_t* config, et_handle_t* out_handle) {
       for (int i = 0; i < count; ++i)
         if ((rc = ws_alloc(h, packed[i].p, packed[i].n * e)) != ET_OK) return bail(rc);
     }
+    if (defer_eligible(c)) {
+      struct { void** p; size_t n; } folded[] = {{&lw.wqkv_f, 3 * H * H}, {&lw.cqkv, 3 * H}, {&lw.bqkv_f, 3 * H},
+                                                  {&lw.w1_f, H * f},       {&lw.c1, f},       {&lw.b1_f, f}};
+      for (auto& it : folded)
+        if ((rc = ws_alloc(h, it.p, it.n * e)) != ET_OK) return bail(rc);
+    }
   }
   Workspace& ws = h->ws;
   ws.cap_tokens = round_up(static_cast<size_t>(c.max_batch_size) * c.max_seq_len, 128);
@@ -998,6 +1122,21 @@ int et_set_fused_layernorm(et_handle_t h, int enable) {
   return ET_OK;
 }
 
+int et_set_deferred_layernorm(et_handle_t h, int enable) {
+  if (h == nullptr) return ET_INVALID_ARGUMENT;
+  if (enable != 0 && !defer_eligible(h->cfg))
+    return set_error(h, ET_INVALID_ARGUMENT,
+                     "deferred LayerNorm needs an fp16 handle whose hidden size and ffn_dim are multiples of 256");
+  if (h->defer_ln != (enable != 0)) {
+    DeviceGuard guard(h->cfg.device);
+    cudaDeviceSynchronize();
+    graph_release(h);        // recorded passes hold the other kernel sequence
+    host_graphs_release(h);
+  }
+  h->defer_ln = enable != 0;
+  return ET_OK;
+}
+
 int et_workspace_allocated_bytes(et_handle_t h, size_t* out_bytes) {
   if (h == nullptr || out_bytes == nullptr) return ET_INVALID_ARGUMENT;
   *out_bytes = h->ws_bytes_allocated;
@@ -1040,6 +1179,7 @@ int et_set_layer_weights(et_handle_t h, int layer, const void* const* weights, i
     for (int i = 0; i < 16; ++i) dev[i] = weights[i];
   }
   if (rc == ET_OK) rc = pack_layer_any(h, layer, dev, h->own_stream);
+  if (rc == ET_OK) rc = fold_all(h, h->own_stream);  // once every layer has its weights
   cudaError_t se = cudaStreamSynchronize(h->own_stream);
   for (void* p : temps) cudaFree(p);
   if (rc == ET_OK && se != cudaSuccess) rc = cuda_fail(h, se, "cudaStreamSynchronize");

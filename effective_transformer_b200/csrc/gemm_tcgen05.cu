@@ -195,34 +195,40 @@ __device__ __forceinline__ Vec16 ld_shared_v4(uint32_t addr) {
   return v;
 }
 
+__device__ __forceinline__ uint32_t hfma2_u(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;
+  asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ uint32_t hmul2_u(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint32_t hadd2_u(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("add.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint32_t half2_of(float x) {
+  const __half2 h = __float2half2_rn(x);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
 // What the deferred-LayerNorm epilogues need beside the accumulator.
 struct NormCtx {
-  // kEpiNormIn(Gelu), one row per thread: C = rstd * acc + nm * csum[n] + bias[n], nm = -rstd * mu
-  float rstd = 1.f, nm = 0.f;
-  const __half* csum = nullptr;   // at the warp's first column
+  // kEpiNormIn(Gelu): C = rstd * acc + bias[n] + nm * csum[n], nm = -rstd * mu
+  float rstd = 1.f;               // of this thread's row (TMEM phase)
+  uint32_t nm2_i[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};  // -rstd * mu of rows 4 i + (lane >> 3), as fp16 pairs
+  Vec16 c2[2] = {{0u, 0u, 0u, 0u}, {0u, 0u, 0u, 0u}};     // csum of this lane's eight columns, per 64-column chunk
   // kEpiNormResidual, rows 4 i + (lane >> 3) of the coalesced phase
   float mu_i[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   float rstd_i[8] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f};
-  const __half* gamma = nullptr;  // at the warp's first column; null: ones / zeros
-  const __half* beta = nullptr;
+  // gamma / beta of this lane's eight columns per 64-column chunk, as fp16 pairs (ones / zeros without)
+  Vec16 g2[2] = {{0x3c003c00u, 0x3c003c00u, 0x3c003c00u, 0x3c003c00u}, {0x3c003c00u, 0x3c003c00u, 0x3c003c00u, 0x3c003c00u}};
+  Vec16 be2[2] = {{0u, 0u, 0u, 0u}, {0u, 0u, 0u, 0u}};
   float* stats = nullptr;         // stats_out at (first row of the warp, first 64-column piece of the warp)
   int s2 = 0;                     // floats per row of stats_out
 };
-
-// Row statistics from the partial sums a producer left: (sum, sum of squares) per 64-column piece.
-__device__ __forceinline__ void row_stats(const float* __restrict__ stats, int slots, int width, float eps,
-                                          float& mu, float& rstd) {
-  float s1 = 0.f, s2 = 0.f;
-  for (int j = 0; j < slots; j += 2) {  // slots is even: widths are multiples of 128
-    const float4 v = *reinterpret_cast<const float4*>(stats + 2 * j);
-    s1 += v.x + v.z;
-    s2 += v.y + v.w;
-  }
-  const float inv = 1.0f / static_cast<float>(width);
-  mu = s1 * inv;
-  const float var = fmaxf(s2 * inv - mu * mu, 0.f);
-  rstd = rsqrtf(var + eps);
-}
 
 // v[i] summed over the 8 lanes of a group (lanes 8g .. 8g+7): afterwards v[0] of the lane with
 // piece p (= lane & 7) holds the total of index p.  7 shuffles instead of 24.
@@ -266,11 +272,12 @@ __device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, __half* ctile
 #pragma unroll
       for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[p * 8 + e]);
       if (EPI == kEpiNormIn || EPI == kEpiNormInGelu) {
-        float fb[8], fc[8];
+        // rstd * acc + bias[n] here, one row per thread; the term with the row's mean, nm * csum[n],
+        // is added in the coalesced phase, where a lane keeps the same eight columns for all rows
+        float fb[8];
         VecTraits<__half>::unpack(ld_shared_v4(bias_s + (c * 64 + p * 8) * 2), fb);
-        VecTraits<__half>::unpack(ld_global_nc_v4(nc.csum + c * 64 + p * 8), fc);  // same address in every lane
 #pragma unroll
-        for (int e = 0; e < 8; ++e) f[e] = fmaf(f[e], nc.rstd, fmaf(nc.nm, fc[e], fb[e]));
+        for (int e = 0; e < 8; ++e) f[e] = fmaf(f[e], nc.rstd, fb[e]);
       } else if (EPI != kEpiNone) {
         float fb[8];
         VecTraits<__half>::unpack(ld_shared_v4(bias_s + (c * 64 + p * 8) * 2), fb);
@@ -282,7 +289,7 @@ __device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, __half* ctile
         for (int e = 0; e < 8; ++e) f[e] = tanhf(f[e]);
       }
       Vec16 o = VecTraits<__half>::pack(f);
-      if (EPI == kEpiBiasGelu || EPI == kEpiNormInGelu) {
+      if (EPI == kEpiBiasGelu) {
         o.x = gelu_tanh_half2(o.x);
         o.y = gelu_tanh_half2(o.y);
         o.z = gelu_tanh_half2(o.z);
@@ -291,7 +298,29 @@ __device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, __half* ctile
       st_shared_v4(buf + lane * 128 + ((p ^ (lane & 7)) << 4), o);
     }
     __syncwarp();
-    if (EPI == kEpiNormResidual) {
+    if (EPI == kEpiNormIn || EPI == kEpiNormInGelu) {
+      const int piece = lane & 7, g = lane >> 3;
+      const Vec16 c2 = c == 0 ? nc.c2[0] : nc.c2[1];  // static indices: the array stays in registers
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int rr = 4 * i + g;
+        const Vec16 v = ld_shared_v4(buf + rr * 128 + ((piece ^ (rr & 7)) << 4));
+        if (rr < rows_valid) {
+          Vec16 o;
+          o.x = hfma2_u(nc.nm2_i[i], c2.x, v.x);
+          o.y = hfma2_u(nc.nm2_i[i], c2.y, v.y);
+          o.z = hfma2_u(nc.nm2_i[i], c2.z, v.z);
+          o.w = hfma2_u(nc.nm2_i[i], c2.w, v.w);
+          if (EPI == kEpiNormInGelu) {
+            o.x = gelu_tanh_half2(o.x);
+            o.y = gelu_tanh_half2(o.y);
+            o.z = gelu_tanh_half2(o.z);
+            o.w = gelu_tanh_half2(o.w);
+          }
+          st_global_v4(ctile + static_cast<size_t>(rr) * N + c * 64 + piece * 8, o);
+        }
+      }
+    } else if (EPI == kEpiNormResidual) {
       // The residual is LN(rtile), taken here where a warp instruction covers four whole 128-byte row
       // segments; the statistics of the rows as they are stored go out beside them.
       const int piece = lane & 7, g = lane >> 3;
@@ -301,13 +330,10 @@ __device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, __half* ctile
         const int rr = 4 * i + g;
         if (rr < rows_valid) res[i] = ld_global_nc_v4(rtile + static_cast<size_t>(rr) * N + c * 64 + piece * 8);
       }
-      float fg[8], fbeta[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) fg[e] = 1.f, fbeta[e] = 0.f;
-      if (nc.gamma != nullptr) {
-        VecTraits<__half>::unpack(ld_global_nc_v4(nc.gamma + c * 64 + piece * 8), fg);
-        VecTraits<__half>::unpack(ld_global_nc_v4(nc.beta + c * 64 + piece * 8), fbeta);
-      }
+      // gamma, beta of this lane's eight columns as fp16 pairs (fetched before the accumulator
+      // arrived); the LayerNorm of the residual runs on pairs too: y = res * t + (beta - mu * t),
+      // t = rstd * gamma
+      const Vec16 g2 = c == 0 ? nc.g2[0] : nc.g2[1], be2 = c == 0 ? nc.be2[0] : nc.be2[1];
       float s1[8], s2[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
@@ -315,16 +341,18 @@ __device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, __half* ctile
         const Vec16 v = ld_shared_v4(buf + rr * 128 + ((piece ^ (rr & 7)) << 4));
         s1[i] = 0.f, s2[i] = 0.f;
         if (rr < rows_valid) {
-          float fv[8], fr[8], fx[8];
-          VecTraits<__half>::unpack(v, fv);
-          VecTraits<__half>::unpack(res[i], fr);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const float t = nc.rstd_i[i] * fg[e];
-            fv[e] += fmaf(fr[e], t, fmaf(-nc.mu_i[i], t, fbeta[e]));
+          const uint32_t r2 = half2_of(nc.rstd_i[i]), nmu2 = half2_of(-nc.mu_i[i]);
+          Vec16 o;
+          {
+            const uint32_t tx = hmul2_u(r2, g2.x), ty = hmul2_u(r2, g2.y), tz = hmul2_u(r2, g2.z),
+                           tw = hmul2_u(r2, g2.w);
+            o.x = hadd2_u(v.x, hfma2_u(res[i].x, tx, hfma2_u(nmu2, tx, be2.x)));
+            o.y = hadd2_u(v.y, hfma2_u(res[i].y, ty, hfma2_u(nmu2, ty, be2.y)));
+            o.z = hadd2_u(v.z, hfma2_u(res[i].z, tz, hfma2_u(nmu2, tz, be2.z)));
+            o.w = hadd2_u(v.w, hfma2_u(res[i].w, tw, hfma2_u(nmu2, tw, be2.w)));
           }
-          const Vec16 o = VecTraits<__half>::pack(fv);
           st_global_v4(ctile + static_cast<size_t>(rr) * N + c * 64 + piece * 8, o);
+          float fx[8];
           VecTraits<__half>::unpack(o, fx);  // the statistics are those of the stored values
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
@@ -852,6 +880,28 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       return any;
     };
 
+    // Deferred-LayerNorm variants: the partial sums of one row, (sum, sum of squares) per 64-column
+    // piece, as they come from memory; which row depends on the phase that uses them (see below).
+    constexpr bool kDeferred = kBase == kEpiNormIn || kBase == kEpiNormInGelu || kBase == kEpiNormResidual;
+    constexpr int kStatVecs = VPL > 0 ? VPL : 1;  // float4s of a row's partial sums: width / 128 (the launcher's VPL)
+    float4 raw[kDeferred ? kStatVecs : 1];
+    auto stat_row = [&](const PairUnit& pu) {
+      const int r0 = pu.m_tile * BM2 + static_cast<int>(rank) * BM + quad * 32;
+      return kBase == kEpiNormResidual ? r0 + 4 * (lane & 7) + (lane >> 3) : r0 + lane;
+    };
+    auto request_stats = [&](int u) {
+      if constexpr (kDeferred) {
+        if (ln.stats_in == nullptr || u >= num_units) return;
+        const int row = stat_row(pair_unit(u, full_tiles, n_tiles, m_tiles, reverse_m));
+        if (row >= M) return;
+        const float4* p = reinterpret_cast<const float4*>(ln.stats_in + static_cast<size_t>(row) * (2 * ln.stat_slots));
+#pragma unroll
+        for (int j = 0; j < kStatVecs; ++j)
+          if (2 * j < ln.stat_slots) raw[j] = p[j];
+      }
+    };
+    request_stats(pair_id);
+
     int it = 0;
     for (int u = pair_id; u < num_units; u += num_pairs, ++it) {
       const PairUnit pu = pair_unit(u, full_tiles, n_tiles, m_tiles, reverse_m);
@@ -863,6 +913,54 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if (kBase != kEpiNone) {
         if (lane < wcols / 8) st_shared_v4(bias_s + lane * 16, ld_global_v4(bias + col0 + lane * 8));
         __syncwarp();
+      }
+      // The row statistics of this unit were requested a unit ago (the loads are a global-memory
+      // latency that would otherwise sit in front of every epilogue: the K = H projections leave the
+      // epilogue warps no slack); reduce them now and request the next unit's.
+      const int row0 = m_tile * BM2 + static_cast<int>(rank) * BM + quad * 32;
+      NormCtx nc;
+      if constexpr (kDeferred) {
+        float mu = 0.f, rstd = 1.f;
+        if (ln.stats_in != nullptr && stat_row(pu) < M) {
+          float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+          for (int j = 0; j < kStatVecs; ++j)
+            if (2 * j < ln.stat_slots) {
+              s1 += raw[j].x + raw[j].z;
+              s2 += raw[j].y + raw[j].w;
+            }
+          const float inv = 1.0f / static_cast<float>(kBase == kEpiNormResidual ? N : K);
+          mu = s1 * inv;
+          rstd = rsqrtf(fmaxf(s2 * inv - mu * mu, 0.f) + ln.eps);
+        }
+        request_stats(u + num_pairs);
+        if constexpr (kBase == kEpiNormResidual) {
+          // lane (g, piece) worked out the statistics of residual row 4 * piece + g; the coalesced
+          // phase needs those of rows 4 i + g, which the lanes of its own group hold
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            nc.mu_i[i] = __shfl_sync(0xffffffffu, mu, (lane & ~7) + i);
+            nc.rstd_i[i] = __shfl_sync(0xffffffffu, rstd, (lane & ~7) + i);
+          }
+          if (ln.gamma != nullptr) {
+            nc.g2[0] = ld_global_nc_v4(ln.gamma + col0 + (lane & 7) * 8);
+            nc.be2[0] = ld_global_nc_v4(ln.beta + col0 + (lane & 7) * 8);
+            if (wcols > 64) {
+              nc.g2[1] = ld_global_nc_v4(ln.gamma + col0 + 64 + (lane & 7) * 8);
+              nc.be2[1] = ld_global_nc_v4(ln.beta + col0 + 64 + (lane & 7) * 8);
+            }
+          }
+          nc.s2 = 2 * (N / 64);
+          nc.stats = ln.stats_out + static_cast<size_t>(row0) * nc.s2 + 2 * (col0 / 64);
+        } else {
+          // this thread's row of A is normalised on the way out
+          nc.rstd = rstd;
+          const float nm = -rstd * mu;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) nc.nm2_i[i] = half2_of(__shfl_sync(0xffffffffu, nm, 4 * i + (lane >> 3)));
+          nc.c2[0] = ld_global_nc_v4(ln.csum + col0 + (lane & 7) * 8);
+          if (wcols > 64) nc.c2[1] = ld_global_nc_v4(ln.csum + col0 + 64 + (lane & 7) * 8);
+        }
       }
       bool got;
       if constexpr (kLn) {
@@ -892,7 +990,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         break;
       }
       tc_fence_after();
-      const int row0 = m_tile * BM2 + static_cast<int>(rank) * BM + quad * 32;
       const uint32_t t_row =
           tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN + half * wcols;
       __half* ctile = C + static_cast<size_t>(row0) * N + col0;
@@ -900,35 +997,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const __half* rtile = (kBase == kEpiBiasResidual || kBase == kEpiNormResidual)
                                 ? residual + static_cast<size_t>(row0) * N + col0
                                 : nullptr;
-      NormCtx nc;
-      if constexpr (kBase == kEpiNormIn || kBase == kEpiNormInGelu) {
-        // this thread's row of A is normalised on the way out: its statistics, once per tile
-        const int row = row0 + lane;
-        float mu = 0.f, rstd = 1.f;
-        if (ln.stats_in != nullptr && row < M)
-          row_stats(ln.stats_in + static_cast<size_t>(row) * (2 * ln.stat_slots), ln.stat_slots, K, ln.eps, mu, rstd);
-        nc.rstd = rstd;
-        nc.nm = -rstd * mu;
-        nc.csum = ln.csum + col0;
-      }
-      if constexpr (kBase == kEpiNormResidual) {
-        // lane (g, piece) works out the statistics of residual row 4 * piece + g; the coalesced phase
-        // needs those of rows 4 i + g, which the lanes of its own group hold
-        const int rr = 4 * (lane & 7) + (lane >> 3);
-        float mu = 0.f, rstd = 1.f;
-        if (ln.stats_in != nullptr && row0 + rr < M)
-          row_stats(ln.stats_in + static_cast<size_t>(row0 + rr) * (2 * ln.stat_slots), ln.stat_slots, N, ln.eps, mu,
-                    rstd);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          nc.mu_i[i] = __shfl_sync(0xffffffffu, mu, (lane & ~7) + i);
-          nc.rstd_i[i] = __shfl_sync(0xffffffffu, rstd, (lane & ~7) + i);
-        }
-        nc.gamma = ln.gamma != nullptr ? ln.gamma + col0 : nullptr;
-        nc.beta = ln.beta != nullptr ? ln.beta + col0 : nullptr;
-        nc.s2 = 2 * (N / 64);
-        nc.stats = ln.stats_out + static_cast<size_t>(row0) * nc.s2 + 2 * (col0 / 64);
-      }
       epilogue_warp_tile<kBase>(t_row, ctile, N, M - row0, bias_s, buf, lane, wcols / 64, rtile, [&] {
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(empty0);
@@ -1099,6 +1167,29 @@ cudaError_t launch_pair_ln(const CUtensorMap& ta, const CUtensorMap& tb, const C
 #undef ETB_LN_CASE
 }
 
+// Deferred-LayerNorm variants: one instantiation per width of the normalised rows (width / 128 float4s
+// of partial sums per row; widths up to 1024, the limit of the fp16 handle's LayerNorm anyway).
+template <int EPI>
+cudaError_t launch_pair_norm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tbh,
+                             const __half* bias, const __half* residual, __half* c, const int* m_ptr, int max_m,
+                             int n, int k, int* status_word, int reverse_m, const GemmLayerNorm& ln,
+                             cudaStream_t stream) {
+#define ETB_NORM_CASE(V)                                                                                          \
+  case V:                                                                                                         \
+    return launch_pair_epi<EPI, V>(ta, tb, tbh, bias, residual, c, m_ptr, max_m, n, k, status_word, reverse_m, ln, \
+                                   stream)
+  const int width = EPI == kEpiNormResidual ? n : k;
+  switch (width / 128) {
+    ETB_NORM_CASE(2);
+    ETB_NORM_CASE(4);
+    ETB_NORM_CASE(6);
+    ETB_NORM_CASE(8);
+    default:
+      return cudaErrorInvalidValue;
+  }
+#undef ETB_NORM_CASE
+}
+
 cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tbh,
                         const __half* bias, const __half* residual, __half* c,
                         const int* m_ptr, int max_m, int n, int k, int epilogue, int* status_word,
@@ -1113,9 +1204,15 @@ cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUte
     ETB_PAIR_CASE(kEpiBiasGelu);
     ETB_PAIR_CASE(kEpiBiasTanh);
     ETB_PAIR_CASE(kEpiBiasResidual);
-    ETB_PAIR_CASE(kEpiNormIn);
-    ETB_PAIR_CASE(kEpiNormInGelu);
-    ETB_PAIR_CASE(kEpiNormResidual);
+    case kEpiNormIn:
+      return launch_pair_norm<kEpiNormIn>(ta, tb, tbh, bias, residual, c, m_ptr, max_m, n, k, status_word, reverse_m,
+                                          ln, stream);
+    case kEpiNormInGelu:
+      return launch_pair_norm<kEpiNormInGelu>(ta, tb, tbh, bias, residual, c, m_ptr, max_m, n, k, status_word,
+                                              reverse_m, ln, stream);
+    case kEpiNormResidual:
+      return launch_pair_norm<kEpiNormResidual>(ta, tb, tbh, bias, residual, c, m_ptr, max_m, n, k, status_word,
+                                                reverse_m, ln, stream);
     case kEpiResidualLayerNorm:
       return launch_pair_ln<kEpiResidualLayerNorm>(ta, tb, tbh, bias, residual, c, m_ptr, max_m, n, k, status_word,
                                                    reverse_m, ln, stream);
@@ -1247,8 +1344,9 @@ cudaError_t launch_gemm_tcgen05(const __half* a, const __half* w_packed, const _
     // the pair kernel only; statistics in 64-column pieces of rows whose width is a multiple of 128
     if (ln == nullptr || (n % 256) != 0) return cudaErrorInvalidValue;
     const int width = epilogue == kEpiNormResidual ? n : k;  // of the tensor the statistics describe
+    if ((width % 256) != 0 || width > 1024) return cudaErrorInvalidValue;
     if (ln->stats_in != nullptr &&
-        (ln->stat_slots != width / 64 || (width % 128) != 0 || (reinterpret_cast<uintptr_t>(ln->stats_in) & 15u)))
+        (ln->stat_slots != width / 64 || (reinterpret_cast<uintptr_t>(ln->stats_in) & 15u)))
       return cudaErrorInvalidValue;
     if (epilogue == kEpiNormResidual) {
       if (ln->stats_out == nullptr || (reinterpret_cast<uintptr_t>(ln->stats_out) & 7u)) return cudaErrorInvalidValue;

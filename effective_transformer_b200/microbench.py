@@ -170,6 +170,24 @@ def main() -> None:
             w, wp, kk, nn = weights[name]
             return lambda: lib.et_gemm_fused(P(a), P(wp), P(bias_h), P(res), P(gamma_h), P(beta_h), 1e-6, P(counters),
                                              P(fused_out), P(tn), n_pos, nn, kk, epi, P(status), st)
+        # the projections with the LayerNorm deferred into them (et_gemm_deferred_norm): 7 / 8 consume
+        # LN(A) from A's row statistics and folded weights, 9 adds LN(residual) on the fly and leaves
+        # the statistics of its output rows
+        rows_cap = (n_pos + 255) // 256 * 256
+        stats_in = torch.rand(rows_cap, 2 * (h // 64), device=dev, dtype=torch.float32) + 64.0
+        stats_out = torch.empty(rows_cap, 2 * (h // 64), device=dev, dtype=torch.float32)
+        csum = rnd(max(3 * h, f))
+
+        def deferred(name, a, epi, resid):
+            w, wp, kk, nn = weights[name]
+            bias_n = bias3 if nn == 3 * h else (bias_f if nn == f else bias_h)
+            return lambda: lib.et_gemm_deferred_norm(P(a), P(wp), P(bias_n), P(csum), P(resid), P(gamma_h), P(beta_h),
+                                                     1e-6, P(stats_in), P(stats_out), P(gemm_out), P(tn), n_pos, nn, kk,
+                                                     epi, P(status), st)
+        kernels["gemm_qkv_deferred_ln"] = (deferred("gemm_qkv", x_packed, 7, None), "tensor", 2.0 * t * h * 3 * h)
+        kernels["gemm_ffn1_deferred_ln"] = (deferred("gemm_ffn1", x_packed, 8, None), "tensor", 2.0 * t * h * f)
+        kernels["gemm_attn_out_deferred_ln"] = (deferred("gemm_attn_out", x_packed, 9, res), "tensor", 2.0 * t * h * h)
+        kernels["gemm_ffn2_deferred_ln"] = (deferred("gemm_ffn2", ffn, 9, res), "tensor", 2.0 * t * h * f)
         kernels["gemm_ffn2_residual"] = (fused("gemm_ffn2", ffn, 4), "tensor", 2.0 * t * h * f)
         kernels["gemm_ffn2_layernorm"] = (fused("gemm_ffn2", ffn, 5), "tensor", 2.0 * t * h * f)
         kernels["gemm_attn_out_layernorm"] = (fused("gemm_attn_out", x_packed, 6), "tensor", 2.0 * t * h * h)

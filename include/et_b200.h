@@ -314,6 +314,14 @@ int et_set_debug_simt(et_handle_t handle, int use_simt);
  * arithmetic in the same order).  Measured on B200 it is slower at the benchmark
  * sizes, which is why it is opt-in.  Changing the setting drops recorded graphs. */
 int et_set_fused_layernorm(et_handle_t handle, int enable);
+/* enable != 0: inside the whole-stack calls (et_forward*, the graph and host-buffer
+ * calls) no LayerNorm between the projections is materialised: the two
+ * hidden-wide projections leave x + sublayer(x) and its row statistics, the
+ * projections behind them run on weights with the LayerNorm's gamma folded in
+ * (et_gemm_deferred_norm below), and only the last layer's LayerNorm runs as a
+ * kernel: 5 launches per layer + 1 instead of 7.  fp16 handles whose hidden size
+ * and ffn_dim are multiples of 256; et_layer always materialises its output. */
+int et_set_deferred_layernorm(et_handle_t handle, int enable);
 
 /* Chunking of the host-buffer call (et_forward_host): number of chunks, share of
  * a middle chunk when the first and the last have 1 (0: the handle found that

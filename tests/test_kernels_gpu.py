@@ -576,8 +576,9 @@ def _deferred_consumer_case(m, cap, n, k, gelu, with_stats, seed=0):
 
 @pytest.mark.parametrize("gelu", [False, True])
 @pytest.mark.parametrize("with_stats", [True, False])
-@pytest.mark.parametrize("m,cap,n,k", [(1, 1, 256, 128), (134, 256, 2304, 768), (257, 300, 3072, 768),
-                                       (1000, 1000, 1024, 1024), (0, 64, 768, 128), (6500, 6500, 768, 768)])
+@pytest.mark.parametrize("m,cap,n,k", [(1, 1, 256, 256), (134, 256, 2304, 768), (257, 300, 3072, 768),
+                                       (1000, 1000, 1024, 1024), (0, 64, 768, 256), (6500, 6500, 768, 768),
+                                       (300, 300, 512, 512)])
 def test_gemm_tcgen05_projection_of_a_layernorm_that_is_not_materialised(m, cap, n, k, gelu, with_stats):
     _deferred_consumer_case(m, cap, n, k, gelu, with_stats)
 

@@ -369,6 +369,52 @@ def test_layernorm_inside_the_gemm_equals_the_layernorm_kernel():
     eng.close()
 
 
+@pytest.mark.parametrize("cfg,ln_params", [(1, "benchmark"), (4, "benchmark"), (1, "random")])
+def test_deferred_layernorm_meets_the_oracle_and_the_layernorm_kernels(cfg, ln_params):
+    """et_set_deferred_layernorm: no LayerNorm between the projections is materialised (row statistics
+    from the producers, gamma folded into the consumers' weights).  With the benchmark's LayerNorm
+    parameters (gamma = 1, beta = 0): the gates of the header, as for the path with LayerNorm kernels.
+    With gamma, beta drawn away from 1, 0 the activations grow heavy tails (|y| up to 20, where one fp16
+    step is 0.016) and the path with LayerNorm kernels itself reaches 0.06: there the mean gate holds
+    and the deferred path may not be worse than the other by more than a step of the largest value."""
+    spec = W.WORKLOADS[cfg]
+    wl = W.make_workload(spec, batch_override=72 if cfg == 4 else None)
+    if ln_params == "random":
+        rng = np.random.RandomState(5)
+        for l in range(spec.shape.num_layers):        # beta, gamma of both LayerNorms: arrays 8, 9, 14, 15
+            for i in (8, 14):
+                wl.weights[16 * l + i] = (0.1 * rng.randn(spec.shape.hidden)).astype(np.float32)
+            for i in (9, 15):
+                wl.weights[16 * l + i] = (1 + 0.2 * rng.randn(spec.shape.hidden)).astype(np.float32)
+    eng = make_engine(spec, wl)
+    y_ln = run_forward(eng, wl).clone()
+    eng.set_deferred_layernorm(True)
+    y_def = run_forward(eng, wl).clone()
+    ref = oracle_valid(wl, spec).double()
+    err_ln = (O.valid_rows(y_ln.cpu().double(), wl.mask) - ref).abs()
+    err_def = (O.valid_rows(y_def.cpu().double(), wl.mask) - ref).abs()
+    if ln_params == "benchmark":
+        assert_parity(y_ln, ref, wl.mask, fp16=True)
+        assert_parity(y_def, ref, wl.mask, fp16=True)
+    else:
+        assert float(err_ln.mean()) <= FP16_MEAN_ABS and float(err_def.mean()) <= FP16_MEAN_ABS
+        assert float(err_def.max()) <= float(err_ln.max()) + 2e-2, (float(err_def.max()), float(err_ln.max()))
+    # twice the same answer, and the replayed pass equals the eager one
+    y_again = run_forward(eng, wl)
+    assert torch.equal(y_again, y_def)
+    x = torch.from_numpy(wl.from_tensor).to(eng.dtype).cuda()
+    m = torch.from_numpy(wl.mask).cuda()
+    out = torch.empty_like(x)
+    eng.capture(x, m, out)
+    eng.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, y_def)
+    # back to the LayerNorm kernels
+    eng.set_deferred_layernorm(False)
+    assert torch.equal(run_forward(eng, wl), y_ln)
+    eng.close()
+
+
 def test_failed_general_mask_call_does_not_poison_the_next_call():
     """et_layer in general-mask mode that returns early (weights of that layer missing) must leave
     the handle in key-only mode: the next plain call gives the plain result."""
