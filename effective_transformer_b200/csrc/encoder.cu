@@ -204,7 +204,7 @@ struct et_handle_s {
   // materialised; producers leave row statistics, consumers run on folded weights (gemm_tcgen05.cu,
   // kEpiNorm*).  folded_ready: the folded weights match the layers' current weights.
   // defer_active: the stack being enqueued runs that way (set by stack_impl for run_layer).
-  bool defer_ln = false;
+  bool defer_ln = true;   // used where the configuration allows it (defer_eligible)
   bool folded_ready = false;
   bool defer_active = false;
   TensorMapCache maps;  // TMA descriptors of this handle's launches
@@ -731,7 +731,8 @@ int stack_impl(et_handle_t h, int batch, int seq, cudaStream_t s) {
               launch_position_rows(ws.batch_idx, ws.word_idx, ws.valid_word_num, batch, seq, ws.pos_row, s));
   // No LayerNorm between the projections: x holds un-normalised sums from the first layer's end on,
   // and the last layer's LayerNorm is the one kernel that runs, behind the loop.
-  h->defer_active = h->defer_ln && h->folded_ready && !h->use_simt && defer_eligible(h->cfg) && max_m > 0;
+  h->defer_active =
+      h->defer_ln && !h->fuse_ln && h->folded_ready && !h->use_simt && defer_eligible(h->cfg) && max_m > 0;
   for (int l = 0; l < h->cfg.num_layers; ++l) {
     if (h->cfg.dtype == ET_FP16)
       rc = run_layer<__half>(h, h->layers[l], static_cast<const __half*>(ws.x), static_cast<__half*>(ws.x),

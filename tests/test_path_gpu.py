@@ -326,7 +326,7 @@ def test_two_handles_and_two_streams_do_not_share_state():
 
 
 def test_layernorm_inside_the_gemm_equals_the_layernorm_kernel():
-    """cfg1 (hidden 768, 12 layers): with a LayerNorm kernel behind each projection (default) and
+    """cfg1 (hidden 768, 12 layers): with a LayerNorm kernel behind each projection and
     with the LayerNorms inside the projection kernels the path launches 7 and 5 kernels per layer,
     computes the same arithmetic in the same order (a kernel-level test shows single last-place
     differences where the compiler contracts a multiply-add in one kernel and not in the other;
@@ -334,6 +334,7 @@ def test_layernorm_inside_the_gemm_equals_the_layernorm_kernel():
     spec = W.WORKLOADS[1]
     wl = W.make_workload(spec, random_gamma_beta=True)
     eng = make_engine(spec, wl)
+    eng.set_deferred_layernorm(False)     # the default materialises no LayerNorm at all
     eng.get_profile(reset=True)
     y_split = run_forward(eng, wl).clone()
     prof = eng.get_profile(reset=True)
@@ -387,9 +388,14 @@ def test_deferred_layernorm_meets_the_oracle_and_the_layernorm_kernels(cfg, ln_p
             for i in (9, 15):
                 wl.weights[16 * l + i] = (1 + 0.2 * rng.randn(spec.shape.hidden)).astype(np.float32)
     eng = make_engine(spec, wl)
+    eng.set_deferred_layernorm(False)
     y_ln = run_forward(eng, wl).clone()
     eng.set_deferred_layernorm(True)
+    eng.get_profile(reset=True)
     y_def = run_forward(eng, wl).clone()
+    prof = eng.get_profile(reset=True)
+    assert prof["layernorm"][1] == 1                      # the last layer's, behind the stack
+    assert sum(v[1] for v in prof.values()) == 5 + 5 * spec.shape.num_layers + 1
     ref = oracle_valid(wl, spec).double()
     err_ln = (O.valid_rows(y_ln.cpu().double(), wl.mask) - ref).abs()
     err_def = (O.valid_rows(y_def.cpu().double(), wl.mask) - ref).abs()
