@@ -533,12 +533,18 @@ def main():
                                     "in the forward pass" % (spec.batch, world)) if scaling == "strong" and world > 1
                                    else "sequences, token-balanced, no collective",
                        "l2": "256 MB buffer written between timed steps (untimed)",
-                       "layernorm": "inside the projection kernels" if args.fused_layernorm
-                                    else "LayerNorm kernels behind the projections",
+                       "layernorm": ("inside the projection kernels" if args.fused_layernorm
+                                     else "LayerNorm kernels behind the projections" if args.deferred_layernorm == 0
+                                     else "deferred: row statistics from the producing projection, gamma folded "
+                                          "into the consuming one, one LayerNorm kernel behind the last layer"
+                                     if fp16 else "LayerNorm kernels behind the projections"),
                        "launch": ("cuda-graph replay (et_graph_launch); per-kernel times from a second, eager pass"
                                   if args.launch == "graph"
                                   else "eager (et_forward), per-kernel events inside the timed steps")},
-            "roofline": roofline_of(main_pass, prof, args.steps, peaks, peak_src, dev, spec.name),
+            "roofline": dict(roofline_of(main_pass, prof, args.steps, peaks, peak_src, dev, spec.name),
+                             # the whole step against the same peak: projections' FLOPs / the step's time
+                             step_frac=(main_pass.gemm_flops() / (ms_per_step / 1000.0) / 1e12 /
+                                        peaks["bf16_tflops_sustained"]) if fp16 and ms_per_step > 0 else None),
             "kernels": {k: {"ms_per_step": v[0] / args.steps, "launches_per_step": v[1] / args.steps}
                         for k, v in prof.items()},
             "gpu_launches": sum(v[1] for v in prof.values()),
@@ -627,6 +633,12 @@ def roofline_of(p: DevicePass, prof, steps, peaks, peak_src, dev, workload_name)
         out.update({"traffic": None, "kernel": "gemm_tf32x3_pair_kernel (+ split_tf32_kernel)",
                     "tf32_matmul_tflops_measured_here": tf32,
                     "cublas_sgemm_tflops_measured_here": measure_matmul_tflops(dev, tf32=False, iters=3)})
+    ln_launches = prof.get("layernorm", (0.0, 0))[1] / max(steps, 1)
+    if p.fp16 and ln_launches <= 1.5:
+        # the default of fp16 handles: the projections' epilogues also do the LayerNorms' work (row
+        # statistics, normalised residuals), so the launches timed here are longer than a bare GEMM's
+        out["note"] = ("no LayerNorm kernel between the projections: their work is inside these launches "
+                       "(bench.py --deferred-layernorm 0 times the projections with LayerNorm kernels beside them)")
     out.update({"peak": peak_tf, "frac": (achieved / peak_tf) if (achieved and peak_tf) else None,
                 "algorithmic_flops_per_launch": flops_step / max(gemm_launches / steps, 1),
                 "launches_per_step": gemm_launches / steps,

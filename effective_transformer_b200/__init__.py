@@ -103,13 +103,14 @@ class EffectiveTransformer:
         _capi.check(self._lib.et_set_debug_simt(self._h, 1 if on else 0), self._h)
 
     def set_fused_layernorm(self, on: bool) -> None:
-        """Off (default): a LayerNorm kernel behind each hidden-wide projection (7 launches per
-        layer); on: bias + residual + LayerNorm run inside those projection kernels (5)."""
+        """On: bias + residual + LayerNorm run inside the two hidden-wide projection kernels, on
+        their own output rows (5 launches per layer); takes precedence over the deferred LayerNorm."""
         _capi.check(self._lib.et_set_fused_layernorm(self._h, 1 if on else 0), self._h)
 
     def set_deferred_layernorm(self, on: bool) -> None:
-        """On: the whole-stack calls materialise no LayerNorm between the projections (producers
-        leave row statistics, consumers run on folded weights); only the last one runs as a kernel."""
+        """On (default where the widths allow it): the whole-stack calls materialise no LayerNorm
+        between the projections (producers leave row statistics, consumers run on folded weights);
+        only the last one runs as a kernel.  Off: a LayerNorm kernel behind each hidden-wide projection."""
         _capi.check(self._lib.et_set_deferred_layernorm(self._h, 1 if on else 0), self._h)
 
     def workspace_bytes(self, batch_size: int, seq_len: int) -> int:

@@ -305,22 +305,26 @@ int et_copy_to_host(void* dst_host, const void* src_device, size_t bytes, void* 
  * (plain fp32 FMA arithmetic; for debugging and as a second opinion). */
 int et_set_debug_simt(et_handle_t handle, int use_simt);
 
-/* 0 (default): one add_bias_input_layernorm kernel behind the attention-output
- * and the second feed-forward projection, as in the reference
- * (tf_op/bert_transformer_op.cu.cc:211-213,242-246): 7 launches per layer.
+/* 0 (default): no LayerNorm inside a projection kernel's own output rows (see
+ * et_set_deferred_layernorm for what runs instead).
  * 1 (fp16 handles with hidden a multiple of 256 up to 1024): both LayerNorms run
  * inside the projection kernels (et_gemm_fused epilogues 6 and 5): 5 launches per
  * layer and no pre-LayerNorm tensor read back from HBM.  Same results (the same
  * arithmetic in the same order).  Measured on B200 it is slower at the benchmark
  * sizes, which is why it is opt-in.  Changing the setting drops recorded graphs. */
 int et_set_fused_layernorm(et_handle_t handle, int enable);
-/* enable != 0: inside the whole-stack calls (et_forward*, the graph and host-buffer
+/* 1 (default on fp16 handles whose hidden size and ffn_dim are multiples of 256):
+ * inside the whole-stack calls (et_forward*, the graph and host-buffer
  * calls) no LayerNorm between the projections is materialised: the two
  * hidden-wide projections leave x + sublayer(x) and its row statistics, the
  * projections behind them run on weights with the LayerNorm's gamma folded in
  * (et_gemm_deferred_norm below), and only the last layer's LayerNorm runs as a
- * kernel: 5 launches per layer + 1 instead of 7.  fp16 handles whose hidden size
- * and ffn_dim are multiples of 256; et_layer always materialises its output. */
+ * kernel: 5 launches per layer + 1 instead of 7.  et_layer always materialises
+ * its output.  0, fp32 handles and the other widths: one add_bias_input_layernorm
+ * kernel behind the attention-output and the second feed-forward projection, as
+ * in the reference (tf_op/bert_transformer_op.cu.cc:211-213,242-246).
+ * et_set_fused_layernorm(1) takes precedence.  Changing the setting drops
+ * recorded graphs. */
 int et_set_deferred_layernorm(et_handle_t handle, int enable);
 
 /* Chunking of the host-buffer call (et_forward_host): number of chunks, share of
