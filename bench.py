@@ -24,7 +24,9 @@ the figure with 1000 sequences per GPU is reported beside it under "weak".
             et_forward_ids_host: embeddings of the valid tokens, the stack and the
             pooler; 12 bytes per position go up, the pooled [B,H] rows come back
   roofline  the tcgen05 GEMM (the dominant kernel): algorithmic FLOPs / CUDA-
-            event time of its launches in an eager pass over the same steps
+            event time of its launches in an eager pass over the same steps.  On fp16
+            handles those launches also carry the layers' LayerNorms (none runs as a
+            kernel): `step_frac` = the same FLOPs over the whole step's time
   gather    N > 1: the optional gather of the shard outputs to rank 0 over NVLink
             (NCCL send/recv into a local buffer, then the batch order restored), timed
             separately and outside `value`
