@@ -217,9 +217,13 @@ __device__ __forceinline__ uint32_t half2_of(float x) {
 // What the deferred-LayerNorm epilogues need beside the accumulator.
 struct NormCtx {
   // kEpiNormIn(Gelu): C = rstd * acc + bias[n] + nm * csum[n], nm = -rstd * mu
-  float rstd = 1.f;               // of this thread's row (TMEM phase)
-  uint32_t nm2_i[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};  // -rstd * mu of rows 4 i + (lane >> 3), as fp16 pairs
-  Vec16 c2[2] = {{0u, 0u, 0u, 0u}, {0u, 0u, 0u, 0u}};     // csum of this lane's eight columns, per 64-column chunk
+  // The whole epilogue runs in the TMEM phase, one row per thread, with bias and csum of the chunk's 64
+  // columns side by side in the warp's 256 staging bytes.
+  float rstd = 1.f;               // of this thread's row
+  uint32_t nm2_own = 0u;          // -rstd * mu of this thread's row, as an fp16 pair
+  const __half* bias_g = nullptr; // bias / csum at the warp's first column
+  const __half* csum_g = nullptr;
+  Vec16 stage0 = {0u, 0u, 0u, 0u};  // lanes 0-7: bias, lanes 8-15: csum of chunk 0 (requested before the accumulator wait)
   // kEpiNormResidual, rows 4 i + (lane >> 3) of the coalesced phase
   float mu_i[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   float rstd_i[8] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f};
@@ -255,11 +259,18 @@ template <int EPI, typename Release>
 __device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, __half* ctile, int N, int rows_valid,
                                                    uint32_t bias_s, uint32_t buf, int lane, int chunks,
                                                    const __half* rtile, Release release, const NormCtx& nc = NormCtx()) {
+  Vec16 staged = nc.stage0;
 #pragma unroll 1
   for (int c = 0; c < chunks; ++c) {
     uint32_t r[64];
     tmem_ld_32x32b_x32(t_row + c * 64, r);
     tmem_ld_32x32b_x32(t_row + c * 64 + 32, r + 32);
+    if (EPI == kEpiNormIn || EPI == kEpiNormInGelu) {
+      if (lane < 16) st_shared_v4(bias_s + lane * 16, staged);
+      if (c + 1 < chunks && lane < 16)  // the next chunk's, under this chunk's work
+        staged = ld_global_nc_v4((lane < 8 ? nc.bias_g : nc.csum_g) + (c + 1) * 64 + (lane & 7) * 8);
+      __syncwarp();
+    }
     tmem_ld_wait();
     if (c == chunks - 1) {
       // the accumulator now lives in registers: hand the TMEM buffer back
@@ -272,12 +283,26 @@ __device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, __half* ctile
 #pragma unroll
       for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[p * 8 + e]);
       if (EPI == kEpiNormIn || EPI == kEpiNormInGelu) {
-        // rstd * acc + bias[n] here, one row per thread; the term with the row's mean, nm * csum[n],
-        // is added in the coalesced phase, where a lane keeps the same eight columns for all rows
-        float fb[8];
-        VecTraits<__half>::unpack(ld_shared_v4(bias_s + (c * 64 + p * 8) * 2), fb);
+        // rstd * acc + bias[n] + nm * csum[n] (then the GELU): the scaling in fp32, the two sums on
+        // fp16 pairs; bias and csum of the chunk's columns lie side by side in the warp's staging bytes
+        const Vec16 b2 = ld_shared_v4(bias_s + p * 16);
+        const Vec16 c2 = ld_shared_v4(bias_s + 128 + p * 16);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) f[e] = fmaf(f[e], nc.rstd, fb[e]);
+        for (int e = 0; e < 8; ++e) f[e] *= nc.rstd;
+        const Vec16 a2 = VecTraits<__half>::pack(f);
+        Vec16 o;
+        o.x = hfma2_u(nc.nm2_own, c2.x, hadd2_u(a2.x, b2.x));
+        o.y = hfma2_u(nc.nm2_own, c2.y, hadd2_u(a2.y, b2.y));
+        o.z = hfma2_u(nc.nm2_own, c2.z, hadd2_u(a2.z, b2.z));
+        o.w = hfma2_u(nc.nm2_own, c2.w, hadd2_u(a2.w, b2.w));
+        if (EPI == kEpiNormInGelu) {
+          o.x = gelu_tanh_half2(o.x);
+          o.y = gelu_tanh_half2(o.y);
+          o.z = gelu_tanh_half2(o.z);
+          o.w = gelu_tanh_half2(o.w);
+        }
+        st_shared_v4(buf + lane * 128 + ((p ^ (lane & 7)) << 4), o);
+        continue;
       } else if (EPI != kEpiNone) {
         float fb[8];
         VecTraits<__half>::unpack(ld_shared_v4(bias_s + (c * 64 + p * 8) * 2), fb);
@@ -298,29 +323,7 @@ __device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, __half* ctile
       st_shared_v4(buf + lane * 128 + ((p ^ (lane & 7)) << 4), o);
     }
     __syncwarp();
-    if (EPI == kEpiNormIn || EPI == kEpiNormInGelu) {
-      const int piece = lane & 7, g = lane >> 3;
-      const Vec16 c2 = c == 0 ? nc.c2[0] : nc.c2[1];  // static indices: the array stays in registers
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int rr = 4 * i + g;
-        const Vec16 v = ld_shared_v4(buf + rr * 128 + ((piece ^ (rr & 7)) << 4));
-        if (rr < rows_valid) {
-          Vec16 o;
-          o.x = hfma2_u(nc.nm2_i[i], c2.x, v.x);
-          o.y = hfma2_u(nc.nm2_i[i], c2.y, v.y);
-          o.z = hfma2_u(nc.nm2_i[i], c2.z, v.z);
-          o.w = hfma2_u(nc.nm2_i[i], c2.w, v.w);
-          if (EPI == kEpiNormInGelu) {
-            o.x = gelu_tanh_half2(o.x);
-            o.y = gelu_tanh_half2(o.y);
-            o.z = gelu_tanh_half2(o.z);
-            o.w = gelu_tanh_half2(o.w);
-          }
-          st_global_v4(ctile + static_cast<size_t>(rr) * N + c * 64 + piece * 8, o);
-        }
-      }
-    } else if (EPI == kEpiNormResidual) {
+    if (EPI == kEpiNormResidual) {
       // The residual is LN(rtile), taken here where a warp instruction covers four whole 128-byte row
       // segments; the statistics of the rows as they are stored go out beside them.
       const int piece = lane & 7, g = lane >> 3;
@@ -910,7 +913,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       const int col0 = pu.col0 + half * wcols;
-      if (kBase != kEpiNone) {
+      if (kBase != kEpiNone && kBase != kEpiNormIn && kBase != kEpiNormInGelu) {
         if (lane < wcols / 8) st_shared_v4(bias_s + lane * 16, ld_global_v4(bias + col0 + lane * 8));
         __syncwarp();
       }
@@ -956,10 +959,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
           // this thread's row of A is normalised on the way out
           nc.rstd = rstd;
           const float nm = -rstd * mu;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) nc.nm2_i[i] = half2_of(__shfl_sync(0xffffffffu, nm, 4 * i + (lane >> 3)));
-          nc.c2[0] = ld_global_nc_v4(ln.csum + col0 + (lane & 7) * 8);
-          if (wcols > 64) nc.c2[1] = ld_global_nc_v4(ln.csum + col0 + 64 + (lane & 7) * 8);
+          nc.nm2_own = half2_of(nm);
+          nc.bias_g = bias + col0;
+          nc.csum_g = ln.csum + col0;
+          if (lane < 16) nc.stage0 = ld_global_nc_v4((lane < 8 ? nc.bias_g : nc.csum_g) + (lane & 7) * 8);
         }
       }
       bool got;
