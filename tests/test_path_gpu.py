@@ -421,6 +421,26 @@ def test_deferred_layernorm_meets_the_oracle_and_the_layernorm_kernels(cfg, ln_p
     eng.close()
 
 
+@pytest.mark.parametrize("heads,ffn,layers,batch,seq", [(4, 1024, 3, 9, 40), (8, 2048, 2, 33, 64), (4, 256, 4, 1, 7)])
+def test_deferred_layernorm_other_widths(heads, ffn, layers, batch, seq):
+    """Hidden sizes 256 and 512 (statistics of 2 and 4 vectors per row), ragged batches down to one
+    short sequence: the default path (deferred LayerNorm) against the oracle and against the path
+    with LayerNorm kernels."""
+    spec = W.tiny_spec(dtype="fp16", layers=layers, heads=heads, ffn=ffn, batch=batch, max_seq_len=seq, seed=11)
+    wl = W.make_workload(spec, random_gamma_beta=True)
+    eng = make_engine(spec, wl)
+    eng.get_profile(reset=True)
+    y_def = run_forward(eng, wl).clone()
+    prof = eng.get_profile(reset=True)
+    assert prof["layernorm"][1] == 1, "the deferred path is the default for these widths"
+    eng.set_deferred_layernorm(False)
+    y_ln = run_forward(eng, wl).clone()
+    ref = oracle_valid(wl, spec)
+    assert_parity(y_def, ref, wl.mask, fp16=True)
+    assert_parity(y_ln, ref, wl.mask, fp16=True)
+    eng.close()
+
+
 def test_failed_general_mask_call_does_not_poison_the_next_call():
     """et_layer in general-mask mode that returns early (weights of that layer missing) must leave
     the handle in key-only mode: the next plain call gives the plain result."""
