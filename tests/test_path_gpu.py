@@ -441,6 +441,27 @@ def test_deferred_layernorm_other_widths(heads, ffn, layers, batch, seq):
     eng.close()
 
 
+def test_sequences_longer_than_an_attention_tile():
+    """max_seq_len 200 on an fp16 handle: the attention kernel for any length (sequences do not fit the
+    128-row tiles) between the deferred-LayerNorm projections, and the same batch under a general mask
+    (all-ones within the valid keys, so the same answer) through the CUDA-core masked attention."""
+    spec = W.tiny_spec(dtype="fp16", layers=2, heads=4, ffn=1024, batch=5, max_seq_len=200, seed=13)
+    wl = W.make_workload(spec, random_gamma_beta=True)
+    wl.lengths[0] = 200
+    wl.mask[:] = W.prefix_mask(wl.lengths, spec.max_seq_len)
+    eng = make_engine(spec, wl)
+    y = run_forward(eng, wl).clone()
+    ref = oracle_valid(wl, spec)
+    assert_parity(y, ref, wl.mask, fp16=True)
+    am = torch.from_numpy(W.attention_mask_from_input_mask(wl.mask)).half().cuda()
+    x = torch.from_numpy(wl.from_tensor).half().cuda()
+    m = torch.from_numpy(wl.mask).cuda()
+    y2 = eng.forward_general_mask(x, m, am)
+    torch.cuda.synchronize()
+    assert_parity(y2, ref, wl.mask, fp16=True)
+    eng.close()
+
+
 def test_failed_general_mask_call_does_not_poison_the_next_call():
     """et_layer in general-mask mode that returns early (weights of that layer missing) must leave
     the handle in key-only mode: the next plain call gives the plain result."""
