@@ -13,6 +13,7 @@
 #include <string>
 #include <type_traits>
 #include <utility>
+#include <chrono>
 #include <vector>
 
 #include "common.cuh"
@@ -227,6 +228,12 @@ struct et_handle_s {
   bool host_share_auto = true;  // pick the middle share from the first call's measured copy and compute times
   bool host_share_measured = false;
   int tuned_batch = -1, tuned_seq = -1;  // shape the chunking was measured on (another shape measures again)
+  // The model's choice is tried against the default shares on replayed calls (wall time of whole
+  // calls, the best of two each): 0 = timing the default, 1 = timing the model's choice, 2 = settled.
+  int tune_state = 0;
+  int tune_replays = 0;
+  int tune_model_share = 6;
+  double tune_ms_default = 0.0, tune_ms_trial = 0.0;
   cudaEvent_t tune_ev[6] = {};  // upload start/end, pass start/end of the first and of the middle chunk
   size_t ws_bytes_allocated = 0;  // sum of the workspace buffers et_create allocated
   int* host_pinned = nullptr;  // [2 + kMaxChunks]: valid_word_num, status, per-chunk token counts
@@ -1347,9 +1354,17 @@ int forward_host_body(et_handle_t h, const void* from_host, const int* mask_host
   if (h->host_share_auto && h->host_share_measured && (h->tuned_batch != batch_size || h->tuned_seq != seq_len)) {
     h->host_share_measured = false;  // another shape: measure again, starting from the default shares
     h->host_mid_share = 6;
+    h->tune_state = 0;
+    h->tune_replays = 0;
+  }
+  if (h->host_share_auto && !h->host_share_measured &&
+      (h->last_host_batch != batch_size || h->last_host_seq != seq_len)) {
+    h->host_mid_share = 6;  // another shape while the shares were still being tried: start over
+    h->tune_state = 0;
+    h->tune_replays = 0;
   }
   if (static_cast<size_t>(batch_size) * seq_bytes < (8u << 20)) chunks = 1;  // too small to be worth it
-  if (h->host_share_measured && h->host_mid_share == 0) chunks = 1;          // measured: chunking does not pay
+  if ((h->host_share_measured || h->tune_state == 1) && h->host_mid_share == 0) chunks = 1;  // one piece
   const std::vector<std::pair<int, int>> plan =
       plan_host_chunks(batch_size, chunks, h->host_mid_share > 0 ? h->host_mid_share : 1);
   const int per = static_cast<int>(plan.size());
@@ -1358,8 +1373,13 @@ int forward_host_body(et_handle_t h, const void* from_host, const int* mask_host
   const bool graphs_allowed = h->host_graph_enabled && !h->prof.enabled && h->cur_attr_mask == nullptr;
   const bool replay = graphs_allowed && hg.batch == batch_size && hg.seq == seq_len && hg.per == per &&
                       hg.mid_share == h->host_mid_share && hg.simt == h->use_simt && !hg.execs.empty();
-  // the first chunked call measures the copy and compute times that choose the shares of the next ones
-  const bool measure = h->host_share_auto && !h->host_share_measured && per >= 3 && h->tune_ev[0] != nullptr;
+  // The first REPLAYED chunked call measures the copy and pass times that choose the shares of the
+  // calls to come: an eager pass over a small chunk is bound by its launches (and the first one by
+  // one-time set-up), which overstates the fixed cost of a pass and chose too narrow a middle chunk.
+  // If the shares change, the next call runs eagerly again and the one after records the new chunks.
+  const bool tuning = h->host_share_auto && !h->host_share_measured && replay;
+  const bool measure = tuning && h->tune_state == 0 && h->tune_replays == 0 && per >= 3 && h->tune_ev[0] != nullptr;
+  const auto call_begin = std::chrono::steady_clock::now();
   if (measure) ET_CUDA(h, cudaEventRecord(h->tune_ev[0], h->h2d_stream));
   for (; nchunks < per; ++nchunks) {
     const size_t b0 = plan[nchunks].first, nb = plan[nchunks].second;
@@ -1407,6 +1427,7 @@ int forward_host_body(et_handle_t h, const void* from_host, const int* mask_host
   if (measure) {
     float up_ms = 0.f, first_ms = 0.f, mid_ms = 0.f;
     const double x0 = static_cast<double>(plan[0].second) / batch_size, x1 = static_cast<double>(plan[1].second) / batch_size;
+    h->tune_model_share = h->host_mid_share;
     if (cudaEventElapsedTime(&up_ms, h->tune_ev[0], h->tune_ev[1]) == cudaSuccess &&
         cudaEventElapsedTime(&first_ms, h->tune_ev[2], h->tune_ev[3]) == cudaSuccess &&
         cudaEventElapsedTime(&mid_ms, h->tune_ev[4], h->tune_ev[5]) == cudaSuccess && up_ms > 0.f && first_ms > 0.f &&
@@ -1415,11 +1436,29 @@ int forward_host_body(et_handle_t h, const void* from_host, const int* mask_host
       if (slope < 0) slope = 0;
       double fixed = first_ms - slope * x0;
       if (fixed < 0) fixed = 0;
-      h->host_mid_share = best_host_chunking(up_ms, fixed, slope);
+      h->tune_model_share = best_host_chunking(up_ms, fixed, slope);
     }
-    h->host_share_measured = true;
-    h->tuned_batch = batch_size;
-    h->tuned_seq = seq_len;
+  }
+  if (tuning) {
+    // The model (copies and passes as straight lines) only proposes: its choice is kept if two
+    // replayed calls with it beat two replayed calls with the default shares by more than 1 %.
+    const double call_ms =
+        std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - call_begin).count();
+    double& best = h->tune_state == 0 ? h->tune_ms_default : h->tune_ms_trial;
+    best = h->tune_replays == 0 ? call_ms : std::min(best, call_ms);
+    if (++h->tune_replays >= 2) {
+      h->tune_replays = 0;
+      if (h->tune_state == 0 && h->tune_model_share != h->host_mid_share) {
+        h->tune_state = 1;                            // the next calls run, record and replay the model's choice
+        h->host_mid_share = h->tune_model_share;
+      } else {
+        if (h->tune_state == 1 && !(h->tune_ms_trial < 0.99 * h->tune_ms_default)) h->host_mid_share = 6;
+        h->tune_state = 2;
+        h->host_share_measured = true;
+        h->tuned_batch = batch_size;
+        h->tuned_seq = seq_len;
+      }
+    }
   }
   // second call in a row with this shape: record its chunks for the calls to come
   if (!replay && graphs_allowed && batch_size > 0 && h->last_host_batch == batch_size &&
