@@ -330,11 +330,12 @@ int et_set_deferred_layernorm(et_handle_t handle, int enable);
 /* Chunking of the host-buffer call (et_forward_host): number of chunks, share of
  * a middle chunk when the first and the last have 1 (0: the handle found that
  * chunking does not pay for the last shape and sends the batch in one piece),
- * and whether that comes from the handle's own measurement: the first chunked
- * call on a (batch, seq) shape times the upload and two passes of different
- * size, and the later calls use the chunking that minimises the copies nothing
- * overlaps plus the fixed cost of the extra passes.  ETB_HOST_MID_SHARE fixes
- * the share instead. */
+ * and whether the handle has settled on it by its own measurement: calls of a
+ * (batch, seq) shape start with 1:6:1; the first replayed call times the upload
+ * and two passes of different size, a model of the copies nothing overlaps plus
+ * the fixed cost of the extra passes proposes shares, and the proposal is kept if
+ * two replayed calls with it beat two with 1:6:1.  ETB_HOST_MID_SHARE fixes the
+ * share instead. */
 int et_host_chunk_shares(et_handle_t handle, int* chunks, int* mid_share, int* measured);
 
 /* Failure-detection self-test: launches one CTA whose bounded wait (2 ms, on a
