@@ -1356,12 +1356,14 @@ int forward_host_body(et_handle_t h, const void* from_host, const int* mask_host
     h->host_mid_share = 6;
     h->tune_state = 0;
     h->tune_replays = 0;
+    h->tune_model_share = 6;
   }
   if (h->host_share_auto && !h->host_share_measured &&
       (h->last_host_batch != batch_size || h->last_host_seq != seq_len)) {
     h->host_mid_share = 6;  // another shape while the shares were still being tried: start over
     h->tune_state = 0;
     h->tune_replays = 0;
+    h->tune_model_share = 6;
   }
   if (static_cast<size_t>(batch_size) * seq_bytes < (8u << 20)) chunks = 1;  // too small to be worth it
   if ((h->host_share_measured || h->tune_state == 1) && h->host_mid_share == 0) chunks = 1;  // one piece
