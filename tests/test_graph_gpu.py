@@ -165,3 +165,31 @@ def test_host_buffer_call_replays_its_chunks_after_two_calls_of_one_shape(monkey
             assert tt == t and np.array_equal(got, want), f"round {rep}"
     assert eng.device_status() == 0
     eng.close()
+
+
+def test_host_buffer_call_settles_its_chunk_shares(monkeypatch):
+    """Without a fixed share the handle tries the shares its model proposes against the default on
+    replayed calls and settles within a dozen calls of one shape; every call along the way (eager,
+    recording, replayed, with whichever shares) returns a result inside the gate of the whole-batch
+    pass, and once settled the calls repeat bit for bit."""
+    monkeypatch.delenv("ETB_HOST_MID_SHARE", raising=False)
+    spec = W.WORKLOADS[1]
+    big = W.WorkloadSpec("cfg1_x8", spec.shape, "fp16", 800, 32, 8, 33, seed=5)   # 39 MB: cut into chunks
+    wl = W.make_workload(big)
+    eng, tdt = engine_for(big, wl)
+    x = wl.from_tensor.astype(np.float16)
+    whole = eng.forward(torch.from_numpy(x).cuda(), torch.from_numpy(wl.mask).cuda())
+    torch.cuda.synchronize()
+    whole = whole.cpu().numpy().astype(np.float32)
+    outs = []
+    for call in range(14):
+        got, tt = eng.forward_host(x, wl.mask)
+        assert tt == wl.valid_tokens
+        diff = np.abs(got.astype(np.float32) - whole)
+        assert float(diff.max()) <= 2e-2 and float(diff.mean()) <= 2e-3, f"call {call}"
+        outs.append(got.copy())
+    chunks, share, measured = eng.host_chunk_shares()
+    assert measured and chunks >= 1 and 0 <= share <= 8
+    assert np.array_equal(outs[-1], outs[-2]) and np.array_equal(outs[-1], outs[-3])
+    assert eng.device_status() == 0
+    eng.close()
