@@ -290,8 +290,9 @@ cudaError_t launch_copy_columns(const T* src, T* dst, int rows, int cols, int ds
 //
 // kEpiNormIn / kEpiNormInGelu / kEpiNormResidual: the LayerNorm is never materialised.  A projection
 // whose input is LN(x) = (x - mu) * rstd * gamma + beta runs on the un-normalised x with gamma folded
-// into its weights (W' = diag(gamma) W): LN(x) W + b = rstd * (x W' - mu * colsum(W')) + (beta W + b),
-// and the row's mu, rstd come from partial sums the producer of x left beside it.
+// into its weights (W' = diag(gamma) W with centred columns, see fold_layernorm_kernel):
+// LN(x) W + b = rstd * (x W' - mu * colsum(W')) + (beta W + b), and the row's mu, rstd come from partial
+// sums the producer of x left beside it.
 //   kEpiNormIn(Gelu)   C = act(rstd[r] * (acc - mu[r] * csum[n]) + bias[n])
 //   kEpiNormResidual   C = acc + bias[n] + ((res[r,n] - mu[r]) * rstd[r] * gamma[n] + beta[n]), i.e. the residual
 //                      is the LayerNorm of `residual`, taken on the fly; and the kernel leaves the sum and
@@ -324,7 +325,9 @@ __host__ __device__ constexpr bool is_deferred_norm(int epi) {
 }
 
 // LayerNorm parameters folded into the projection that consumes it (kEpiNormIn): w_packed [N,K]
-// K-major -> w_folded = w * gamma[k], csum[n] = sum_k w_folded, bias_folded = bias + beta W.
+// K-major -> w_folded = w * gamma[k] with the mean over k taken from every output row (it multiplies
+// sum_k (x_k - mu) = 0), csum[n] = sum_k w_folded as stored (what fp16 rounding leaves of zero),
+// bias_folded = bias + beta W.
 cudaError_t launch_fold_layernorm(const __half* w_packed, const __half* bias, const __half* gamma,
                                   const __half* beta, __half* w_folded, __half* csum, __half* bias_folded, int n,
                                   int k, cudaStream_t stream);

@@ -242,9 +242,14 @@ inline int grid_for(long long work_items) {
 }
 
 
-// LayerNorm folded into the projection behind it: for LN(x) = (x - mu) * rstd * gamma + beta and
-// y = LN(x) W + b,   y = rstd * (x W' - mu * csum) + b'   with W' = diag(gamma) W, csum = column sums
-// of W' as stored (fp16), b' = b + beta W.  W is the packed [N, K] K-major copy; one CTA per row n.
+// LayerNorm folded into the projection behind it.  For LN(x) = (x - mu) * rstd * gamma + beta and
+// y = LN(x) W + b:   y = rstd * sum_k (x_k - mu) V_kn + b'_n   with V = diag(gamma) W, b' = b + beta W.
+// Since sum_k (x_k - mu) = 0, any constant may be taken from a column of V: the folded weights are
+// the CENTRED columns  W'_kn = V_kn - mean_k V_kn,  so that  y = rstd * (x W' - mu * csum) + b'  with
+// csum_n = sum_k W'_kn, which is only what rounding W' to fp16 leaves (~1e-4): the large term
+// mu * colsum(V), which a row with |mu| >> sigma would have to cancel against x V in the epilogue, is
+// gone, and the cancellation happens inside the tensor core's fp32 accumulation instead.
+// W is the packed [N, K] K-major copy; one CTA per output row n.
 __global__ void __launch_bounds__(256)
 fold_layernorm_kernel(const __half* __restrict__ w, const __half* __restrict__ bias,
                       const __half* __restrict__ gamma, const __half* __restrict__ beta, __half* __restrict__ wf,
@@ -252,22 +257,37 @@ fold_layernorm_kernel(const __half* __restrict__ w, const __half* __restrict__ b
   const int n = blockIdx.x;
   const __half* wrow = w + static_cast<size_t>(n) * k;
   __half* frow = wf + static_cast<size_t>(n) * k;
-  float s = 0.f, bw = 0.f;
+  __shared__ float red[2][8];
+  __shared__ float mean_s;
+  auto block_sum2 = [&](float a, float b, float& ta, float& tb) {
+    a = warp_sum(a);
+    b = warp_sum(b);
+    __syncthreads();  // red[] may still be read from the previous use
+    if ((threadIdx.x & 31) == 0) red[0][threadIdx.x >> 5] = a, red[1][threadIdx.x >> 5] = b;
+    __syncthreads();
+    ta = 0.f, tb = 0.f;
+    for (int i = 0; i < 8; ++i) ta += red[0][i], tb += red[1][i];
+  };
+  float v_sum = 0.f, bw = 0.f;
   for (int j = threadIdx.x; j < k; j += blockDim.x) {
     const float wv = __half2float(wrow[j]);
-    const __half f = __float2half_rn(wv * __half2float(gamma[j]));
-    frow[j] = f;
-    s += __half2float(f);
+    v_sum += wv * __half2float(gamma[j]);
     bw += __half2float(beta[j]) * wv;
   }
-  __shared__ float red[2][8];
-  s = warp_sum(s);
-  bw = warp_sum(bw);
-  if ((threadIdx.x & 31) == 0) red[0][threadIdx.x >> 5] = s, red[1][threadIdx.x >> 5] = bw;
+  float tv, tb;
+  block_sum2(v_sum, bw, tv, tb);
+  if (threadIdx.x == 0) mean_s = tv / static_cast<float>(k);
   __syncthreads();
+  const float mean = mean_s;
+  float s = 0.f;
+  for (int j = threadIdx.x; j < k; j += blockDim.x) {
+    const __half f = __float2half_rn(__half2float(wrow[j]) * __half2float(gamma[j]) - mean);
+    frow[j] = f;
+    s += __half2float(f);
+  }
+  float ts, unused;
+  block_sum2(s, 0.f, ts, unused);
   if (threadIdx.x == 0) {
-    float ts = 0.f, tb = 0.f;
-    for (int i = 0; i < 8; ++i) ts += red[0][i], tb += red[1][i];
     csum[n] = __float2half_rn(ts);
     bias_f[n] = __float2half_rn(__half2float(bias[n]) + tb);
   }

@@ -200,11 +200,6 @@ __device__ __forceinline__ uint32_t hfma2_u(uint32_t a, uint32_t b, uint32_t c) 
   asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
   return d;
 }
-__device__ __forceinline__ uint32_t hmul2_u(uint32_t a, uint32_t b) {
-  uint32_t d;
-  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-  return d;
-}
 __device__ __forceinline__ uint32_t hadd2_u(uint32_t a, uint32_t b) {
   uint32_t d;
   asm("add.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
@@ -334,8 +329,7 @@ __device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, __half* ctile
         if (rr < rows_valid) res[i] = ld_global_nc_v4(rtile + static_cast<size_t>(rr) * N + c * 64 + piece * 8);
       }
       // gamma, beta of this lane's eight columns as fp16 pairs (fetched before the accumulator
-      // arrived); the LayerNorm of the residual runs on pairs too: y = res * t + (beta - mu * t),
-      // t = rstd * gamma
+      // arrived)
       const Vec16 g2 = c == 0 ? nc.g2[0] : nc.g2[1], be2 = c == 0 ? nc.be2[0] : nc.be2[1];
       float s1[8], s2[8];
 #pragma unroll
@@ -344,16 +338,19 @@ __device__ __forceinline__ void epilogue_warp_tile(uint32_t t_row, __half* ctile
         const Vec16 v = ld_shared_v4(buf + rr * 128 + ((piece ^ (rr & 7)) << 4));
         s1[i] = 0.f, s2[i] = 0.f;
         if (rr < rows_valid) {
-          const uint32_t r2 = half2_of(nc.rstd_i[i]), nmu2 = half2_of(-nc.mu_i[i]);
+          // (res - mu) * rstd in fp32: a row whose mean dwarfs its spread has res * rstd and mu * rstd in
+          // the thousands and their difference of order one; then * gamma + beta and the sum on fp16 pairs
+          float fr[8];
+          VecTraits<__half>::unpack(res[i], fr);
+          const float rs = nc.rstd_i[i], nmr = -nc.mu_i[i] * nc.rstd_i[i];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) fr[e] = fmaf(fr[e], rs, nmr);
+          const Vec16 d2 = VecTraits<__half>::pack(fr);
           Vec16 o;
-          {
-            const uint32_t tx = hmul2_u(r2, g2.x), ty = hmul2_u(r2, g2.y), tz = hmul2_u(r2, g2.z),
-                           tw = hmul2_u(r2, g2.w);
-            o.x = hadd2_u(v.x, hfma2_u(res[i].x, tx, hfma2_u(nmu2, tx, be2.x)));
-            o.y = hadd2_u(v.y, hfma2_u(res[i].y, ty, hfma2_u(nmu2, ty, be2.y)));
-            o.z = hadd2_u(v.z, hfma2_u(res[i].z, tz, hfma2_u(nmu2, tz, be2.z)));
-            o.w = hadd2_u(v.w, hfma2_u(res[i].w, tw, hfma2_u(nmu2, tw, be2.w)));
-          }
+          o.x = hadd2_u(v.x, hfma2_u(d2.x, g2.x, be2.x));
+          o.y = hadd2_u(v.y, hfma2_u(d2.y, g2.y, be2.y));
+          o.z = hadd2_u(v.z, hfma2_u(d2.z, g2.z, be2.z));
+          o.w = hadd2_u(v.w, hfma2_u(d2.w, g2.w, be2.w));
           st_global_v4(ctile + static_cast<size_t>(rr) * N + c * 64 + piece * 8, o);
           float fx[8];
           VecTraits<__half>::unpack(o, fx);  // the statistics are those of the stored values

@@ -535,7 +535,10 @@ int et_gemm_fused(const void* a, const void* w_packed, const void* bias, const v
  * between the projections (tf_op/bert_transformer_op.cu.cc:211-213,242-246);
  * the handle uses these inside et_forward* when et_set_deferred_layernorm is on.
  * et_fold_layernorm: w_packed [N,K] (et_pack_weight), bias [N], gamma / beta [K]
- * -> w_folded [N,K], csum [N], bias_folded [N] (fp16).
+ * -> w_folded [N,K] = gamma-scaled weights with the mean over K taken from every
+ * output row (it multiplies sum_k (x_k - mu) = 0, and removes the large term
+ * mu * colsum that would otherwise cancel in the epilogue), csum [N] = the row
+ * sums fp16 rounding leaves, bias_folded [N] (fp16).
  * et_gemm_deferred_norm (fp16, n % 256 == 0): epilogue
  *   7  C = rstd[r] * (A W' - mu[r] * csum[n]) + bias[n]          (bias = bias_folded)
  *   8  the same, then GELU
