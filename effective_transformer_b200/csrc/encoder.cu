@@ -129,7 +129,8 @@ inline size_t ws_round(size_t bytes) { return round_up(bytes == 0 ? 16 : bytes, 
 // projection on the CTA-pair kernel, statistics in 64-column pieces of rows of 128 * j columns).
 bool defer_eligible(const et_config_t& c) {
   const int H = c.head_num * c.size_per_head;
-  return c.dtype == ET_FP16 && H % 256 == 0 && c.ffn_dim % 256 == 0 && c.num_layers > 0;
+  // rows of up to 1024 columns: the epilogues hold a row's partial sums in registers (width / 128 vectors)
+  return c.dtype == ET_FP16 && H % 256 == 0 && H <= 1024 && c.ffn_dim % 256 == 0 && c.num_layers > 0;
 }
 
 std::vector<WsItem> workspace_items(const et_config_t& c, size_t batch, size_t seq, Workspace& ws) {
@@ -1134,7 +1135,7 @@ int et_set_deferred_layernorm(et_handle_t h, int enable) {
   if (h == nullptr) return ET_INVALID_ARGUMENT;
   if (enable != 0 && !defer_eligible(h->cfg))
     return set_error(h, ET_INVALID_ARGUMENT,
-                     "deferred LayerNorm needs an fp16 handle whose hidden size and ffn_dim are multiples of 256");
+                     "deferred LayerNorm needs an fp16 handle whose hidden size (at most 1024) and ffn_dim are multiples of 256");
   if (h->defer_ln != (enable != 0)) {
     DeviceGuard guard(h->cfg.device);
     cudaDeviceSynchronize();

@@ -313,7 +313,8 @@ int et_set_debug_simt(et_handle_t handle, int use_simt);
  * arithmetic in the same order).  Measured on B200 it is slower at the benchmark
  * sizes, which is why it is opt-in.  Changing the setting drops recorded graphs. */
 int et_set_fused_layernorm(et_handle_t handle, int enable);
-/* 1 (default on fp16 handles whose hidden size and ffn_dim are multiples of 256):
+/* 1 (default on fp16 handles whose hidden size, at most 1024, and ffn_dim are
+ * multiples of 256):
  * inside the whole-stack calls (et_forward*, the graph and host-buffer
  * calls) no LayerNorm between the projections is materialised: the two
  * hidden-wide projections leave x + sublayer(x) and its row statistics, the

@@ -421,6 +421,21 @@ def test_deferred_layernorm_meets_the_oracle_and_the_layernorm_kernels(cfg, ln_p
     eng.close()
 
 
+def test_hidden_sizes_beyond_the_deferred_layernorm_run_the_layernorm_kernels():
+    """hidden 1280 (a multiple of 256 above 1024): the handle falls back to LayerNorm kernels by itself,
+    and asking for the deferred form is refused."""
+    spec = W.tiny_spec(dtype="fp16", layers=2, heads=20, ffn=1280, batch=4, max_seq_len=24, seed=17)
+    wl = W.make_workload(spec, random_gamma_beta=True)
+    eng = make_engine(spec, wl)
+    eng.get_profile(reset=True)
+    y = run_forward(eng, wl)
+    assert eng.get_profile(reset=True)["layernorm"][1] == 2 * spec.shape.num_layers
+    assert_parity(y, oracle_valid(wl, spec), wl.mask, fp16=True)
+    with pytest.raises(_capi.EtError):
+        eng.set_deferred_layernorm(True)
+    eng.close()
+
+
 @pytest.mark.parametrize("heads,ffn,layers,batch,seq", [(4, 1024, 3, 9, 40), (8, 2048, 2, 33, 64), (4, 256, 4, 1, 7)])
 def test_deferred_layernorm_other_widths(heads, ffn, layers, batch, seq):
     """Hidden sizes 256 and 512 (statistics of 2 and 4 vectors per row), ragged batches down to one
